@@ -1,0 +1,223 @@
+/*
+ * nmoe.h -- C ABI of the B200 NVFP4 mixture-of-experts expert layer.
+ *
+ * Drop-in replacement for the expert-layer operator of kwindla/nemotron-inference
+ * (nemotron::ExpertLayerSlice, runtime/include/nemotron/expert_layer.h:84-105):
+ * RMSNorm, sigmoid top-k router with correction bias, token permute, routed
+ * expert grouped GEMMs (up_proj -> relu^2 -> down_proj, dynamic per-16-block
+ * NVFP4 activation quantisation), shared expert, weighted combine, residual.
+ *
+ * Plain pointers and sizes only.  Weight pointers may be host or device
+ * addresses (unified addressing); they are copied at creation and need not
+ * outlive it.  Activation pointers are device addresses.  Every call takes the
+ * CUDA stream to run on (passed as void*, a cudaStream_t); nothing here
+ * synchronises unless it says so.  All functions return an nmoe_status
+ * (0 = success); nmoe_status_string() and nmoe_layer_last_error() describe a
+ * failure.  The library has no CPU fallback: without a CUDA device every
+ * compute entry point fails with NMOE_ERR_CUDA.
+ *
+ * Citations are file:line inside the reference project.
+ */
+#ifndef NMOE_H_
+#define NMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NMOE_API __attribute__((visibility("default")))
+
+typedef enum nmoe_status {
+  NMOE_OK = 0,
+  NMOE_ERR_INVALID_ARGUMENT = 1,
+  NMOE_ERR_CUDA = 2,            /* a CUDA runtime / driver call failed */
+  NMOE_ERR_UNSUPPORTED = 3,     /* valid in the reference, not built here */
+  NMOE_ERR_DEVICE_TIMEOUT = 4,  /* a bounded device-side wait gave up */
+  NMOE_ERR_ACTIVATION_RANGE = 5,/* an activated row exceeded 6*448 (tensor scale != 1) */
+  NMOE_ERR_CAPACITY = 6         /* more tokens / row tiles than the layer was created for */
+} nmoe_status;
+
+typedef enum nmoe_dtype { NMOE_F32 = 0, NMOE_BF16 = 1 } nmoe_dtype;
+
+/* Mirrors nemotron::ExpertLayerConfig (expert_layer.h:18-31).  The latent
+ * projections fc1_latent/fc2_latent of the reference layer
+ * (expert_layer.cpp:809-813, :1047-1048) are the identity here, so
+ * moe_latent_size must equal hidden_size. */
+typedef struct nmoe_config {
+  int32_t layer_index;
+  int32_t hidden_size;
+  int32_t moe_latent_size;
+  int32_t routed_expert_intermediate_size;
+  int32_t shared_expert_intermediate_size;
+  int32_t n_routed_experts;
+  int32_t top_k;
+  int32_t n_group;
+  int32_t topk_group;
+  int32_t norm_topk_prob;
+  float rms_epsilon;
+  float routed_scaling_factor;
+  int32_t max_tokens; /* capacity of one nmoe_layer_run call (not in the reference,
+                         which allocates scratch per call, expert_layer.cpp:782-787) */
+} nmoe_config;
+
+/* One NVFP4 matrix in the reference's weight layout: the byte fields of
+ * nemotron::GemmDescriptor (gemm_catalog.h:20-42) for kernel family
+ * kCublasLtNvfp4BlockScaled / layout "cublaslt_fp4_tn_v1"
+ * (nvfp4_weight.cpp:59-70).  packed: [output_rows][input_cols/2], column 2j in
+ * the low nibble; block_scales: [output_rows][input_cols/16] E4M3, row-major;
+ * tensor_scale: 4-byte FP32. */
+typedef struct nmoe_nvfp4_matrix {
+  size_t output_rows;
+  size_t input_cols;
+  const uint8_t* packed_data;
+  size_t packed_nbytes;
+  const uint8_t* block_scales_data;
+  size_t block_scales_nbytes;
+  const uint8_t* tensor_scale_data;
+  size_t tensor_scale_nbytes;
+} nmoe_nvfp4_matrix;
+
+/* A dense row-major tensor (KernelTensorDescriptor / dense GemmDescriptor,
+ * kernel_catalog.h:14-34): norm weight [hidden], gate weight [experts][hidden],
+ * e_score_correction_bias [experts]; FP32 or bf16. */
+typedef struct nmoe_dense_tensor {
+  const void* data;
+  size_t nbytes;
+  nmoe_dtype dtype;
+  size_t rows;
+  size_t cols;
+} nmoe_dense_tensor;
+
+/* Mirrors nemotron::ExpertLayerBindings (expert_layer.h:38-56) for the
+ * all-NVFP4 expert weights.  routed_up/routed_down hold n_local_experts
+ * entries: the experts [first_local_expert, first_local_expert +
+ * n_local_experts) of the layer. */
+typedef struct nmoe_weights {
+  nmoe_dense_tensor input_norm_weight;
+  nmoe_dense_tensor gate_weight;
+  nmoe_dense_tensor gate_score_correction_bias;
+  const nmoe_nvfp4_matrix* routed_up;   /* each [intermediate][hidden] */
+  const nmoe_nvfp4_matrix* routed_down; /* each [hidden][intermediate] */
+  int32_t n_local_experts;
+  int32_t first_local_expert;
+  nmoe_nvfp4_matrix shared_up;   /* [shared_intermediate][hidden] */
+  nmoe_nvfp4_matrix shared_down; /* [hidden][shared_intermediate] */
+} nmoe_weights;
+
+typedef struct nmoe_layer nmoe_layer;
+
+NMOE_API const char* nmoe_status_string(nmoe_status status);
+
+/* ExpertLayerSlice::Create (expert_layer.cpp:494-709): validates config and
+ * shapes (:505-528, :646-689), uploads every weight to HBM (the reference keeps
+ * host pointers to the routed experts, :707) and allocates all scratch for
+ * max_tokens.  Synchronises the device once. */
+NMOE_API nmoe_status nmoe_layer_create(const nmoe_config* config, const nmoe_weights* weights,
+                                       nmoe_layer** out_layer);
+NMOE_API void nmoe_layer_destroy(nmoe_layer* layer);
+
+/* ExpertLayerSlice::Run (expert_layer.cpp:752-1092) for `tokens` rows:
+ * output = input + routed + shared with the input RMSNorm inside.  input and
+ * output are device [tokens][hidden] in the given dtypes and must not alias.
+ * Enqueues on `stream` and returns; device-side failures surface through
+ * nmoe_layer_sync_status(). */
+NMOE_API nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void* input,
+                                    nmoe_dtype input_dtype, int64_t tokens, void* output,
+                                    nmoe_dtype output_dtype);
+
+/* Waits for `stream` and reports what the kernels left in the layer's device
+ * error slot (and clears it): the boolean the reference's synchronous Run
+ * returns. */
+NMOE_API nmoe_status nmoe_layer_sync_status(nmoe_layer* layer, void* stream);
+NMOE_API const char* nmoe_layer_last_error(const nmoe_layer* layer);
+
+/* The intermediates ExpertLayerRunTrace exposes (expert_layer.h:63-76), for any
+ * token count, as device buffers of the LAST run.  A field stays NULL when the
+ * layer does not hold it.  Valid until the next run or destroy. */
+typedef struct nmoe_trace_view {
+  const float* normalized_input;   /* [tokens][hidden] */
+  const float* router_logits;      /* [tokens][experts] */
+  const int32_t* selected_index;   /* [tokens][top_k], selection order */
+  const float* selected_weight;    /* [tokens][top_k] */
+  const uint8_t* act_packed;       /* [tokens][hidden/2]  quantised normalised input */
+  const uint8_t* act_scales;       /* [tokens][hidden/16] row-major E4M3 */
+  const float* act_tensor_scale;   /* [tokens] */
+  const float* parts;              /* [tokens][top_k+1][hidden]: weighted routed
+                                      contributions in selection order, then shared */
+} nmoe_trace_view;
+NMOE_API nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out);
+
+/* Copies the quantised relu^2 intermediates of the LAST run into
+ * (token, slot)-ordered row-major buffers (device pointers):
+ * routed_packed [tokens][top_k][I/2], routed_scales [tokens][top_k][I/16],
+ * shared_packed [tokens][S/2], shared_scales [tokens][S/16].  Any may be NULL. */
+NMOE_API nmoe_status nmoe_layer_export_hidden(nmoe_layer* layer, void* stream,
+                                              uint8_t* routed_packed, uint8_t* routed_scales,
+                                              uint8_t* shared_packed, uint8_t* shared_scales);
+
+/* --- one expert FFN: down(relu^2(up(x))) with NVFP4 weights ----------------
+ * The composition ExpertLayerSlice::Run applies per (token, expert)
+ * (expert_layer.cpp:913-922: RunNvfp4LinearHost, ApplyRelu2,
+ * RunNvfp4LinearHost).  No norm, no residual. */
+typedef struct nmoe_ffn nmoe_ffn;
+NMOE_API nmoe_status nmoe_ffn_create(const nmoe_nvfp4_matrix* up, const nmoe_nvfp4_matrix* down,
+                                     int32_t max_rows, nmoe_ffn** out_ffn);
+NMOE_API void nmoe_ffn_destroy(nmoe_ffn* ffn);
+/* input [rows][hidden] device FP32/bf16 -> output [rows][hidden] device FP32.
+ * gemm_variant: 0 = choose by size, otherwise 1 + a tile-shape index (for tests). */
+NMOE_API nmoe_status nmoe_ffn_run(nmoe_ffn* ffn, void* stream, const void* input,
+                                  nmoe_dtype input_dtype, int64_t rows, float* output,
+                                  int32_t gemm_variant);
+NMOE_API nmoe_status nmoe_ffn_sync_status(nmoe_ffn* ffn, void* stream);
+/* Quantised relu^2 intermediate of the last run: [rows][I/2], [rows][I/16]. */
+NMOE_API nmoe_status nmoe_ffn_export_hidden(nmoe_ffn* ffn, void* stream, uint8_t* packed,
+                                            uint8_t* scales);
+
+/* --- unit operators (all pointers device, all asynchronous) ---------------- */
+
+/* PackRowMajorFp32ToNvfp4 (nvfp4_packing.cpp:90-157) /
+ * PackDeviceRowMajorFp32ToNvfp4 (device_nvfp4_matrix.cu:339-435).
+ * per_row != 0: every row is packed as its own call (rows == 1 semantics, the
+ * way the layer calls it, expert_layer.cpp:913) and tensor_scale has `rows`
+ * entries; per_row == 0: one tensor scale for the whole matrix (input must be
+ * FP32).  scales_row_major [rows][cols/16]; scales_swizzled (nullable) in the
+ * 128x4 tile order of nvfp4_scale_layout.cpp:14-28, nmoe_swizzled_scale_bytes()
+ * bytes, zero padded. */
+NMOE_API nmoe_status nmoe_quantize_nvfp4(void* stream, const void* input, nmoe_dtype dtype,
+                                         int64_t rows, int64_t cols, int32_t per_row,
+                                         uint8_t* packed, uint8_t* scales_row_major,
+                                         uint8_t* scales_swizzled, float* tensor_scale);
+/* DequantizeNvfp4Matrix (expert_layer.cpp:154-186). */
+NMOE_API nmoe_status nmoe_dequant_nvfp4(void* stream, const uint8_t* packed,
+                                        const uint8_t* scales_row_major,
+                                        const float* tensor_scale, int32_t per_row, int64_t rows,
+                                        int64_t cols, float* output);
+/* SwizzleRowMajorNvfp4ScalesForExecution (nvfp4_scale_layout.cpp:68-87). */
+NMOE_API size_t nmoe_swizzled_scale_bytes(int64_t rows, int64_t cols);
+NMOE_API nmoe_status nmoe_swizzle_scales(void* stream, const uint8_t* scales_row_major,
+                                         int64_t rows, int64_t cols, uint8_t* scales_swizzled);
+/* RmsNormFp32 (primitive_ops.cu:92-108) on [rows][hidden]. */
+NMOE_API nmoe_status nmoe_rmsnorm(void* stream, const void* input, nmoe_dtype dtype, int64_t rows,
+                                  int64_t hidden, const float* weight, float epsilon,
+                                  float* output);
+/* Gate projection (linear_op.cpp:97-118): logits[rows][experts] from FP32
+ * activations and FP32 gate weights [experts][hidden]. */
+NMOE_API nmoe_status nmoe_router_logits(void* stream, const float* normalized, const float* gate,
+                                        int64_t rows, int32_t experts, int32_t hidden,
+                                        float* logits);
+/* SelectTopExperts (expert_layer.cpp:277-367) per row: indices (int32) and
+ * weights in selection order. */
+NMOE_API nmoe_status nmoe_router_topk(void* stream, const float* logits, const float* bias,
+                                      int64_t rows, int32_t experts, int32_t top_k,
+                                      int32_t n_group, int32_t topk_group,
+                                      int32_t norm_topk_prob, float routed_scaling,
+                                      int32_t* top_index, float* top_weight);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* NMOE_H_ */

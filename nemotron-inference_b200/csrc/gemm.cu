@@ -1,0 +1,431 @@
+// Grouped NVFP4 GEMM for the routed and shared experts: tcgen05 block-scaled
+// FP4 MMA (kind::mxf4nvf4, 16-element UE4M3 blocks) with TMA-fed shared-memory
+// stages and double-buffered TMEM accumulators.
+//
+// Replaces, for all (token, expert) pairs at once, the reference's per-row host
+// linear RunNvfp4LinearHost (runtime/src/backend/expert_layer.cpp:231-267:
+// dequantise activation, dequantise weight, CpuMatmulRowMajor :212-229) and
+// the steps fused behind it:
+//   kGemmUp  : ApplyRelu2 (:269-275) and the re-quantisation of the activated
+//              row that the next RunNvfp4LinearHost call performs through
+//              PackRowMajorFp32ToNvfp4 (runtime/src/backend/nvfp4_packing.cpp:130-153);
+//   kGemmDown: the routing-weight multiply of :951-953 (the sum over slots is
+//              done by the combine kernel so that it stays in slot order).
+//
+// Operand roles: A = activations (128 token rows per tile, K-major packed E2M1),
+// B = expert weights (BN output features per tile, K-major packed E2M1).  One
+// K block is 256 elements = one 128-byte swizzled shared-memory row = four
+// K=64 MMAs.  Block scales travel shared memory -> TMEM with tcgen05.cp in the
+// 32-lane x 16-byte form; activations use the reference's 128x4 tile order
+// (runtime/src/backend/nvfp4_scale_layout.cpp:14-28) unchanged.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// owner, warps 2-5 = epilogue (one TMEM lane quarter each).  Every mbarrier
+// wait is bounded; on a timeout the CTA records kDevWaitTimeout and unwinds.
+#include <algorithm>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace nmoe {
+namespace {
+
+template <int BN_, int A_ROWS_, int SFB_GS_, int STAGES_>
+struct TileCfg {
+  static constexpr int BN = BN_;
+  static constexpr int A_ROWS = A_ROWS_;
+  static constexpr int SFB_GS = SFB_GS_;  // 32-row scale groups stored per K tile
+  static constexpr int STAGES = STAGES_;
+  static constexpr int A_BYTES = A_ROWS * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int SFA_BYTES = 2048;
+  static constexpr int SFB_BYTES = SFB_GS * 512;
+  static constexpr int STAGE_TX = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int ACC_STRIDE = BN;  // TMEM columns per accumulator
+  static constexpr int SFA_COL = 2 * ACC_STRIDE;
+  static constexpr int SFB_COL = SFA_COL + 16;
+  static constexpr int TMEM_USED = SFB_COL + 4 * SFB_GS;
+  static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  // The MMA always reads 128 A rows; with a smaller box the tail rows alias the
+  // following stages, which is harmless (those output rows are never stored)
+  // but must stay inside the allocation: the B region follows the A region.
+  static constexpr int SMEM_BYTES =
+      STAGES * (A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES) + BAR_BYTES + 1024;
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "BN");
+  static_assert(TMEM_USED <= 512, "TMEM budget");
+  static_assert(STAGES * B_BYTES >= 128 * 128, "A over-read must stay inside shared memory");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
+using CfgPrefillUp = TileCfg<208, 128, 8, 4>;
+using CfgPrefillDown = TileCfg<224, 128, 8, 4>;
+using CfgDecode32 = TileCfg<32, 32, 1, 16>;
+using CfgDecode32Padded = TileCfg<32, 32, 4, 14>;
+using CfgDecode32Wide = TileCfg<32, 128, 1, 9>;
+using CfgDecode32WidePadded = TileCfg<32, 128, 4, 8>;
+
+__device__ __forceinline__ void report_timeout(int32_t* error, volatile int* abort_flag) {
+  *abort_flag = 1;
+  if (error != nullptr) atomicCAS(error, kDevOk, kDevWaitTimeout);
+}
+
+template <class C, int MODE>
+__global__ void __launch_bounds__(192, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) &
+                                             ~static_cast<uintptr_t>(1023u));
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + C::STAGES * C::A_BYTES;
+  uint8_t* sSFA = sB + C::STAGES * C::B_BYTES;
+  uint8_t* sSFB = sSFA + C::STAGES * C::SFA_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sSFB + C::STAGES * C::SFB_BYTES);
+  uint64_t* empty_bar = full_bar + C::STAGES;
+  uint64_t* tmem_full_bar = empty_bar + C::STAGES;
+  uint64_t* tmem_empty_bar = tmem_full_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_row_tiles =
+      args.row_tiles != nullptr ? *args.num_row_tiles : (args.dense_rows + 127) / 128;
+  const int total_tiles = num_row_tiles * args.n_tiles;
+  const int k_mmas = args.K / 64;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int rt = t / args.n_tiles;
+        const int nt = t - rt * args.n_tiles;
+        int row0, expert;
+        if (args.row_tiles != nullptr) {
+          row0 = args.row_tiles[rt].row0;
+          expert = args.row_tiles[rt].expert;
+        } else {
+          row0 = rt * 128;
+          expert = 0;
+        }
+        const uint8_t* sfa_src =
+            args.sfa + static_cast<size_t>(row0 >> 7) * args.k_blocks * C::SFA_BYTES;
+        const uint8_t* sfb_src = args.sfb + (static_cast<size_t>(expert) * args.n_tiles + nt) *
+                                                args.k_blocks * C::SFB_BYTES;
+        const int b_row = expert * args.N + nt * C::BN;
+        for (int kb = 0; kb < args.k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
+            report_timeout(args.error, abort_flag);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_TX);
+          tma_load_2d(sA + stage * C::A_BYTES, &tmap_a, kb * 128, row0, &full_bar[stage]);
+          tma_load_2d(sB + stage * C::B_BYTES, &tmap_b, kb * 128, b_row, &full_bar[stage]);
+          bulk_load(sSFA + stage * C::SFA_BYTES, sfa_src + kb * C::SFA_BYTES, C::SFA_BYTES,
+                    &full_bar[stage]);
+          bulk_load(sSFB + stage * C::SFB_BYTES, sfb_src + kb * C::SFB_BYTES, C::SFB_BYTES,
+                    &full_bar[stage]);
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_nvf4(C::BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u)) {
+          report_timeout(args.error, abort_flag);
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * C::ACC_STRIDE;
+        for (int kb = 0; kb < args.k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            report_timeout(args.error, abort_flag);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * C::A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * C::B_BYTES);
+          const uint32_t sfa_addr = smem_u32(sSFA + stage * C::SFA_BYTES);
+          const uint32_t sfb_addr = smem_u32(sSFB + stage * C::SFB_BYTES);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            tcgen05_cp_32x128b_warpx4(tmem_base + C::SFA_COL + 4 * c,
+                                      make_smem_desc(sfa_addr + c * 512, 0, 128, 0));
+          }
+#pragma unroll
+          for (int c = 0; c < C::SFB_GS; ++c) {
+            tcgen05_cp_32x128b_warpx4(tmem_base + C::SFB_COL + 4 * c,
+                                      make_smem_desc(sfb_addr + c * 512, 0, 128, 0));
+          }
+          const int kt_count = min(4, k_mmas - kb * 4);
+          for (int kt = 0; kt < kt_count; ++kt) {
+            tcgen05_mma_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
+                             make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
+                             tmem_base + C::SFA_COL + 4 * kt,
+                             tmem_base + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
+          }
+          tcgen05_commit(&empty_bar[stage]);
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tcgen05_commit(&tmem_full_bar[acc]);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
+    int local = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      const int rt = t / args.n_tiles;
+      const int nt = t - rt * args.n_tiles;
+      int row0, rows, expert;
+      if (args.row_tiles != nullptr) {
+        row0 = args.row_tiles[rt].row0;
+        rows = args.row_tiles[rt].rows;
+        expert = args.row_tiles[rt].expert;
+      } else {
+        row0 = rt * 128;
+        rows = min(128, args.dense_rows - row0);
+        expert = 0;
+      }
+      const bool row_valid = r < rows;
+      const int grow = row0 + r;
+      float scale = args.w_tensor_scale[expert];
+      if (args.a_tensor_scale != nullptr && row_valid) scale *= args.a_tensor_scale[grow];
+
+      if (!mbar_wait(&tmem_full_bar[acc], acc_phase)) {
+        report_timeout(args.error, abort_flag);
+        break;
+      }
+      tcgen05_fence_after();
+      const uint32_t t_addr =
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::ACC_STRIDE;
+      const int n0 = nt * C::BN;
+
+      if constexpr (MODE == kGemmUp) {
+        uint8_t* packed_row = args.out_packed + static_cast<size_t>(grow) * (args.N / 2);
+        bool range_error = false;
+        for (int c = 0; c < C::BN; c += 16) {
+          const int n = n0 + c;
+          if (n >= args.N) break;
+          float v[16];
+          tmem_ld_x16(t_addr + c, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float x = v[i] * scale;
+            v[i] = x > 0.0f ? x * x : 0.0f;
+            range_error |= v[i] > kFp4Max * kFp8Max;
+          }
+          uint32_t lo, hi;
+          const uint32_t sf = quantize_block16(v, 1.0f, lo, hi);
+          if (row_valid) {
+            *reinterpret_cast<uint2*>(packed_row + n / 2) = make_uint2(lo, hi);
+            args.out_sf[swizzled_scale_offset(grow, n / 16, args.out_k_blocks * 4)] =
+                static_cast<uint8_t>(sf);
+          }
+        }
+        if (range_error && row_valid && args.error != nullptr) {
+          atomicCAS(args.error, kDevOk, kDevActivationRange);
+        }
+      } else {
+        int dest = 0;
+        float wt = 1.0f;
+        if (row_valid) {
+          dest = args.dest_row != nullptr ? args.dest_row[grow]
+                                          : grow * args.dest_mul + args.dest_add;
+          if (args.row_weight != nullptr) wt = args.row_weight[grow];
+        }
+        float* out_row = args.out_rows + static_cast<size_t>(dest) * args.N;
+        for (int c = 0; c < C::BN; c += 16) {
+          const int n = n0 + c;
+          if (n >= args.N) break;
+          float v[16];
+          tmem_ld_x16(t_addr + c, v);
+          if (row_valid) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              v[i] = v[i] * scale;
+              if (args.row_weight != nullptr) v[i] = v[i] * wt;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              *reinterpret_cast<float4*>(out_row + n + i) =
+                  make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+template <class C>
+cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                       const GemmArgs& args, int num_sms, cudaStream_t stream) {
+  int grid = num_sms;
+  if (args.row_tiles == nullptr) {
+    const int tiles = ((args.dense_rows + 127) / 128) * args.n_tiles;
+    if (tiles < grid) grid = tiles;
+    if (grid < 1) grid = 1;
+  }
+  cudaError_t err;
+  if (mode == kGemmUp) {
+    auto kernel = grouped_gemm_kernel<C, kGemmUp>;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (err != cudaSuccess) return err;
+    kernel<<<grid, 192, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, args);
+  } else {
+    auto kernel = grouped_gemm_kernel<C, kGemmDown>;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (err != cudaSuccess) return err;
+    kernel<<<grid, 192, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, args);
+  }
+  return cudaGetLastError();
+}
+
+template <class C>
+GemmVariantInfo info_of() {
+  return GemmVariantInfo{C::BN, C::A_ROWS, C::SFB_GS, C::SFB_BYTES, C::SMEM_BYTES};
+}
+
+__global__ void relayout_weight_scales_kernel(const uint8_t* __restrict__ src, int experts, int N,
+                                              int K, int bn, int gs, int n_tiles, int k_blocks,
+                                              uint32_t* __restrict__ out, size_t words) {
+  const int blocks_per_row = K / 16;
+  for (size_t w = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; w < words;
+       w += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    // word index = ((((e*n_tiles + nt)*k_blocks + kb)*gs + chunk)*32 + lane)*4 + j
+    size_t rest = w;
+    const int j = rest & 3;
+    rest >>= 2;
+    const int lane = rest & 31;
+    rest >>= 5;
+    const int chunk = rest % gs;
+    rest /= gs;
+    const int kb = rest % k_blocks;
+    rest /= k_blocks;
+    const int nt = rest % n_tiles;
+    const int e = static_cast<int>(rest / n_tiles);
+    const int col = chunk * 4 + j;  // TMEM column inside this K block
+    const int kt = col / gs;        // K tile (64 elements) inside the K block
+    const int g = col - kt * gs;    // 32-row group inside the N tile
+    const int local_row = g * 32 + lane;
+    const int n = nt * bn + local_row;
+    uint32_t word = 0;
+    if (local_row < bn && n < N) {
+      const uint8_t* row = src + (static_cast<size_t>(e) * N + n) * blocks_per_row;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int block = (kb * 4 + kt) * 4 + b;
+        if (block < blocks_per_row) word |= static_cast<uint32_t>(row[block]) << (8 * b);
+      }
+    }
+    out[w] = word;
+  }
+}
+
+}  // namespace
+
+GemmVariantInfo gemm_variant_info(GemmVariant v) {
+  switch (v) {
+    case kVariantPrefillUp: return info_of<CfgPrefillUp>();
+    case kVariantPrefillDown: return info_of<CfgPrefillDown>();
+    case kVariantDecode32: return info_of<CfgDecode32>();
+    case kVariantDecode32Padded: return info_of<CfgDecode32Padded>();
+    case kVariantDecode32Wide: return info_of<CfgDecode32Wide>();
+    case kVariantDecode32WidePadded: return info_of<CfgDecode32WidePadded>();
+    default: return GemmVariantInfo{0, 0, 0, 0, 0};
+  }
+}
+
+cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const CUtensorMap& tmap_a,
+                                const CUtensorMap& tmap_b, const GemmArgs& args, int num_sms,
+                                cudaStream_t stream) {
+  switch (v) {
+    case kVariantPrefillUp: return launch_cfg<CfgPrefillUp>(mode, tmap_a, tmap_b, args, num_sms, stream);
+    case kVariantPrefillDown: return launch_cfg<CfgPrefillDown>(mode, tmap_a, tmap_b, args, num_sms, stream);
+    case kVariantDecode32: return launch_cfg<CfgDecode32>(mode, tmap_a, tmap_b, args, num_sms, stream);
+    case kVariantDecode32Padded: return launch_cfg<CfgDecode32Padded>(mode, tmap_a, tmap_b, args, num_sms, stream);
+    case kVariantDecode32Wide: return launch_cfg<CfgDecode32Wide>(mode, tmap_a, tmap_b, args, num_sms, stream);
+    case kVariantDecode32WidePadded: return launch_cfg<CfgDecode32WidePadded>(mode, tmap_a, tmap_b, args, num_sms, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+size_t weight_scale_layout_bytes(int experts, int N, int K, int bn, int sfb_groups) {
+  const size_t n_tiles = (N + bn - 1) / bn;
+  const size_t k_blocks = (K + 255) / 256;
+  return static_cast<size_t>(experts) * n_tiles * k_blocks * sfb_groups * 512;
+}
+
+cudaError_t relayout_weight_scales(const uint8_t* row_major, int experts, int N, int K, int bn,
+                                   int sfb_groups, uint8_t* out, cudaStream_t stream) {
+  const int n_tiles = (N + bn - 1) / bn;
+  const int k_blocks = (K + 255) / 256;
+  const size_t words = weight_scale_layout_bytes(experts, N, K, bn, sfb_groups) / 4;
+  const int threads = 256;
+  const int blocks = static_cast<int>(std::min<size_t>((words + threads - 1) / threads, 65535));
+  relayout_weight_scales_kernel<<<blocks, threads, 0, stream>>>(
+      row_major, experts, N, K, bn, sfb_groups, n_tiles, k_blocks,
+      reinterpret_cast<uint32_t*>(out), words);
+  return cudaGetLastError();
+}
+
+}  // namespace nmoe

@@ -1,0 +1,143 @@
+// Host-visible declarations of the kernel launchers.  Everything takes an
+// explicit stream and returns cudaError_t from the launch.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace nmoe {
+
+// A row tile is a 128-row aligned slot of the expert-sorted activation buffer
+// holding `rows` (<= 128) valid rows that all belong to `expert`.
+struct RowTile {
+  int32_t row0;    // first row of the slot (multiple of 128)
+  int32_t rows;    // valid rows in the slot
+  int32_t expert;  // index into the stacked expert weights
+  int32_t reserved;
+};
+
+enum GemmMode : int {
+  kGemmUp = 0,    // D -> *scales -> relu^2 -> NVFP4 (packed + tiled scales)
+  kGemmDown = 1,  // D -> *scales [* routing weight] -> FP32 rows scattered by dest_row
+};
+
+struct GemmArgs {
+  int32_t K = 0;         // contraction length, multiple of 64
+  int32_t N = 0;         // output features per expert
+  int32_t n_tiles = 0;   // ceil(N / BN)
+  int32_t k_blocks = 0;  // ceil(K / 256)
+  // A-side block scales, tiled: [row slot][k_blocks][2048 bytes]
+  const uint8_t* sfa = nullptr;
+  // weight block scales, [expert][n_tile][k_block][sfb_bytes] in the layout
+  // produced by relayout_weight_scales()
+  const uint8_t* sfb = nullptr;
+  const float* a_tensor_scale = nullptr;  // per activation row, nullptr => 1.0
+  const float* w_tensor_scale = nullptr;  // [expert]
+  // schedule: grouped (row_tiles + device count) or dense (row_tiles == nullptr)
+  const RowTile* row_tiles = nullptr;
+  const int32_t* num_row_tiles = nullptr;
+  int32_t dense_rows = 0;
+  // kGemmUp outputs
+  uint8_t* out_packed = nullptr;  // [row][N/2]
+  uint8_t* out_sf = nullptr;      // tiled [row slot][out_k_blocks][2048]
+  int32_t out_k_blocks = 0;       // ceil(N / 256)
+  // kGemmDown outputs
+  float* out_rows = nullptr;          // [dest][N]
+  const int32_t* dest_row = nullptr;  // per activation row; nullptr => row*dest_mul+dest_add
+  int32_t dest_mul = 1;
+  int32_t dest_add = 0;
+  const float* row_weight = nullptr;  // per activation row routing weight, nullptr => none
+  int32_t* error = nullptr;           // device error slot (DeviceError)
+};
+
+// Tile shapes compiled into the library.
+enum GemmVariant : int {
+  kVariantPrefillUp = 0,    // BN 208, 128-row A box
+  kVariantPrefillDown = 1,  // BN 224, 128-row A box
+  kVariantDecode32 = 2,     // BN 32, 32-row A box, compact weight scales
+  kVariantDecode32Padded = 3,  // BN 32, 32-row A box, weight scales padded to 4 groups
+  kVariantDecode32Wide = 4,        // BN 32, 128-row A box, compact weight scales
+  kVariantDecode32WidePadded = 5,  // BN 32, 128-row A box, padded weight scales
+  kVariantCount = 6,
+};
+
+struct GemmVariantInfo {
+  int bn;            // output features per tile
+  int a_rows;        // rows of the activation box / valid rows per row tile
+  int sfb_groups;    // 32-row groups of weight scales stored per K-tile
+  int sfb_bytes;     // bytes of weight scales per (n_tile, k_block)
+  int smem_bytes;    // dynamic shared memory of the kernel
+};
+
+GemmVariantInfo gemm_variant_info(GemmVariant v);
+cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const CUtensorMap& tmap_a,
+                                const CUtensorMap& tmap_b, const GemmArgs& args, int num_sms,
+                                cudaStream_t stream);
+
+// Re-tile row-major E4M3 weight block scales [experts][N][K/16] into the layout
+// the GEMM variant consumes (device to device).
+cudaError_t relayout_weight_scales(const uint8_t* row_major, int experts, int N, int K, int bn,
+                                   int sfb_groups, uint8_t* out, cudaStream_t stream);
+size_t weight_scale_layout_bytes(int experts, int N, int K, int bn, int sfb_groups);
+
+// --- quantiser / norm ------------------------------------------------------
+// RMSNorm (optional) + per-row dynamic NVFP4 quantisation.
+//   in: [rows][cols] fp32 or bf16; norm_weight nullptr => no normalisation
+//   normalized (optional) fp32 [rows][cols]
+//   packed [rows][cols/2]; sf_row_major (optional) [rows][cols/16];
+//   sf_tiled (optional) tiled layout with k_blocks*4 K-tiles per 128-row slot;
+//   tensor_scale (optional) [rows]
+cudaError_t launch_norm_quant(const void* in, bool in_bf16, int rows, int cols,
+                              const float* norm_weight, float eps, float* normalized,
+                              uint8_t* packed, uint8_t* sf_row_major, uint8_t* sf_tiled,
+                              int k_blocks, float* tensor_scale, cudaStream_t stream);
+// Whole-matrix dynamic quantisation with ONE tensor scale (the reference
+// packer's semantics for rows > 1).  `amax_scratch` is one float of device
+// memory; it is overwritten.
+cudaError_t launch_quant_matrix(const float* in, int rows, int cols, uint8_t* packed,
+                                uint8_t* sf_row_major, float* tensor_scale,
+                                float* amax_scratch, cudaStream_t stream);
+cudaError_t launch_dequant(const uint8_t* packed, const uint8_t* sf_row_major,
+                           const float* tensor_scale, bool per_row_scale, int rows, int cols,
+                           float* out, cudaStream_t stream);
+cudaError_t launch_swizzle_scales(const uint8_t* row_major, int rows, int cols, uint8_t* tiled,
+                                  cudaStream_t stream);
+
+// --- router ------------------------------------------------------------------
+cudaError_t launch_router_logits(const float* normalized, const float* gate, int rows,
+                                 int experts, int hidden, float* logits, cudaStream_t stream);
+cudaError_t launch_router_topk(const float* logits, const float* bias, int rows, int experts,
+                               int top_k, int n_group, int topk_group, bool norm_topk_prob,
+                               float routed_scaling, int32_t* top_index, float* top_weight,
+                               int32_t* expert_counts /* nullable, += histogram */,
+                               cudaStream_t stream);
+
+// --- plan / permute / combine -------------------------------------------------
+struct PlanBuffers {
+  int32_t* expert_counts;   // [experts]  (input, filled by the router)
+  int32_t* expert_cursor;   // [experts]  (scratch, zeroed by the plan kernel)
+  int32_t* expert_slot0;    // [experts]  first row slot of each expert
+  RowTile* row_tiles;       // [max_row_tiles]
+  int32_t* num_row_tiles;   // [1]
+};
+cudaError_t launch_route_plan(const PlanBuffers& plan, int experts, int tile_rows,
+                              int max_row_tiles, int32_t* error, cudaStream_t stream);
+// Copies each (token, slot) pair's quantised activation row into its expert's
+// row slots and records where it went.
+cudaError_t launch_permute(const PlanBuffers& plan, const int32_t* top_index,
+                           const float* top_weight, int rows, int top_k, int tile_rows,
+                           int max_row_tiles, const uint8_t* packed, const uint8_t* sf_row_major,
+                           const float* tensor_scale, int cols, int k_blocks,
+                           uint8_t* sorted_packed, uint8_t* sorted_sf_tiled,
+                           float* sorted_tensor_scale, float* sorted_weight,
+                           int32_t* sorted_dest, int32_t* pair_row, int dest_stride,
+                           cudaStream_t stream);
+// out[t] = in[t] + ((sum_k parts[t][k]) + parts[t][top_k]) with the routed
+// parts added in slot order.
+cudaError_t launch_combine(const void* in, bool in_bf16, const float* parts, int rows, int hidden,
+                           int top_k, void* out, bool out_bf16, cudaStream_t stream);
+
+}  // namespace nmoe

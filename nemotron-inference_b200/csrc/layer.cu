@@ -1,0 +1,883 @@
+// Host side of the C ABI declared in include/nmoe.h: weight upload, scratch,
+// tensor maps and the launch sequence of the expert layer.
+//
+// Mirrors ExpertLayerSlice::Create / ::Run
+// (runtime/src/backend/expert_layer.cpp:494-709, :752-1092) with three
+// differences that follow from running on the device: all weights are
+// uploaded once (the reference keeps host pointers to the routed experts,
+// :707), scratch is allocated once for `max_tokens` (the reference allocates
+// six tensors per call, :782-787) and nothing synchronises inside Run.
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/nmoe.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace nmoe {
+namespace {
+
+// ---------------------------------------------------------------------------
+// small helpers
+// ---------------------------------------------------------------------------
+
+struct Failure {
+  nmoe_status status;
+  std::string message;
+};
+
+#define NMOE_CUDA(expr)                                                                    \
+  do {                                                                                     \
+    const cudaError_t err__ = (expr);                                                      \
+    if (err__ != cudaSuccess) {                                                            \
+      throw Failure{NMOE_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(err__)}; \
+    }                                                                                      \
+  } while (0)
+
+#define NMOE_REQUIRE(cond, text)                                        \
+  do {                                                                  \
+    if (!(cond)) throw Failure{NMOE_ERR_INVALID_ARGUMENT, (text)};      \
+  } while (0)
+
+class DeviceBuffer {
+ public:
+  DeviceBuffer() = default;
+  DeviceBuffer(const DeviceBuffer&) = delete;
+  DeviceBuffer& operator=(const DeviceBuffer&) = delete;
+  ~DeviceBuffer() { reset(); }
+  void allocate(size_t bytes, bool zero = false) {
+    reset();
+    bytes_ = bytes == 0 ? 16 : bytes;
+    NMOE_CUDA(cudaMalloc(&ptr_, bytes_));
+    if (zero) NMOE_CUDA(cudaMemset(ptr_, 0, bytes_));
+  }
+  void reset() {
+    if (ptr_ != nullptr) cudaFree(ptr_);
+    ptr_ = nullptr;
+    bytes_ = 0;
+  }
+  template <typename T>
+  T* as() const {
+    return reinterpret_cast<T*>(ptr_);
+  }
+  size_t bytes() const { return bytes_; }
+
+ private:
+  void* ptr_ = nullptr;
+  size_t bytes_ = 0;
+};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    NMOE_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &query));
+    if (sym == nullptr || query != cudaDriverEntryPointSuccess) {
+      throw Failure{NMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver"};
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// Packed E2M1 rows viewed as bytes: [rows][row_bytes], box = 128 bytes x
+// box_rows, 128-byte swizzle (one box row = one K block of 256 elements).
+CUtensorMap make_packed_map(const void* base, size_t rows, size_t row_bytes, int box_rows) {
+  NMOE_REQUIRE(reinterpret_cast<uintptr_t>(base) % 16 == 0, "tensor map base must be 16-byte aligned");
+  NMOE_REQUIRE(row_bytes % 16 == 0, "packed row pitch must be a multiple of 16 bytes (K % 32 == 0)");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {row_bytes, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[2] = {1u, 1u};
+  const CUresult rc = encode_tiled_fn()(
+      &map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    throw Failure{NMOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(rc)};
+  }
+  return map;
+}
+
+int k_blocks_of(int k) { return (k + 255) / 256; }
+size_t tiled_sf_bytes(size_t row_slots, int k) { return row_slots * k_blocks_of(k) * 2048; }
+
+bool padded_weight_scales() {
+  const char* env = std::getenv("NMOE_SFB_PADDED");
+  return env != nullptr && env[0] == '1';
+}
+
+int device_sm_count() {
+  int device = 0, sms = 0;
+  NMOE_CUDA(cudaGetDevice(&device));
+  NMOE_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  return sms;
+}
+
+void validate_matrix(const nmoe_nvfp4_matrix& m, size_t rows, size_t cols, const char* name) {
+  // shape checks of expert_layer.cpp:646-689 plus the byte counts of
+  // DequantizeNvfp4Matrix (:162-169) and the 4-byte tensor scale (:189-195)
+  const std::string n(name);
+  NMOE_REQUIRE(m.output_rows == rows && m.input_cols == cols, n + ": shape mismatch");
+  NMOE_REQUIRE(cols % 64 == 0, n + ": input_cols must be a multiple of 64");
+  NMOE_REQUIRE(m.packed_data != nullptr && m.packed_nbytes == rows * cols / 2,
+               n + ": packed bytes");
+  NMOE_REQUIRE(m.block_scales_data != nullptr && m.block_scales_nbytes == rows * (cols / 16),
+               n + ": block scale bytes");
+  NMOE_REQUIRE(m.tensor_scale_data != nullptr && m.tensor_scale_nbytes == sizeof(float),
+               n + ": tensor scale must be one FP32");
+}
+
+// ---------------------------------------------------------------------------
+// A stack of same-shaped NVFP4 matrices resident in HBM with the scale layouts
+// and tensor maps of every GEMM tile shape that may consume it.
+// ---------------------------------------------------------------------------
+enum TileClass : int { kClassPrefill = 0, kClassDecode = 1, kClassDecodeWide = 2 };
+
+struct WeightStack {
+  int experts = 0;
+  int n = 0;  // output rows per expert
+  int k = 0;  // input cols
+  DeviceBuffer packed;        // [experts][n][k/2]
+  DeviceBuffer tensor_scale;  // [experts]
+  DeviceBuffer sf_prefill;    // scale layout for the prefill tile of this projection
+  DeviceBuffer sf_decode;     // scale layout for the BN=32 tiles
+  GemmVariant prefill_variant = kVariantPrefillUp;
+  GemmVariant decode_variant = kVariantDecode32;
+  GemmVariant decode_wide_variant = kVariantDecode32Wide;
+  CUtensorMap map_prefill;
+  CUtensorMap map_decode;
+
+  void upload(const nmoe_nvfp4_matrix* matrices, int count, int rows, int cols, bool is_up,
+              const char* name, cudaStream_t stream) {
+    experts = count;
+    n = rows;
+    k = cols;
+    prefill_variant = is_up ? kVariantPrefillUp : kVariantPrefillDown;
+    const bool padded = padded_weight_scales();
+    decode_variant = padded ? kVariantDecode32Padded : kVariantDecode32;
+    decode_wide_variant = padded ? kVariantDecode32WidePadded : kVariantDecode32Wide;
+    const size_t packed_each = static_cast<size_t>(rows) * cols / 2;
+    const size_t sf_each = static_cast<size_t>(rows) * (cols / 16);
+    packed.allocate(packed_each * count);
+    tensor_scale.allocate(sizeof(float) * count);
+    DeviceBuffer sf_row_major;
+    sf_row_major.allocate(sf_each * count);
+    for (int e = 0; e < count; ++e) {
+      validate_matrix(matrices[e], rows, cols, name);
+      NMOE_CUDA(cudaMemcpyAsync(packed.as<uint8_t>() + packed_each * e, matrices[e].packed_data,
+                                packed_each, cudaMemcpyDefault, stream));
+      NMOE_CUDA(cudaMemcpyAsync(sf_row_major.as<uint8_t>() + sf_each * e,
+                                matrices[e].block_scales_data, sf_each, cudaMemcpyDefault,
+                                stream));
+      NMOE_CUDA(cudaMemcpyAsync(tensor_scale.as<float>() + e, matrices[e].tensor_scale_data,
+                                sizeof(float), cudaMemcpyDefault, stream));
+    }
+    const GemmVariantInfo pi = gemm_variant_info(prefill_variant);
+    const GemmVariantInfo di = gemm_variant_info(decode_variant);
+    sf_prefill.allocate(weight_scale_layout_bytes(count, rows, cols, pi.bn, pi.sfb_groups));
+    sf_decode.allocate(weight_scale_layout_bytes(count, rows, cols, di.bn, di.sfb_groups));
+    NMOE_CUDA(relayout_weight_scales(sf_row_major.as<uint8_t>(), count, rows, cols, pi.bn,
+                                     pi.sfb_groups, sf_prefill.as<uint8_t>(), stream));
+    NMOE_CUDA(relayout_weight_scales(sf_row_major.as<uint8_t>(), count, rows, cols, di.bn,
+                                     di.sfb_groups, sf_decode.as<uint8_t>(), stream));
+    NMOE_CUDA(cudaStreamSynchronize(stream));  // sf_row_major dies here
+    map_prefill = make_packed_map(packed.as<uint8_t>(), static_cast<size_t>(count) * rows,
+                                  static_cast<size_t>(cols) / 2, pi.bn);
+    map_decode = make_packed_map(packed.as<uint8_t>(), static_cast<size_t>(count) * rows,
+                                 static_cast<size_t>(cols) / 2, di.bn);
+  }
+
+  GemmVariant variant(TileClass c) const {
+    return c == kClassPrefill ? prefill_variant
+                              : c == kClassDecode ? decode_variant : decode_wide_variant;
+  }
+  const CUtensorMap& map(TileClass c) const { return c == kClassPrefill ? map_prefill : map_decode; }
+  const uint8_t* sf(TileClass c) const {
+    return (c == kClassPrefill ? sf_prefill : sf_decode).as<uint8_t>();
+  }
+};
+
+// Packed activation rows + tiled scales as a GEMM A operand.
+struct ActivationOperand {
+  const uint8_t* packed = nullptr;
+  const uint8_t* sf_tiled = nullptr;
+  CUtensorMap map_box128;
+  CUtensorMap map_box32;
+  void bind(const uint8_t* packed_rows, const uint8_t* sf, size_t rows, int k) {
+    packed = packed_rows;
+    sf_tiled = sf;
+    map_box128 = make_packed_map(packed_rows, rows, static_cast<size_t>(k) / 2, 128);
+    map_box32 = make_packed_map(packed_rows, rows, static_cast<size_t>(k) / 2, 32);
+  }
+  const CUtensorMap& map(TileClass c) const { return c == kClassDecode ? map_box32 : map_box128; }
+};
+
+struct Schedule {
+  const RowTile* row_tiles = nullptr;  // grouped when non-null
+  const int32_t* num_row_tiles = nullptr;
+  int dense_rows = 0;
+};
+
+// up GEMM (relu^2 + quantise) followed by down GEMM (scale, weight, scatter).
+void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass tile_class,
+                      const ActivationOperand& a, const float* a_tensor_scale,
+                      const Schedule& schedule, uint8_t* hidden_packed, uint8_t* hidden_sf,
+                      const ActivationOperand& hidden, float* out_rows, const int32_t* dest_row,
+                      int dest_mul, int dest_add, const float* row_weight, int32_t* error,
+                      int num_sms, cudaStream_t stream) {
+  GemmArgs g;
+  const GemmVariant up_variant = up.variant(tile_class);
+  g.K = up.k;
+  g.N = up.n;
+  g.n_tiles = (up.n + gemm_variant_info(up_variant).bn - 1) / gemm_variant_info(up_variant).bn;
+  g.k_blocks = k_blocks_of(up.k);
+  g.sfa = a.sf_tiled;
+  g.sfb = up.sf(tile_class);
+  g.a_tensor_scale = a_tensor_scale;
+  g.w_tensor_scale = up.tensor_scale.as<float>();
+  g.row_tiles = schedule.row_tiles;
+  g.num_row_tiles = schedule.num_row_tiles;
+  g.dense_rows = schedule.dense_rows;
+  g.out_packed = hidden_packed;
+  g.out_sf = hidden_sf;
+  g.out_k_blocks = k_blocks_of(up.n);
+  g.error = error;
+  NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, a.map(tile_class), up.map(tile_class), g,
+                                num_sms, stream));
+
+  GemmArgs d;
+  const GemmVariant down_variant = down.variant(tile_class);
+  d.K = down.k;
+  d.N = down.n;
+  d.n_tiles = (down.n + gemm_variant_info(down_variant).bn - 1) / gemm_variant_info(down_variant).bn;
+  d.k_blocks = k_blocks_of(down.k);
+  d.sfa = hidden.sf_tiled;
+  d.sfb = down.sf(tile_class);
+  d.a_tensor_scale = nullptr;  // the fused quantiser always uses tensor scale 1
+  d.w_tensor_scale = down.tensor_scale.as<float>();
+  d.row_tiles = schedule.row_tiles;
+  d.num_row_tiles = schedule.num_row_tiles;
+  d.dense_rows = schedule.dense_rows;
+  d.out_rows = out_rows;
+  d.dest_row = dest_row;
+  d.dest_mul = dest_mul;
+  d.dest_add = dest_add;
+  d.row_weight = row_weight;
+  d.error = error;
+  NMOE_CUDA(launch_grouped_gemm(down_variant, kGemmDown, hidden.map(tile_class),
+                                down.map(tile_class), d, num_sms, stream));
+}
+
+nmoe_status status_from_device(int code) {
+  switch (code) {
+    case kDevOk: return NMOE_OK;
+    case kDevWaitTimeout: return NMOE_ERR_DEVICE_TIMEOUT;
+    case kDevActivationRange: return NMOE_ERR_ACTIVATION_RANGE;
+    case kDevPlanOverflow: return NMOE_ERR_CAPACITY;
+    default: return NMOE_ERR_CUDA;
+  }
+}
+
+struct ErrorSlot {
+  DeviceBuffer device;
+  int32_t* host = nullptr;  // pinned
+  void create() {
+    device.allocate(sizeof(int32_t), true);
+    NMOE_CUDA(cudaMallocHost(&host, sizeof(int32_t)));
+    *host = 0;
+  }
+  ~ErrorSlot() {
+    if (host != nullptr) cudaFreeHost(host);
+  }
+  nmoe_status sync(cudaStream_t stream) {
+    NMOE_CUDA(cudaMemcpyAsync(host, device.as<int32_t>(), sizeof(int32_t), cudaMemcpyDeviceToHost,
+                              stream));
+    NMOE_CUDA(cudaMemsetAsync(device.as<int32_t>(), 0, sizeof(int32_t), stream));
+    NMOE_CUDA(cudaStreamSynchronize(stream));
+    return status_from_device(*host);
+  }
+};
+
+// Un-tile block scales of selected rows into row-major order (trace export).
+__global__ void export_rows_kernel(const uint8_t* __restrict__ packed,
+                                   const uint8_t* __restrict__ sf_tiled,
+                                   const int32_t* __restrict__ row_of, int count, int cols,
+                                   int k_tiles, uint8_t* __restrict__ out_packed,
+                                   uint8_t* __restrict__ out_sf) {
+  const int i = blockIdx.x;
+  if (i >= count) return;
+  const int row = row_of != nullptr ? row_of[i] : i;
+  if (out_packed != nullptr) {
+    for (int b = threadIdx.x; b < cols / 2; b += blockDim.x) {
+      out_packed[static_cast<size_t>(i) * (cols / 2) + b] =
+          packed[static_cast<size_t>(row) * (cols / 2) + b];
+    }
+  }
+  if (out_sf != nullptr) {
+    for (int b = threadIdx.x; b < cols / 16; b += blockDim.x) {
+      out_sf[static_cast<size_t>(i) * (cols / 16) + b] =
+          sf_tiled[swizzled_scale_offset(row, b, k_tiles)];
+    }
+  }
+}
+
+__global__ void widen_bf16_kernel(const __nv_bfloat16* __restrict__ in, size_t count,
+                                  float* __restrict__ out) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < count;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    out[i] = __bfloat162float(in[i]);
+  }
+}
+
+// ReadVectorWeightToHostFp32 / UploadVectorWeightToDeviceFp32 and the dense
+// upload of linear_op.cpp:274-303: FP32 as is, bf16 widened.
+void upload_dense_fp32(const nmoe_dense_tensor& t, size_t count, const char* name,
+                       DeviceBuffer* out, cudaStream_t stream) {
+  NMOE_REQUIRE(t.data != nullptr, std::string(name) + ": null data");
+  NMOE_REQUIRE(t.rows * t.cols == count, std::string(name) + ": shape mismatch");
+  out->allocate(count * sizeof(float));
+  if (t.dtype == NMOE_F32) {
+    NMOE_REQUIRE(t.nbytes == count * 4, std::string(name) + ": byte count");
+    NMOE_CUDA(cudaMemcpyAsync(out->as<float>(), t.data, count * 4, cudaMemcpyDefault, stream));
+  } else {
+    NMOE_REQUIRE(t.nbytes == count * 2, std::string(name) + ": byte count");
+    DeviceBuffer staging;
+    staging.allocate(count * 2);
+    NMOE_CUDA(cudaMemcpyAsync(staging.as<void>(), t.data, count * 2, cudaMemcpyDefault, stream));
+    widen_bf16_kernel<<<148, 256, 0, stream>>>(staging.as<__nv_bfloat16>(), count, out->as<float>());
+    NMOE_CUDA(cudaGetLastError());
+    NMOE_CUDA(cudaStreamSynchronize(stream));
+  }
+}
+
+}  // namespace
+}  // namespace nmoe
+
+using namespace nmoe;
+
+// ===========================================================================
+// nmoe_ffn
+// ===========================================================================
+struct nmoe_ffn {
+  int hidden = 0;
+  int inter = 0;
+  int max_rows = 0;
+  int num_sms = 0;
+  WeightStack up, down;
+  DeviceBuffer a_packed, a_sf, a_ts, h_packed, h_sf;
+  ActivationOperand a_op, h_op;
+  ErrorSlot error;
+  int last_rows = 0;
+  std::string last_error;
+};
+
+extern "C" {
+
+const char* nmoe_status_string(nmoe_status status) {
+  switch (status) {
+    case NMOE_OK: return "ok";
+    case NMOE_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case NMOE_ERR_CUDA: return "CUDA error";
+    case NMOE_ERR_UNSUPPORTED: return "unsupported configuration";
+    case NMOE_ERR_DEVICE_TIMEOUT: return "a device-side wait timed out";
+    case NMOE_ERR_ACTIVATION_RANGE: return "activated row exceeds the NVFP4 range for tensor scale 1";
+    case NMOE_ERR_CAPACITY: return "token or row-tile capacity exceeded";
+  }
+  return "unknown status";
+}
+
+nmoe_status nmoe_ffn_create(const nmoe_nvfp4_matrix* up, const nmoe_nvfp4_matrix* down,
+                            int32_t max_rows, nmoe_ffn** out_ffn) {
+  if (up == nullptr || down == nullptr || out_ffn == nullptr || max_rows <= 0) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  *out_ffn = nullptr;
+  std::unique_ptr<nmoe_ffn> f(new (std::nothrow) nmoe_ffn);
+  if (!f) return NMOE_ERR_CUDA;
+  try {
+    f->hidden = static_cast<int>(up->input_cols);
+    f->inter = static_cast<int>(up->output_rows);
+    f->max_rows = max_rows;
+    f->num_sms = device_sm_count();
+    cudaStream_t stream = nullptr;
+    f->up.upload(up, 1, f->inter, f->hidden, true, "up_proj", stream);
+    f->down.upload(down, 1, f->hidden, f->inter, false, "down_proj", stream);
+    const size_t slots = (static_cast<size_t>(max_rows) + 127) / 128;
+    f->a_packed.allocate(slots * 128 * f->hidden / 2, true);
+    f->a_sf.allocate(tiled_sf_bytes(slots, f->hidden), true);
+    f->a_ts.allocate(slots * 128 * sizeof(float), true);
+    f->h_packed.allocate(slots * 128 * f->inter / 2, true);
+    f->h_sf.allocate(tiled_sf_bytes(slots, f->inter), true);
+    f->a_op.bind(f->a_packed.as<uint8_t>(), f->a_sf.as<uint8_t>(), slots * 128, f->hidden);
+    f->h_op.bind(f->h_packed.as<uint8_t>(), f->h_sf.as<uint8_t>(), slots * 128, f->inter);
+    f->error.create();
+    NMOE_CUDA(cudaDeviceSynchronize());
+  } catch (const Failure& failure) {
+    std::fprintf(stderr, "nmoe_ffn_create: %s\n", failure.message.c_str());
+    return failure.status;
+  }
+  *out_ffn = f.release();
+  return NMOE_OK;
+}
+
+void nmoe_ffn_destroy(nmoe_ffn* ffn) { delete ffn; }
+
+nmoe_status nmoe_ffn_run(nmoe_ffn* ffn, void* stream_ptr, const void* input,
+                         nmoe_dtype input_dtype, int64_t rows, float* output,
+                         int32_t gemm_variant) {
+  if (ffn == nullptr || input == nullptr || output == nullptr || rows <= 0) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  if (rows > ffn->max_rows) return NMOE_ERR_CAPACITY;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  try {
+    TileClass tile_class = rows <= 32 ? kClassDecode : rows <= 256 ? kClassDecodeWide : kClassPrefill;
+    if (gemm_variant >= 1 && gemm_variant <= 3) tile_class = static_cast<TileClass>(gemm_variant - 1);
+    if (tile_class == kClassDecode && rows > 32) return NMOE_ERR_INVALID_ARGUMENT;
+    NMOE_CUDA(launch_norm_quant(input, input_dtype == NMOE_BF16, static_cast<int>(rows),
+                                ffn->hidden, nullptr, 0.0f, nullptr, ffn->a_packed.as<uint8_t>(),
+                                nullptr, ffn->a_sf.as<uint8_t>(), k_blocks_of(ffn->hidden),
+                                ffn->a_ts.as<float>(), stream));
+    Schedule schedule;
+    schedule.dense_rows = static_cast<int>(rows);
+    run_expert_gemms(ffn->up, ffn->down, tile_class, ffn->a_op, ffn->a_ts.as<float>(), schedule,
+                     ffn->h_packed.as<uint8_t>(), ffn->h_sf.as<uint8_t>(), ffn->h_op, output,
+                     nullptr, 1, 0, nullptr, ffn->error.device.as<int32_t>(), ffn->num_sms,
+                     stream);
+    ffn->last_rows = static_cast<int>(rows);
+  } catch (const Failure& failure) {
+    ffn->last_error = failure.message;
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_ffn_sync_status(nmoe_ffn* ffn, void* stream_ptr) {
+  if (ffn == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  try {
+    return ffn->error.sync(static_cast<cudaStream_t>(stream_ptr));
+  } catch (const Failure& failure) {
+    ffn->last_error = failure.message;
+    return failure.status;
+  }
+}
+
+nmoe_status nmoe_ffn_export_hidden(nmoe_ffn* ffn, void* stream_ptr, uint8_t* packed,
+                                   uint8_t* scales) {
+  if (ffn == nullptr || ffn->last_rows <= 0) return NMOE_ERR_INVALID_ARGUMENT;
+  export_rows_kernel<<<ffn->last_rows, 128, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      ffn->h_packed.as<uint8_t>(), ffn->h_sf.as<uint8_t>(), nullptr, ffn->last_rows, ffn->inter,
+      k_blocks_of(ffn->inter) * 4, packed, scales);
+  return cudaGetLastError() == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
+}
+
+}  // extern "C"
+
+// ===========================================================================
+// nmoe_layer
+// ===========================================================================
+struct nmoe_layer {
+  nmoe_config cfg{};
+  int num_sms = 0;
+  int local_experts = 0;
+  int first_local_expert = 0;
+  int max_row_tiles = 0;
+  int decode_pairs_limit = 0;
+
+  DeviceBuffer norm_weight, gate, bias;
+  WeightStack up, down, shared_up, shared_down;
+
+  // token-order scratch
+  DeviceBuffer normalized, logits, top_index, top_weight;
+  DeviceBuffer y_packed, y_sf_row_major, y_sf_tiled, y_ts;
+  DeviceBuffer sh_packed, sh_sf;
+  DeviceBuffer parts;
+  // plan
+  DeviceBuffer counts, cursor, slot0, row_tiles, num_row_tiles, pair_row;
+  // expert-sorted scratch
+  DeviceBuffer a_packed, a_sf, a_ts, a_weight, a_dest, h_packed, h_sf;
+
+  ActivationOperand y_op, sh_op, a_op, h_op;
+  ErrorSlot error;
+  int last_tokens = 0;
+  std::string last_error;
+};
+
+namespace {
+
+void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& w) {
+  // config checks of expert_layer.cpp:505-528
+  NMOE_REQUIRE(c.hidden_size > 0 && c.routed_expert_intermediate_size > 0 &&
+                   c.shared_expert_intermediate_size > 0 && c.n_routed_experts > 0 &&
+                   c.top_k > 0 && c.top_k <= c.n_routed_experts && c.n_group > 0 &&
+                   c.topk_group > 0 && c.n_routed_experts % c.n_group == 0 &&
+                   c.rms_epsilon > 0.0f && c.max_tokens > 0,
+               "invalid config");
+  if (c.moe_latent_size != c.hidden_size) {
+    throw Failure{NMOE_ERR_UNSUPPORTED, "latent projections are not built: moe_latent_size must equal hidden_size"};
+  }
+  NMOE_REQUIRE(c.n_routed_experts % 32 == 0 && c.n_routed_experts <= 512 && c.top_k <= 32 &&
+                   c.n_group <= 32,
+               "router limits: experts % 32 == 0, experts <= 512, top_k <= 32, n_group <= 32");
+  NMOE_REQUIRE(c.hidden_size % 64 == 0 && c.routed_expert_intermediate_size % 64 == 0 &&
+                   c.shared_expert_intermediate_size % 64 == 0,
+               "hidden and intermediate sizes must be multiples of 64");
+  if (w.n_local_experts != c.n_routed_experts || w.first_local_expert != 0) {
+    throw Failure{NMOE_ERR_UNSUPPORTED, "this entry point holds all routed experts on one device"};
+  }
+  NMOE_REQUIRE(w.routed_up != nullptr && w.routed_down != nullptr, "missing routed expert weights");
+
+  L->cfg = c;
+  L->num_sms = device_sm_count();
+  L->local_experts = w.n_local_experts;
+  L->first_local_expert = w.first_local_expert;
+  cudaStream_t stream = nullptr;
+  const int H = c.hidden_size, I = c.routed_expert_intermediate_size,
+            S = c.shared_expert_intermediate_size, E = c.n_routed_experts, K = c.top_k;
+  const size_t T = static_cast<size_t>(c.max_tokens);
+
+  upload_dense_fp32(w.input_norm_weight, H, "input_norm_weight", &L->norm_weight, stream);
+  upload_dense_fp32(w.gate_weight, static_cast<size_t>(E) * H, "gate_weight", &L->gate, stream);
+  upload_dense_fp32(w.gate_score_correction_bias, E, "gate_score_correction_bias", &L->bias, stream);
+  L->up.upload(w.routed_up, E, I, H, true, "routed up_proj", stream);
+  L->down.upload(w.routed_down, E, H, I, false, "routed down_proj", stream);
+  L->shared_up.upload(&w.shared_up, 1, S, H, true, "shared up_proj", stream);
+  L->shared_down.upload(&w.shared_down, 1, H, S, false, "shared down_proj", stream);
+
+  const size_t token_slots = (T + 127) / 128;
+  L->normalized.allocate(T * H * sizeof(float));
+  L->logits.allocate(T * E * sizeof(float));
+  L->top_index.allocate(T * K * sizeof(int32_t));
+  L->top_weight.allocate(T * K * sizeof(float));
+  L->y_packed.allocate(token_slots * 128 * H / 2, true);
+  L->y_sf_row_major.allocate(T * (H / 16));
+  L->y_sf_tiled.allocate(tiled_sf_bytes(token_slots, H), true);
+  L->y_ts.allocate(token_slots * 128 * sizeof(float), true);
+  L->sh_packed.allocate(token_slots * 128 * S / 2, true);
+  L->sh_sf.allocate(tiled_sf_bytes(token_slots, S), true);
+  L->parts.allocate(T * (K + 1) * H * sizeof(float));
+
+  // Row tiles: every expert may leave one partly filled slot.  Small batches
+  // use 32-row tiles (decode tile class), large ones 128-row tiles.
+  L->decode_pairs_limit = 32 * E;
+  const size_t pairs = T * K;
+  const size_t tiles_prefill = E + (pairs + 127) / 128;
+  const size_t tiles_decode = E + (std::min<size_t>(pairs, L->decode_pairs_limit) + 31) / 32;
+  L->max_row_tiles = static_cast<int>(std::max(tiles_prefill, tiles_decode));
+  const size_t slots = static_cast<size_t>(L->max_row_tiles);
+  L->counts.allocate(E * sizeof(int32_t), true);
+  L->cursor.allocate(E * sizeof(int32_t), true);
+  L->slot0.allocate(E * sizeof(int32_t), true);
+  L->row_tiles.allocate(slots * sizeof(RowTile), true);
+  L->num_row_tiles.allocate(sizeof(int32_t), true);
+  L->pair_row.allocate(pairs * sizeof(int32_t), true);
+  L->a_packed.allocate(slots * 128 * H / 2, true);
+  L->a_sf.allocate(tiled_sf_bytes(slots, H), true);
+  L->a_ts.allocate(slots * 128 * sizeof(float), true);
+  L->a_weight.allocate(slots * 128 * sizeof(float), true);
+  L->a_dest.allocate(slots * 128 * sizeof(int32_t), true);
+  L->h_packed.allocate(slots * 128 * I / 2, true);
+  L->h_sf.allocate(tiled_sf_bytes(slots, I), true);
+
+  L->y_op.bind(L->y_packed.as<uint8_t>(), L->y_sf_tiled.as<uint8_t>(), token_slots * 128, H);
+  L->sh_op.bind(L->sh_packed.as<uint8_t>(), L->sh_sf.as<uint8_t>(), token_slots * 128, S);
+  L->a_op.bind(L->a_packed.as<uint8_t>(), L->a_sf.as<uint8_t>(), slots * 128, H);
+  L->h_op.bind(L->h_packed.as<uint8_t>(), L->h_sf.as<uint8_t>(), slots * 128, I);
+  L->error.create();
+  NMOE_CUDA(cudaDeviceSynchronize());
+}
+
+void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dtype in_dtype,
+                    int tokens, void* output, nmoe_dtype out_dtype) {
+  const nmoe_config& c = L->cfg;
+  const int H = c.hidden_size, E = c.n_routed_experts, K = c.top_k;
+  int32_t* error = L->error.device.as<int32_t>();
+
+  // RMSNorm (:795-796) fused with the activation quantiser every expert's
+  // up_proj applies to the same normalised row (:913 -> nvfp4_packing.cpp:90)
+  NMOE_CUDA(launch_norm_quant(input, in_dtype == NMOE_BF16, tokens, H, L->norm_weight.as<float>(),
+                              c.rms_epsilon, L->normalized.as<float>(), L->y_packed.as<uint8_t>(),
+                              L->y_sf_row_major.as<uint8_t>(), L->y_sf_tiled.as<uint8_t>(),
+                              k_blocks_of(H), L->y_ts.as<float>(), stream));
+  // gate projection (:797-799) and top-k (:881)
+  NMOE_CUDA(launch_router_logits(L->normalized.as<float>(), L->gate.as<float>(), tokens, E, H,
+                                 L->logits.as<float>(), stream));
+  NMOE_CUDA(cudaMemsetAsync(L->counts.as<int32_t>(), 0, E * sizeof(int32_t), stream));
+  NMOE_CUDA(launch_router_topk(L->logits.as<float>(), L->bias.as<float>(), tokens, E, K,
+                               c.n_group, c.topk_group, c.norm_topk_prob != 0,
+                               c.routed_scaling_factor, L->top_index.as<int32_t>(),
+                               L->top_weight.as<float>(), L->counts.as<int32_t>(), stream));
+
+  const bool decode = static_cast<long long>(tokens) * K <= L->decode_pairs_limit / 2;
+  const TileClass routed_class = decode ? kClassDecode : kClassPrefill;
+  const int tile_rows = decode ? 32 : 128;
+  PlanBuffers plan;
+  plan.expert_counts = L->counts.as<int32_t>();
+  plan.expert_cursor = L->cursor.as<int32_t>();
+  plan.expert_slot0 = L->slot0.as<int32_t>();
+  plan.row_tiles = L->row_tiles.as<RowTile>();
+  plan.num_row_tiles = L->num_row_tiles.as<int32_t>();
+  NMOE_CUDA(launch_route_plan(plan, E, tile_rows, L->max_row_tiles, error, stream));
+  NMOE_CUDA(launch_permute(plan, L->top_index.as<int32_t>(), L->top_weight.as<float>(), tokens, K,
+                           tile_rows, L->max_row_tiles, L->y_packed.as<uint8_t>(),
+                           L->y_sf_row_major.as<uint8_t>(), L->y_ts.as<float>(), H,
+                           k_blocks_of(H), L->a_packed.as<uint8_t>(), L->a_sf.as<uint8_t>(),
+                           L->a_ts.as<float>(), L->a_weight.as<float>(), L->a_dest.as<int32_t>(),
+                           L->pair_row.as<int32_t>(), K + 1, stream));
+
+  // routed experts (:896-954)
+  Schedule routed;
+  routed.row_tiles = L->row_tiles.as<RowTile>();
+  routed.num_row_tiles = L->num_row_tiles.as<int32_t>();
+  run_expert_gemms(L->up, L->down, routed_class, L->a_op, L->a_ts.as<float>(), routed,
+                   L->h_packed.as<uint8_t>(), L->h_sf.as<uint8_t>(), L->h_op,
+                   L->parts.as<float>(), L->a_dest.as<int32_t>(), 1, 0, L->a_weight.as<float>(),
+                   error, L->num_sms, stream);
+
+  // shared expert (:814-818, :956-964, :981-1005) on the same quantised rows
+  const TileClass shared_class =
+      tokens <= 32 ? kClassDecode : tokens <= 256 ? kClassDecodeWide : kClassPrefill;
+  Schedule shared;
+  shared.dense_rows = tokens;
+  run_expert_gemms(L->shared_up, L->shared_down, shared_class, L->y_op, L->y_ts.as<float>(),
+                   shared, L->sh_packed.as<uint8_t>(), L->sh_sf.as<uint8_t>(), L->sh_op,
+                   L->parts.as<float>(), nullptr, K + 1, K, nullptr, error, L->num_sms, stream);
+
+  // routed sum in selection order, mixer and residual (:951-953, :1064-1069)
+  NMOE_CUDA(launch_combine(input, in_dtype == NMOE_BF16, L->parts.as<float>(), tokens, H, K,
+                           output, out_dtype == NMOE_BF16, stream));
+  L->last_tokens = tokens;
+}
+
+}  // namespace
+
+extern "C" {
+
+nmoe_status nmoe_layer_create(const nmoe_config* config, const nmoe_weights* weights,
+                              nmoe_layer** out_layer) {
+  if (config == nullptr || weights == nullptr || out_layer == nullptr) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  *out_layer = nullptr;
+  std::unique_ptr<nmoe_layer> layer(new (std::nothrow) nmoe_layer);
+  if (!layer) return NMOE_ERR_CUDA;
+  try {
+    layer_create_impl(layer.get(), *config, *weights);
+  } catch (const Failure& failure) {
+    if (std::getenv("NEMOTRON_FORWARD_DEBUG") != nullptr) {
+      std::fprintf(stderr, "expert_layer_create: layer %d failed: %s\n", config->layer_index,
+                   failure.message.c_str());
+    }
+    return failure.status;
+  }
+  *out_layer = layer.release();
+  return NMOE_OK;
+}
+
+void nmoe_layer_destroy(nmoe_layer* layer) { delete layer; }
+
+nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void* input,
+                           nmoe_dtype input_dtype, int64_t tokens, void* output,
+                           nmoe_dtype output_dtype) {
+  if (layer == nullptr || input == nullptr || output == nullptr || tokens <= 0 ||
+      input == output) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  if (tokens > layer->cfg.max_tokens) return NMOE_ERR_CAPACITY;
+  try {
+    layer_run_impl(layer, static_cast<cudaStream_t>(stream), input, input_dtype,
+                   static_cast<int>(tokens), output, output_dtype);
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    if (std::getenv("NEMOTRON_FORWARD_DEBUG") != nullptr) {
+      std::fprintf(stderr, "expert_layer: %s\n", failure.message.c_str());
+    }
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_layer_sync_status(nmoe_layer* layer, void* stream) {
+  if (layer == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  try {
+    const nmoe_status status = layer->error.sync(static_cast<cudaStream_t>(stream));
+    if (status != NMOE_OK) layer->last_error = nmoe_status_string(status);
+    return status;
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+}
+
+const char* nmoe_layer_last_error(const nmoe_layer* layer) {
+  return layer == nullptr ? "null layer" : layer->last_error.c_str();
+}
+
+nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out) {
+  if (layer == nullptr || out == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  out->normalized_input = layer->normalized.as<float>();
+  out->router_logits = layer->logits.as<float>();
+  out->selected_index = layer->top_index.as<int32_t>();
+  out->selected_weight = layer->top_weight.as<float>();
+  out->act_packed = layer->y_packed.as<uint8_t>();
+  out->act_scales = layer->y_sf_row_major.as<uint8_t>();
+  out->act_tensor_scale = layer->y_ts.as<float>();
+  out->parts = layer->parts.as<float>();
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_layer_export_hidden(nmoe_layer* layer, void* stream_ptr, uint8_t* routed_packed,
+                                     uint8_t* routed_scales, uint8_t* shared_packed,
+                                     uint8_t* shared_scales) {
+  if (layer == nullptr || layer->last_tokens <= 0) return NMOE_ERR_INVALID_ARGUMENT;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const nmoe_config& c = layer->cfg;
+  const int pairs = layer->last_tokens * c.top_k;
+  if (routed_packed != nullptr || routed_scales != nullptr) {
+    export_rows_kernel<<<pairs, 128, 0, stream>>>(
+        layer->h_packed.as<uint8_t>(), layer->h_sf.as<uint8_t>(), layer->pair_row.as<int32_t>(),
+        pairs, c.routed_expert_intermediate_size,
+        k_blocks_of(c.routed_expert_intermediate_size) * 4, routed_packed, routed_scales);
+  }
+  if (shared_packed != nullptr || shared_scales != nullptr) {
+    export_rows_kernel<<<layer->last_tokens, 128, 0, stream>>>(
+        layer->sh_packed.as<uint8_t>(), layer->sh_sf.as<uint8_t>(), nullptr, layer->last_tokens,
+        c.shared_expert_intermediate_size, k_blocks_of(c.shared_expert_intermediate_size) * 4,
+        shared_packed, shared_scales);
+  }
+  return cudaGetLastError() == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------------------
+// unit operators
+// ---------------------------------------------------------------------------
+
+nmoe_status nmoe_quantize_nvfp4(void* stream_ptr, const void* input, nmoe_dtype dtype,
+                                int64_t rows, int64_t cols, int32_t per_row, uint8_t* packed,
+                                uint8_t* scales_row_major, uint8_t* scales_swizzled,
+                                float* tensor_scale) {
+  // argument checks of nvfp4_packing.cpp:95-97
+  if (input == nullptr || packed == nullptr || scales_row_major == nullptr ||
+      tensor_scale == nullptr || rows <= 0 || cols <= 0 || cols % 16 != 0) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  cudaError_t err;
+  if (per_row != 0) {
+    if (scales_swizzled != nullptr) {
+      err = cudaMemsetAsync(scales_swizzled, 0, nmoe_swizzled_scale_bytes(rows, cols), stream);
+      if (err != cudaSuccess) return NMOE_ERR_CUDA;
+    }
+    // the tiled layout of this entry point pads blocks to 4, not to a K block
+    err = launch_norm_quant(input, dtype == NMOE_BF16, static_cast<int>(rows),
+                            static_cast<int>(cols), nullptr, 0.0f, nullptr, packed,
+                            scales_row_major, nullptr, 0, tensor_scale, stream);
+    if (err == cudaSuccess && scales_swizzled != nullptr) {
+      err = launch_swizzle_scales(scales_row_major, static_cast<int>(rows),
+                                  static_cast<int>(cols), scales_swizzled, stream);
+    }
+  } else {
+    if (dtype != NMOE_F32) return NMOE_ERR_INVALID_ARGUMENT;
+    float* scratch = nullptr;
+    if (cudaMallocAsync(reinterpret_cast<void**>(&scratch), sizeof(float), stream) != cudaSuccess) {
+      return NMOE_ERR_CUDA;
+    }
+    err = launch_quant_matrix(static_cast<const float*>(input), static_cast<int>(rows),
+                              static_cast<int>(cols), packed, scales_row_major, tensor_scale,
+                              scratch, stream);
+    cudaFreeAsync(scratch, stream);
+    if (err == cudaSuccess && scales_swizzled != nullptr) {
+      err = launch_swizzle_scales(scales_row_major, static_cast<int>(rows),
+                                  static_cast<int>(cols), scales_swizzled, stream);
+    }
+  }
+  return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
+}
+
+nmoe_status nmoe_dequant_nvfp4(void* stream, const uint8_t* packed,
+                               const uint8_t* scales_row_major, const float* tensor_scale,
+                               int32_t per_row, int64_t rows, int64_t cols, float* output) {
+  if (packed == nullptr || scales_row_major == nullptr || tensor_scale == nullptr ||
+      output == nullptr || rows <= 0 || cols <= 0 || cols % 16 != 0) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  return launch_dequant(packed, scales_row_major, tensor_scale, per_row != 0,
+                        static_cast<int>(rows), static_cast<int>(cols), output,
+                        static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? NMOE_OK
+             : NMOE_ERR_CUDA;
+}
+
+size_t nmoe_swizzled_scale_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0 || cols % 16 != 0) return 0;
+  const size_t padded_rows = (static_cast<size_t>(rows) + 127) / 128 * 128;
+  const size_t padded_blocks = (static_cast<size_t>(cols) / 16 + 3) / 4 * 4;
+  return padded_rows * padded_blocks;
+}
+
+nmoe_status nmoe_swizzle_scales(void* stream, const uint8_t* scales_row_major, int64_t rows,
+                                int64_t cols, uint8_t* scales_swizzled) {
+  if (scales_row_major == nullptr || scales_swizzled == nullptr || rows <= 0 || cols <= 0 ||
+      cols % 16 != 0) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  return launch_swizzle_scales(scales_row_major, static_cast<int>(rows), static_cast<int>(cols),
+                               scales_swizzled, static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? NMOE_OK
+             : NMOE_ERR_CUDA;
+}
+
+nmoe_status nmoe_rmsnorm(void* stream_ptr, const void* input, nmoe_dtype dtype, int64_t rows,
+                         int64_t hidden, const float* weight, float epsilon, float* output) {
+  if (input == nullptr || weight == nullptr || output == nullptr || rows <= 0 || hidden <= 0 ||
+      hidden % 16 != 0 || !(epsilon > 0.0f)) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const cudaError_t err = launch_norm_quant(input, dtype == NMOE_BF16, static_cast<int>(rows),
+                                            static_cast<int>(hidden), weight, epsilon, output,
+                                            nullptr, nullptr, nullptr, 0, nullptr, stream);
+  return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
+}
+
+nmoe_status nmoe_router_logits(void* stream, const float* normalized, const float* gate,
+                               int64_t rows, int32_t experts, int32_t hidden, float* logits) {
+  if (normalized == nullptr || gate == nullptr || logits == nullptr) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  return launch_router_logits(normalized, gate, static_cast<int>(rows), experts, hidden, logits,
+                              static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? NMOE_OK
+             : NMOE_ERR_INVALID_ARGUMENT;
+}
+
+nmoe_status nmoe_router_topk(void* stream, const float* logits, const float* bias, int64_t rows,
+                             int32_t experts, int32_t top_k, int32_t n_group, int32_t topk_group,
+                             int32_t norm_topk_prob, float routed_scaling, int32_t* top_index,
+                             float* top_weight) {
+  if (logits == nullptr || bias == nullptr || top_index == nullptr || top_weight == nullptr) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  return launch_router_topk(logits, bias, static_cast<int>(rows), experts, top_k, n_group,
+                            topk_group, norm_topk_prob != 0, routed_scaling, top_index,
+                            top_weight, nullptr,
+                            static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? NMOE_OK
+             : NMOE_ERR_INVALID_ARGUMENT;
+}
+
+}  // extern "C"
