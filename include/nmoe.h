@@ -105,6 +105,9 @@ typedef struct nmoe_weights {
   int32_t first_local_expert;
   nmoe_nvfp4_matrix shared_up;   /* [shared_intermediate][hidden] */
   nmoe_nvfp4_matrix shared_down; /* [hidden][shared_intermediate] */
+  /* Optional FP32 [experts] added to the gate logits (NULL = none).  Not in the
+   * reference: a hook for synthetic workloads with skewed expert load. */
+  const float* gate_logit_offset;
 } nmoe_weights;
 
 typedef struct nmoe_layer nmoe_layer;
@@ -149,6 +152,11 @@ typedef struct nmoe_trace_view {
                                       contributions in selection order, then shared */
 } nmoe_trace_view;
 NMOE_API nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out);
+/* Copies one nmoe_trace_view field (index in declaration order, 0 =
+ * normalized_input) of the last run into `dst` (device or host), `nbytes`
+ * bytes, in stream order. */
+NMOE_API nmoe_status nmoe_layer_copy_trace_field(nmoe_layer* layer, void* stream, int32_t field,
+                                                 void* dst, size_t nbytes);
 
 /* Copies the quantised relu^2 intermediates of the LAST run into
  * (token, slot)-ordered row-major buffers (device pointers):

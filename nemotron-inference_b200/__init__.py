@@ -1,0 +1,517 @@
+"""B200 NVFP4 mixture-of-experts expert layer: Python host side over the C ABI.
+
+The classes mirror the reference operator's interface
+(`nemotron::ExpertLayerConfig`, `ExpertLayerBindings`, `ExpertLayerSlice`,
+runtime/include/nemotron/expert_layer.h:18-105) so that a test written against
+the reference reads the same here.  torch is used for device memory and streams
+only; every computation goes through `libnmoe_b200.so` (include/nmoe.h).  There
+is no CPU path: without the built library, or without a CUDA device, the
+operators raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY_PATH = os.path.join(_HERE, "libnmoe_b200.so")
+
+NMOE_OK = 0
+NMOE_F32 = 0
+NMOE_BF16 = 1
+
+STATUS_NAMES = {
+    0: "NMOE_OK", 1: "NMOE_ERR_INVALID_ARGUMENT", 2: "NMOE_ERR_CUDA", 3: "NMOE_ERR_UNSUPPORTED",
+    4: "NMOE_ERR_DEVICE_TIMEOUT", 5: "NMOE_ERR_ACTIVATION_RANGE", 6: "NMOE_ERR_CAPACITY",
+}
+
+# Every symbol include/nmoe.h declares.
+EXPORTED_SYMBOLS = (
+    "nmoe_status_string", "nmoe_layer_create", "nmoe_layer_destroy", "nmoe_layer_run",
+    "nmoe_layer_sync_status", "nmoe_layer_last_error", "nmoe_layer_trace_view",
+    "nmoe_layer_copy_trace_field",
+    "nmoe_layer_export_hidden", "nmoe_ffn_create", "nmoe_ffn_destroy", "nmoe_ffn_run",
+    "nmoe_ffn_sync_status", "nmoe_ffn_export_hidden", "nmoe_quantize_nvfp4",
+    "nmoe_dequant_nvfp4", "nmoe_swizzled_scale_bytes", "nmoe_swizzle_scales", "nmoe_rmsnorm",
+    "nmoe_router_logits", "nmoe_router_topk",
+)
+
+
+class NmoeError(RuntimeError):
+    def __init__(self, status: int, where: str, detail: str = ""):
+        self.status = status
+        name = STATUS_NAMES.get(status, str(status))
+        super().__init__(f"{where}: {name}" + (f" ({detail})" if detail else ""))
+
+
+class _Config(ctypes.Structure):
+    _fields_ = [("layer_index", ctypes.c_int32), ("hidden_size", ctypes.c_int32),
+                ("moe_latent_size", ctypes.c_int32),
+                ("routed_expert_intermediate_size", ctypes.c_int32),
+                ("shared_expert_intermediate_size", ctypes.c_int32),
+                ("n_routed_experts", ctypes.c_int32), ("top_k", ctypes.c_int32),
+                ("n_group", ctypes.c_int32), ("topk_group", ctypes.c_int32),
+                ("norm_topk_prob", ctypes.c_int32), ("rms_epsilon", ctypes.c_float),
+                ("routed_scaling_factor", ctypes.c_float), ("max_tokens", ctypes.c_int32)]
+
+
+class _Nvfp4Matrix(ctypes.Structure):
+    _fields_ = [("output_rows", ctypes.c_size_t), ("input_cols", ctypes.c_size_t),
+                ("packed_data", ctypes.c_void_p), ("packed_nbytes", ctypes.c_size_t),
+                ("block_scales_data", ctypes.c_void_p), ("block_scales_nbytes", ctypes.c_size_t),
+                ("tensor_scale_data", ctypes.c_void_p), ("tensor_scale_nbytes", ctypes.c_size_t)]
+
+
+class _DenseTensor(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("nbytes", ctypes.c_size_t),
+                ("dtype", ctypes.c_int), ("rows", ctypes.c_size_t), ("cols", ctypes.c_size_t)]
+
+
+class _Weights(ctypes.Structure):
+    _fields_ = [("input_norm_weight", _DenseTensor), ("gate_weight", _DenseTensor),
+                ("gate_score_correction_bias", _DenseTensor),
+                ("routed_up", ctypes.POINTER(_Nvfp4Matrix)),
+                ("routed_down", ctypes.POINTER(_Nvfp4Matrix)),
+                ("n_local_experts", ctypes.c_int32), ("first_local_expert", ctypes.c_int32),
+                ("shared_up", _Nvfp4Matrix), ("shared_down", _Nvfp4Matrix),
+                ("gate_logit_offset", ctypes.c_void_p)]
+
+
+class _TraceView(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_void_p) for name in (
+        "normalized_input", "router_logits", "selected_index", "selected_weight", "act_packed",
+        "act_scales", "act_tensor_scale", "parts")]
+
+
+_lib = None
+
+
+def load_library() -> ctypes.CDLL:
+    """Loads the C-ABI library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIBRARY_PATH):
+        raise FileNotFoundError(
+            f"{LIBRARY_PATH} is missing: run __graft_entry__.build() (there is no fallback path)")
+    lib = ctypes.CDLL(LIBRARY_PATH)
+    vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_float
+    lib.nmoe_status_string.restype = ctypes.c_char_p
+    lib.nmoe_status_string.argtypes = [ctypes.c_int]
+    lib.nmoe_layer_create.argtypes = [ctypes.POINTER(_Config), ctypes.POINTER(_Weights),
+                                      ctypes.POINTER(vp)]
+    lib.nmoe_layer_destroy.argtypes = [vp]
+    lib.nmoe_layer_destroy.restype = None
+    lib.nmoe_layer_run.argtypes = [vp, vp, vp, ctypes.c_int, i64, vp, ctypes.c_int]
+    lib.nmoe_layer_sync_status.argtypes = [vp, vp]
+    lib.nmoe_layer_last_error.argtypes = [vp]
+    lib.nmoe_layer_last_error.restype = ctypes.c_char_p
+    lib.nmoe_layer_trace_view.argtypes = [vp, ctypes.POINTER(_TraceView)]
+    lib.nmoe_layer_copy_trace_field.argtypes = [vp, vp, i32, vp, ctypes.c_size_t]
+    lib.nmoe_layer_export_hidden.argtypes = [vp, vp, vp, vp, vp, vp]
+    lib.nmoe_ffn_create.argtypes = [ctypes.POINTER(_Nvfp4Matrix), ctypes.POINTER(_Nvfp4Matrix),
+                                    i32, ctypes.POINTER(vp)]
+    lib.nmoe_ffn_destroy.argtypes = [vp]
+    lib.nmoe_ffn_destroy.restype = None
+    lib.nmoe_ffn_run.argtypes = [vp, vp, vp, ctypes.c_int, i64, vp, i32]
+    lib.nmoe_ffn_sync_status.argtypes = [vp, vp]
+    lib.nmoe_ffn_export_hidden.argtypes = [vp, vp, vp, vp]
+    lib.nmoe_quantize_nvfp4.argtypes = [vp, vp, ctypes.c_int, i64, i64, i32, vp, vp, vp, vp]
+    lib.nmoe_dequant_nvfp4.argtypes = [vp, vp, vp, vp, i32, i64, i64, vp]
+    lib.nmoe_swizzled_scale_bytes.argtypes = [i64, i64]
+    lib.nmoe_swizzled_scale_bytes.restype = ctypes.c_size_t
+    lib.nmoe_swizzle_scales.argtypes = [vp, vp, i64, i64, vp]
+    lib.nmoe_rmsnorm.argtypes = [vp, vp, ctypes.c_int, i64, i64, vp, f32, vp]
+    lib.nmoe_router_logits.argtypes = [vp, vp, vp, i64, i32, i32, vp]
+    lib.nmoe_router_topk.argtypes = [vp, vp, vp, i64, i32, i32, i32, i32, i32, f32, vp, vp]
+    _lib = lib
+    return lib
+
+
+def _check(status: int, where: str, detail: str = "") -> None:
+    if status != NMOE_OK:
+        raise NmoeError(status, where, detail)
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor: this library has no CPU path")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return NMOE_F32
+    if t.dtype == torch.bfloat16:
+        return NMOE_BF16
+    raise ValueError(f"unsupported dtype {t.dtype}: expected float32 or bfloat16")
+
+
+# ---------------------------------------------------------------------------
+# Reference-shaped types
+# ---------------------------------------------------------------------------
+
+@dataclass
+class ExpertLayerConfig:
+    """Field for field `nemotron::ExpertLayerConfig` (expert_layer.h:18-31), plus the
+    token capacity the device scratch is sized for."""
+    layer_index: int = 0
+    hidden_size: int = 0
+    moe_latent_size: int = 0
+    routed_expert_intermediate_size: int = 0
+    shared_expert_intermediate_size: int = 0
+    n_routed_experts: int = 0
+    top_k: int = 0
+    n_group: int = 1
+    topk_group: int = 1
+    rms_epsilon: float = 1.0e-5
+    routed_scaling_factor: float = 1.0
+    norm_topk_prob: bool = True
+    max_tokens: int = 8192
+
+
+@dataclass
+class Nvfp4Matrix:
+    """The byte fields of an NVFP4 `GemmDescriptor` (gemm_catalog.h:20-42):
+    packed [N, K/2] uint8 (column 2j in the low nibble), block_scales [N, K/16]
+    uint8 E4M3 row-major, tensor_scale FP32.  Tensors may live on host or device."""
+    packed: torch.Tensor
+    block_scales: torch.Tensor
+    tensor_scale: float
+
+    @property
+    def output_rows(self) -> int:
+        return self.packed.shape[0]
+
+    @property
+    def input_cols(self) -> int:
+        return self.packed.shape[1] * 2
+
+    def _as_c(self, keep: list) -> _Nvfp4Matrix:
+        packed = self.packed.contiguous()
+        scales = self.block_scales.contiguous()
+        ts = torch.tensor([self.tensor_scale], dtype=torch.float32)
+        keep.extend([packed, scales, ts])
+        return _Nvfp4Matrix(packed.shape[0], packed.shape[1] * 2, packed.data_ptr(),
+                            packed.numel(), scales.data_ptr(), scales.numel(), ts.data_ptr(), 4)
+
+
+@dataclass
+class ExpertWeightPair:
+    up_proj: Nvfp4Matrix
+    down_proj: Nvfp4Matrix
+
+
+@dataclass
+class ExpertLayerBindings:
+    """`nemotron::ExpertLayerBindings` (expert_layer.h:38-56) for all-NVFP4 expert
+    weights and identity latent projections."""
+    input_norm_weight: torch.Tensor            # [hidden] fp32 / bf16
+    gate_weight: torch.Tensor                  # [experts, hidden] fp32 / bf16
+    gate_score_correction_bias: torch.Tensor   # [experts]
+    shared_up: Nvfp4Matrix
+    shared_down: Nvfp4Matrix
+    routed_experts: List[ExpertWeightPair] = field(default_factory=list)
+    gate_logit_offset: Optional[torch.Tensor] = None  # [experts] fp32, synthetic-skew hook
+
+
+def _dense(t: torch.Tensor, keep: list) -> _DenseTensor:
+    t = t.contiguous()
+    keep.append(t)
+    rows, cols = (t.shape[0], t.shape[1]) if t.dim() == 2 else (1, t.numel())
+    return _DenseTensor(t.data_ptr(), t.numel() * t.element_size(), _dtype_code(t), rows, cols)
+
+
+@dataclass
+class ExpertLayerTrace:
+    """Device views of the intermediates of the last run (`ExpertLayerRunTrace`,
+    expert_layer.h:63-76, for any token count)."""
+    normalized_input: torch.Tensor
+    router_logits: torch.Tensor
+    selected_index: torch.Tensor
+    selected_weight: torch.Tensor
+    act_packed: torch.Tensor
+    act_scales: torch.Tensor
+    act_tensor_scale: torch.Tensor
+    parts: torch.Tensor
+    routed_hidden_packed: torch.Tensor
+    routed_hidden_scales: torch.Tensor
+    shared_hidden_packed: torch.Tensor
+    shared_hidden_scales: torch.Tensor
+
+
+class ExpertLayerSlice:
+    """`nemotron::ExpertLayerSlice` (expert_layer.h:84-105).  `create` returns None
+    on invalid configuration or bindings, `run` returns False on failure, as the
+    reference does; `last_error` says why."""
+
+    def __init__(self, handle: int, config: ExpertLayerConfig):
+        self._handle = ctypes.c_void_p(handle)
+        self._config = config
+        self.last_error = ""
+
+    @staticmethod
+    def create(config: ExpertLayerConfig, bindings: ExpertLayerBindings
+               ) -> Optional["ExpertLayerSlice"]:
+        lib = load_library()
+        if not torch.cuda.is_available():
+            raise RuntimeError("ExpertLayerSlice needs a CUDA device: there is no CPU path")
+        keep: list = []
+        c = _Config(config.layer_index, config.hidden_size, config.moe_latent_size,
+                    config.routed_expert_intermediate_size,
+                    config.shared_expert_intermediate_size, config.n_routed_experts,
+                    config.top_k, config.n_group, config.topk_group,
+                    1 if config.norm_topk_prob else 0, config.rms_epsilon,
+                    config.routed_scaling_factor, config.max_tokens)
+        n = len(bindings.routed_experts)
+        ups = (_Nvfp4Matrix * max(n, 1))()
+        downs = (_Nvfp4Matrix * max(n, 1))()
+        for i, pair in enumerate(bindings.routed_experts):
+            ups[i] = pair.up_proj._as_c(keep)
+            downs[i] = pair.down_proj._as_c(keep)
+        w = _Weights()
+        w.input_norm_weight = _dense(bindings.input_norm_weight, keep)
+        w.gate_weight = _dense(bindings.gate_weight, keep)
+        w.gate_score_correction_bias = _dense(bindings.gate_score_correction_bias, keep)
+        w.routed_up = ups
+        w.routed_down = downs
+        w.n_local_experts = n
+        w.first_local_expert = 0
+        w.shared_up = bindings.shared_up._as_c(keep)
+        w.shared_down = bindings.shared_down._as_c(keep)
+        w.gate_logit_offset = None
+        if bindings.gate_logit_offset is not None:
+            offset = bindings.gate_logit_offset.to(torch.float32).contiguous()
+            keep.append(offset)
+            w.gate_logit_offset = offset.data_ptr()
+        handle = ctypes.c_void_p()
+        status = lib.nmoe_layer_create(ctypes.byref(c), ctypes.byref(w), ctypes.byref(handle))
+        if status != NMOE_OK or not handle.value:
+            ExpertLayerSlice.create_error = STATUS_NAMES.get(status, str(status))
+            return None
+        return ExpertLayerSlice(handle.value, config)
+
+    create_error = ""
+
+    def valid(self) -> bool:
+        return bool(self._handle and self._handle.value)
+
+    def config(self) -> ExpertLayerConfig:
+        return self._config
+
+    def run_async(self, input: torch.Tensor, output: torch.Tensor) -> None:
+        """Enqueues the layer on the current stream; raises on a host-side error."""
+        _require_cuda(input, "input")
+        _require_cuda(output, "output")
+        if input.dim() != 2 or input.shape[1] != self._config.hidden_size or \
+                output.shape != input.shape:
+            raise NmoeError(1, "ExpertLayerSlice.run", "shape must be [tokens, hidden] for both")
+        lib = load_library()
+        _check(lib.nmoe_layer_run(self._handle, _stream(), input.data_ptr(), _dtype_code(input),
+                                  input.shape[0], output.data_ptr(), _dtype_code(output)),
+               "nmoe_layer_run", self._last_error())
+
+    def sync_status(self) -> int:
+        return load_library().nmoe_layer_sync_status(self._handle, _stream())
+
+    def run(self, input: torch.Tensor, output: torch.Tensor) -> bool:
+        """Synchronous, boolean, like ExpertLayerSlice::Run (expert_layer.cpp:752)."""
+        try:
+            self.run_async(input, output)
+        except (NmoeError, ValueError) as error:
+            self.last_error = str(error)
+            return False
+        status = self.sync_status()
+        if status != NMOE_OK:
+            self.last_error = STATUS_NAMES.get(status, str(status))
+            return False
+        return True
+
+    def _last_error(self) -> str:
+        raw = load_library().nmoe_layer_last_error(self._handle)
+        return raw.decode() if raw else ""
+
+    def trace(self, tokens: int) -> ExpertLayerTrace:
+        """Copies the intermediates of the last run (which had `tokens` rows)."""
+        lib = load_library()
+        cfg = self._config
+        dev = torch.device("cuda", torch.cuda.current_device())
+        H, E, K = cfg.hidden_size, cfg.n_routed_experts, cfg.top_k
+        I, S = cfg.routed_expert_intermediate_size, cfg.shared_expert_intermediate_size
+
+        fields = ("normalized_input", "router_logits", "selected_index", "selected_weight",
+                  "act_packed", "act_scales", "act_tensor_scale", "parts")
+
+        def grab(name, shape, dtype):
+            out = torch.empty(shape, dtype=dtype, device=dev)
+            _check(lib.nmoe_layer_copy_trace_field(self._handle, _stream(), fields.index(name),
+                                                   out.data_ptr(), out.numel() * out.element_size()),
+                   "nmoe_layer_copy_trace_field")
+            return out
+
+        rp = torch.empty((tokens, K, I // 2), dtype=torch.uint8, device=dev)
+        rs = torch.empty((tokens, K, I // 16), dtype=torch.uint8, device=dev)
+        sp = torch.empty((tokens, S // 2), dtype=torch.uint8, device=dev)
+        ss = torch.empty((tokens, S // 16), dtype=torch.uint8, device=dev)
+        _check(lib.nmoe_layer_export_hidden(self._handle, _stream(), rp.data_ptr(), rs.data_ptr(),
+                                            sp.data_ptr(), ss.data_ptr()),
+               "nmoe_layer_export_hidden")
+        trace = ExpertLayerTrace(
+            normalized_input=grab("normalized_input", (tokens, H), torch.float32),
+            router_logits=grab("router_logits", (tokens, E), torch.float32),
+            selected_index=grab("selected_index", (tokens, K), torch.int32),
+            selected_weight=grab("selected_weight", (tokens, K), torch.float32),
+            act_packed=grab("act_packed", (tokens, H // 2), torch.uint8),
+            act_scales=grab("act_scales", (tokens, H // 16), torch.uint8),
+            act_tensor_scale=grab("act_tensor_scale", (tokens,), torch.float32),
+            parts=grab("parts", (tokens, K + 1, H), torch.float32),
+            routed_hidden_packed=rp, routed_hidden_scales=rs,
+            shared_hidden_packed=sp, shared_hidden_scales=ss)
+        torch.cuda.current_stream().synchronize()
+        return trace
+
+    def close(self) -> None:
+        if self._handle and self._handle.value:
+            load_library().nmoe_layer_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class ExpertFfn:
+    """One NVFP4 expert FFN down(relu^2(up(x))): the per-(token, expert) composition
+    of expert_layer.cpp:913-922."""
+
+    def __init__(self, up: Nvfp4Matrix, down: Nvfp4Matrix, max_rows: int):
+        lib = load_library()
+        if not torch.cuda.is_available():
+            raise RuntimeError("ExpertFfn needs a CUDA device: there is no CPU path")
+        keep: list = []
+        cu, cd = up._as_c(keep), down._as_c(keep)
+        handle = ctypes.c_void_p()
+        _check(lib.nmoe_ffn_create(ctypes.byref(cu), ctypes.byref(cd), max_rows,
+                                   ctypes.byref(handle)), "nmoe_ffn_create")
+        self._handle = handle
+        self.hidden = up.input_cols
+        self.intermediate = up.output_rows
+
+    def run(self, x: torch.Tensor, variant: int = 0) -> torch.Tensor:
+        _require_cuda(x, "x")
+        out = torch.empty((x.shape[0], self.hidden), dtype=torch.float32, device=x.device)
+        lib = load_library()
+        _check(lib.nmoe_ffn_run(self._handle, _stream(), x.data_ptr(), _dtype_code(x), x.shape[0],
+                                out.data_ptr(), variant), "nmoe_ffn_run")
+        _check(lib.nmoe_ffn_sync_status(self._handle, _stream()), "nmoe_ffn_sync_status")
+        return out
+
+    def hidden_codes(self, rows: int):
+        dev = torch.device("cuda", torch.cuda.current_device())
+        packed = torch.empty((rows, self.intermediate // 2), dtype=torch.uint8, device=dev)
+        scales = torch.empty((rows, self.intermediate // 16), dtype=torch.uint8, device=dev)
+        _check(load_library().nmoe_ffn_export_hidden(self._handle, _stream(), packed.data_ptr(),
+                                                     scales.data_ptr()), "nmoe_ffn_export_hidden")
+        torch.cuda.current_stream().synchronize()
+        return packed, scales
+
+    def close(self) -> None:
+        if self._handle and self._handle.value:
+            load_library().nmoe_ffn_destroy(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---------------------------------------------------------------------------
+# Unit operators
+# ---------------------------------------------------------------------------
+
+def quantize_nvfp4(x: torch.Tensor, per_row: bool = True, swizzled: bool = False):
+    """PackRowMajorFp32ToNvfp4 on the device.  Returns (packed, scales, tensor_scale[,
+    swizzled_scales])."""
+    _require_cuda(x, "x")
+    lib = load_library()
+    rows, cols = x.shape
+    packed = torch.empty((rows, cols // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((rows, cols // 16), dtype=torch.uint8, device=x.device)
+    ts = torch.empty((rows if per_row else 1,), dtype=torch.float32, device=x.device)
+    sw = None
+    if swizzled:
+        sw = torch.empty((lib.nmoe_swizzled_scale_bytes(rows, cols),), dtype=torch.uint8,
+                         device=x.device)
+    _check(lib.nmoe_quantize_nvfp4(_stream(), x.data_ptr(), _dtype_code(x), rows, cols,
+                                   1 if per_row else 0, packed.data_ptr(), scales.data_ptr(),
+                                   sw.data_ptr() if sw is not None else None, ts.data_ptr()),
+           "nmoe_quantize_nvfp4")
+    return (packed, scales, ts, sw) if swizzled else (packed, scales, ts)
+
+
+def dequant_nvfp4(packed: torch.Tensor, scales: torch.Tensor, tensor_scale: torch.Tensor,
+                  per_row: bool = True) -> torch.Tensor:
+    _require_cuda(packed, "packed")
+    rows, cols = packed.shape[0], packed.shape[1] * 2
+    out = torch.empty((rows, cols), dtype=torch.float32, device=packed.device)
+    _check(load_library().nmoe_dequant_nvfp4(_stream(), packed.data_ptr(), scales.data_ptr(),
+                                             tensor_scale.data_ptr(), 1 if per_row else 0, rows,
+                                             cols, out.data_ptr()), "nmoe_dequant_nvfp4")
+    return out
+
+
+def swizzle_scales(scales: torch.Tensor, cols: int) -> torch.Tensor:
+    _require_cuda(scales, "scales")
+    lib = load_library()
+    rows = scales.shape[0]
+    out = torch.empty((lib.nmoe_swizzled_scale_bytes(rows, cols),), dtype=torch.uint8,
+                      device=scales.device)
+    _check(lib.nmoe_swizzle_scales(_stream(), scales.data_ptr(), rows, cols, out.data_ptr()),
+           "nmoe_swizzle_scales")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    _require_cuda(x, "x")
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    _check(load_library().nmoe_rmsnorm(_stream(), x.data_ptr(), _dtype_code(x), x.shape[0],
+                                       x.shape[1], weight.data_ptr(), eps, out.data_ptr()),
+           "nmoe_rmsnorm")
+    return out
+
+
+def router_logits(normalized: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    _require_cuda(normalized, "normalized")
+    rows, hidden = normalized.shape
+    experts = gate.shape[0]
+    out = torch.empty((rows, experts), dtype=torch.float32, device=normalized.device)
+    _check(load_library().nmoe_router_logits(_stream(), normalized.data_ptr(), gate.data_ptr(),
+                                             rows, experts, hidden, out.data_ptr()),
+           "nmoe_router_logits")
+    return out
+
+
+def router_topk(logits: torch.Tensor, bias: torch.Tensor, top_k: int, n_group: int = 1,
+                topk_group: int = 1, norm_topk_prob: bool = True, routed_scaling: float = 1.0):
+    _require_cuda(logits, "logits")
+    rows, experts = logits.shape
+    idx = torch.empty((rows, top_k), dtype=torch.int32, device=logits.device)
+    wt = torch.empty((rows, top_k), dtype=torch.float32, device=logits.device)
+    _check(load_library().nmoe_router_topk(_stream(), logits.data_ptr(), bias.data_ptr(), rows,
+                                           experts, top_k, n_group, topk_group,
+                                           1 if norm_topk_prob else 0, routed_scaling,
+                                           idx.data_ptr(), wt.data_ptr()), "nmoe_router_topk")
+    return idx, wt

@@ -107,7 +107,8 @@ cudaError_t launch_swizzle_scales(const uint8_t* row_major, int rows, int cols, 
                                   cudaStream_t stream);
 
 // --- router ------------------------------------------------------------------
-cudaError_t launch_router_logits(const float* normalized, const float* gate, int rows,
+cudaError_t launch_router_logits(const float* normalized, const float* gate,
+                                 const float* logit_offset /* nullable [experts] */, int rows,
                                  int experts, int hidden, float* logits, cudaStream_t stream);
 cudaError_t launch_router_topk(const float* logits, const float* bias, int rows, int experts,
                                int top_k, int n_group, int topk_group, bool norm_topk_prob,

@@ -498,7 +498,8 @@ struct nmoe_layer {
   int max_row_tiles = 0;
   int decode_pairs_limit = 0;
 
-  DeviceBuffer norm_weight, gate, bias;
+  DeviceBuffer norm_weight, gate, bias, logit_offset;
+  bool has_logit_offset = false;
   WeightStack up, down, shared_up, shared_down;
 
   // token-order scratch
@@ -553,6 +554,12 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
   upload_dense_fp32(w.input_norm_weight, H, "input_norm_weight", &L->norm_weight, stream);
   upload_dense_fp32(w.gate_weight, static_cast<size_t>(E) * H, "gate_weight", &L->gate, stream);
   upload_dense_fp32(w.gate_score_correction_bias, E, "gate_score_correction_bias", &L->bias, stream);
+  if (w.gate_logit_offset != nullptr) {
+    L->logit_offset.allocate(E * sizeof(float));
+    NMOE_CUDA(cudaMemcpyAsync(L->logit_offset.as<float>(), w.gate_logit_offset,
+                              E * sizeof(float), cudaMemcpyDefault, stream));
+    L->has_logit_offset = true;
+  }
   L->up.upload(w.routed_up, E, I, H, true, "routed up_proj", stream);
   L->down.upload(w.routed_down, E, H, I, false, "routed down_proj", stream);
   L->shared_up.upload(&w.shared_up, 1, S, H, true, "shared up_proj", stream);
@@ -614,8 +621,9 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
                               L->y_sf_row_major.as<uint8_t>(), L->y_sf_tiled.as<uint8_t>(),
                               k_blocks_of(H), L->y_ts.as<float>(), stream));
   // gate projection (:797-799) and top-k (:881)
-  NMOE_CUDA(launch_router_logits(L->normalized.as<float>(), L->gate.as<float>(), tokens, E, H,
-                                 L->logits.as<float>(), stream));
+  NMOE_CUDA(launch_router_logits(L->normalized.as<float>(), L->gate.as<float>(),
+                                 L->has_logit_offset ? L->logit_offset.as<float>() : nullptr,
+                                 tokens, E, H, L->logits.as<float>(), stream));
   NMOE_CUDA(cudaMemsetAsync(L->counts.as<int32_t>(), 0, E * sizeof(int32_t), stream));
   NMOE_CUDA(launch_router_topk(L->logits.as<float>(), L->bias.as<float>(), tokens, E, K,
                                c.n_group, c.topk_group, c.norm_topk_prob != 0,
@@ -740,6 +748,21 @@ nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out) {
   return NMOE_OK;
 }
 
+nmoe_status nmoe_layer_copy_trace_field(nmoe_layer* layer, void* stream, int32_t field, void* dst,
+                                        size_t nbytes) {
+  if (layer == nullptr || dst == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  nmoe_trace_view view;
+  nmoe_layer_trace_view(layer, &view);
+  const void* sources[8] = {view.normalized_input, view.router_logits, view.selected_index,
+                            view.selected_weight,  view.act_packed,    view.act_scales,
+                            view.act_tensor_scale, view.parts};
+  if (field < 0 || field >= 8) return NMOE_ERR_INVALID_ARGUMENT;
+  return cudaMemcpyAsync(dst, sources[field], nbytes, cudaMemcpyDefault,
+                         static_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? NMOE_OK
+             : NMOE_ERR_CUDA;
+}
+
 nmoe_status nmoe_layer_export_hidden(nmoe_layer* layer, void* stream_ptr, uint8_t* routed_packed,
                                      uint8_t* routed_scales, uint8_t* shared_packed,
                                      uint8_t* shared_scales) {
@@ -859,7 +882,8 @@ nmoe_status nmoe_router_logits(void* stream, const float* normalized, const floa
   if (normalized == nullptr || gate == nullptr || logits == nullptr) {
     return NMOE_ERR_INVALID_ARGUMENT;
   }
-  return launch_router_logits(normalized, gate, static_cast<int>(rows), experts, hidden, logits,
+  return launch_router_logits(normalized, gate, nullptr, static_cast<int>(rows), experts, hidden,
+                              logits,
                               static_cast<cudaStream_t>(stream)) == cudaSuccess
              ? NMOE_OK
              : NMOE_ERR_INVALID_ARGUMENT;

@@ -21,8 +21,9 @@ constexpr int kWarps = 8;
 // One warp computes TPW tokens x EPW experts; lanes split the hidden dimension.
 template <int TPW, int EPW>
 __global__ void __launch_bounds__(kWarps * 32)
-router_logits_kernel(const float* __restrict__ y, const float* __restrict__ gate, int rows,
-                     int experts, int hidden, float* __restrict__ logits) {
+router_logits_kernel(const float* __restrict__ y, const float* __restrict__ gate,
+                     const float* __restrict__ logit_offset, int rows, int experts, int hidden,
+                     float* __restrict__ logits) {
   const int lane = threadIdx.x & 31;
   const int warp_global = blockIdx.x * kWarps + (threadIdx.x >> 5);
   const int expert_tiles = experts / EPW;
@@ -62,7 +63,9 @@ router_logits_kernel(const float* __restrict__ y, const float* __restrict__ gate
         v += __shfl_xor_sync(0xffffffffu, v, stride);
       }
       if (lane == 0 && t0 + i < rows) {
-        logits[static_cast<size_t>(t0 + i) * experts + e0 + j] = static_cast<float>(v);
+        float logit = static_cast<float>(v);
+        if (logit_offset != nullptr) logit = __fadd_rn(logit, logit_offset[e0 + j]);
+        logits[static_cast<size_t>(t0 + i) * experts + e0 + j] = logit;
       }
     }
   }
@@ -226,21 +229,22 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ b
 
 }  // namespace
 
-cudaError_t launch_router_logits(const float* normalized, const float* gate, int rows,
-                                 int experts, int hidden, float* logits, cudaStream_t stream) {
+cudaError_t launch_router_logits(const float* normalized, const float* gate,
+                                 const float* logit_offset, int rows, int experts, int hidden,
+                                 float* logits, cudaStream_t stream) {
   if (rows <= 0 || experts <= 0 || hidden <= 0) return cudaErrorInvalidValue;
   if (rows >= 256 && experts % 16 == 0) {
     const int warps = ((rows + 1) / 2) * (experts / 16);
     router_logits_kernel<2, 16><<<(warps + kWarps - 1) / kWarps, kWarps * 32, 0, stream>>>(
-        normalized, gate, rows, experts, hidden, logits);
+        normalized, gate, logit_offset, rows, experts, hidden, logits);
   } else if (experts % 4 == 0) {
     const int warps = rows * (experts / 4);
     router_logits_kernel<1, 4><<<(warps + kWarps - 1) / kWarps, kWarps * 32, 0, stream>>>(
-        normalized, gate, rows, experts, hidden, logits);
+        normalized, gate, logit_offset, rows, experts, hidden, logits);
   } else {
     const int warps = rows * experts;
     router_logits_kernel<1, 1><<<(warps + kWarps - 1) / kWarps, kWarps * 32, 0, stream>>>(
-        normalized, gate, rows, experts, hidden, logits);
+        normalized, gate, logit_offset, rows, experts, hidden, logits);
   }
   return cudaGetLastError();
 }

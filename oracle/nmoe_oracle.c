@@ -675,6 +675,8 @@ typedef struct {
   const nmo_nvfp4_weight* down; /* [E] each [H][I] */
   nmo_nvfp4_weight shared_up;   /* [S][H] */
   nmo_nvfp4_weight shared_down; /* [H][S] */
+  const float* logit_offset;    /* optional [E] added to the FP32 logits (not in the
+                                   reference: synthetic skewed-load hook) */
 } nmo_layer_weights;
 
 /* Optional outputs (NULL to skip) and optional device candidates for the
@@ -751,6 +753,9 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
   /* :795-799 RMSNorm + gate projection */
   nmo_rmsnorm(x, w->norm_weight, Tn, H, cfg->rms_eps, y);
   nmo_router_logits(y, w->gate, Tn, E, H, logits);
+  if (w->logit_offset != NULL) {
+    for (size_t i = 0; i < Tn * E; ++i) logits[i] = logits[i] + w->logit_offset[i % E];
+  }
 
   /* :881 top-k per token; :913 activation pack per row (rows == 1) */
 #pragma omp parallel for schedule(static)
@@ -950,6 +955,9 @@ NMO_EXPORT int nmo_layer_forward_literal(const nmo_layer_config* cfg,
   int status = 0;
   nmo_rmsnorm(x, w->norm_weight, Tn, H, cfg->rms_eps, y);
   nmo_router_logits(y, w->gate, Tn, E, H, logits);
+  if (w->logit_offset != NULL) {
+    for (size_t i = 0; i < Tn * E; ++i) logits[i] = logits[i] + w->logit_offset[i % E];
+  }
   for (size_t t = 0; t < Tn && status == 0; ++t) {
     if (nmo_select_top_experts(logits + t * E, w->bias, (int)E, (int)K, cfg->n_group,
                                cfg->topk_group, cfg->norm_topk_prob, cfg->routed_scaling,

@@ -1,0 +1,161 @@
+"""Shared test helpers: conversion of synthetic layers to oracle inputs and the
+layer parity report used by the GPU tests, smoke() and bench.py."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+import __graft_entry__ as entry
+
+MAX_ABS_TOL = 2e-2      # north-star tolerance on the layer output
+COSINE_TOL = 0.9995
+OVERRIDE_EPS = 1e-4     # relative perturbation that defines an admissible code difference
+
+
+def oracle_config(cfg):
+    oracle = entry.load_oracle()
+    return oracle.LayerConfig(
+        hidden=cfg.hidden_size, routed_intermediate=cfg.routed_expert_intermediate_size,
+        shared_intermediate=cfg.shared_expert_intermediate_size, experts=cfg.n_routed_experts,
+        top_k=cfg.top_k, n_group=cfg.n_group, topk_group=cfg.topk_group,
+        norm_topk_prob=cfg.norm_topk_prob, rms_eps=cfg.rms_epsilon,
+        routed_scaling=cfg.routed_scaling_factor)
+
+
+def _np(t: torch.Tensor) -> np.ndarray:
+    if t.dtype == torch.bfloat16:
+        t = t.to(torch.float32)
+    return t.detach().cpu().numpy()
+
+
+def oracle_weights(layer_data):
+    oracle = entry.load_oracle()
+    b = layer_data.bindings
+    up_p, up_s, up_t = _np(layer_data.up_packed), _np(layer_data.up_scales), _np(layer_data.up_ts)
+    dn_p, dn_s, dn_t = (_np(layer_data.down_packed), _np(layer_data.down_scales),
+                        _np(layer_data.down_ts))
+    E = up_p.shape[0]
+    return oracle.LayerWeights(
+        norm_weight=_np(b.input_norm_weight), gate=_np(b.gate_weight),
+        bias=_np(b.gate_score_correction_bias),
+        up=[oracle.Nvfp4Weight(up_p[e], up_s[e], float(up_t[e])) for e in range(E)],
+        down=[oracle.Nvfp4Weight(dn_p[e], dn_s[e], float(dn_t[e])) for e in range(E)],
+        shared_up=oracle.Nvfp4Weight(_np(b.shared_up.packed), _np(b.shared_up.block_scales),
+                                     b.shared_up.tensor_scale),
+        shared_down=oracle.Nvfp4Weight(_np(b.shared_down.packed), _np(b.shared_down.block_scales),
+                                       b.shared_down.tensor_scale),
+        logit_offset=None if b.gate_logit_offset is None else _np(b.gate_logit_offset))
+
+
+def max_abs_and_cosine(a: np.ndarray, b: np.ndarray):
+    a64, b64 = a.astype(np.float64).ravel(), b.astype(np.float64).ravel()
+    denom = np.linalg.norm(a64) * np.linalg.norm(b64)
+    cosine = float(a64 @ b64 / denom) if denom > 0 else 1.0
+    return float(np.max(np.abs(a64 - b64))), cosine
+
+
+def nibble_mismatches(a: np.ndarray, b: np.ndarray) -> int:
+    x = np.bitwise_xor(a, b)
+    return int(np.count_nonzero(x & 0x0f) + np.count_nonzero(x & 0xf0))
+
+
+@dataclass
+class ParityReport:
+    tokens: int = 0
+    index_set_mismatches: int = 0
+    index_order_mismatches: int = 0
+    min_margin: float = 0.0
+    norm_max_diff: float = 0.0
+    logits_max_diff: float = 0.0
+    weight_max_diff: float = 0.0
+    act_code_mismatches: int = 0
+    act_scale_mismatches: int = 0
+    hidden_code_mismatches: int = 0
+    hidden_scale_mismatches: int = 0
+    hidden_codes_total: int = 0
+    adopted_codes: int = 0
+    adopted_scales: int = 0
+    inadmissible_codes: int = 0
+    inadmissible_scales: int = 0
+    raw_max_abs: float = 0.0
+    raw_cosine: float = 0.0
+    max_abs: float = 0.0      # against the oracle run with admissible device codes adopted
+    cosine: float = 0.0
+    out_is_bf16: bool = False
+    bf16_excess: float = 0.0  # worst (|err| - half ulp of bf16 at the reference value)
+    notes: list = field(default_factory=list)
+
+    def ok(self) -> bool:
+        exact = (self.index_set_mismatches == 0 and self.act_code_mismatches == 0 and
+                 self.act_scale_mismatches == 0 and self.inadmissible_codes == 0 and
+                 self.inadmissible_scales == 0)
+        if self.out_is_bf16:
+            close = self.bf16_excess <= MAX_ABS_TOL
+        else:
+            close = self.max_abs <= MAX_ABS_TOL
+        return exact and close and self.cosine >= COSINE_TOL and self.raw_cosine >= COSINE_TOL
+
+    def summary(self) -> str:
+        return (f"T={self.tokens} idx_set_mismatch={self.index_set_mismatches} "
+                f"min_margin={self.min_margin:.3g} act_code_mismatch={self.act_code_mismatches} "
+                f"hidden_code_mismatch={self.hidden_code_mismatches}/{self.hidden_codes_total} "
+                f"hidden_scale_mismatch={self.hidden_scale_mismatches} "
+                f"adopted={self.adopted_codes}+{self.adopted_scales} "
+                f"inadmissible={self.inadmissible_codes}+{self.inadmissible_scales} "
+                f"raw_max_abs={self.raw_max_abs:.3g} raw_cos={self.raw_cosine:.6f} "
+                f"max_abs={self.max_abs:.3g} cos={self.cosine:.6f} "
+                f"norm_diff={self.norm_max_diff:.3g} logits_diff={self.logits_max_diff:.3g} "
+                f"weight_diff={self.weight_max_diff:.3g}"
+                + (f" bf16_excess={self.bf16_excess:.3g}" if self.out_is_bf16 else ""))
+
+
+def bf16_half_ulp(reference: np.ndarray) -> np.ndarray:
+    """Half the bf16 spacing at |reference| (8 significant bits)."""
+    mag = np.maximum(np.abs(reference.astype(np.float64)), 2.0 ** -126)
+    return 2.0 ** (np.floor(np.log2(mag)) - 8)
+
+
+def compare_layer_with_oracle(layer, layer_data, x: torch.Tensor, out: torch.Tensor,
+                              raw_run: bool = True) -> ParityReport:
+    """Runs the CPU oracle on the same inputs and compares every stage with the
+    intermediates of the layer's last run."""
+    oracle = entry.load_oracle()
+    cfg = layer.config()
+    T = x.shape[0]
+    ocfg, ow = oracle_config(cfg), oracle_weights(layer_data)
+    x_np = _np(x).astype(np.float32)
+    out_np = _np(out).astype(np.float32)
+    trace = layer.trace(T)
+
+    rep = ParityReport(tokens=T, out_is_bf16=out.dtype == torch.bfloat16)
+    cands = (_np(trace.routed_hidden_packed), _np(trace.routed_hidden_scales),
+             _np(trace.shared_hidden_packed), _np(trace.shared_hidden_scales))
+    forced = oracle.layer_forward(ocfg, ow, x_np, candidates=cands, override_eps=OVERRIDE_EPS)
+    raw = oracle.layer_forward(ocfg, ow, x_np) if raw_run else forced
+
+    gi, oi = _np(trace.selected_index), raw.top_index
+    rep.index_set_mismatches = int(np.count_nonzero(
+        np.any(np.sort(gi, axis=1) != np.sort(oi, axis=1), axis=1)))
+    rep.index_order_mismatches = int(np.count_nonzero(np.any(gi != oi, axis=1)))
+    rep.min_margin = float(np.min(oracle.selection_margins(raw.logits, ow.bias, cfg.top_k)))
+    rep.norm_max_diff = float(np.max(np.abs(_np(trace.normalized_input) - raw.normalized)))
+    rep.logits_max_diff = float(np.max(np.abs(_np(trace.router_logits) - raw.logits)))
+    rep.weight_max_diff = float(np.max(np.abs(_np(trace.selected_weight) - raw.top_weight)))
+    rep.act_code_mismatches = nibble_mismatches(_np(trace.act_packed), raw.act_packed)
+    rep.act_scale_mismatches = int(np.count_nonzero(_np(trace.act_scales) != raw.act_scales))
+    rep.hidden_code_mismatches = (nibble_mismatches(cands[0], raw.hid_packed) +
+                                  nibble_mismatches(cands[2], raw.shid_packed))
+    rep.hidden_scale_mismatches = int(np.count_nonzero(cands[1] != raw.hid_scales) +
+                                      np.count_nonzero(cands[3] != raw.shid_scales))
+    rep.hidden_codes_total = int(cands[0].size * 2 + cands[2].size * 2)
+    rep.adopted_codes, rep.adopted_scales = forced.adopted_codes, forced.adopted_scales
+    rep.inadmissible_codes = forced.inadmissible_codes
+    rep.inadmissible_scales = forced.inadmissible_scales
+    rep.raw_max_abs, rep.raw_cosine = max_abs_and_cosine(out_np, raw.out)
+    rep.max_abs, rep.cosine = max_abs_and_cosine(out_np, forced.out)
+    if rep.out_is_bf16:
+        err = np.abs(out_np.astype(np.float64) - forced.out.astype(np.float64))
+        rep.bf16_excess = float(np.max(err - bf16_half_ulp(forced.out)))
+    return rep
