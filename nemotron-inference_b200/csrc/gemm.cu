@@ -34,7 +34,8 @@ template <int BN_, int A_ROWS_, int SFB_GS_, int STAGES_>
 struct TileCfg {
   static constexpr int BN = BN_;
   static constexpr int A_ROWS = A_ROWS_;
-  static constexpr int SFB_GS = SFB_GS_;  // 32-row scale groups stored per K tile
+  static constexpr int SFB_GS = SFB_GS_;  // 32-row scale groups stored per K tile (multiple of 4:
+                                          // an MMA's scale address must be 4-column aligned)
   static constexpr int STAGES = STAGES_;
   static constexpr int A_BYTES = A_ROWS * 128;
   static constexpr int B_BYTES = BN * 128;
@@ -53,6 +54,7 @@ struct TileCfg {
   static constexpr int SMEM_BYTES =
       STAGES * (A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES) + BAR_BYTES + 1024;
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "BN");
+  static_assert(SFB_GS % 4 == 0 && SFB_GS * 32 >= BN, "weight scale groups");
   static_assert(TMEM_USED <= 512, "TMEM budget");
   static_assert(STAGES * B_BYTES >= 128 * 128, "A over-read must stay inside shared memory");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
@@ -60,10 +62,8 @@ struct TileCfg {
 
 using CfgPrefillUp = TileCfg<208, 128, 8, 4>;
 using CfgPrefillDown = TileCfg<224, 128, 8, 4>;
-using CfgDecode32 = TileCfg<32, 32, 1, 16>;
-using CfgDecode32Padded = TileCfg<32, 32, 4, 14>;
-using CfgDecode32Wide = TileCfg<32, 128, 1, 9>;
-using CfgDecode32WidePadded = TileCfg<32, 128, 4, 8>;
+using CfgDecode = TileCfg<128, 32, 4, 9>;
+using CfgDecodeWide = TileCfg<128, 128, 4, 6>;
 
 __device__ __forceinline__ void report_timeout(int32_t* error, volatile int* abort_flag) {
   *abort_flag = 1;
@@ -387,10 +387,8 @@ GemmVariantInfo gemm_variant_info(GemmVariant v) {
   switch (v) {
     case kVariantPrefillUp: return info_of<CfgPrefillUp>();
     case kVariantPrefillDown: return info_of<CfgPrefillDown>();
-    case kVariantDecode32: return info_of<CfgDecode32>();
-    case kVariantDecode32Padded: return info_of<CfgDecode32Padded>();
-    case kVariantDecode32Wide: return info_of<CfgDecode32Wide>();
-    case kVariantDecode32WidePadded: return info_of<CfgDecode32WidePadded>();
+    case kVariantDecode: return info_of<CfgDecode>();
+    case kVariantDecodeWide: return info_of<CfgDecodeWide>();
     default: return GemmVariantInfo{0, 0, 0, 0, 0};
   }
 }
@@ -401,10 +399,8 @@ cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const CUtensorMap&
   switch (v) {
     case kVariantPrefillUp: return launch_cfg<CfgPrefillUp>(mode, tmap_a, tmap_b, args, num_sms, stream);
     case kVariantPrefillDown: return launch_cfg<CfgPrefillDown>(mode, tmap_a, tmap_b, args, num_sms, stream);
-    case kVariantDecode32: return launch_cfg<CfgDecode32>(mode, tmap_a, tmap_b, args, num_sms, stream);
-    case kVariantDecode32Padded: return launch_cfg<CfgDecode32Padded>(mode, tmap_a, tmap_b, args, num_sms, stream);
-    case kVariantDecode32Wide: return launch_cfg<CfgDecode32Wide>(mode, tmap_a, tmap_b, args, num_sms, stream);
-    case kVariantDecode32WidePadded: return launch_cfg<CfgDecode32WidePadded>(mode, tmap_a, tmap_b, args, num_sms, stream);
+    case kVariantDecode: return launch_cfg<CfgDecode>(mode, tmap_a, tmap_b, args, num_sms, stream);
+    case kVariantDecodeWide: return launch_cfg<CfgDecodeWide>(mode, tmap_a, tmap_b, args, num_sms, stream);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -53,15 +53,15 @@ struct GemmArgs {
   int32_t* error = nullptr;           // device error slot (DeviceError)
 };
 
-// Tile shapes compiled into the library.
+// Tile shapes compiled into the library.  The block scales of every MMA must
+// start on a 4-column TMEM boundary, so a weight tile stores its scales in
+// whole groups of 128 rows; BN = 128 makes that exact for the HBM-bound sizes.
 enum GemmVariant : int {
   kVariantPrefillUp = 0,    // BN 208, 128-row A box
   kVariantPrefillDown = 1,  // BN 224, 128-row A box
-  kVariantDecode32 = 2,     // BN 32, 32-row A box, compact weight scales
-  kVariantDecode32Padded = 3,  // BN 32, 32-row A box, weight scales padded to 4 groups
-  kVariantDecode32Wide = 4,        // BN 32, 128-row A box, compact weight scales
-  kVariantDecode32WidePadded = 5,  // BN 32, 128-row A box, padded weight scales
-  kVariantCount = 6,
+  kVariantDecode = 2,       // BN 128, 32-row A box, deep pipeline
+  kVariantDecodeWide = 3,   // BN 128, 128-row A box
+  kVariantCount = 4,
 };
 
 struct GemmVariantInfo {

@@ -115,11 +115,6 @@ CUtensorMap make_packed_map(const void* base, size_t rows, size_t row_bytes, int
 int k_blocks_of(int k) { return (k + 255) / 256; }
 size_t tiled_sf_bytes(size_t row_slots, int k) { return row_slots * k_blocks_of(k) * 2048; }
 
-bool padded_weight_scales() {
-  const char* env = std::getenv("NMOE_SFB_PADDED");
-  return env != nullptr && env[0] == '1';
-}
-
 int device_sm_count() {
   int device = 0, sms = 0;
   NMOE_CUDA(cudaGetDevice(&device));
@@ -154,10 +149,10 @@ struct WeightStack {
   DeviceBuffer packed;        // [experts][n][k/2]
   DeviceBuffer tensor_scale;  // [experts]
   DeviceBuffer sf_prefill;    // scale layout for the prefill tile of this projection
-  DeviceBuffer sf_decode;     // scale layout for the BN=32 tiles
+  DeviceBuffer sf_decode;     // scale layout for the BN=128 tiles
   GemmVariant prefill_variant = kVariantPrefillUp;
-  GemmVariant decode_variant = kVariantDecode32;
-  GemmVariant decode_wide_variant = kVariantDecode32Wide;
+  GemmVariant decode_variant = kVariantDecode;
+  GemmVariant decode_wide_variant = kVariantDecodeWide;
   CUtensorMap map_prefill;
   CUtensorMap map_decode;
 
@@ -167,9 +162,6 @@ struct WeightStack {
     n = rows;
     k = cols;
     prefill_variant = is_up ? kVariantPrefillUp : kVariantPrefillDown;
-    const bool padded = padded_weight_scales();
-    decode_variant = padded ? kVariantDecode32Padded : kVariantDecode32;
-    decode_wide_variant = padded ? kVariantDecode32WidePadded : kVariantDecode32Wide;
     const size_t packed_each = static_cast<size_t>(rows) * cols / 2;
     const size_t sf_each = static_cast<size_t>(rows) * (cols / 16);
     packed.allocate(packed_each * count);

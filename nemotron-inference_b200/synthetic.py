@@ -87,18 +87,22 @@ def _normal(shape, std, generator, device):
     return torch.randn(shape, generator=generator, device=device, dtype=torch.float32) * std
 
 
-def zipf_logit_offset(experts: int, seed: int, strength: float = 1.0, s: float = 1.1
-                      ) -> torch.Tensor:
-    """Per-expert logit offset following a Zipf(s) popularity over a seeded random
-    ranking: offset = strength * (log p_rank - mean log p)."""
+def zipf_logit_offset(experts: int, seed: int, head: float = 0.2, tail: float = 2.5,
+                      s: float = 1.1) -> torch.Tensor:
+    """Per-expert gate-logit offset that skews the expert load (configs[2]).  A seeded
+    random ranking gives each expert a Zipf(s) popularity p ~ rank^-s; the offset is
+    log p centred on its mean, with the popular side scaled by `head` and the unpopular
+    side by `tail`.  With ~N(0,1) logits and top-6 of 128 the defaults give a hottest
+    expert near 5x the mean load and a handful of experts with no tokens at T=8192."""
     g = torch.Generator().manual_seed(seed)
     ranks = torch.randperm(experts, generator=g).to(torch.float32) + 1.0
     logp = -s * torch.log(ranks)
-    return (strength * (logp - logp.mean())).to(torch.float32)
+    centred = logp - logp.mean()
+    return torch.where(centred > 0, head * centred, tail * centred).to(torch.float32)
 
 
 def make_layer(config: ExpertLayerConfig, seed: int, device="cpu", norm_weight_uniform=False,
-               zipf_strength: Optional[float] = None, chunk: int = 16) -> SyntheticLayer:
+               skewed: bool = False, chunk: int = 16) -> SyntheticLayer:
     """Seeded layer weights.  Generation runs on `device` (the stream of random
     numbers depends on the device type); the quantised bytes stay there."""
     dev = torch.device(device)
@@ -125,8 +129,8 @@ def make_layer(config: ExpertLayerConfig, seed: int, device="cpu", norm_weight_u
                                Nvfp4Matrix(dn_p[e], dn_s[e], float(dn_t_host[e])))
               for e in range(E)]
     offset = None
-    if zipf_strength is not None:
-        offset = zipf_logit_offset(E, seed + 7, zipf_strength).to(dev)
+    if skewed:
+        offset = zipf_logit_offset(E, seed + 7).to(dev)
     bindings = ExpertLayerBindings(
         input_norm_weight=norm, gate_weight=gate, gate_score_correction_bias=bias,
         shared_up=Nvfp4Matrix(su[0], su[1], float(su[2])),

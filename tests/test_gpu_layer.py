@@ -1,0 +1,90 @@
+"""GPU parity of the whole MoE layer against the CPU oracle: configs[1] (decode sizes),
+configs[2] (skewed prefill) and reduced-size variants, through ExpertLayerSlice."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def baseline_layer(package, synthetic):
+    cfg = synthetic.baseline_config(max_tokens=8192)
+    data = synthetic.make_layer(cfg, seed=1000, device="cuda")
+    layer = package.ExpertLayerSlice.create(cfg, data.bindings)
+    assert layer is not None and layer.valid(), package.ExpertLayerSlice.create_error
+    yield layer, data
+    layer.close()
+
+
+def _run(layer, x, out_dtype=torch.float32):
+    out = torch.empty(x.shape, dtype=out_dtype, device="cuda")
+    assert layer.run(x, out), layer.last_error
+    return out
+
+
+def test_small_layer_every_stage(package, synthetic):
+    cfg = synthetic.baseline_config(max_tokens=256, experts=32, hidden=512, routed=256, shared=512)
+    data = synthetic.make_layer(cfg, seed=21, device="cuda", norm_weight_uniform=True)
+    layer = package.ExpertLayerSlice.create(cfg, data.bindings)
+    assert layer is not None
+    for tokens in (1, 3, 33, 200):
+        x = synthetic.make_tokens(tokens, cfg.hidden_size, seed=tokens, device="cuda")
+        out = _run(layer, x)
+        rep = helpers.compare_layer_with_oracle(layer, data, x, out)
+        print(rep.summary())
+        assert rep.ok(), rep.summary()
+        assert rep.norm_max_diff == 0.0 and rep.logits_max_diff == 0.0
+    layer.close()
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 32, 64])
+def test_decode_sizes_config1(baseline_layer, synthetic, tokens):
+    layer, data = baseline_layer
+    x = synthetic.make_tokens(tokens, 2688, seed=2000 + tokens, device="cuda")
+    out = _run(layer, x)
+    rep = helpers.compare_layer_with_oracle(layer, data, x, out)
+    print(rep.summary())
+    assert rep.ok(), rep.summary()
+    out_bf16 = _run(layer, x, torch.bfloat16)
+    rep16 = helpers.compare_layer_with_oracle(layer, data, x, out_bf16, raw_run=False)
+    print(rep16.summary())
+    assert rep16.ok(), rep16.summary()
+
+
+def test_results_do_not_depend_on_batching(baseline_layer, synthetic):
+    # expert_layer_oracle_test.cpp:1086-1161: a 3-token batch equals three single-token runs
+    layer, _ = baseline_layer
+    x = synthetic.make_tokens(3, 2688, seed=77, device="cuda")
+    batched = _run(layer, x)
+    for t in range(3):
+        single = _run(layer, x[t:t + 1].contiguous())
+        assert torch.equal(single[0], batched[t])
+
+
+def test_run_rejects_bad_shapes(baseline_layer):
+    layer, _ = baseline_layer
+    x = torch.zeros((2, 100), device="cuda")
+    assert not layer.run(x, torch.empty_like(x))
+    big = torch.zeros((8193, 2688), device="cuda", dtype=torch.bfloat16)
+    assert not layer.run(big, torch.empty((8193, 2688), device="cuda"))
+
+
+def test_prefill_skewed_config2(package, synthetic):
+    cfg = synthetic.baseline_config(max_tokens=8192)
+    data = synthetic.make_layer(cfg, seed=3000, device="cuda", skewed=True)
+    layer = package.ExpertLayerSlice.create(cfg, data.bindings)
+    assert layer is not None
+    x = synthetic.make_tokens(8192, 2688, seed=3001, device="cuda")
+    out = _run(layer, x)
+    trace_idx = layer.trace(8192).selected_index.cpu().numpy()
+    counts = np.bincount(trace_idx.ravel(), minlength=128)
+    print("expert load: max/mean = %.2f, empty experts = %d" % (counts.max() / counts.mean(),
+                                                                 int((counts == 0).sum())))
+    rep = helpers.compare_layer_with_oracle(layer, data, x, out)
+    print(rep.summary())
+    assert rep.ok(), rep.summary()
+    assert counts.max() / counts.mean() > 3.0
+    layer.close()

@@ -89,16 +89,16 @@ def test_expert_ffn_matches_reference(oracle, golden):
     assert np.array_equal(out, golden["ffn_out"])
 
 
-def _tiny_layer(synthetic, seed=5, experts=32, hidden=128, routed=64, shared=128, zipf=None):
+def _tiny_layer(synthetic, seed=5, experts=32, hidden=128, routed=64, shared=128, zipf=False):
     cfg = synthetic.baseline_config(64, experts=experts, hidden=hidden, routed=routed,
                                     shared=shared, top_k=4)
     return cfg, synthetic.make_layer(cfg, seed=seed, device="cpu", norm_weight_uniform=True,
-                                     zipf_strength=zipf)
+                                     skewed=zipf)
 
 
 def test_grouped_layer_is_bit_equal_to_literal_loop(oracle, synthetic):
     import helpers
-    cfg, data = _tiny_layer(synthetic, zipf=1.0)
+    cfg, data = _tiny_layer(synthetic, zipf=True)
     x = synthetic.make_tokens(9, cfg.hidden_size, seed=3).to(torch.float32).numpy()
     ocfg, ow = helpers.oracle_config(cfg), helpers.oracle_weights(data)
     fast = oracle.layer_forward(ocfg, ow, x, want_routed_out=True)
