@@ -1,0 +1,405 @@
+"""Benchmark of the NVFP4 MoE expert layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  A step is one pass of the whole layer (RMSNorm, router, permute,
+routed + shared expert GEMMs, combine) over one batch of seeded synthetic tokens.
+
+Main workload (every N): the expert-parallel configuration of the benchmark definition,
+T = 16384 tokens with uniform routing, hidden 2688, 128 experts (intermediate 1856, top-6),
+shared expert 3712, experts and tokens split evenly over the N GPUs (N = 1 keeps all 128
+experts on one GPU).  Total work is fixed as N grows (strong scaling).  At N = 1 the line
+also carries, under "also", the decode sizes (T = 1, 8, 32, 64) and the skewed prefill
+(T = 8192) with the roofline of their expert GEMMs.
+
+`value` is device-timed with inputs resident in HBM; `e2e` runs the same step through the
+public operator call from pinned HOST buffers, host<->device copies inside the timed
+region.  `cpu_baseline` times the CPU oracle on a bounded sample of the same workload.
+`--impl reference` times the reference's own host implementation (oracle/_ref, compiled
+from the reference sources) on the host cores instead.
+"""
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+import __graft_entry__ as entry  # noqa: E402
+
+H, I, S, E, K = 2688, 1856, 3712, 128, 6
+MAIN_TOKENS = 16384
+METRIC = "nvfp4_moe_layer_tokens_per_s"
+FLOP_PER_TOKEN_TENSOR = K * 2 * (2 * H * I) + 2 * (2 * H * S)  # routed + shared, 159,645,696
+UP_BYTES = I * H // 2 + I * H // 16 + 4      # one routed up_proj: packed + block scales + scale
+DOWN_BYTES = H * I // 2 + H * I // 16 + 4
+SHARED_BYTES = 2 * (S * H // 2 + S * H // 16 + 4)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while a region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        self.proc.wait()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, value in zip(names, f[5:9]):
+                if value == "Active":
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def flush_l2(buf):
+    buf.add_(1)
+
+
+def time_steps(run_step, steps, warmup, flush_buf, before=None):
+    """Per-step CUDA-event times (ms) on the current stream; L2 is flushed between steps,
+    outside the timed events."""
+    for _ in range(warmup):
+        run_step()
+    torch.cuda.synchronize()
+    if before is not None:
+        before()
+    times = []
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        flush_l2(flush_buf)
+        starts[i].record()
+        run_step()
+        ends[i].record()
+    torch.cuda.synchronize()
+    for s, e in zip(starts, ends):
+        times.append(s.elapsed_time(e))
+    return times
+
+
+def stage_profile(layer, x, out, steps, flush_buf):
+    """Mean device time of every stage over `steps` runs (events inside the library)."""
+    layer.enable_stage_timing(True)
+    acc = {}
+    for _ in range(steps):
+        flush_l2(flush_buf)
+        layer.run_async(x, out)
+        for name, ms in layer.stage_times_ms().items():
+            acc[name] = acc.get(name, 0.0) + ms / steps
+    layer.enable_stage_timing(False)
+    return acc
+
+
+def cpu_baseline_port(layer_data, cfg, sample_tokens, seed):
+    """The CPU oracle (port of the reference host path, OpenMP over all cores) timed on
+    `sample_tokens` tokens of the workload."""
+    import helpers
+    oracle = entry.load_oracle()
+    synthetic = importlib.import_module("nemotron_inference_b200.synthetic")
+    x = synthetic.make_tokens(sample_tokens, H, seed=seed).to(torch.float32).numpy()
+    ocfg, ow = helpers.oracle_config(cfg), helpers.oracle_weights(layer_data)
+    t0 = time.perf_counter()
+    oracle.layer_forward(ocfg, ow, x)
+    dt = time.perf_counter() - t0
+    return {"value": sample_tokens / dt, "unit": "tokens/s", "cores": oracle.num_threads(),
+            "kind": "port", "seconds": dt,
+            "sample": f"{sample_tokens} tokens of the same layer (all 128 experts, top-6, shared "
+                      f"expert), restructured bit-identical host path, gcc -O2 -ffp-contract=off"}
+
+
+def run_reference_arm(args):
+    """Times the reference's own host implementation (literal per-token loop of
+    ExpertLayerSlice::Run built from the reference's functions) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    package = entry.load_package()
+    oracle = entry.load_oracle()
+    synthetic = importlib.import_module("nemotron_inference_b200.synthetic")
+    import helpers
+    cores = os.cpu_count() or 1
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    cfg = synthetic.baseline_config(max_tokens=64)
+    data = synthetic.make_layer(cfg, seed=4000, device=device)
+    ow = helpers.oracle_weights(data)
+    workload = {"workload": "configs[3]: T=16384 uniform routing, hidden 2688, 128 experts x 1856 "
+                            "top-6, shared 3712 (bounded sample per step)",
+                "l2": "host only", "parallelism": f"{cores} host processes"}
+    if not oracle.have_reference():
+        base = cpu_baseline_port(data, cfg, 256, seed=4001)
+        line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s",
+                "n_gpus": args.gpus, "steps": 1, "warmup": 0, "ms_per_step": base["seconds"] * 1e3,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": workload, "cpu_baseline": base,
+                "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+    tokens_per_proc = 1
+    sample = cores * tokens_per_proc
+    x = synthetic.make_tokens(sample, H, seed=4001).to(torch.float32).numpy()
+    normalized = oracle.rmsnorm(x, ow.norm_weight, cfg.rms_epsilon)
+    with tempfile.TemporaryDirectory() as tmp:
+        def dump(name, arr):
+            np.ascontiguousarray(arr).tofile(os.path.join(tmp, name))
+        dump("gate.f32", ow.gate.astype(np.float32))
+        dump("bias.f32", ow.bias.astype(np.float32))
+        dump("up_p.u8", np.stack([w.packed for w in ow.up]))
+        dump("up_s.u8", np.stack([w.scales for w in ow.up]))
+        dump("up_ts.f32", np.array([w.tensor_scale for w in ow.up], np.float32))
+        dump("down_p.u8", np.stack([w.packed for w in ow.down]))
+        dump("down_s.u8", np.stack([w.scales for w in ow.down]))
+        dump("down_ts.f32", np.array([w.tensor_scale for w in ow.down], np.float32))
+        dump("sup_p.u8", ow.shared_up.packed)
+        dump("sup_s.u8", ow.shared_up.scales)
+        dump("sup_ts.f32", np.array([ow.shared_up.tensor_scale], np.float32))
+        dump("sdown_p.u8", ow.shared_down.packed)
+        dump("sdown_s.u8", ow.shared_down.scales)
+        dump("sdown_ts.f32", np.array([ow.shared_down.tensor_scale], np.float32))
+        for p in range(cores):
+            rows = slice(p * tokens_per_proc, (p + 1) * tokens_per_proc)
+            dump(f"n{p}.f32", normalized[rows])
+            dump(f"x{p}.f32", x[rows])
+
+        def one_step():
+            procs = [subprocess.Popen(
+                [oracle.REF_BIN, "layer_rows", tmp, str(tokens_per_proc), str(H), str(I), str(S),
+                 str(E), str(K), "2.5", os.path.join(tmp, f"n{p}.f32"),
+                 os.path.join(tmp, f"x{p}.f32"), os.path.join(tmp, f"o{p}.f32")],
+                stdout=subprocess.PIPE, text=True) for p in range(cores)]
+            secs = [float(p.communicate()[0].strip() or "nan") for p in procs]
+            return max(secs)  # slowest process: the step ends when every token is done
+
+        for _ in range(min(args.warmup, 1)):
+            one_step()
+        steps = max(1, min(args.steps, 3))
+        secs = [one_step() for _ in range(steps)]
+        # parity of the literal reference loop against the oracle port on this sample
+        ref_out = np.concatenate([np.fromfile(os.path.join(tmp, f"o{p}.f32"), np.float32)
+                                  for p in range(cores)]).reshape(sample, H)
+    port_out = oracle.layer_forward(helpers.oracle_config(cfg), ow, x).out
+    mean_s = float(np.mean(secs))
+    value = sample / mean_s
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+            "ms_per_step": mean_s * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload,
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores,
+                             "kind": "reference",
+                             "sample": f"{sample} tokens per step, one per host process, literal "
+                                       "per-token loop of the reference's own functions "
+                                       "(weights resident; token loop timed)"},
+            "reference_equals_port": bool(np.array_equal(ref_out, port_out)),
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def run_side_workloads(package, synthetic, layer, data, peaks, steps, warmup, flush_buf):
+    """configs[1] decode sizes on the main layer's weights and configs[2] skewed prefill."""
+    results = []
+    for tokens in (1, 8, 32, 64):
+        x = synthetic.make_tokens(tokens, H, seed=5000 + tokens, device="cuda")
+        out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+        times = time_steps(lambda: layer.run_async(x, out), steps, warmup, flush_buf)
+        stages = stage_profile(layer, x, out, max(3, steps // 2), flush_buf)
+        idx = layer.trace(tokens).selected_index
+        distinct = int(torch.unique(idx).numel())
+        ms = float(np.mean(times))
+        layer_bytes = distinct * (UP_BYTES + DOWN_BYTES) + SHARED_BYTES + E * H * 4 + 4 * tokens * H
+        up_gbs = distinct * UP_BYTES / (stages["routed_up_gemm"] * 1e-3) / 1e9
+        down_gbs = distinct * DOWN_BYTES / (stages["routed_down_gemm"] * 1e-3) / 1e9
+        gemm_ms = sum(stages[k] for k in ("routed_up_gemm", "routed_down_gemm", "shared_up_gemm",
+                                          "shared_down_gemm"))
+        gemm_gbs = (distinct * (UP_BYTES + DOWN_BYTES) + SHARED_BYTES) / (gemm_ms * 1e-3) / 1e9
+        results.append({
+            "workload": f"configs[1] decode T={tokens}", "tokens_per_s": tokens / (ms * 1e-3),
+            "ms_per_step": ms, "distinct_experts": distinct,
+            "layer_hbm_gbs": layer_bytes / (ms * 1e-3) / 1e9,
+            "layer_hbm_frac": layer_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "expert_gemms": {"bound": "hbm", "achieved": gemm_gbs, "peak": peaks["hbm_gbs"],
+                             "unit": "GB/s", "frac": gemm_gbs / peaks["hbm_gbs"],
+                             "routed_up_gbs": up_gbs, "routed_down_gbs": down_gbs},
+            "stage_ms": {k: round(v, 5) for k, v in stages.items()}})
+    # configs[2]: skewed routing needs its own gate offset, hence its own layer
+    cfg = synthetic.baseline_config(max_tokens=8192)
+    skew = synthetic.make_layer(cfg, seed=3000, device="cuda", skewed=True)
+    skew_layer = package.ExpertLayerSlice.create(cfg, skew.bindings)
+    x = synthetic.make_tokens(8192, H, seed=3001, device="cuda")
+    out = torch.empty((8192, H), dtype=torch.bfloat16, device="cuda")
+    times = time_steps(lambda: skew_layer.run_async(x, out), steps, warmup, flush_buf)
+    stages = stage_profile(skew_layer, x, out, max(3, steps // 2), flush_buf)
+    counts = torch.bincount(skew_layer.trace(8192).selected_index.flatten().long(), minlength=E)
+    ms = float(np.mean(times))
+    tf = 8192 * FLOP_PER_TOKEN_TENSOR / (ms * 1e-3) / 1e12
+    up_tf = 8192 * K * 4 * H * I / (stages["routed_up_gemm"] * 1e-3) / 1e12
+    fp4_peak = 4 * peaks["bf16_tflops_sustained"]
+    results.append({
+        "workload": "configs[2] skewed prefill T=8192", "tokens_per_s": 8192 / (ms * 1e-3),
+        "ms_per_step": ms, "layer_tflops": tf,
+        "load_max_over_mean": float(counts.max() / counts.float().mean()),
+        "empty_experts": int((counts == 0).sum()),
+        "routed_up_gemm": {"bound": "tensor", "achieved": up_tf, "peak": fp4_peak,
+                           "unit": "TFLOP/s", "frac": up_tf / fp4_peak},
+        "stage_ms": {k: round(v, 5) for k, v in stages.items()}})
+    skew_layer.close()
+    return results
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=MAIN_TOKENS)
+    ap.add_argument("--no-side", action="store_true", help="skip the decode / skewed side workloads")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); "
+                         "use --impl reference for the host baseline")
+    torch.cuda.set_device(local_rank)
+    package = entry.load_package()
+    synthetic = importlib.import_module("nemotron_inference_b200.synthetic")
+    peaks = load_peaks()
+    flush_buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device="cuda")
+
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        ep = importlib.import_module("nemotron_inference_b200.expert_parallel")
+        line = ep.bench_main(args, package, synthetic, peaks, flush_buf, dist)
+        if rank == 0:
+            print(json.dumps(line))
+        dist.destroy_process_group()
+        return
+
+    tokens = args.tokens
+    cfg = synthetic.baseline_config(max_tokens=tokens)
+    data = synthetic.make_layer(cfg, seed=4000, device="cuda")
+    layer = package.ExpertLayerSlice.create(cfg, data.bindings)
+    if layer is None:
+        raise SystemExit("layer creation failed: " + package.ExpertLayerSlice.create_error)
+    x_host = synthetic.make_tokens(tokens, H, seed=4001).pin_memory()
+    x = x_host.cuda()
+    out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+    out_host = torch.empty((tokens, H), dtype=torch.bfloat16).pin_memory()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    torch.cuda.synchronize()
+    times = time_steps(lambda: layer.run_async(x, out), args.steps, args.warmup, flush_buf)
+    clocks = sampler.stop()
+    status = layer.sync_status()
+    if status != 0:
+        raise SystemExit(f"device error during the timed region: {package.STATUS_NAMES.get(status)}")
+    ms = float(np.mean(times))
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        layer.run_async(x, out)
+        out_host.copy_(out, non_blocking=True)
+
+    e2e_times = time_steps(e2e_step, args.steps, args.warmup, flush_buf)
+    e2e_ms = float(np.mean(e2e_times))
+    stages = stage_profile(layer, x, out, max(3, args.steps // 2), flush_buf)
+
+    up_flops = tokens * K * 4 * H * I
+    up_tf = up_flops / (stages["routed_up_gemm"] * 1e-3) / 1e12
+    fp4_peak = 4 * peaks["bf16_tflops_sustained"]
+    line = {
+        "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": f"configs[3] shapes on N GPUs: T={tokens} tokens, uniform routing, "
+                               "hidden 2688, 128 experts x 1856 top-6, shared 3712, bf16 in/out",
+                   "global_tokens": tokens, "parallelism": "ep1",
+                   "l2": "256 MB buffer written between timed steps; working set > L2"},
+        "layer_tflops": tokens * FLOP_PER_TOKEN_TENSOR / (ms * 1e-3) / 1e12,
+        "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
+        "gpu_launches": 10 * args.steps,
+        "clocks": clocks,
+        "roofline": {"kernel": "grouped_gemm_kernel<BN=208, up: relu^2 + NVFP4 quantise epilogue>",
+                     "bound": "tensor", "achieved": up_tf, "peak": fp4_peak, "unit": "TFLOP/s",
+                     "frac": up_tf / fp4_peak, "traffic": None,
+                     "peak_note": f"4 x {peaks['source']} sustained dense bf16 "
+                                  f"({peaks['bf16_tflops_sustained']} TF/s); no FP4 figure is "
+                                  "measured on this pool; nominal dense FP4 is 9000 TF/s",
+                     "frac_of_nominal_9000": up_tf / 9000.0,
+                     "flops_per_launch": up_flops},
+        "stage_ms": {k: round(v, 5) for k, v in stages.items()},
+    }
+    if not args.no_side:
+        line["also"] = run_side_workloads(package, synthetic, layer, data, peaks,
+                                          max(5, args.steps), args.warmup, flush_buf)
+    if not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline_port(data, cfg, 1024, seed=4001)
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

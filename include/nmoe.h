@@ -137,6 +137,19 @@ NMOE_API nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void*
 NMOE_API nmoe_status nmoe_layer_sync_status(nmoe_layer* layer, void* stream);
 NMOE_API const char* nmoe_layer_last_error(const nmoe_layer* layer);
 
+/* Per-stage device timing (the reference has no profiler hooks; its benchmarks
+ * time with steady_clock around synchronous calls,
+ * benchmarks/gb10_nvfp4_gemm/gb10_nvfp4_gemm_bench.cpp:655-676).  When enabled,
+ * nmoe_layer_run records a CUDA event before every stage; after the run,
+ * nmoe_layer_stage_times waits for the last one and returns the elapsed
+ * milliseconds of the NMOE_STAGE_COUNT stages, in this order: norm+quantise,
+ * router logits, top-k, route plan, permute, routed up GEMM, routed down GEMM,
+ * shared up GEMM, shared down GEMM, combine. */
+#define NMOE_STAGE_COUNT 10
+NMOE_API nmoe_status nmoe_layer_enable_stage_timing(nmoe_layer* layer, int32_t enable);
+NMOE_API nmoe_status nmoe_layer_stage_times(nmoe_layer* layer, float* milliseconds,
+                                            int32_t count);
+
 /* The intermediates ExpertLayerRunTrace exposes (expert_layer.h:63-76), for any
  * token count, as device buffers of the LAST run.  A field stays NULL when the
  * layer does not hold it.  Valid until the next run or destroy. */

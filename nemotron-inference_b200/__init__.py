@@ -33,7 +33,7 @@ STATUS_NAMES = {
 EXPORTED_SYMBOLS = (
     "nmoe_status_string", "nmoe_layer_create", "nmoe_layer_destroy", "nmoe_layer_run",
     "nmoe_layer_sync_status", "nmoe_layer_last_error", "nmoe_layer_trace_view",
-    "nmoe_layer_copy_trace_field",
+    "nmoe_layer_copy_trace_field", "nmoe_layer_enable_stage_timing", "nmoe_layer_stage_times",
     "nmoe_layer_export_hidden", "nmoe_ffn_create", "nmoe_ffn_destroy", "nmoe_ffn_run",
     "nmoe_ffn_sync_status", "nmoe_ffn_export_hidden", "nmoe_quantize_nvfp4",
     "nmoe_dequant_nvfp4", "nmoe_swizzled_scale_bytes", "nmoe_swizzle_scales", "nmoe_rmsnorm",
@@ -113,6 +113,8 @@ def load_library() -> ctypes.CDLL:
     lib.nmoe_layer_trace_view.argtypes = [vp, ctypes.POINTER(_TraceView)]
     lib.nmoe_layer_copy_trace_field.argtypes = [vp, vp, i32, vp, ctypes.c_size_t]
     lib.nmoe_layer_export_hidden.argtypes = [vp, vp, vp, vp, vp, vp]
+    lib.nmoe_layer_enable_stage_timing.argtypes = [vp, i32]
+    lib.nmoe_layer_stage_times.argtypes = [vp, ctypes.POINTER(ctypes.c_float), i32]
     lib.nmoe_ffn_create.argtypes = [ctypes.POINTER(_Nvfp4Matrix), ctypes.POINTER(_Nvfp4Matrix),
                                     i32, ctypes.POINTER(vp)]
     lib.nmoe_ffn_destroy.argtypes = [vp]
@@ -335,6 +337,20 @@ class ExpertLayerSlice:
             self.last_error = STATUS_NAMES.get(status, str(status))
             return False
         return True
+
+    STAGES = ("norm_quant", "router_logits", "router_topk", "route_plan", "permute",
+              "routed_up_gemm", "routed_down_gemm", "shared_up_gemm", "shared_down_gemm", "combine")
+
+    def enable_stage_timing(self, enable: bool = True) -> None:
+        _check(load_library().nmoe_layer_enable_stage_timing(self._handle, 1 if enable else 0),
+               "nmoe_layer_enable_stage_timing")
+
+    def stage_times_ms(self) -> dict:
+        """Device time of every stage of the last run (waits for it)."""
+        buf = (ctypes.c_float * len(self.STAGES))()
+        _check(load_library().nmoe_layer_stage_times(self._handle, buf, len(self.STAGES)),
+               "nmoe_layer_stage_times")
+        return dict(zip(self.STAGES, [float(v) for v in buf]))
 
     def _last_error(self) -> str:
         raw = load_library().nmoe_layer_last_error(self._handle)

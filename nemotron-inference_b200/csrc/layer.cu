@@ -230,7 +230,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
                       const Schedule& schedule, uint8_t* hidden_packed, uint8_t* hidden_sf,
                       const ActivationOperand& hidden, float* out_rows, const int32_t* dest_row,
                       int dest_mul, int dest_add, const float* row_weight, int32_t* error,
-                      int num_sms, cudaStream_t stream) {
+                      int num_sms, cudaStream_t stream, cudaEvent_t between = nullptr) {
   GemmArgs g;
   const GemmVariant up_variant = up.variant(tile_class);
   g.K = up.k;
@@ -250,6 +250,8 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   g.error = error;
   NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, a.map(tile_class), up.map(tile_class), g,
                                 num_sms, stream));
+
+  if (between != nullptr) cudaEventRecord(between, stream);
 
   GemmArgs d;
   const GemmVariant down_variant = down.variant(tile_class);
@@ -482,6 +484,8 @@ nmoe_status nmoe_ffn_export_hidden(nmoe_ffn* ffn, void* stream_ptr, uint8_t* pac
 // ===========================================================================
 // nmoe_layer
 // ===========================================================================
+enum { kStageCount = NMOE_STAGE_COUNT };
+
 struct nmoe_layer {
   nmoe_config cfg{};
   int num_sms = 0;
@@ -508,6 +512,17 @@ struct nmoe_layer {
   ErrorSlot error;
   int last_tokens = 0;
   std::string last_error;
+
+  // optional per-stage CUDA events (nmoe_layer_enable_stage_timing)
+  bool stage_timing = false;
+  cudaEvent_t stage_events[kStageCount + 1] = {};
+  ~nmoe_layer() {
+    for (cudaEvent_t e : stage_events)
+      if (e != nullptr) cudaEventDestroy(e);
+  }
+  void mark(int index, cudaStream_t stream) {
+    if (stage_timing) cudaEventRecord(stage_events[index], stream);
+  }
 };
 
 namespace {
@@ -606,22 +621,26 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
   const int H = c.hidden_size, E = c.n_routed_experts, K = c.top_k;
   int32_t* error = L->error.device.as<int32_t>();
 
+  L->mark(0, stream);
   // RMSNorm (:795-796) fused with the activation quantiser every expert's
   // up_proj applies to the same normalised row (:913 -> nvfp4_packing.cpp:90)
   NMOE_CUDA(launch_norm_quant(input, in_dtype == NMOE_BF16, tokens, H, L->norm_weight.as<float>(),
                               c.rms_epsilon, L->normalized.as<float>(), L->y_packed.as<uint8_t>(),
                               L->y_sf_row_major.as<uint8_t>(), L->y_sf_tiled.as<uint8_t>(),
                               k_blocks_of(H), L->y_ts.as<float>(), stream));
+  L->mark(1, stream);
   // gate projection (:797-799) and top-k (:881)
   NMOE_CUDA(launch_router_logits(L->normalized.as<float>(), L->gate.as<float>(),
                                  L->has_logit_offset ? L->logit_offset.as<float>() : nullptr,
                                  tokens, E, H, L->logits.as<float>(), stream));
+  L->mark(2, stream);
   NMOE_CUDA(cudaMemsetAsync(L->counts.as<int32_t>(), 0, E * sizeof(int32_t), stream));
   NMOE_CUDA(launch_router_topk(L->logits.as<float>(), L->bias.as<float>(), tokens, E, K,
                                c.n_group, c.topk_group, c.norm_topk_prob != 0,
                                c.routed_scaling_factor, L->top_index.as<int32_t>(),
                                L->top_weight.as<float>(), L->counts.as<int32_t>(), stream));
 
+  L->mark(3, stream);
   const bool decode = static_cast<long long>(tokens) * K <= L->decode_pairs_limit / 2;
   const TileClass routed_class = decode ? kClassDecode : kClassPrefill;
   const int tile_rows = decode ? 32 : 128;
@@ -632,6 +651,7 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
   plan.row_tiles = L->row_tiles.as<RowTile>();
   plan.num_row_tiles = L->num_row_tiles.as<int32_t>();
   NMOE_CUDA(launch_route_plan(plan, E, tile_rows, L->max_row_tiles, error, stream));
+  L->mark(4, stream);
   NMOE_CUDA(launch_permute(plan, L->top_index.as<int32_t>(), L->top_weight.as<float>(), tokens, K,
                            tile_rows, L->max_row_tiles, L->y_packed.as<uint8_t>(),
                            L->y_sf_row_major.as<uint8_t>(), L->y_ts.as<float>(), H,
@@ -639,6 +659,7 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
                            L->a_ts.as<float>(), L->a_weight.as<float>(), L->a_dest.as<int32_t>(),
                            L->pair_row.as<int32_t>(), K + 1, stream));
 
+  L->mark(5, stream);
   // routed experts (:896-954)
   Schedule routed;
   routed.row_tiles = L->row_tiles.as<RowTile>();
@@ -646,20 +667,24 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
   run_expert_gemms(L->up, L->down, routed_class, L->a_op, L->a_ts.as<float>(), routed,
                    L->h_packed.as<uint8_t>(), L->h_sf.as<uint8_t>(), L->h_op,
                    L->parts.as<float>(), L->a_dest.as<int32_t>(), 1, 0, L->a_weight.as<float>(),
-                   error, L->num_sms, stream);
+                   error, L->num_sms, stream, L->stage_timing ? L->stage_events[6] : nullptr);
 
   // shared expert (:814-818, :956-964, :981-1005) on the same quantised rows
+  L->mark(7, stream);
   const TileClass shared_class =
       tokens <= 32 ? kClassDecode : tokens <= 256 ? kClassDecodeWide : kClassPrefill;
   Schedule shared;
   shared.dense_rows = tokens;
   run_expert_gemms(L->shared_up, L->shared_down, shared_class, L->y_op, L->y_ts.as<float>(),
                    shared, L->sh_packed.as<uint8_t>(), L->sh_sf.as<uint8_t>(), L->sh_op,
-                   L->parts.as<float>(), nullptr, K + 1, K, nullptr, error, L->num_sms, stream);
+                   L->parts.as<float>(), nullptr, K + 1, K, nullptr, error, L->num_sms, stream,
+                   L->stage_timing ? L->stage_events[8] : nullptr);
 
   // routed sum in selection order, mixer and residual (:951-953, :1064-1069)
+  L->mark(9, stream);
   NMOE_CUDA(launch_combine(input, in_dtype == NMOE_BF16, L->parts.as<float>(), tokens, H, K,
                            output, out_dtype == NMOE_BF16, stream));
+  L->mark(10, stream);
   L->last_tokens = tokens;
 }
 
@@ -721,6 +746,31 @@ nmoe_status nmoe_layer_sync_status(nmoe_layer* layer, void* stream) {
     layer->last_error = failure.message;
     return failure.status;
   }
+}
+
+nmoe_status nmoe_layer_enable_stage_timing(nmoe_layer* layer, int32_t enable) {
+  if (layer == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  if (enable != 0) {
+    for (cudaEvent_t& e : layer->stage_events) {
+      if (e == nullptr && cudaEventCreate(&e) != cudaSuccess) return NMOE_ERR_CUDA;
+    }
+  }
+  layer->stage_timing = enable != 0;
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_layer_stage_times(nmoe_layer* layer, float* milliseconds, int32_t count) {
+  if (layer == nullptr || milliseconds == nullptr || count < kStageCount || !layer->stage_timing) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  if (cudaEventSynchronize(layer->stage_events[kStageCount]) != cudaSuccess) return NMOE_ERR_CUDA;
+  for (int i = 0; i < kStageCount; ++i) {
+    if (cudaEventElapsedTime(&milliseconds[i], layer->stage_events[i],
+                             layer->stage_events[i + 1]) != cudaSuccess) {
+      return NMOE_ERR_CUDA;
+    }
+  }
+  return NMOE_OK;
 }
 
 const char* nmoe_layer_last_error(const nmoe_layer* layer) {

@@ -14,6 +14,7 @@
 // little-endian binary file.
 #include "runtime/src/backend/expert_layer.cpp"
 
+#include <chrono>
 #include <cstdio>
 #include <fstream>
 #include <sstream>
@@ -232,6 +233,82 @@ int main(int argc, char** argv) {
     std::vector<float> out(rows * N);
     ref_dense_matmul_double(act.data(), rows, weights.data(), N, K, out.data());
     WriteFile(argv[7], out);
+    return 0;
+  }
+  if (cmd == "layer_rows" && argc == 13) {
+    // layer_rows dir rows H I S E k scaling normalized.f32 x.f32 out.f32
+    // The per-token loop of ExpertLayerSlice::Run (expert_layer.cpp:871-1005,
+    // :1064-1069) built from the reference's own functions: gate projection by
+    // the double-accumulate host matmul, SelectTopExperts, RunNvfp4LinearHost +
+    // ApplyRelu2 per selected expert, the NVFP4 shared expert, weighted
+    // accumulate, mixer and residual.  RMSNorm is a device kernel in the
+    // reference, so normalised rows come in from the caller.  Weights are raw
+    // files in `dir`: gate.f32, bias.f32, up_p.u8, up_s.u8, up_ts.f32 (stacked
+    // over experts), down_*, sup_*, sdown_*.  Prints the seconds spent in the
+    // token loop (weights already in memory).
+    const std::string dir = argv[2];
+    const std::size_t rows = ToSize(argv[3]), H = ToSize(argv[4]), I = ToSize(argv[5]),
+                      S = ToSize(argv[6]), E = ToSize(argv[7]);
+    ExpertLayerConfig config;
+    config.n_routed_experts = E;
+    config.top_k = ToSize(argv[8]);
+    config.routed_scaling_factor = std::strtof(argv[9], nullptr);
+    const auto normalized = ReadFile<float>(argv[10]);
+    const auto x = ReadFile<float>(argv[11]);
+    const auto gate = ReadFile<float>(dir + "/gate.f32");
+    const auto bias = ReadFile<float>(dir + "/bias.f32");
+    const auto up_p = ReadFile<std::uint8_t>(dir + "/up_p.u8");
+    const auto up_s = ReadFile<std::uint8_t>(dir + "/up_s.u8");
+    const auto up_ts = ReadFile<float>(dir + "/up_ts.f32");
+    const auto down_p = ReadFile<std::uint8_t>(dir + "/down_p.u8");
+    const auto down_s = ReadFile<std::uint8_t>(dir + "/down_s.u8");
+    const auto down_ts = ReadFile<float>(dir + "/down_ts.f32");
+    const auto sup_p = ReadFile<std::uint8_t>(dir + "/sup_p.u8");
+    const auto sup_s = ReadFile<std::uint8_t>(dir + "/sup_s.u8");
+    const auto sup_ts = ReadFile<float>(dir + "/sup_ts.f32");
+    const auto sdown_p = ReadFile<std::uint8_t>(dir + "/sdown_p.u8");
+    const auto sdown_s = ReadFile<std::uint8_t>(dir + "/sdown_s.u8");
+    const auto sdown_ts = ReadFile<float>(dir + "/sdown_ts.f32");
+    auto slice = [](const std::vector<std::uint8_t>& v, std::size_t e, std::size_t each) {
+      return std::vector<std::uint8_t>(v.begin() + e * each, v.begin() + (e + 1) * each);
+    };
+    std::vector<std::vector<std::uint8_t>> upp(E), ups(E), dnp(E), dns(E);
+    std::vector<GemmDescriptor> up(E), down(E);
+    for (std::size_t e = 0; e < E; ++e) {
+      upp[e] = slice(up_p, e, I * H / 2);
+      ups[e] = slice(up_s, e, I * H / 16);
+      dnp[e] = slice(down_p, e, I * H / 2);
+      dns[e] = slice(down_s, e, I * H / 16);
+      up[e] = MakeNvfp4Descriptor(I, H, upp[e], ups[e], &up_ts[e]);
+      down[e] = MakeNvfp4Descriptor(H, I, dnp[e], dns[e], &down_ts[e]);
+    }
+    const GemmDescriptor shared_up = MakeNvfp4Descriptor(S, H, sup_p, sup_s, &sup_ts[0]);
+    const GemmDescriptor shared_down = MakeNvfp4Descriptor(H, S, sdown_p, sdown_s, &sdown_ts[0]);
+    std::vector<float> out(rows * H);
+    const auto start = std::chrono::steady_clock::now();
+    std::vector<float> logits(rows * E);
+    ref_dense_matmul_double(normalized.data(), rows, gate.data(), E, H, logits.data());
+    for (std::size_t t = 0; t < rows; ++t) {
+      const std::vector<float> logit_row(logits.begin() + t * E, logits.begin() + (t + 1) * E);
+      const std::vector<float> row(normalized.begin() + t * H, normalized.begin() + (t + 1) * H);
+      const auto selections = SelectTopExperts(config, logit_row, bias);
+      std::vector<float> routed(H, 0.0f);
+      for (const auto& selection : selections) {
+        const auto u = RunNvfp4LinearHost(row, 1, up[selection.expert_index]);
+        const auto d = RunNvfp4LinearHost(ApplyRelu2(*u), 1, down[selection.expert_index]);
+        for (std::size_t i = 0; i < H; ++i) routed[i] += (*d)[i] * selection.weight;
+      }
+      const auto su = RunNvfp4LinearHost(row, 1, shared_up);
+      const auto sd = RunNvfp4LinearHost(ApplyRelu2(*su), 1, shared_down);
+      for (std::size_t i = 0; i < H; ++i) {
+        const float mixer = routed[i] + (*sd)[i];
+        out[t * H + i] = x[t * H + i] + mixer;
+      }
+    }
+    const double seconds =
+        std::chrono::duration<double>(std::chrono::steady_clock::now() - start).count();
+    WriteFile(argv[12], out);
+    std::printf("%.6f\n", seconds);
     return 0;
   }
   std::fprintf(stderr, "ref_driver: unknown command or wrong argument count: %s\n", cmd.c_str());
