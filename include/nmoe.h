@@ -237,6 +237,40 @@ NMOE_API nmoe_status nmoe_router_topk(void* stream, const float* logits, const f
                                       int32_t norm_topk_prob, float routed_scaling,
                                       int32_t* top_index, float* top_weight);
 
+/* --- routing without any allocation ------------------------------------------
+ * Has no counterpart in the reference (whose Run allocates six scratch tensors
+ * per call, expert_layer.cpp:782-787).  For callers that are not allowed to
+ * allocate device memory when they route tokens: a host whose memory all comes
+ * from an arena reserved at start-up, a serving loop that cannot risk an
+ * allocation stalling or failing, a plugin under foreign memory accounting.
+ *
+ * Computes, for `rows` rows of `input` [rows][hidden] (FP32 or bf16, device):
+ * RMSNorm with `norm_weight`, gate logits against `gate` [experts][hidden] FP32,
+ * then SelectTopExperts -- the same three kernels as nmoe_rmsnorm,
+ * nmoe_router_logits and nmoe_router_topk, with identical results -- and writes
+ * top_index / top_weight [rows][top_k].  The normalised rows and the logits
+ * live in a fixed 4.5 MiB array inside the library image instead of in
+ * caller buffers; the call performs no cudaMalloc, cudaFree or any other
+ * allocating routine.
+ *
+ * Limits: rows*hidden <= NMOE_NOALLOC_MAX_ROWS_X_HIDDEN and rows*experts <=
+ * NMOE_NOALLOC_MAX_ROWS_X_EXPERTS, otherwise NMOE_ERR_CAPACITY (e.g. 390 rows at
+ * hidden 2688, 256 rows at hidden 4096 or at 512 experts).
+ * Every GPU that loads the library holds the array until the process exits.
+ * All calls on one GPU share it and it keeps the previous call's contents
+ * (nothing in it needs clearing: each call overwrites what it reads), so two
+ * calls whose kernels can overlap on the GPU -- different streams, no ordering
+ * between them -- race; serialise them.
+ * The first call on each device looks up the array's device address (the
+ * device must be current); make that first call outside any stream capture. */
+#define NMOE_NOALLOC_MAX_ROWS_X_HIDDEN 1048576
+#define NMOE_NOALLOC_MAX_ROWS_X_EXPERTS 131072
+NMOE_API nmoe_status nmoe_route_tokens_noalloc(
+    void* stream, const void* input, nmoe_dtype dtype, int64_t rows, int32_t hidden,
+    const float* norm_weight, float epsilon, const float* gate, const float* bias,
+    int32_t experts, int32_t top_k, int32_t n_group, int32_t topk_group,
+    int32_t norm_topk_prob, float routed_scaling, int32_t* top_index, float* top_weight);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

@@ -37,7 +37,7 @@ EXPORTED_SYMBOLS = (
     "nmoe_layer_export_hidden", "nmoe_ffn_create", "nmoe_ffn_destroy", "nmoe_ffn_run",
     "nmoe_ffn_sync_status", "nmoe_ffn_export_hidden", "nmoe_quantize_nvfp4",
     "nmoe_dequant_nvfp4", "nmoe_swizzled_scale_bytes", "nmoe_swizzle_scales", "nmoe_rmsnorm",
-    "nmoe_router_logits", "nmoe_router_topk",
+    "nmoe_router_logits", "nmoe_router_topk", "nmoe_route_tokens_noalloc",
 )
 
 
@@ -130,6 +130,8 @@ def load_library() -> ctypes.CDLL:
     lib.nmoe_rmsnorm.argtypes = [vp, vp, ctypes.c_int, i64, i64, vp, f32, vp]
     lib.nmoe_router_logits.argtypes = [vp, vp, vp, i64, i32, i32, vp]
     lib.nmoe_router_topk.argtypes = [vp, vp, vp, i64, i32, i32, i32, i32, i32, f32, vp, vp]
+    lib.nmoe_route_tokens_noalloc.argtypes = [vp, vp, ctypes.c_int, i64, i32, vp, f32, vp, vp, i32,
+                                              i32, i32, i32, i32, f32, vp, vp]
     _lib = lib
     return lib
 
@@ -530,4 +532,25 @@ def router_topk(logits: torch.Tensor, bias: torch.Tensor, top_k: int, n_group: i
                                            experts, top_k, n_group, topk_group,
                                            1 if norm_topk_prob else 0, routed_scaling,
                                            idx.data_ptr(), wt.data_ptr()), "nmoe_router_topk")
+    return idx, wt
+
+
+def route_tokens_noalloc(x: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                         gate: torch.Tensor, bias: torch.Tensor, top_k: int, n_group: int = 1,
+                         topk_group: int = 1, norm_topk_prob: bool = True,
+                         routed_scaling: float = 1.0):
+    """RMSNorm -> gate logits -> top-k in one call that allocates nothing inside the
+    library (the intermediates live in a fixed array of the library image; see
+    nmoe_route_tokens_noalloc in include/nmoe.h for who needs that and for the limits).
+    The two result tensors are allocated here, by the caller, before the call."""
+    _require_cuda(x, "x")
+    rows, hidden = x.shape
+    experts = gate.shape[0]
+    idx = torch.empty((rows, top_k), dtype=torch.int32, device=x.device)
+    wt = torch.empty((rows, top_k), dtype=torch.float32, device=x.device)
+    _check(load_library().nmoe_route_tokens_noalloc(
+        _stream(), x.data_ptr(), _dtype_code(x), rows, hidden, norm_weight.data_ptr(), eps,
+        gate.data_ptr(), bias.data_ptr(), experts, top_k, n_group, topk_group,
+        1 if norm_topk_prob else 0, routed_scaling, idx.data_ptr(), wt.data_ptr()),
+        "nmoe_route_tokens_noalloc")
     return idx, wt
