@@ -86,6 +86,47 @@ __device__ __forceinline__ uint32_t quantize_block16(const float (&v)[16], float
   return scale_byte;
 }
 
+// Correctly rounded x / d for d > 0 given r = RN(1/d): one multiply and two
+// FMAs (q = RN(x r); q + r * RN(x - q d)).  The residual correction yields the
+// IEEE quotient whenever r is the correctly rounded reciprocal and d's
+// significand is not all ones (Markstein); the caller handles that one
+// significand with a full division.
+__device__ __forceinline__ float div_by_reciprocal(float x, float d, float r) {
+  const float q = __fmul_rn(x, r);
+  const float e = __fmaf_rn(-q, d, x);
+  return __fmaf_rn(e, r, q);
+}
+
+// The fused quantiser of the up-projection epilogue: 16 non-negative values
+// whose maximum is `amax`, per-row tensor scale 1 (nvfp4_packing.cpp:119-153
+// with tensor_scale == 1.0).  Bit-identical to quantize_block16(v, 1.0f, ..).
+__device__ __forceinline__ uint32_t quantize_block16_unit_scale(const float (&v)[16], float amax,
+                                                                uint32_t& lo_word,
+                                                                uint32_t& hi_word) {
+  float bs = 1.0f;
+  if (amax > 0.0f) bs = clamp_scale(__fdiv_rn(amax, kFp4Max));
+  const uint32_t scale_byte = encode_e4m3(bs);
+  uint32_t w[2] = {0u, 0u};
+  if ((__float_as_uint(bs) & 0x007fffffu) != 0x007fffffu) {
+    const float r = __frcp_rn(bs);
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const uint32_t byte = encode_e2m1x2(div_by_reciprocal(v[i], bs, r),
+                                          div_by_reciprocal(v[i + 1], bs, r));
+      w[i / 8] |= (byte & 0xffu) << (8 * ((i / 2) & 3));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const uint32_t byte = encode_e2m1x2(__fdiv_rn(v[i], bs), __fdiv_rn(v[i + 1], bs));
+      w[i / 8] |= (byte & 0xffu) << (8 * ((i / 2) & 3));
+    }
+  }
+  lo_word = w[0];
+  hi_word = w[1];
+  return scale_byte;
+}
+
 // Offset of the scale of (row, 16-block) inside the 128-row x 4-block tiled
 // layout of runtime/src/backend/nvfp4_scale_layout.cpp:14-28.  `k_tiles` is the
 // number of 4-block groups each 128-row tile stores.

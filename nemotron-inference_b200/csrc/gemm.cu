@@ -19,8 +19,9 @@
 // 32-lane x 16-byte form; activations use the reference's 128x4 tile order
 // (runtime/src/backend/nvfp4_scale_layout.cpp:14-28) unchanged.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
-// owner, warps 2-5 = epilogue (one TMEM lane quarter each).  Every mbarrier
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// owner, warps 2-9 = epilogue (two warps per TMEM lane quarter, splitting the
+// tile's columns).  Every mbarrier
 // wait is bounded; on a timeout the CTA records kDevWaitTimeout and unwinds.
 #include <algorithm>
 
@@ -29,6 +30,10 @@
 
 namespace nmoe {
 namespace {
+
+constexpr int kEpilogueWarps = 8;
+constexpr int kGemmThreads = (2 + kEpilogueWarps) * 32;
+constexpr int kStageStride = 20;  // floats per staged row: 16 + 4 keeps float4 stores conflict-free
 
 template <int BN_, int A_ROWS_, int SFB_GS_, int STAGES_>
 struct TileCfg {
@@ -48,11 +53,12 @@ struct TileCfg {
   static constexpr int TMEM_USED = SFB_COL + 4 * SFB_GS;
   static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
   static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int EPI_STAGE_BYTES = kEpilogueWarps * 32 * kStageStride * 4;
   // The MMA always reads 128 A rows; with a smaller box the tail rows alias the
   // following stages, which is harmless (those output rows are never stored)
   // but must stay inside the allocation: the B region follows the A region.
   static constexpr int SMEM_BYTES =
-      STAGES * (A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES) + BAR_BYTES + 1024;
+      STAGES * (A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES) + BAR_BYTES + EPI_STAGE_BYTES + 1024;
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "BN");
   static_assert(SFB_GS % 4 == 0 && SFB_GS * 32 >= BN, "weight scale groups");
   static_assert(TMEM_USED <= 512, "TMEM budget");
@@ -62,8 +68,8 @@ struct TileCfg {
 
 using CfgPrefillUp = TileCfg<208, 128, 8, 4>;
 using CfgPrefillDown = TileCfg<224, 128, 8, 4>;
-using CfgDecode = TileCfg<128, 32, 4, 9>;
-using CfgDecodeWide = TileCfg<128, 128, 4, 6>;
+using CfgDecode = TileCfg<128, 32, 4, 8>;
+using CfgDecodeWide = TileCfg<128, 128, 4, 5>;
 
 __device__ __forceinline__ void report_timeout(int32_t* error, volatile int* abort_flag) {
   *abort_flag = 1;
@@ -71,7 +77,7 @@ __device__ __forceinline__ void report_timeout(int32_t* error, volatile int* abo
 }
 
 template <class C, int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -87,6 +93,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* stage_base = reinterpret_cast<float*>(
+      reinterpret_cast<uint8_t*>(full_bar) + C::BAR_BYTES);  // down epilogue staging
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -98,7 +106,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full_bar[a], 1);
-      mbar_init(&tmem_empty_bar[a], 4);
+      mbar_init(&tmem_empty_bar[a], kEpilogueWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -217,8 +225,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else {
     // -------------------------------------------------------------- epilogue
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
+    const int quarter = warp & 3;           // TMEM lanes a warp may read: 32 * (warp % 4)
+    const int half = (warp - 2) >> 2;       // which half of the tile's columns
+    const int r = quarter * 32 + lane;      // row inside the tile == TMEM lane
     int local = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
       const int acc = local & 1;
@@ -248,56 +257,76 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t t_addr =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::ACC_STRIDE;
       const int n0 = nt * C::BN;
+      // the two warps of a lane quarter split the tile's 16-column chunks
+      constexpr int kChunks = C::BN / 16;
+      const int chunk_begin = half == 0 ? 0 : (kChunks + 1) / 2;
+      const int chunk_end = half == 0 ? (kChunks + 1) / 2 : kChunks;
 
       if constexpr (MODE == kGemmUp) {
         uint8_t* packed_row = args.out_packed + static_cast<size_t>(grow) * (args.N / 2);
-        bool range_error = false;
-        for (int c = 0; c < C::BN; c += 16) {
-          const int n = n0 + c;
+        float row_max = 0.0f;
+        for (int ch = chunk_begin; ch < chunk_end; ++ch) {
+          const int n = n0 + ch * 16;
           if (n >= args.N) break;
           float v[16];
-          tmem_ld_x16(t_addr + c, v);
+          tmem_ld_x16(t_addr + ch * 16, v);
+          float amax = 0.0f;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float x = v[i] * scale;
-            v[i] = x > 0.0f ? x * x : 0.0f;
-            range_error |= v[i] > kFp4Max * kFp8Max;
+            const float x = fmaxf(__fmul_rn(v[i], scale), 0.0f);  // Relu2: x > 0 ? x*x : 0
+            v[i] = __fmul_rn(x, x);
+            amax = fmaxf(amax, v[i]);
           }
+          row_max = fmaxf(row_max, amax);
           uint32_t lo, hi;
-          const uint32_t sf = quantize_block16(v, 1.0f, lo, hi);
+          const uint32_t sf = quantize_block16_unit_scale(v, amax, lo, hi);
           if (row_valid) {
             *reinterpret_cast<uint2*>(packed_row + n / 2) = make_uint2(lo, hi);
             args.out_sf[swizzled_scale_offset(grow, n / 16, args.out_k_blocks * 4)] =
                 static_cast<uint8_t>(sf);
           }
         }
-        if (range_error && row_valid && args.error != nullptr) {
+        if (row_valid && row_max > kFp4Max * kFp8Max && args.error != nullptr) {
           atomicCAS(args.error, kDevOk, kDevActivationRange);
         }
       } else {
-        int dest = 0;
+        int dest = -1;
         float wt = 1.0f;
         if (row_valid) {
           dest = args.dest_row != nullptr ? args.dest_row[grow]
                                           : grow * args.dest_mul + args.dest_add;
           if (args.row_weight != nullptr) wt = args.row_weight[grow];
         }
-        float* out_row = args.out_rows + static_cast<size_t>(dest) * args.N;
-        for (int c = 0; c < C::BN; c += 16) {
-          const int n = n0 + c;
+        // Each thread owns one output row of the tile, but a store instruction
+        // should write whole rows: stage 16 columns of 32 rows in shared memory,
+        // then let half-warps write 64 contiguous bytes of one row each.
+        float* stage = stage_base + (warp - 2) * (32 * kStageStride);
+        for (int ch = chunk_begin; ch < chunk_end; ++ch) {
+          const int n = n0 + ch * 16;
           if (n >= args.N) break;
           float v[16];
-          tmem_ld_x16(t_addr + c, v);
-          if (row_valid) {
+          tmem_ld_x16(t_addr + ch * 16, v);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              v[i] = v[i] * scale;
-              if (args.row_weight != nullptr) v[i] = v[i] * wt;
-            }
+          for (int i = 0; i < 16; ++i) {
+            v[i] = __fmul_rn(v[i], scale);
+            if (args.row_weight != nullptr) v[i] = __fmul_rn(v[i], wt);
+          }
+          __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-              *reinterpret_cast<float4*>(out_row + n + i) =
-                  make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          for (int i = 0; i < 16; i += 4) {
+            *reinterpret_cast<float4*>(stage + lane * kStageStride + i) =
+                make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+          }
+          __syncwarp();
+          const int sub = lane >> 4;
+          const int col = lane & 15;
+#pragma unroll 4
+          for (int it = 0; it < 16; ++it) {
+            const int rr = 2 * it + sub;
+            const int d = __shfl_sync(0xffffffffu, dest, rr);
+            if (d >= 0) {
+              args.out_rows[static_cast<size_t>(d) * args.N + n + col] =
+                  stage[rr * kStageStride + col];
             }
           }
         }
@@ -330,12 +359,12 @@ cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a, const CUtensorM
     auto kernel = grouped_gemm_kernel<C, kGemmUp>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (err != cudaSuccess) return err;
-    kernel<<<grid, 192, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, args);
+    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, args);
   } else {
     auto kernel = grouped_gemm_kernel<C, kGemmDown>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (err != cudaSuccess) return err;
-    kernel<<<grid, 192, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, args);
+    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, args);
   }
   return cudaGetLastError();
 }

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstddef>
@@ -93,7 +94,9 @@ size_t weight_scale_layout_bytes(int experts, int N, int K, int bn, int sfb_grou
 cudaError_t launch_norm_quant(const void* in, bool in_bf16, int rows, int cols,
                               const float* norm_weight, float eps, float* normalized,
                               uint8_t* packed, uint8_t* sf_row_major, uint8_t* sf_tiled,
-                              int k_blocks, float* tensor_scale, cudaStream_t stream);
+                              int k_blocks, float* tensor_scale, cudaStream_t stream,
+                              __nv_bfloat16* split = nullptr, size_t split_plane = 0);
+// `split` (optional): three bf16 planes [3][split_plane] with y = hi + mid + lo.
 // Whole-matrix dynamic quantisation with ONE tensor scale (the reference
 // packer's semantics for rows > 1).  `amax_scratch` is one float of device
 // memory; it is overwritten.
@@ -115,6 +118,22 @@ cudaError_t launch_router_topk(const float* logits, const float* bias, int rows,
                                float routed_scaling, int32_t* top_index, float* top_weight,
                                int32_t* expert_counts /* nullable, += histogram */,
                                cudaStream_t stream);
+
+// Two-pass router for large batches.  Pass 1: logits from the three bf16 planes
+// of the normalised activations and the bf16 gate on the tensor cores (FP32
+// accumulate).  Pass 2, per token: every expert whose pass-1 choice score is
+// within `tie_margin` of the top_k-th is re-evaluated in FP64 (and written back
+// into `logits`), then top-k runs on the exact values.  Requires n_group == 1,
+// experts % 32 == 0, experts <= 256, hidden % 64 == 0.
+cudaError_t launch_router_fast_logits(const CUtensorMap& tmap_split, const CUtensorMap& tmap_gate,
+                                      int rows, int split_plane_rows, int experts, int hidden,
+                                      float* logits, int32_t* error, cudaStream_t stream);
+cudaError_t launch_router_select_exact(float* logits, const float* normalized,
+                                       const __nv_bfloat16* gate, const float* logit_offset,
+                                       const float* bias, int rows, int experts, int hidden,
+                                       int top_k, bool norm_topk_prob, float routed_scaling,
+                                       float tie_margin, int32_t* top_index, float* top_weight,
+                                       int32_t* expert_counts, cudaStream_t stream);
 
 // --- plan / permute / combine -------------------------------------------------
 struct PlanBuffers {

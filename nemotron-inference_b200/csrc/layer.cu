@@ -112,6 +112,25 @@ CUtensorMap make_packed_map(const void* base, size_t rows, size_t row_bytes, int
   return map;
 }
 
+// bf16 rows [rows][cols], box = 64 elements (128 bytes) x box_rows, 128-byte swizzle.
+CUtensorMap make_bf16_map(const void* base, size_t rows, size_t cols, int box_rows) {
+  NMOE_REQUIRE(reinterpret_cast<uintptr_t>(base) % 16 == 0, "tensor map base must be 16-byte aligned");
+  NMOE_REQUIRE((cols * 2) % 16 == 0, "bf16 row pitch must be a multiple of 16 bytes");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[2] = {1u, 1u};
+  const CUresult rc = encode_tiled_fn()(
+      &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    throw Failure{NMOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(rc)};
+  }
+  return map;
+}
+
 int k_blocks_of(int k) { return (k + 255) / 256; }
 size_t tiled_sf_bytes(size_t row_slots, int k) { return row_slots * k_blocks_of(k) * 2048; }
 
@@ -496,6 +515,13 @@ struct nmoe_layer {
 
   DeviceBuffer norm_weight, gate, bias, logit_offset;
   bool has_logit_offset = false;
+  // two-pass router (tensor-core logits + FP64 re-evaluation of near-ties)
+  bool fast_router = false;
+  int fast_router_min_tokens = 256;
+  float router_tie_margin = 2.0e-4f;
+  int split_plane_rows = 0;
+  DeviceBuffer gate_bf16, y_split;
+  CUtensorMap split_map, gate_map;
   WeightStack up, down, shared_up, shared_down;
 
   // token-order scratch
@@ -573,6 +599,20 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
   L->shared_down.upload(&w.shared_down, 1, H, S, false, "shared down_proj", stream);
 
   const size_t token_slots = (T + 127) / 128;
+  // The tensor-core pass needs the gate exactly in bf16.
+  L->fast_router = w.gate_weight.dtype == NMOE_BF16 && c.n_group == 1 && E % 32 == 0 &&
+                   E <= 256 && H % 64 == 0 && std::getenv("NMOE_ROUTER_FP64_ONLY") == nullptr;
+  if (L->fast_router) {
+    L->gate_bf16.allocate(static_cast<size_t>(E) * H * 2);
+    NMOE_CUDA(cudaMemcpyAsync(L->gate_bf16.as<void>(), w.gate_weight.data,
+                              static_cast<size_t>(E) * H * 2, cudaMemcpyDefault, stream));
+    L->split_plane_rows = static_cast<int>(token_slots * 128);
+    L->y_split.allocate(3 * token_slots * 128 * H * 2, true);
+    L->split_map = make_bf16_map(L->y_split.as<void>(), 3 * token_slots * 128, H, 128);
+    L->gate_map = make_bf16_map(L->gate_bf16.as<void>(), E, H, E);
+    if (const char* env = std::getenv("NMOE_ROUTER_TIE_MARGIN")) L->router_tie_margin = std::strtof(env, nullptr);
+    if (const char* env = std::getenv("NMOE_ROUTER_FAST_MIN_TOKENS")) L->fast_router_min_tokens = std::atoi(env);
+  }
   L->normalized.allocate(T * H * sizeof(float));
   L->logits.allocate(T * E * sizeof(float));
   L->top_index.allocate(T * K * sizeof(int32_t));
@@ -622,23 +662,37 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
   int32_t* error = L->error.device.as<int32_t>();
 
   L->mark(0, stream);
+  const bool two_pass_router = L->fast_router && tokens >= L->fast_router_min_tokens;
   // RMSNorm (:795-796) fused with the activation quantiser every expert's
   // up_proj applies to the same normalised row (:913 -> nvfp4_packing.cpp:90)
   NMOE_CUDA(launch_norm_quant(input, in_dtype == NMOE_BF16, tokens, H, L->norm_weight.as<float>(),
                               c.rms_epsilon, L->normalized.as<float>(), L->y_packed.as<uint8_t>(),
                               L->y_sf_row_major.as<uint8_t>(), L->y_sf_tiled.as<uint8_t>(),
-                              k_blocks_of(H), L->y_ts.as<float>(), stream));
+                              k_blocks_of(H), L->y_ts.as<float>(), stream,
+                              two_pass_router ? L->y_split.as<__nv_bfloat16>() : nullptr,
+                              static_cast<size_t>(L->split_plane_rows) * H));
   L->mark(1, stream);
   // gate projection (:797-799) and top-k (:881)
-  NMOE_CUDA(launch_router_logits(L->normalized.as<float>(), L->gate.as<float>(),
-                                 L->has_logit_offset ? L->logit_offset.as<float>() : nullptr,
-                                 tokens, E, H, L->logits.as<float>(), stream));
-  L->mark(2, stream);
   NMOE_CUDA(cudaMemsetAsync(L->counts.as<int32_t>(), 0, E * sizeof(int32_t), stream));
-  NMOE_CUDA(launch_router_topk(L->logits.as<float>(), L->bias.as<float>(), tokens, E, K,
-                               c.n_group, c.topk_group, c.norm_topk_prob != 0,
-                               c.routed_scaling_factor, L->top_index.as<int32_t>(),
-                               L->top_weight.as<float>(), L->counts.as<int32_t>(), stream));
+  const float* offset = L->has_logit_offset ? L->logit_offset.as<float>() : nullptr;
+  if (two_pass_router) {
+    NMOE_CUDA(launch_router_fast_logits(L->split_map, L->gate_map, tokens, L->split_plane_rows, E,
+                                        H, L->logits.as<float>(), error, stream));
+    L->mark(2, stream);
+    NMOE_CUDA(launch_router_select_exact(
+        L->logits.as<float>(), L->normalized.as<float>(), L->gate_bf16.as<__nv_bfloat16>(), offset,
+        L->bias.as<float>(), tokens, E, H, K, c.norm_topk_prob != 0, c.routed_scaling_factor,
+        L->router_tie_margin, L->top_index.as<int32_t>(), L->top_weight.as<float>(),
+        L->counts.as<int32_t>(), stream));
+  } else {
+    NMOE_CUDA(launch_router_logits(L->normalized.as<float>(), L->gate.as<float>(), offset, tokens,
+                                   E, H, L->logits.as<float>(), stream));
+    L->mark(2, stream);
+    NMOE_CUDA(launch_router_topk(L->logits.as<float>(), L->bias.as<float>(), tokens, E, K,
+                                 c.n_group, c.topk_group, c.norm_topk_prob != 0,
+                                 c.routed_scaling_factor, L->top_index.as<int32_t>(),
+                                 L->top_weight.as<float>(), L->counts.as<int32_t>(), stream));
+  }
 
   L->mark(3, stream);
   const bool decode = static_cast<long long>(tokens) * K <= L->decode_pairs_limit / 2;

@@ -26,17 +26,20 @@ def _run(layer, x, out_dtype=torch.float32):
 
 
 def test_small_layer_every_stage(package, synthetic):
-    cfg = synthetic.baseline_config(max_tokens=256, experts=32, hidden=512, routed=256, shared=512)
+    cfg = synthetic.baseline_config(max_tokens=1024, experts=32, hidden=512, routed=256, shared=512)
     data = synthetic.make_layer(cfg, seed=21, device="cuda", norm_weight_uniform=True)
     layer = package.ExpertLayerSlice.create(cfg, data.bindings)
     assert layer is not None
-    for tokens in (1, 3, 33, 200):
+    for tokens in (1, 3, 33, 200, 300, 1000):
         x = synthetic.make_tokens(tokens, cfg.hidden_size, seed=tokens, device="cuda")
         out = _run(layer, x)
         rep = helpers.compare_layer_with_oracle(layer, data, x, out)
         print(rep.summary())
         assert rep.ok(), rep.summary()
-        assert rep.norm_max_diff == 0.0 and rep.logits_max_diff == 0.0
+        # weights may differ in the last bit where glibc's expf is not the correctly rounded exp
+        assert rep.norm_max_diff == 0.0 and rep.weight_max_diff <= 1.2e-7
+        # below 256 tokens every logit is an FP64 sum; above, only the candidates' are
+        assert rep.logits_max_diff == 0.0 or tokens >= 256
     layer.close()
 
 
