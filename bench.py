@@ -330,7 +330,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         ep = importlib.import_module("nemotron_inference_b200.expert_parallel")
-        line = ep.bench_main(args, package, synthetic, peaks, flush_buf, dist)
+        line = ep.bench_main(args, package, synthetic, peaks, flush_buf, dist, sys.modules[__name__])
         if rank == 0:
             print(json.dumps(line))
         dist.destroy_process_group()

@@ -61,6 +61,8 @@ typedef struct nmoe_config {
   float routed_scaling_factor;
   int32_t max_tokens; /* capacity of one nmoe_layer_run call (not in the reference,
                          which allocates scratch per call, expert_layer.cpp:782-787) */
+  int32_t max_recv_pairs; /* expert parallelism only: most (token, slot) pairs this rank
+                             accepts from all ranks in one step; 0 = 2*max_tokens*top_k */
 } nmoe_config;
 
 /* One NVFP4 matrix in the reference's weight layout: the byte fields of
@@ -178,6 +180,41 @@ NMOE_API nmoe_status nmoe_layer_copy_trace_field(nmoe_layer* layer, void* stream
 NMOE_API nmoe_status nmoe_layer_export_hidden(nmoe_layer* layer, void* stream,
                                               uint8_t* routed_packed, uint8_t* routed_scales,
                                               uint8_t* shared_packed, uint8_t* shared_scales);
+
+/* --- expert parallelism ------------------------------------------------------
+ * No counterpart in the reference (single GPU, no collectives).  A layer created
+ * with n_local_experts < n_routed_experts holds an equal share of the routed
+ * experts (rank = first_local_expert / n_local_experts) and replicated router
+ * and shared-expert weights.  One step = four device stages with two
+ * all-to-all exchanges between them, which the HOST issues (NCCL): the library
+ * never communicates.  Results equal the single-device layer's (bit for bit
+ * with FP32 return rows).
+ *
+ *   nmoe_ep_dispatch   routes `tokens` own tokens and packs one record of
+ *                      nmoe_ep_record_bytes() bytes per (token, slot) pair,
+ *                      grouped by destination rank; returns the device address
+ *                      of the records and of the int32[world] per-rank counts.
+ *   -- exchange counts, then records (all-to-all-v, rows = records) --
+ *   nmoe_ep_experts    runs this rank's experts over `count` received records
+ *                      and writes one weighted down_proj row per record, in
+ *                      arrival order, to out_rows [count][hidden] (FP32 or bf16).
+ *   nmoe_ep_shared     shared expert over the tokens of the last dispatch (any
+ *                      stream; independent of the exchange).
+ *   -- return the rows (all-to-all-v with the splits swapped) --
+ *   nmoe_ep_combine    output = input + (sum of the returned rows of each token
+ *                      in selection order + shared).  returned_rows holds one
+ *                      row per pair in the order the records were sent.
+ */
+NMOE_API size_t nmoe_ep_record_bytes(const nmoe_layer* layer);
+NMOE_API nmoe_status nmoe_ep_dispatch(nmoe_layer* layer, void* stream, const void* input,
+                                      nmoe_dtype input_dtype, int64_t tokens,
+                                      const void** send_records, const int32_t** send_counts);
+NMOE_API nmoe_status nmoe_ep_experts(nmoe_layer* layer, void* stream, const void* recv_records,
+                                     int64_t count, void* out_rows, nmoe_dtype rows_dtype);
+NMOE_API nmoe_status nmoe_ep_shared(nmoe_layer* layer, void* stream);
+NMOE_API nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream, const void* input,
+                                     nmoe_dtype input_dtype, const void* returned_rows,
+                                     nmoe_dtype rows_dtype, void* output, nmoe_dtype output_dtype);
 
 /* --- one expert FFN: down(relu^2(up(x))) with NVFP4 weights ----------------
  * The composition ExpertLayerSlice::Run applies per (token, expert)

@@ -38,6 +38,8 @@ EXPORTED_SYMBOLS = (
     "nmoe_ffn_sync_status", "nmoe_ffn_export_hidden", "nmoe_quantize_nvfp4",
     "nmoe_dequant_nvfp4", "nmoe_swizzled_scale_bytes", "nmoe_swizzle_scales", "nmoe_rmsnorm",
     "nmoe_router_logits", "nmoe_router_topk", "nmoe_route_tokens_noalloc",
+    "nmoe_ep_record_bytes", "nmoe_ep_dispatch", "nmoe_ep_experts", "nmoe_ep_shared",
+    "nmoe_ep_combine",
 )
 
 
@@ -56,7 +58,8 @@ class _Config(ctypes.Structure):
                 ("n_routed_experts", ctypes.c_int32), ("top_k", ctypes.c_int32),
                 ("n_group", ctypes.c_int32), ("topk_group", ctypes.c_int32),
                 ("norm_topk_prob", ctypes.c_int32), ("rms_epsilon", ctypes.c_float),
-                ("routed_scaling_factor", ctypes.c_float), ("max_tokens", ctypes.c_int32)]
+                ("routed_scaling_factor", ctypes.c_float), ("max_tokens", ctypes.c_int32),
+                ("max_recv_pairs", ctypes.c_int32)]
 
 
 class _Nvfp4Matrix(ctypes.Structure):
@@ -130,6 +133,13 @@ def load_library() -> ctypes.CDLL:
     lib.nmoe_rmsnorm.argtypes = [vp, vp, ctypes.c_int, i64, i64, vp, f32, vp]
     lib.nmoe_router_logits.argtypes = [vp, vp, vp, i64, i32, i32, vp]
     lib.nmoe_router_topk.argtypes = [vp, vp, vp, i64, i32, i32, i32, i32, i32, f32, vp, vp]
+    lib.nmoe_ep_record_bytes.argtypes = [vp]
+    lib.nmoe_ep_record_bytes.restype = ctypes.c_size_t
+    lib.nmoe_ep_dispatch.argtypes = [vp, vp, vp, ctypes.c_int, i64, ctypes.POINTER(vp),
+                                     ctypes.POINTER(vp)]
+    lib.nmoe_ep_experts.argtypes = [vp, vp, vp, i64, vp, ctypes.c_int]
+    lib.nmoe_ep_shared.argtypes = [vp, vp]
+    lib.nmoe_ep_combine.argtypes = [vp, vp, vp, ctypes.c_int, vp, ctypes.c_int, vp, ctypes.c_int]
     lib.nmoe_route_tokens_noalloc.argtypes = [vp, vp, ctypes.c_int, i64, i32, vp, f32, vp, vp, i32,
                                               i32, i32, i32, i32, f32, vp, vp]
     _lib = lib
@@ -181,6 +191,7 @@ class ExpertLayerConfig:
     routed_scaling_factor: float = 1.0
     norm_topk_prob: bool = True
     max_tokens: int = 8192
+    max_recv_pairs: int = 0  # expert parallelism only (0 = 2 * max_tokens * top_k)
 
 
 @dataclass
@@ -226,6 +237,7 @@ class ExpertLayerBindings:
     shared_down: Nvfp4Matrix
     routed_experts: List[ExpertWeightPair] = field(default_factory=list)
     gate_logit_offset: Optional[torch.Tensor] = None  # [experts] fp32, synthetic-skew hook
+    first_local_expert: int = 0  # expert parallelism: global index of routed_experts[0]
 
 
 def _dense(t: torch.Tensor, keep: list) -> _DenseTensor:
@@ -275,7 +287,7 @@ class ExpertLayerSlice:
                     config.shared_expert_intermediate_size, config.n_routed_experts,
                     config.top_k, config.n_group, config.topk_group,
                     1 if config.norm_topk_prob else 0, config.rms_epsilon,
-                    config.routed_scaling_factor, config.max_tokens)
+                    config.routed_scaling_factor, config.max_tokens, config.max_recv_pairs)
         n = len(bindings.routed_experts)
         ups = (_Nvfp4Matrix * max(n, 1))()
         downs = (_Nvfp4Matrix * max(n, 1))()
@@ -289,7 +301,7 @@ class ExpertLayerSlice:
         w.routed_up = ups
         w.routed_down = downs
         w.n_local_experts = n
-        w.first_local_expert = 0
+        w.first_local_expert = bindings.first_local_expert
         w.shared_up = bindings.shared_up._as_c(keep)
         w.shared_down = bindings.shared_down._as_c(keep)
         w.gate_logit_offset = None

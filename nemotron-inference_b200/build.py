@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnmoe_b200.so")
-SOURCES = ["gemm.cu", "quant.cu", "router.cu", "router_fast.cu", "plan.cu", "layer.cu",
+SOURCES = ["gemm.cu", "quant.cu", "router.cu", "router_fast.cu", "plan.cu", "ep.cu", "layer.cu",
            "route_noalloc.cu"]
 HEADERS = ["common.cuh", "kernels.h", os.path.join("..", "..", "include", "nmoe.h")]
 NVCC = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")

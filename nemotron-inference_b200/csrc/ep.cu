@@ -1,0 +1,236 @@
+// Expert-parallel dispatch / return kernels.
+//
+// The reference has no multi-GPU code at all; correctness here is defined as
+// "the expert-parallel layer equals the single-GPU layer".  Every rank routes
+// its own tokens, packs one DISPATCH RECORD per (token, slot) pair -- the
+// already quantised activation row, so that what an expert multiplies is bit
+// for bit what it would multiply on one GPU -- grouped by destination rank, and
+// an all-to-all (NCCL, issued by the host side) moves the records.  The
+// receiving rank feeds them to the same plan / permute / grouped-GEMM kernels
+// as local pairs and returns one weighted down_proj row per record in arrival
+// order; the home rank adds them in selection order.
+//
+// Record layout (record_bytes, a multiple of 16):
+//   [0, H/2)            packed E2M1 row
+//   [H/2, H/2 + H/16)   E4M3 block scales, row-major
+//   then FP32 tensor scale, FP32 routing weight, int32 expert index LOCAL to
+//   the destination rank, zero padding.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace nmoe {
+namespace {
+
+__global__ void dispatch_plan_kernel(const int32_t* __restrict__ expert_counts, int experts,
+                                     int experts_per_rank, int world,
+                                     int32_t* __restrict__ send_counts,
+                                     int32_t* __restrict__ send_offsets,
+                                     int32_t* __restrict__ rank_cursor) {
+  __shared__ int32_t per_rank[64];
+  const int r = threadIdx.x;
+  if (r < world) {
+    int total = 0;
+    for (int e = r * experts_per_rank; e < (r + 1) * experts_per_rank && e < experts; ++e) {
+      total += expert_counts[e];
+    }
+    per_rank[r] = total;
+    send_counts[r] = total;
+    rank_cursor[r] = 0;
+  }
+  __syncthreads();
+  if (r == 0) {
+    int running = 0;
+    for (int i = 0; i < world; ++i) {
+      send_offsets[i] = running;
+      running += per_rank[i];
+    }
+  }
+}
+
+constexpr int kPackWarps = 8;
+
+__global__ void __launch_bounds__(kPackWarps * 32)
+pack_records_kernel(const int32_t* __restrict__ top_index, const float* __restrict__ top_weight,
+                    int pairs, int top_k, int experts_per_rank,
+                    const uint8_t* __restrict__ packed, const uint8_t* __restrict__ sf_row_major,
+                    const float* __restrict__ tensor_scale, int cols, int record_bytes,
+                    const int32_t* __restrict__ send_offsets, int32_t* __restrict__ rank_cursor,
+                    uint8_t* __restrict__ records, int32_t* __restrict__ send_position) {
+  const int lane = threadIdx.x & 31;
+  const int pair = blockIdx.x * kPackWarps + (threadIdx.x >> 5);
+  if (pair >= pairs) return;
+  const int token = pair / top_k;
+  const int expert = top_index[pair];
+  const int rank = expert / experts_per_rank;
+  int position = 0;
+  if (lane == 0) position = send_offsets[rank] + atomicAdd(&rank_cursor[rank], 1);
+  position = __shfl_sync(0xffffffffu, position, 0);
+  uint8_t* record = records + static_cast<size_t>(position) * record_bytes;
+  const int packed_words = cols / 8;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(packed) + static_cast<size_t>(token) * packed_words;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(record);
+  for (int w = lane; w < packed_words; w += 32) dst[w] = src[w];
+  const int sf_bytes = cols / 16;
+  const uint8_t* sf_src = sf_row_major + static_cast<size_t>(token) * sf_bytes;
+  uint8_t* sf_dst = record + cols / 2;
+  for (int b = lane; b < sf_bytes; b += 32) sf_dst[b] = sf_src[b];
+  if (lane == 0) {
+    // the tail starts at a multiple of 4: cols % 64 == 0 is required
+    uint8_t* tail = record + cols / 2 + sf_bytes;
+    *reinterpret_cast<float*>(tail) = tensor_scale[token];
+    *reinterpret_cast<float*>(tail + 4) = top_weight[pair];
+    *reinterpret_cast<int32_t*>(tail + 8) = expert - rank * experts_per_rank;
+    send_position[pair] = position;
+  }
+}
+
+__global__ void record_histogram_kernel(const uint8_t* __restrict__ records, int count,
+                                        int record_bytes, int expert_offset, int local_experts,
+                                        int32_t* __restrict__ expert_counts,
+                                        int32_t* __restrict__ error) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) {
+    const int e = *reinterpret_cast<const int32_t*>(
+        records + static_cast<size_t>(i) * record_bytes + expert_offset);
+    if (e >= 0 && e < local_experts) {
+      atomicAdd(&expert_counts[e], 1);
+    } else if (error != nullptr) {
+      atomicCAS(error, kDevOk, kDevPlanOverflow);  // a corrupt or misrouted record
+    }
+  }
+}
+
+// out[t] = in[t] + ((sum_k routed[position[t][k]]) + shared[t]), routed parts
+// added in selection order (expert_layer.cpp:951-953, :1064-1069).
+template <bool IN_BF16, bool OUT_BF16, bool ROWS_BF16>
+__global__ void combine_indexed_kernel(const void* __restrict__ in,
+                                       const void* __restrict__ returned_rows,
+                                       const int32_t* __restrict__ position,
+                                       const float* __restrict__ shared_rows, int rows, int hidden,
+                                       int top_k, void* __restrict__ out) {
+  const int quads = hidden / 4;
+  const size_t total = static_cast<size_t>(rows) * quads;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = i / quads;
+    const int c = static_cast<int>(i - t * quads) * 4;
+    float4 routed = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < top_k; ++k) {
+      const size_t row = static_cast<size_t>(position[t * top_k + k]);
+      float4 p;
+      if constexpr (ROWS_BF16) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(
+            reinterpret_cast<const __nv_bfloat16*>(returned_rows) + row * hidden + c);
+        p = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                        __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+      } else {
+        p = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(returned_rows) +
+                                             row * hidden + c);
+      }
+      if (k == 0) {
+        routed = p;
+      } else {
+        routed.x = __fadd_rn(routed.x, p.x);
+        routed.y = __fadd_rn(routed.y, p.y);
+        routed.z = __fadd_rn(routed.z, p.z);
+        routed.w = __fadd_rn(routed.w, p.w);
+      }
+    }
+    const float4 shared = *reinterpret_cast<const float4*>(shared_rows + t * hidden + c);
+    float x[4];
+    if constexpr (IN_BF16) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(
+          reinterpret_cast<const __nv_bfloat16*>(in) + t * hidden + c);
+      x[0] = __uint_as_float(raw.x << 16);
+      x[1] = __uint_as_float(raw.x & 0xffff0000u);
+      x[2] = __uint_as_float(raw.y << 16);
+      x[3] = __uint_as_float(raw.y & 0xffff0000u);
+    } else {
+      const float4 raw = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(in) + t * hidden + c);
+      x[0] = raw.x; x[1] = raw.y; x[2] = raw.z; x[3] = raw.w;
+    }
+    float r[4];
+    r[0] = __fadd_rn(x[0], __fadd_rn(routed.x, shared.x));
+    r[1] = __fadd_rn(x[1], __fadd_rn(routed.y, shared.y));
+    r[2] = __fadd_rn(x[2], __fadd_rn(routed.z, shared.z));
+    r[3] = __fadd_rn(x[3], __fadd_rn(routed.w, shared.w));
+    if constexpr (OUT_BF16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(r[2], r[3]);
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + t * hidden + c) = packed;
+    } else {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + t * hidden + c) =
+          make_float4(r[0], r[1], r[2], r[3]);
+    }
+  }
+}
+
+template <bool A, bool B, bool C>
+void launch_combine_indexed_t(const void* in, const void* rows_in, const int32_t* position,
+                              const float* shared_rows, int rows, int hidden, int top_k, void* out,
+                              int blocks, cudaStream_t stream) {
+  combine_indexed_kernel<A, B, C><<<blocks, 256, 0, stream>>>(in, rows_in, position, shared_rows,
+                                                             rows, hidden, top_k, out);
+}
+
+}  // namespace
+
+int dispatch_record_bytes(int cols) { return (cols / 2 + cols / 16 + 12 + 15) / 16 * 16; }
+
+cudaError_t launch_dispatch_plan(const int32_t* expert_counts, int experts, int experts_per_rank,
+                                 int world, int32_t* send_counts, int32_t* send_offsets,
+                                 int32_t* rank_cursor, cudaStream_t stream) {
+  if (world <= 0 || world > 64) return cudaErrorInvalidValue;
+  dispatch_plan_kernel<<<1, 64, 0, stream>>>(expert_counts, experts, experts_per_rank, world,
+                                             send_counts, send_offsets, rank_cursor);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_records(const int32_t* top_index, const float* top_weight, int rows,
+                                int top_k, int experts_per_rank, const uint8_t* packed,
+                                const uint8_t* sf_row_major, const float* tensor_scale, int cols,
+                                const int32_t* send_offsets, int32_t* rank_cursor,
+                                uint8_t* records, int32_t* send_position, cudaStream_t stream) {
+  const int pairs = rows * top_k;
+  if (pairs <= 0 || cols % 64 != 0) return cudaErrorInvalidValue;
+  pack_records_kernel<<<(pairs + kPackWarps - 1) / kPackWarps, kPackWarps * 32, 0, stream>>>(
+      top_index, top_weight, pairs, top_k, experts_per_rank, packed, sf_row_major, tensor_scale,
+      cols, dispatch_record_bytes(cols), send_offsets, rank_cursor, records, send_position);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_record_histogram(const uint8_t* records, int count, int cols,
+                                    int local_experts, int32_t* expert_counts, int32_t* error,
+                                    cudaStream_t stream) {
+  if (count <= 0) return cudaSuccess;
+  const int blocks = (count + 255) / 256 < 592 ? (count + 255) / 256 : 592;
+  record_histogram_kernel<<<blocks, 256, 0, stream>>>(records, count, dispatch_record_bytes(cols),
+                                                      cols / 2 + cols / 16 + 8, local_experts,
+                                                      expert_counts, error);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_combine_indexed(const void* in, bool in_bf16, const void* returned_rows,
+                                   bool rows_bf16, const int32_t* position,
+                                   const float* shared_rows, int rows, int hidden, int top_k,
+                                   void* out, bool out_bf16, cudaStream_t stream) {
+  if (rows <= 0 || hidden % 4 != 0 || top_k < 1) return cudaErrorInvalidValue;
+  const size_t total = static_cast<size_t>(rows) * (hidden / 4);
+  const int blocks = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const int key = (in_bf16 ? 4 : 0) | (out_bf16 ? 2 : 0) | (rows_bf16 ? 1 : 0);
+  switch (key) {
+    case 0: launch_combine_indexed_t<false, false, false>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
+    case 1: launch_combine_indexed_t<false, false, true>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
+    case 2: launch_combine_indexed_t<false, true, false>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
+    case 3: launch_combine_indexed_t<false, true, true>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
+    case 4: launch_combine_indexed_t<true, false, false>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
+    case 5: launch_combine_indexed_t<true, false, true>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
+    case 6: launch_combine_indexed_t<true, true, false>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
+    default: launch_combine_indexed_t<true, true, true>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace nmoe

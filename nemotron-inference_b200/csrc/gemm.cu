@@ -325,8 +325,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int rr = 2 * it + sub;
             const int d = __shfl_sync(0xffffffffu, dest, rr);
             if (d >= 0) {
-              args.out_rows[static_cast<size_t>(d) * args.N + n + col] =
-                  stage[rr * kStageStride + col];
+              const size_t at = static_cast<size_t>(d) * args.N + n + col;
+              const float value = stage[rr * kStageStride + col];
+              if (args.out_bf16) {
+                reinterpret_cast<__nv_bfloat16*>(args.out_rows)[at] = __float2bfloat16_rn(value);
+              } else {
+                args.out_rows[at] = value;
+              }
             }
           }
         }

@@ -46,7 +46,8 @@ struct GemmArgs {
   uint8_t* out_sf = nullptr;      // tiled [row slot][out_k_blocks][2048]
   int32_t out_k_blocks = 0;       // ceil(N / 256)
   // kGemmDown outputs
-  float* out_rows = nullptr;          // [dest][N]
+  float* out_rows = nullptr;          // [dest][N], FP32 or (out_bf16) bf16
+  int32_t out_bf16 = 0;
   const int32_t* dest_row = nullptr;  // per activation row; nullptr => row*dest_mul+dest_add
   int32_t dest_mul = 1;
   int32_t dest_add = 0;
@@ -145,16 +146,49 @@ struct PlanBuffers {
 };
 cudaError_t launch_route_plan(const PlanBuffers& plan, int experts, int tile_rows,
                               int max_row_tiles, int32_t* error, cudaStream_t stream);
-// Copies each (token, slot) pair's quantised activation row into its expert's
-// row slots and records where it went.
-cudaError_t launch_permute(const PlanBuffers& plan, const int32_t* top_index,
-                           const float* top_weight, int rows, int top_k, int tile_rows,
-                           int max_row_tiles, const uint8_t* packed, const uint8_t* sf_row_major,
-                           const float* tensor_scale, int cols, int k_blocks,
+// Where permute reads a (row, slot) pair from.  Quantised rows are indexed by
+// source row = pair / pairs_per_row, routing weight and expert id by pair; all
+// strides are in bytes.  Local routing: pairs_per_row = top_k over the token
+// arrays.  Expert-parallel receive: pairs_per_row = 1 over dispatch records.
+struct PermuteSource {
+  const uint8_t* packed;
+  size_t packed_stride;
+  const uint8_t* sf;  // row-major E4M3 block scales
+  size_t sf_stride;
+  const float* tensor_scale;
+  size_t tensor_scale_stride;
+  const float* weight;
+  size_t weight_stride;
+  const int32_t* expert;  // index into the LOCAL expert stack
+  size_t expert_stride;
+  int pairs_per_row;
+};
+// Copies each pair's quantised activation row into its expert's row slots and
+// records where it went; sorted_dest[row] = source_row * dest_stride + slot.
+cudaError_t launch_permute(const PlanBuffers& plan, const PermuteSource& src, int pairs,
+                           int tile_rows, int max_row_tiles, int cols, int k_blocks,
                            uint8_t* sorted_packed, uint8_t* sorted_sf_tiled,
                            float* sorted_tensor_scale, float* sorted_weight,
-                           int32_t* sorted_dest, int32_t* pair_row, int dest_stride,
-                           cudaStream_t stream);
+                           int32_t* sorted_dest, int32_t* pair_row /* nullable */,
+                           int dest_stride, cudaStream_t stream);
+// --- expert-parallel dispatch / return (csrc/ep.cu) ---------------------------
+int dispatch_record_bytes(int cols);
+cudaError_t launch_dispatch_plan(const int32_t* expert_counts, int experts, int experts_per_rank,
+                                 int world, int32_t* send_counts, int32_t* send_offsets,
+                                 int32_t* rank_cursor, cudaStream_t stream);
+cudaError_t launch_pack_records(const int32_t* top_index, const float* top_weight, int rows,
+                                int top_k, int experts_per_rank, const uint8_t* packed,
+                                const uint8_t* sf_row_major, const float* tensor_scale, int cols,
+                                const int32_t* send_offsets, int32_t* rank_cursor,
+                                uint8_t* records, int32_t* send_position, cudaStream_t stream);
+cudaError_t launch_record_histogram(const uint8_t* records, int count, int cols,
+                                    int local_experts, int32_t* expert_counts, int32_t* error,
+                                    cudaStream_t stream);
+cudaError_t launch_combine_indexed(const void* in, bool in_bf16, const void* returned_rows,
+                                   bool rows_bf16, const int32_t* position,
+                                   const float* shared_rows, int rows, int hidden, int top_k,
+                                   void* out, bool out_bf16, cudaStream_t stream);
+
 // out[t] = in[t] + ((sum_k parts[t][k]) + parts[t][top_k]) with the routed
 // parts added in slot order.
 cudaError_t launch_combine(const void* in, bool in_bf16, const float* parts, int rows, int hidden,

@@ -247,9 +247,10 @@ struct Schedule {
 void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass tile_class,
                       const ActivationOperand& a, const float* a_tensor_scale,
                       const Schedule& schedule, uint8_t* hidden_packed, uint8_t* hidden_sf,
-                      const ActivationOperand& hidden, float* out_rows, const int32_t* dest_row,
+                      const ActivationOperand& hidden, void* out_rows, const int32_t* dest_row,
                       int dest_mul, int dest_add, const float* row_weight, int32_t* error,
-                      int num_sms, cudaStream_t stream, cudaEvent_t between = nullptr) {
+                      int num_sms, cudaStream_t stream, cudaEvent_t between = nullptr,
+                      bool out_bf16 = false) {
   GemmArgs g;
   const GemmVariant up_variant = up.variant(tile_class);
   g.K = up.k;
@@ -285,7 +286,8 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   d.row_tiles = schedule.row_tiles;
   d.num_row_tiles = schedule.num_row_tiles;
   d.dense_rows = schedule.dense_rows;
-  d.out_rows = out_rows;
+  d.out_rows = static_cast<float*>(out_rows);
+  d.out_bf16 = out_bf16 ? 1 : 0;
   d.dest_row = dest_row;
   d.dest_mul = dest_mul;
   d.dest_add = dest_add;
@@ -534,6 +536,13 @@ struct nmoe_layer {
   // expert-sorted scratch
   DeviceBuffer a_packed, a_sf, a_ts, a_weight, a_dest, h_packed, h_sf;
 
+  // expert parallelism
+  int ep_world = 1;
+  int ep_rank = 0;
+  int64_t max_pairs = 0;
+  int record_bytes = 0;
+  DeviceBuffer send_records, send_position, send_counts, send_offsets, rank_cursor, shared_out;
+
   ActivationOperand y_op, sh_op, a_op, h_op;
   ErrorSlot error;
   int last_tokens = 0;
@@ -570,9 +579,13 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
   NMOE_REQUIRE(c.hidden_size % 64 == 0 && c.routed_expert_intermediate_size % 64 == 0 &&
                    c.shared_expert_intermediate_size % 64 == 0,
                "hidden and intermediate sizes must be multiples of 64");
-  if (w.n_local_experts != c.n_routed_experts || w.first_local_expert != 0) {
-    throw Failure{NMOE_ERR_UNSUPPORTED, "this entry point holds all routed experts on one device"};
-  }
+  // Expert parallelism: this device holds experts [first_local_expert,
+  // first_local_expert + n_local_experts), an equal share of all of them.
+  NMOE_REQUIRE(w.n_local_experts > 0 && c.n_routed_experts % w.n_local_experts == 0 &&
+                   w.first_local_expert >= 0 && w.first_local_expert % w.n_local_experts == 0 &&
+                   w.first_local_expert + w.n_local_experts <= c.n_routed_experts &&
+                   c.n_routed_experts / w.n_local_experts <= 64,
+               "local experts must be an equal, aligned share of the routed experts");
   NMOE_REQUIRE(w.routed_up != nullptr && w.routed_down != nullptr, "missing routed expert weights");
 
   L->cfg = c;
@@ -582,6 +595,9 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
   cudaStream_t stream = nullptr;
   const int H = c.hidden_size, I = c.routed_expert_intermediate_size,
             S = c.shared_expert_intermediate_size, E = c.n_routed_experts, K = c.top_k;
+  const int EL = w.n_local_experts;
+  L->ep_world = E / EL;
+  L->ep_rank = w.first_local_expert / EL;
   const size_t T = static_cast<size_t>(c.max_tokens);
 
   upload_dense_fp32(w.input_norm_weight, H, "input_norm_weight", &L->norm_weight, stream);
@@ -593,8 +609,8 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
                               E * sizeof(float), cudaMemcpyDefault, stream));
     L->has_logit_offset = true;
   }
-  L->up.upload(w.routed_up, E, I, H, true, "routed up_proj", stream);
-  L->down.upload(w.routed_down, E, H, I, false, "routed down_proj", stream);
+  L->up.upload(w.routed_up, EL, I, H, true, "routed up_proj", stream);
+  L->down.upload(w.routed_down, EL, H, I, false, "routed down_proj", stream);
   L->shared_up.upload(&w.shared_up, 1, S, H, true, "shared up_proj", stream);
   L->shared_down.upload(&w.shared_down, 1, H, S, false, "shared down_proj", stream);
 
@@ -623,14 +639,20 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
   L->y_ts.allocate(token_slots * 128 * sizeof(float), true);
   L->sh_packed.allocate(token_slots * 128 * S / 2, true);
   L->sh_sf.allocate(tiled_sf_bytes(token_slots, S), true);
-  L->parts.allocate(T * (K + 1) * H * sizeof(float));
+  if (L->ep_world == 1) L->parts.allocate(T * (K + 1) * H * sizeof(float));
 
   // Row tiles: every expert may leave one partly filled slot.  Small batches
   // use 32-row tiles (decode tile class), large ones 128-row tiles.
-  L->decode_pairs_limit = 32 * E;
-  const size_t pairs = T * K;
-  const size_t tiles_prefill = E + (pairs + 127) / 128;
-  const size_t tiles_decode = E + (std::min<size_t>(pairs, L->decode_pairs_limit) + 31) / 32;
+  // With expert parallelism the rows come from every rank: the capacity is
+  // max_recv_pairs (default: twice the local pairs, i.e. 2x the uniform share).
+  L->decode_pairs_limit = 32 * EL;
+  const size_t local_pairs = T * K;
+  const size_t pairs = L->ep_world == 1 ? local_pairs
+                       : c.max_recv_pairs > 0 ? static_cast<size_t>(c.max_recv_pairs)
+                                              : 2 * local_pairs;
+  L->max_pairs = static_cast<int64_t>(pairs);
+  const size_t tiles_prefill = EL + (pairs + 127) / 128;
+  const size_t tiles_decode = EL + (std::min<size_t>(pairs, L->decode_pairs_limit) + 31) / 32;
   L->max_row_tiles = static_cast<int>(std::max(tiles_prefill, tiles_decode));
   const size_t slots = static_cast<size_t>(L->max_row_tiles);
   L->counts.allocate(E * sizeof(int32_t), true);
@@ -639,6 +661,15 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
   L->row_tiles.allocate(slots * sizeof(RowTile), true);
   L->num_row_tiles.allocate(sizeof(int32_t), true);
   L->pair_row.allocate(pairs * sizeof(int32_t), true);
+  if (L->ep_world > 1) {
+    L->record_bytes = dispatch_record_bytes(H);
+    L->send_records.allocate(local_pairs * L->record_bytes, true);
+    L->send_position.allocate(local_pairs * sizeof(int32_t), true);
+    L->send_counts.allocate(64 * sizeof(int32_t), true);
+    L->send_offsets.allocate(64 * sizeof(int32_t), true);
+    L->rank_cursor.allocate(64 * sizeof(int32_t), true);
+    L->shared_out.allocate(T * H * sizeof(float));
+  }
   L->a_packed.allocate(slots * 128 * H / 2, true);
   L->a_sf.allocate(tiled_sf_bytes(slots, H), true);
   L->a_ts.allocate(slots * 128 * sizeof(float), true);
@@ -655,12 +686,13 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
   NMOE_CUDA(cudaDeviceSynchronize());
 }
 
-void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dtype in_dtype,
-                    int tokens, void* output, nmoe_dtype out_dtype) {
+// RMSNorm + activation quantiser + router: fills normalized, y_*, logits,
+// top_index / top_weight and the per-expert histogram `counts` (global ids).
+void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dtype in_dtype,
+                  int tokens) {
   const nmoe_config& c = L->cfg;
   const int H = c.hidden_size, E = c.n_routed_experts, K = c.top_k;
   int32_t* error = L->error.device.as<int32_t>();
-
   L->mark(0, stream);
   const bool two_pass_router = L->fast_router && tokens >= L->fast_router_min_tokens;
   // RMSNorm (:795-796) fused with the activation quantiser every expert's
@@ -693,9 +725,17 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
                                  c.routed_scaling_factor, L->top_index.as<int32_t>(),
                                  L->top_weight.as<float>(), L->counts.as<int32_t>(), stream));
   }
-
   L->mark(3, stream);
-  const bool decode = static_cast<long long>(tokens) * K <= L->decode_pairs_limit / 2;
+}
+
+// Plan + permute + the two grouped GEMMs over `pairs` (row, slot) pairs whose
+// per-local-expert histogram is already in `counts`.
+void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& source, int pairs,
+                    int dest_stride, void* out_rows, bool out_bf16) {
+  const nmoe_config& c = L->cfg;
+  const int H = c.hidden_size;
+  int32_t* error = L->error.device.as<int32_t>();
+  const bool decode = static_cast<long long>(pairs) <= L->decode_pairs_limit / 2;
   const TileClass routed_class = decode ? kClassDecode : kClassPrefill;
   const int tile_rows = decode ? 32 : 128;
   PlanBuffers plan;
@@ -704,36 +744,63 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
   plan.expert_slot0 = L->slot0.as<int32_t>();
   plan.row_tiles = L->row_tiles.as<RowTile>();
   plan.num_row_tiles = L->num_row_tiles.as<int32_t>();
-  NMOE_CUDA(launch_route_plan(plan, E, tile_rows, L->max_row_tiles, error, stream));
+  NMOE_CUDA(launch_route_plan(plan, L->local_experts, tile_rows, L->max_row_tiles, error, stream));
   L->mark(4, stream);
-  NMOE_CUDA(launch_permute(plan, L->top_index.as<int32_t>(), L->top_weight.as<float>(), tokens, K,
-                           tile_rows, L->max_row_tiles, L->y_packed.as<uint8_t>(),
-                           L->y_sf_row_major.as<uint8_t>(), L->y_ts.as<float>(), H,
-                           k_blocks_of(H), L->a_packed.as<uint8_t>(), L->a_sf.as<uint8_t>(),
-                           L->a_ts.as<float>(), L->a_weight.as<float>(), L->a_dest.as<int32_t>(),
-                           L->pair_row.as<int32_t>(), K + 1, stream));
-
+  NMOE_CUDA(launch_permute(plan, source, pairs, tile_rows, L->max_row_tiles, H, k_blocks_of(H),
+                           L->a_packed.as<uint8_t>(), L->a_sf.as<uint8_t>(), L->a_ts.as<float>(),
+                           L->a_weight.as<float>(), L->a_dest.as<int32_t>(),
+                           L->ep_world == 1 ? L->pair_row.as<int32_t>() : nullptr, dest_stride,
+                           stream));
   L->mark(5, stream);
   // routed experts (:896-954)
   Schedule routed;
   routed.row_tiles = L->row_tiles.as<RowTile>();
   routed.num_row_tiles = L->num_row_tiles.as<int32_t>();
   run_expert_gemms(L->up, L->down, routed_class, L->a_op, L->a_ts.as<float>(), routed,
-                   L->h_packed.as<uint8_t>(), L->h_sf.as<uint8_t>(), L->h_op,
-                   L->parts.as<float>(), L->a_dest.as<int32_t>(), 1, 0, L->a_weight.as<float>(),
-                   error, L->num_sms, stream, L->stage_timing ? L->stage_events[6] : nullptr);
+                   L->h_packed.as<uint8_t>(), L->h_sf.as<uint8_t>(), L->h_op, out_rows,
+                   L->a_dest.as<int32_t>(), 1, 0, L->a_weight.as<float>(), error, L->num_sms,
+                   stream, L->stage_timing ? L->stage_events[6] : nullptr, out_bf16);
+}
 
-  // shared expert (:814-818, :956-964, :981-1005) on the same quantised rows
-  L->mark(7, stream);
+// shared expert (:814-818, :956-964, :981-1005) on the token-order quantised rows
+void shared_expert(nmoe_layer* L, cudaStream_t stream, int tokens, float* out_rows, int dest_mul,
+                   int dest_add, cudaEvent_t between) {
   const TileClass shared_class =
       tokens <= 32 ? kClassDecode : tokens <= 256 ? kClassDecodeWide : kClassPrefill;
   Schedule shared;
   shared.dense_rows = tokens;
   run_expert_gemms(L->shared_up, L->shared_down, shared_class, L->y_op, L->y_ts.as<float>(),
-                   shared, L->sh_packed.as<uint8_t>(), L->sh_sf.as<uint8_t>(), L->sh_op,
-                   L->parts.as<float>(), nullptr, K + 1, K, nullptr, error, L->num_sms, stream,
-                   L->stage_timing ? L->stage_events[8] : nullptr);
+                   shared, L->sh_packed.as<uint8_t>(), L->sh_sf.as<uint8_t>(), L->sh_op, out_rows,
+                   nullptr, dest_mul, dest_add, nullptr, L->error.device.as<int32_t>(),
+                   L->num_sms, stream, between, false);
+}
 
+PermuteSource local_source(nmoe_layer* L) {
+  const int H = L->cfg.hidden_size;
+  PermuteSource source;
+  source.packed = L->y_packed.as<uint8_t>();
+  source.packed_stride = static_cast<size_t>(H) / 2;
+  source.sf = L->y_sf_row_major.as<uint8_t>();
+  source.sf_stride = static_cast<size_t>(H) / 16;
+  source.tensor_scale = L->y_ts.as<float>();
+  source.tensor_scale_stride = sizeof(float);
+  source.weight = L->top_weight.as<float>();
+  source.weight_stride = sizeof(float);
+  source.expert = L->top_index.as<int32_t>();
+  source.expert_stride = sizeof(int32_t);
+  source.pairs_per_row = L->cfg.top_k;
+  return source;
+}
+
+void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dtype in_dtype,
+                    int tokens, void* output, nmoe_dtype out_dtype) {
+  const nmoe_config& c = L->cfg;
+  const int H = c.hidden_size, K = c.top_k;
+  route_tokens(L, stream, input, in_dtype, tokens);
+  routed_experts(L, stream, local_source(L), tokens * K, K + 1, L->parts.as<float>(), false);
+  L->mark(7, stream);
+  shared_expert(L, stream, tokens, L->parts.as<float>(), K + 1, K,
+                L->stage_timing ? L->stage_events[8] : nullptr);
   // routed sum in selection order, mixer and residual (:951-953, :1064-1069)
   L->mark(9, stream);
   NMOE_CUDA(launch_combine(input, in_dtype == NMOE_BF16, L->parts.as<float>(), tokens, H, K,
@@ -777,6 +844,7 @@ nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void* input,
     return NMOE_ERR_INVALID_ARGUMENT;
   }
   if (tokens > layer->cfg.max_tokens) return NMOE_ERR_CAPACITY;
+  if (layer->ep_world != 1) return NMOE_ERR_INVALID_ARGUMENT;  // use the nmoe_ep_* stages
   try {
     layer_run_impl(layer, static_cast<cudaStream_t>(stream), input, input_dtype,
                    static_cast<int>(tokens), output, output_dtype);
@@ -825,6 +893,119 @@ nmoe_status nmoe_layer_stage_times(nmoe_layer* layer, float* milliseconds, int32
     }
   }
   return NMOE_OK;
+}
+
+// ---------------------------------------------------------------------------
+// expert-parallel stages
+// ---------------------------------------------------------------------------
+
+size_t nmoe_ep_record_bytes(const nmoe_layer* layer) {
+  return layer == nullptr ? 0 : static_cast<size_t>(dispatch_record_bytes(layer->cfg.hidden_size));
+}
+
+nmoe_status nmoe_ep_dispatch(nmoe_layer* layer, void* stream_ptr, const void* input,
+                             nmoe_dtype input_dtype, int64_t tokens, const void** send_records,
+                             const int32_t** send_counts) {
+  if (layer == nullptr || input == nullptr || send_records == nullptr || send_counts == nullptr ||
+      tokens <= 0 || layer->ep_world <= 1) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  if (tokens > layer->cfg.max_tokens) return NMOE_ERR_CAPACITY;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  try {
+    const nmoe_config& c = layer->cfg;
+    route_tokens(layer, stream, input, input_dtype, static_cast<int>(tokens));
+    NMOE_CUDA(launch_dispatch_plan(layer->counts.as<int32_t>(), c.n_routed_experts,
+                                   layer->local_experts, layer->ep_world,
+                                   layer->send_counts.as<int32_t>(),
+                                   layer->send_offsets.as<int32_t>(),
+                                   layer->rank_cursor.as<int32_t>(), stream));
+    NMOE_CUDA(launch_pack_records(layer->top_index.as<int32_t>(), layer->top_weight.as<float>(),
+                                  static_cast<int>(tokens), c.top_k, layer->local_experts,
+                                  layer->y_packed.as<uint8_t>(),
+                                  layer->y_sf_row_major.as<uint8_t>(), layer->y_ts.as<float>(),
+                                  c.hidden_size, layer->send_offsets.as<int32_t>(),
+                                  layer->rank_cursor.as<int32_t>(),
+                                  layer->send_records.as<uint8_t>(),
+                                  layer->send_position.as<int32_t>(), stream));
+    layer->last_tokens = static_cast<int>(tokens);
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+  *send_records = layer->send_records.as<uint8_t>();
+  *send_counts = layer->send_counts.as<int32_t>();
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_ep_experts(nmoe_layer* layer, void* stream_ptr, const void* recv_records,
+                            int64_t count, void* out_rows, nmoe_dtype rows_dtype) {
+  if (layer == nullptr || layer->ep_world <= 1 || count < 0 ||
+      (count > 0 && (recv_records == nullptr || out_rows == nullptr))) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  if (count > layer->max_pairs) return NMOE_ERR_CAPACITY;
+  if (count == 0) return NMOE_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  try {
+    const int H = layer->cfg.hidden_size;
+    NMOE_CUDA(cudaMemsetAsync(layer->counts.as<int32_t>(), 0,
+                              layer->local_experts * sizeof(int32_t), stream));
+    NMOE_CUDA(launch_record_histogram(static_cast<const uint8_t*>(recv_records),
+                                      static_cast<int>(count), H, layer->local_experts,
+                                      layer->counts.as<int32_t>(),
+                                      layer->error.device.as<int32_t>(), stream));
+    const uint8_t* records = static_cast<const uint8_t*>(recv_records);
+    const size_t stride = static_cast<size_t>(layer->record_bytes);
+    const size_t tail = static_cast<size_t>(H) / 2 + static_cast<size_t>(H) / 16;
+    PermuteSource source;
+    source.packed = records;
+    source.packed_stride = stride;
+    source.sf = records + H / 2;
+    source.sf_stride = stride;
+    source.tensor_scale = reinterpret_cast<const float*>(records + tail);
+    source.tensor_scale_stride = stride;
+    source.weight = reinterpret_cast<const float*>(records + tail + 4);
+    source.weight_stride = stride;
+    source.expert = reinterpret_cast<const int32_t*>(records + tail + 8);
+    source.expert_stride = stride;
+    source.pairs_per_row = 1;
+    routed_experts(layer, stream, source, static_cast<int>(count), 1, out_rows,
+                   rows_dtype == NMOE_BF16);
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_ep_shared(nmoe_layer* layer, void* stream_ptr) {
+  if (layer == nullptr || layer->ep_world <= 1 || layer->last_tokens <= 0) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  try {
+    shared_expert(layer, static_cast<cudaStream_t>(stream_ptr), layer->last_tokens,
+                  layer->shared_out.as<float>(), 1, 0, nullptr);
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream_ptr, const void* input,
+                            nmoe_dtype input_dtype, const void* returned_rows,
+                            nmoe_dtype rows_dtype, void* output, nmoe_dtype output_dtype) {
+  if (layer == nullptr || layer->ep_world <= 1 || layer->last_tokens <= 0 || input == nullptr ||
+      returned_rows == nullptr || output == nullptr) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  const cudaError_t err = launch_combine_indexed(
+      input, input_dtype == NMOE_BF16, returned_rows, rows_dtype == NMOE_BF16,
+      layer->send_position.as<int32_t>(), layer->shared_out.as<float>(), layer->last_tokens,
+      layer->cfg.hidden_size, layer->cfg.top_k, output, output_dtype == NMOE_BF16,
+      static_cast<cudaStream_t>(stream_ptr));
+  return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
 }
 
 const char* nmoe_layer_last_error(const nmoe_layer* layer) {

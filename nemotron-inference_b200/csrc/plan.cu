@@ -63,20 +63,18 @@ __global__ void route_plan_kernel(PlanBuffers plan, int experts, int tile_rows, 
 constexpr int kPermuteWarps = 8;
 
 __global__ void __launch_bounds__(kPermuteWarps * 32)
-permute_kernel(PlanBuffers plan, const int32_t* __restrict__ top_index,
-               const float* __restrict__ top_weight, int rows, int top_k, int tile_rows,
-               int max_row_tiles, const uint8_t* __restrict__ packed,
-               const uint8_t* __restrict__ sf_row_major, const float* __restrict__ tensor_scale,
+permute_kernel(PlanBuffers plan, PermuteSource src, int pairs, int tile_rows, int max_row_tiles,
                int cols, int k_tiles, uint8_t* __restrict__ sorted_packed,
                uint8_t* __restrict__ sorted_sf_tiled, float* __restrict__ sorted_tensor_scale,
                float* __restrict__ sorted_weight, int32_t* __restrict__ sorted_dest,
                int32_t* __restrict__ pair_row, int dest_stride) {
   const int lane = threadIdx.x & 31;
   const int pair = blockIdx.x * kPermuteWarps + (threadIdx.x >> 5);
-  if (pair >= rows * top_k) return;
-  const int token = pair / top_k;
-  const int slot = pair - token * top_k;
-  const int expert = top_index[pair];
+  if (pair >= pairs) return;
+  const int source_row = pair / src.pairs_per_row;
+  const int slot = pair - source_row * src.pairs_per_row;
+  const int expert = *reinterpret_cast<const int32_t*>(
+      reinterpret_cast<const uint8_t*>(src.expert) + static_cast<size_t>(pair) * src.expert_stride);
   int position = 0;
   if (lane == 0) position = atomicAdd(&plan.expert_cursor[expert], 1);
   position = __shfl_sync(0xffffffffu, position, 0);
@@ -85,12 +83,13 @@ permute_kernel(PlanBuffers plan, const int32_t* __restrict__ top_index,
   const int row = tile * 128 + position % tile_rows;
 
   const int words = cols / 8;
-  const uint32_t* src = reinterpret_cast<const uint32_t*>(packed) + static_cast<size_t>(token) * words;
+  const uint32_t* from = reinterpret_cast<const uint32_t*>(
+      src.packed + static_cast<size_t>(source_row) * src.packed_stride);
   uint32_t* dst = reinterpret_cast<uint32_t*>(sorted_packed) + static_cast<size_t>(row) * words;
-  for (int w = lane; w < words; w += 32) dst[w] = src[w];
+  for (int w = lane; w < words; w += 32) dst[w] = from[w];
 
   const int blocks = cols / 16;
-  const uint8_t* sf_src = sf_row_major + static_cast<size_t>(token) * blocks;
+  const uint8_t* sf_src = src.sf + static_cast<size_t>(source_row) * src.sf_stride;
   if ((blocks & 3) == 0) {
     // four consecutive blocks are one aligned 32-bit word on both sides
     const uint32_t* sf_src_w = reinterpret_cast<const uint32_t*>(sf_src);
@@ -104,10 +103,13 @@ permute_kernel(PlanBuffers plan, const int32_t* __restrict__ top_index,
     }
   }
   if (lane == 0) {
-    sorted_tensor_scale[row] = tensor_scale[token];
-    sorted_weight[row] = top_weight[pair];
-    sorted_dest[row] = token * dest_stride + slot;
-    pair_row[pair] = row;
+    sorted_tensor_scale[row] = *reinterpret_cast<const float*>(
+        reinterpret_cast<const uint8_t*>(src.tensor_scale) +
+        static_cast<size_t>(source_row) * src.tensor_scale_stride);
+    sorted_weight[row] = *reinterpret_cast<const float*>(
+        reinterpret_cast<const uint8_t*>(src.weight) + static_cast<size_t>(pair) * src.weight_stride);
+    sorted_dest[row] = source_row * dest_stride + slot;
+    if (pair_row != nullptr) pair_row[pair] = row;
   }
 }
 
@@ -170,20 +172,16 @@ cudaError_t launch_route_plan(const PlanBuffers& plan, int experts, int tile_row
   return cudaGetLastError();
 }
 
-cudaError_t launch_permute(const PlanBuffers& plan, const int32_t* top_index,
-                           const float* top_weight, int rows, int top_k, int tile_rows,
-                           int max_row_tiles, const uint8_t* packed, const uint8_t* sf_row_major,
-                           const float* tensor_scale, int cols, int k_blocks,
+cudaError_t launch_permute(const PlanBuffers& plan, const PermuteSource& src, int pairs,
+                           int tile_rows, int max_row_tiles, int cols, int k_blocks,
                            uint8_t* sorted_packed, uint8_t* sorted_sf_tiled,
                            float* sorted_tensor_scale, float* sorted_weight,
                            int32_t* sorted_dest, int32_t* pair_row, int dest_stride,
                            cudaStream_t stream) {
-  const int pairs = rows * top_k;
-  if (pairs <= 0) return cudaErrorInvalidValue;
+  if (pairs <= 0 || src.pairs_per_row <= 0) return cudaErrorInvalidValue;
   permute_kernel<<<(pairs + kPermuteWarps - 1) / kPermuteWarps, kPermuteWarps * 32, 0, stream>>>(
-      plan, top_index, top_weight, rows, top_k, tile_rows, max_row_tiles, packed, sf_row_major,
-      tensor_scale, cols, k_blocks * 4, sorted_packed, sorted_sf_tiled, sorted_tensor_scale,
-      sorted_weight, sorted_dest, pair_row, dest_stride);
+      plan, src, pairs, tile_rows, max_row_tiles, cols, k_blocks * 4, sorted_packed,
+      sorted_sf_tiled, sorted_tensor_scale, sorted_weight, sorted_dest, pair_row, dest_stride);
   return cudaGetLastError();
 }
 

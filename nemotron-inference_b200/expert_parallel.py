@@ -1,0 +1,256 @@
+"""Expert-parallel MoE layer: one process per GPU, experts sharded by rank, token
+dispatch and return as all-to-all over NCCL.
+
+The reference is single-GPU; this module's contract is "the expert-parallel layer returns
+what the single-device layer returns".  Rank r owns experts [r*E/W, (r+1)*E/W) and its own
+slice of the tokens; router and shared-expert weights are replicated.
+
+One step (see nmoe_ep_* in include/nmoe.h for the device stages):
+
+    dispatch   route own tokens, pack one record per (token, slot) pair by destination rank
+    exchange   per-rank counts (all-to-all), then the records (all-to-all-v)
+    experts    local experts over the received records -> one weighted row per record
+    shared     shared expert on the own tokens (side stream, overlaps the exchange)
+    return     the rows travel back (all-to-all-v, splits swapped)
+    combine    out = x + (sum of the token's returned rows in selection order + shared)
+
+The exchange protocol lives in `ExpertParallelEngine`, which is generic over a `stages`
+object, so that the protocol itself is testable on CPU with gloo and a numpy stage
+implementation; `DeviceStages` is the CUDA implementation over the C ABI.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import (ExpertLayerBindings, ExpertLayerConfig, ExpertLayerSlice, NMOE_OK, NmoeError,
+               _check, _dtype_code, _stream, load_library)
+
+
+class DeviceStages:
+    """The four device stages of one rank, over libnmoe_b200.so."""
+
+    def __init__(self, config: ExpertLayerConfig, bindings: ExpertLayerBindings, rank: int,
+                 world: int, rows_dtype: torch.dtype = torch.bfloat16):
+        experts_per_rank = config.n_routed_experts // world
+        assert len(bindings.routed_experts) == experts_per_rank
+        bindings.first_local_expert = rank * experts_per_rank
+        self.layer = ExpertLayerSlice.create(config, bindings)
+        if self.layer is None:
+            raise RuntimeError("expert-parallel layer creation failed: " +
+                               ExpertLayerSlice.create_error)
+        self.config = config
+        self.world = world
+        self.rows_dtype = rows_dtype
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        lib = load_library()
+        self.record_bytes = int(lib.nmoe_ep_record_bytes(self.layer._handle))
+        self.capacity = config.max_recv_pairs or 2 * config.max_tokens * config.top_k
+        pairs = config.max_tokens * config.top_k
+        H = config.hidden_size
+        # exchange buffers are owned here; the library owns only the send records
+        self.recv_records = torch.empty((self.capacity, self.record_bytes), dtype=torch.uint8,
+                                        device=self.device)
+        self.rows_out = torch.empty((self.capacity, H), dtype=rows_dtype, device=self.device)
+        self.rows_back = torch.empty((pairs, H), dtype=rows_dtype, device=self.device)
+        self.side_stream = torch.cuda.Stream()
+        self._send_view = None
+
+    def dispatch(self, x: torch.Tensor):
+        lib = load_library()
+        records, counts = ctypes.c_void_p(), ctypes.c_void_p()
+        _check(lib.nmoe_ep_dispatch(self.layer._handle, _stream(), x.data_ptr(), _dtype_code(x),
+                                    x.shape[0], ctypes.byref(records), ctypes.byref(counts)),
+               "nmoe_ep_dispatch", self.layer._last_error())
+        pairs = x.shape[0] * self.config.top_k
+        send_records = _as_tensor(records.value, (pairs, self.record_bytes), torch.uint8,
+                                  self.device)
+        send_counts = _as_tensor(counts.value, (self.world,), torch.int32, self.device)
+        return send_records, send_counts
+
+    def experts(self, recv_records: torch.Tensor, count: int) -> torch.Tensor:
+        _check(load_library().nmoe_ep_experts(self.layer._handle, _stream(),
+                                              recv_records.data_ptr(), count,
+                                              self.rows_out.data_ptr(),
+                                              _dtype_code(self.rows_out)),
+               "nmoe_ep_experts", self.layer._last_error())
+        return self.rows_out[:count]
+
+    def shared(self) -> None:
+        """Shared expert on a side stream, ordered after the dispatch stage."""
+        ready = torch.cuda.Event()
+        ready.record()
+        with torch.cuda.stream(self.side_stream):
+            self.side_stream.wait_event(ready)
+            _check(load_library().nmoe_ep_shared(self.layer._handle, _stream()),
+                   "nmoe_ep_shared", self.layer._last_error())
+            self._shared_done = torch.cuda.Event()
+            self._shared_done.record()
+
+    def combine(self, x: torch.Tensor, rows_back: torch.Tensor, out: torch.Tensor) -> None:
+        torch.cuda.current_stream().wait_event(self._shared_done)
+        _check(load_library().nmoe_ep_combine(self.layer._handle, _stream(), x.data_ptr(),
+                                              _dtype_code(x), rows_back.data_ptr(),
+                                              _dtype_code(rows_back), out.data_ptr(),
+                                              _dtype_code(out)), "nmoe_ep_combine")
+
+    def recv_buffer(self, count: int) -> torch.Tensor:
+        if count > self.capacity:
+            raise NmoeError(6, "expert-parallel receive",
+                            f"{count} pairs exceed the capacity of {self.capacity}")
+        return self.recv_records[:count]
+
+    def back_buffer(self, count: int) -> torch.Tensor:
+        return self.rows_back[:count]
+
+    def sync_status(self) -> int:
+        return self.layer.sync_status()
+
+
+def _as_tensor(address: int, shape, dtype, device) -> torch.Tensor:
+    """A torch view of library-owned device memory (no copy, no ownership)."""
+    numel = 1
+    for s in shape:
+        numel *= s
+    itemsize = torch.empty((), dtype=dtype).element_size()
+
+    class _Holder:
+        pass
+
+    holder = _Holder()
+    holder.__cuda_array_interface__ = {
+        "shape": (numel * itemsize,), "typestr": "|u1", "data": (address, False), "version": 3}
+    flat = torch.as_tensor(holder, device=device)
+    return flat.view(dtype).view(shape)
+
+
+class ExpertParallelEngine:
+    """The exchange protocol of one rank.  `stages` provides dispatch / experts / shared /
+    combine plus recv_buffer / back_buffer; tensors may live on any device the process
+    group's backend can move (CUDA with NCCL, CPU with gloo)."""
+
+    def __init__(self, stages, group=None):
+        self.stages = stages
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.last_send_splits: List[int] = []
+        self.last_recv_splits: List[int] = []
+
+    def step(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        st = self.stages
+        send_records, send_counts = st.dispatch(x)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        st.shared()
+        # the split sizes of the variable-size exchange must be known on the host
+        both = torch.stack([send_counts, recv_counts]).cpu()
+        send_splits = [int(v) for v in both[0]]
+        recv_splits = [int(v) for v in both[1]]
+        if min(send_splits + recv_splits) < 0 or sum(send_splits) != send_records.shape[0]:
+            raise RuntimeError(f"rank {self.rank}: inconsistent dispatch counts {send_splits}")
+        n_recv = sum(recv_splits)
+        recv = st.recv_buffer(n_recv)
+        dist.all_to_all_single(recv, send_records, recv_splits, send_splits, group=self.group)
+        rows = st.experts(recv, n_recv)
+        back = st.back_buffer(sum(send_splits))
+        dist.all_to_all_single(back, rows, send_splits, recv_splits, group=self.group)
+        st.combine(x, back, out)
+        self.last_send_splits, self.last_recv_splits = send_splits, recv_splits
+
+
+def shard_bindings(bindings: ExpertLayerBindings, rank: int, world: int) -> ExpertLayerBindings:
+    """The bindings of rank `rank`: its slice of the routed experts, everything else shared."""
+    per_rank = len(bindings.routed_experts) // world
+    return ExpertLayerBindings(
+        input_norm_weight=bindings.input_norm_weight, gate_weight=bindings.gate_weight,
+        gate_score_correction_bias=bindings.gate_score_correction_bias,
+        shared_up=bindings.shared_up, shared_down=bindings.shared_down,
+        routed_experts=bindings.routed_experts[rank * per_rank:(rank + 1) * per_rank],
+        gate_logit_offset=bindings.gate_logit_offset, first_local_expert=rank * per_rank)
+
+
+def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_module):
+    """bench.py's N > 1 arm: T tokens in total, T / N per rank, experts split over the ranks."""
+    import numpy as np
+    rank, world = dist_module.get_rank(), dist_module.get_world_size()
+    tokens_total = args.tokens
+    tokens = tokens_total // world
+    H = synthetic.HIDDEN
+    cfg = synthetic.baseline_config(max_tokens=tokens)
+    cfg.max_recv_pairs = int(1.5 * tokens * cfg.top_k) + 1024
+    data = synthetic.make_layer(cfg, seed=4000, device="cuda")
+    stages = DeviceStages(cfg, shard_bindings(data.bindings, rank, world), rank, world)
+    del data
+    torch.cuda.empty_cache()
+    engine = ExpertParallelEngine(stages)
+    x_all = synthetic.make_tokens(tokens_total, H, seed=4001)
+    x_host = x_all[rank * tokens:(rank + 1) * tokens].contiguous().pin_memory()
+    x = x_host.cuda()
+    out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+    out_host = torch.empty((tokens, H), dtype=torch.bfloat16).pin_memory()
+
+    def timed(step_fn, steps, warmup):
+        for _ in range(warmup):
+            step_fn()
+        torch.cuda.synchronize()
+        dist_module.barrier()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(steps):
+            flush_buf.add_(1)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            step_fn()
+            end.record()
+            end.synchronize()
+            total += start.elapsed_time(end)
+        torch.cuda.synchronize()
+        dist_module.barrier()
+        t = torch.tensor([total / steps], device="cuda")
+        dist_module.all_reduce(t, op=dist_module.ReduceOp.MAX)
+        return float(t.item())
+
+    ClockSampler, FLOP_PER_TOKEN_TENSOR, METRIC = (bench_module.ClockSampler,
+                                                   bench_module.FLOP_PER_TOKEN_TENSOR,
+                                                   bench_module.METRIC)
+    sampler = ClockSampler(torch.cuda.current_device())
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda: engine.step(x, out), args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    status = stages.sync_status()
+    if status != NMOE_OK:
+        raise SystemExit(f"rank {rank}: device error {status}")
+
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        engine.step(x, out)
+        out_host.copy_(out, non_blocking=True)
+
+    e2e_ms = timed(e2e_step, args.steps, args.warmup)
+    sent = sum(engine.last_send_splits) - engine.last_send_splits[rank]
+    return {
+        "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"configs[3]: T={tokens_total} tokens, uniform routing, hidden 2688, "
+                               f"128 experts x 1856 top-6 ({128 // world} per GPU), shared 3712 "
+                               "replicated, bf16 in/out",
+                   "global_tokens": tokens_total, "parallelism": f"ep{world}",
+                   "dispatch": f"NVFP4 records, {stages.record_bytes} B per pair, NCCL all-to-all-v",
+                   "return": "bf16 rows, NCCL all-to-all-v",
+                   "l2": "256 MB buffer written between timed steps; working set > L2"},
+        "layer_tflops": tokens_total * FLOP_PER_TOKEN_TENSOR / (ms * 1e-3) / 1e12,
+        "e2e": {"value": tokens_total / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": x_host.numel() * 2 * world,
+                "d2h_bytes_per_step": out_host.numel() * 2 * world},
+        "gpu_launches": 13 * args.steps * world,
+        "clocks": clocks,
+        "a2a_bytes_rank0": {"dispatch": sent * stages.record_bytes, "return": sent * H * 2},
+        "roofline": None,
+    }

@@ -1,0 +1,75 @@
+"""Multi-GPU test of the expert-parallel layer (needs >= 2 GPUs, skipped otherwise): NCCL
+ranks as child processes; every rank also runs the single-device layer over all tokens and
+checks that its slice of the expert-parallel output is identical (FP32 return rows) or within
+the layer tolerance (bf16 return rows)."""
+import importlib
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import __graft_entry__ as entry
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, shape, tokens_per_rank):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        package = entry.load_package()
+        synthetic = importlib.import_module("nemotron_inference_b200.synthetic")
+        ep = importlib.import_module("nemotron_inference_b200.expert_parallel")
+        experts, hidden, routed, shared = shape
+        total = tokens_per_rank * world
+        cfg = synthetic.baseline_config(total, experts=experts, hidden=hidden, routed=routed,
+                                        shared=shared)
+        data = synthetic.make_layer(cfg, seed=31, device="cuda", norm_weight_uniform=True)
+        single = package.ExpertLayerSlice.create(cfg, data.bindings)
+        x_all = synthetic.make_tokens(total, hidden, seed=9, device="cuda")
+        expected = torch.empty((total, hidden), dtype=torch.float32, device="cuda")
+        assert single.run(x_all, expected), single.last_error
+        mine = slice(rank * tokens_per_rank, (rank + 1) * tokens_per_rank)
+        x = x_all[mine].contiguous()
+        for rows_dtype in (torch.float32, torch.bfloat16):
+            ep_cfg = synthetic.baseline_config(tokens_per_rank, experts=experts, hidden=hidden,
+                                               routed=routed, shared=shared)
+            ep_cfg.max_recv_pairs = total * cfg.top_k
+            stages = ep.DeviceStages(ep_cfg, ep.shard_bindings(data.bindings, rank, world), rank,
+                                     world, rows_dtype=rows_dtype)
+            engine = ep.ExpertParallelEngine(stages)
+            out = torch.empty((tokens_per_rank, hidden), dtype=torch.float32, device="cuda")
+            for _ in range(2):
+                engine.step(x, out)
+            torch.cuda.synchronize()
+            assert stages.sync_status() == 0
+            if rows_dtype == torch.float32:
+                assert torch.equal(out, expected[mine]), (out - expected[mine]).abs().max().item()
+            else:
+                assert (out - expected[mine]).abs().max().item() <= 2e-2
+            stages.layer.close()
+        single.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("tokens_per_rank", [24, 700])
+def test_expert_parallel_equals_single_device(tokens_per_rank):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    mp.spawn(_worker, args=(world, _free_port(), (32, 512, 256, 512), tokens_per_rank),
+             nprocs=world, join=True)
