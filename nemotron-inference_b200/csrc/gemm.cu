@@ -79,7 +79,8 @@ __device__ __forceinline__ void report_timeout(int32_t* error, volatile int* abo
 template <class C, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, const GemmArgs args) {
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_b_tail, const GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) &
                                              ~static_cast<uintptr_t>(1023u));
@@ -112,6 +113,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    prefetch_tensormap(&tmap_b_tail);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
@@ -148,7 +150,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             args.sfa + static_cast<size_t>(row0 >> 7) * args.k_blocks * C::SFA_BYTES;
         const uint8_t* sfb_src = args.sfb + (static_cast<size_t>(expert) * args.n_tiles + nt) *
                                                 args.k_blocks * C::SFB_BYTES;
-        const int b_row = expert * args.N + nt * C::BN;
+        // weights are stored K-block-major: [expert][k block][row][128 B], then the
+        // partial last K block as [expert][row][tail bytes]
+        const int b_row = nt * C::BN;
         for (int kb = 0; kb < args.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
             report_timeout(args.error, abort_flag);
@@ -157,7 +161,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_TX);
           tma_load_2d(sA + stage * C::A_BYTES, &tmap_a, kb * 128, row0, &full_bar[stage]);
-          tma_load_2d(sB + stage * C::B_BYTES, &tmap_b, kb * 128, b_row, &full_bar[stage]);
+          if (kb < args.kb_full) {
+            tma_load_2d(sB + stage * C::B_BYTES, &tmap_b, 0,
+                        (expert * args.kb_full + kb) * args.N + b_row, &full_bar[stage]);
+          } else {
+            tma_load_2d(sB + stage * C::B_BYTES, &tmap_b_tail, 0, expert * args.N + b_row,
+                        &full_bar[stage]);
+          }
           bulk_load(sSFA + stage * C::SFA_BYTES, sfa_src + kb * C::SFA_BYTES, C::SFA_BYTES,
                     &full_bar[stage]);
           bulk_load(sSFB + stage * C::SFB_BYTES, sfb_src + kb * C::SFB_BYTES, C::SFB_BYTES,
@@ -352,7 +362,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 template <class C>
 cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
-                       const GemmArgs& args, int num_sms, cudaStream_t stream) {
+                       const CUtensorMap& tmap_b_tail, const GemmArgs& args, int num_sms,
+                       cudaStream_t stream) {
   int grid = num_sms;
   if (args.row_tiles == nullptr) {
     const int tiles = ((args.dense_rows + 127) / 128) * args.n_tiles;
@@ -364,12 +375,12 @@ cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a, const CUtensorM
     auto kernel = grouped_gemm_kernel<C, kGemmUp>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (err != cudaSuccess) return err;
-    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, args);
+    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, tmap_b_tail, args);
   } else {
     auto kernel = grouped_gemm_kernel<C, kGemmDown>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (err != cudaSuccess) return err;
-    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, args);
+    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, tmap_b_tail, args);
   }
   return cudaGetLastError();
 }
@@ -415,7 +426,41 @@ __global__ void relayout_weight_scales_kernel(const uint8_t* __restrict__ src, i
   }
 }
 
+// [experts][N][K/2] row-major -> K-block-major: full 128-byte K blocks as
+// [expert][k block][row][128], the partial last block as [expert][row][tail_pitch].
+__global__ void relayout_weight_packed_kernel(const uint4* __restrict__ src, int experts, int N,
+                                              int row_chunks, int kb_full, int tail_pitch_chunks,
+                                              uint4* __restrict__ dst_full,
+                                              uint4* __restrict__ dst_tail, size_t chunks) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < chunks;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % row_chunks);  // 16-byte chunk inside the row
+    const size_t row = i / row_chunks;               // expert * N + n
+    const int n = static_cast<int>(row % N);
+    const size_t e = row / N;
+    const int kb = c >> 3;
+    if (kb < kb_full) {
+      dst_full[((e * kb_full + kb) * N + n) * 8 + (c & 7)] = src[i];
+    } else {
+      dst_tail[row * tail_pitch_chunks + (c - kb_full * 8)] = src[i];
+    }
+  }
+}
+
 }  // namespace
+
+cudaError_t relayout_weight_packed(const uint8_t* row_major, int experts, int N, int K,
+                                   int tail_pitch_bytes, uint8_t* full, uint8_t* tail,
+                                   cudaStream_t stream) {
+  const int row_chunks = K / 32;
+  const size_t chunks = static_cast<size_t>(experts) * N * row_chunks;
+  const int blocks = static_cast<int>(std::min<size_t>((chunks + 255) / 256, 148 * 32));
+  relayout_weight_packed_kernel<<<blocks, 256, 0, stream>>>(
+      reinterpret_cast<const uint4*>(row_major), experts, N, row_chunks, K / 256,
+      tail_pitch_bytes / 16, reinterpret_cast<uint4*>(full), reinterpret_cast<uint4*>(tail),
+      chunks);
+  return cudaGetLastError();
+}
 
 GemmVariantInfo gemm_variant_info(GemmVariant v) {
   switch (v) {
@@ -428,13 +473,13 @@ GemmVariantInfo gemm_variant_info(GemmVariant v) {
 }
 
 cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const CUtensorMap& tmap_a,
-                                const CUtensorMap& tmap_b, const GemmArgs& args, int num_sms,
-                                cudaStream_t stream) {
+                                const CUtensorMap& tmap_b, const CUtensorMap& tmap_b_tail,
+                                const GemmArgs& args, int num_sms, cudaStream_t stream) {
   switch (v) {
-    case kVariantPrefillUp: return launch_cfg<CfgPrefillUp>(mode, tmap_a, tmap_b, args, num_sms, stream);
-    case kVariantPrefillDown: return launch_cfg<CfgPrefillDown>(mode, tmap_a, tmap_b, args, num_sms, stream);
-    case kVariantDecode: return launch_cfg<CfgDecode>(mode, tmap_a, tmap_b, args, num_sms, stream);
-    case kVariantDecodeWide: return launch_cfg<CfgDecodeWide>(mode, tmap_a, tmap_b, args, num_sms, stream);
+    case kVariantPrefillUp: return launch_cfg<CfgPrefillUp>(mode, tmap_a, tmap_b, tmap_b_tail, args, num_sms, stream);
+    case kVariantPrefillDown: return launch_cfg<CfgPrefillDown>(mode, tmap_a, tmap_b, tmap_b_tail, args, num_sms, stream);
+    case kVariantDecode: return launch_cfg<CfgDecode>(mode, tmap_a, tmap_b, tmap_b_tail, args, num_sms, stream);
+    case kVariantDecodeWide: return launch_cfg<CfgDecodeWide>(mode, tmap_a, tmap_b, tmap_b_tail, args, num_sms, stream);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -30,6 +30,7 @@ struct GemmArgs {
   int32_t N = 0;         // output features per expert
   int32_t n_tiles = 0;   // ceil(N / BN)
   int32_t k_blocks = 0;  // ceil(K / 256)
+  int32_t kb_full = 0;   // K / 256: K blocks stored in the full-block weight region
   // A-side block scales, tiled: [row slot][k_blocks][2048 bytes]
   const uint8_t* sfa = nullptr;
   // weight block scales, [expert][n_tile][k_block][sfb_bytes] in the layout
@@ -76,8 +77,16 @@ struct GemmVariantInfo {
 
 GemmVariantInfo gemm_variant_info(GemmVariant v);
 cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const CUtensorMap& tmap_a,
-                                const CUtensorMap& tmap_b, const GemmArgs& args, int num_sms,
-                                cudaStream_t stream);
+                                const CUtensorMap& tmap_b, const CUtensorMap& tmap_b_tail,
+                                const GemmArgs& args, int num_sms, cudaStream_t stream);
+
+// Packed weights [experts][N][K/2] -> K-block-major (device to device): every
+// (expert, 128-byte K block) becomes a contiguous [N][128 B] panel in `full`, so a
+// weight tile of any height is ONE contiguous read; the partial last K block
+// goes to `tail` as [experts * N][tail_pitch_bytes].
+cudaError_t relayout_weight_packed(const uint8_t* row_major, int experts, int N, int K,
+                                   int tail_pitch_bytes, uint8_t* full, uint8_t* tail,
+                                   cudaStream_t stream);
 
 // Re-tile row-major E4M3 weight block scales [experts][N][K/16] into the layout
 // the GEMM variant consumes (device to device).

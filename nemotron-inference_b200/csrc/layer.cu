@@ -165,7 +165,12 @@ struct WeightStack {
   int experts = 0;
   int n = 0;  // output rows per expert
   int k = 0;  // input cols
-  DeviceBuffer packed;        // [experts][n][k/2]
+  // K-block-major packed weights: every (expert, 256-element K block) is a
+  // contiguous [n][128 B] panel, so a weight tile is one contiguous read; the
+  // partial last K block lives in `packed_tail` as [experts * n][tail_pitch].
+  DeviceBuffer packed;        // [experts][k/256][n][128]
+  DeviceBuffer packed_tail;   // [experts][n][tail_pitch]
+  int kb_full = 0;
   DeviceBuffer tensor_scale;  // [experts]
   DeviceBuffer sf_prefill;    // scale layout for the prefill tile of this projection
   DeviceBuffer sf_decode;     // scale layout for the BN=128 tiles
@@ -174,6 +179,8 @@ struct WeightStack {
   GemmVariant decode_wide_variant = kVariantDecodeWide;
   CUtensorMap map_prefill;
   CUtensorMap map_decode;
+  CUtensorMap tail_prefill;
+  CUtensorMap tail_decode;
 
   void upload(const nmoe_nvfp4_matrix* matrices, int count, int rows, int cols, bool is_up,
               const char* name, cudaStream_t stream) {
@@ -183,13 +190,14 @@ struct WeightStack {
     prefill_variant = is_up ? kVariantPrefillUp : kVariantPrefillDown;
     const size_t packed_each = static_cast<size_t>(rows) * cols / 2;
     const size_t sf_each = static_cast<size_t>(rows) * (cols / 16);
-    packed.allocate(packed_each * count);
+    DeviceBuffer row_major;
+    row_major.allocate(packed_each * count);
     tensor_scale.allocate(sizeof(float) * count);
     DeviceBuffer sf_row_major;
     sf_row_major.allocate(sf_each * count);
     for (int e = 0; e < count; ++e) {
       validate_matrix(matrices[e], rows, cols, name);
-      NMOE_CUDA(cudaMemcpyAsync(packed.as<uint8_t>() + packed_each * e, matrices[e].packed_data,
+      NMOE_CUDA(cudaMemcpyAsync(row_major.as<uint8_t>() + packed_each * e, matrices[e].packed_data,
                                 packed_each, cudaMemcpyDefault, stream));
       NMOE_CUDA(cudaMemcpyAsync(sf_row_major.as<uint8_t>() + sf_each * e,
                                 matrices[e].block_scales_data, sf_each, cudaMemcpyDefault,
@@ -205,11 +213,48 @@ struct WeightStack {
                                      pi.sfb_groups, sf_prefill.as<uint8_t>(), stream));
     NMOE_CUDA(relayout_weight_scales(sf_row_major.as<uint8_t>(), count, rows, cols, di.bn,
                                      di.sfb_groups, sf_decode.as<uint8_t>(), stream));
-    NMOE_CUDA(cudaStreamSynchronize(stream));  // sf_row_major dies here
-    map_prefill = make_packed_map(packed.as<uint8_t>(), static_cast<size_t>(count) * rows,
-                                  static_cast<size_t>(cols) / 2, pi.bn);
-    map_decode = make_packed_map(packed.as<uint8_t>(), static_cast<size_t>(count) * rows,
-                                 static_cast<size_t>(cols) / 2, di.bn);
+    kb_full = cols / 256;
+    const int tail_bytes = (cols % 256) / 2;
+    const size_t panel_rows = static_cast<size_t>(count) * rows;
+    packed.allocate(panel_rows * kb_full * 128);
+    // The tail map reads `tail_bytes` per row and lets TMA zero-fill the rest of
+    // the 128-byte box; if the driver refuses a box wider than the tensor, the
+    // tail rows are padded to 128 bytes instead.
+    int tail_pitch = tail_bytes;
+    bool narrow_tail = tail_bytes > 0;
+    if (narrow_tail) {
+      packed_tail.allocate(panel_rows * tail_pitch);
+      try {
+        tail_prefill = make_packed_map(packed_tail.as<uint8_t>(), panel_rows, tail_pitch, pi.bn);
+        tail_decode = make_packed_map(packed_tail.as<uint8_t>(), panel_rows, tail_pitch, di.bn);
+      } catch (const Failure&) {
+        narrow_tail = false;
+      }
+    }
+    if (!narrow_tail && tail_bytes > 0) {
+      tail_pitch = 128;
+      packed_tail.allocate(panel_rows * tail_pitch, true);
+      tail_prefill = make_packed_map(packed_tail.as<uint8_t>(), panel_rows, tail_pitch, pi.bn);
+      tail_decode = make_packed_map(packed_tail.as<uint8_t>(), panel_rows, tail_pitch, di.bn);
+    }
+    if (tail_bytes == 0) {
+      tail_pitch = 16;
+      packed_tail.allocate(16);
+    }
+    NMOE_CUDA(relayout_weight_packed(row_major.as<uint8_t>(), count, rows, cols, tail_pitch,
+                                     packed.as<uint8_t>(), packed_tail.as<uint8_t>(), stream));
+    NMOE_CUDA(cudaStreamSynchronize(stream));  // the row-major staging copies die here
+    if (kb_full > 0) {
+      map_prefill = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, pi.bn);
+      map_decode = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, di.bn);
+    } else {
+      map_prefill = tail_prefill;
+      map_decode = tail_decode;
+    }
+    if (tail_bytes == 0) {  // never read: k_blocks == kb_full
+      tail_prefill = map_prefill;
+      tail_decode = map_decode;
+    }
   }
 
   GemmVariant variant(TileClass c) const {
@@ -217,6 +262,9 @@ struct WeightStack {
                               : c == kClassDecode ? decode_variant : decode_wide_variant;
   }
   const CUtensorMap& map(TileClass c) const { return c == kClassPrefill ? map_prefill : map_decode; }
+  const CUtensorMap& tail_map(TileClass c) const {
+    return c == kClassPrefill ? tail_prefill : tail_decode;
+  }
   const uint8_t* sf(TileClass c) const {
     return (c == kClassPrefill ? sf_prefill : sf_decode).as<uint8_t>();
   }
@@ -257,6 +305,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   g.N = up.n;
   g.n_tiles = (up.n + gemm_variant_info(up_variant).bn - 1) / gemm_variant_info(up_variant).bn;
   g.k_blocks = k_blocks_of(up.k);
+  g.kb_full = up.kb_full;
   g.sfa = a.sf_tiled;
   g.sfb = up.sf(tile_class);
   g.a_tensor_scale = a_tensor_scale;
@@ -268,8 +317,8 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   g.out_sf = hidden_sf;
   g.out_k_blocks = k_blocks_of(up.n);
   g.error = error;
-  NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, a.map(tile_class), up.map(tile_class), g,
-                                num_sms, stream));
+  NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, a.map(tile_class), up.map(tile_class),
+                                up.tail_map(tile_class), g, num_sms, stream));
 
   if (between != nullptr) cudaEventRecord(between, stream);
 
@@ -279,6 +328,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   d.N = down.n;
   d.n_tiles = (down.n + gemm_variant_info(down_variant).bn - 1) / gemm_variant_info(down_variant).bn;
   d.k_blocks = k_blocks_of(down.k);
+  d.kb_full = down.kb_full;
   d.sfa = hidden.sf_tiled;
   d.sfb = down.sf(tile_class);
   d.a_tensor_scale = nullptr;  // the fused quantiser always uses tensor scale 1
@@ -294,7 +344,8 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   d.row_weight = row_weight;
   d.error = error;
   NMOE_CUDA(launch_grouped_gemm(down_variant, kGemmDown, hidden.map(tile_class),
-                                down.map(tile_class), d, num_sms, stream));
+                                down.map(tile_class), down.tail_map(tile_class), d, num_sms,
+                                stream));
 }
 
 nmoe_status status_from_device(int code) {

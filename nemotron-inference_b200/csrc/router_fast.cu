@@ -282,9 +282,12 @@ router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__
   }
   __syncwarp();
 
-  // FP64 logits of the candidates, eight at a time; lanes split the hidden dimension
+  // FP64 logits of the candidates, up to eight at a time; every lane takes
+  // eight consecutive hidden elements per step (16-byte gate loads)
   const float* y = normalized + static_cast<size_t>(row) * hidden;
+  const int chunks = hidden / 8;
   for (int base = 0; base < total; base += 8) {
+    const int batch = min(8, total - base);
     int e[8];
     double acc[8];
 #pragma unroll
@@ -292,23 +295,36 @@ router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__
       e[i] = candidate_list[warp][min(base + i, total - 1)];
       acc[i] = 0.0;
     }
-    for (int k = lane; k < hidden; k += 32) {
-      const double a = static_cast<double>(y[k]);
+    for (int ch = lane; ch < chunks; ch += 32) {
+      const float4 y0 = *reinterpret_cast<const float4*>(y + ch * 8);
+      const float4 y1 = *reinterpret_cast<const float4*>(y + ch * 8 + 4);
+      const double a[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        acc[i] = fma(a, static_cast<double>(__bfloat162float(gate[static_cast<size_t>(e[i]) * hidden + k])),
-                     acc[i]);
+        if (i < batch) {
+          const uint4 g = *reinterpret_cast<const uint4*>(gate + static_cast<size_t>(e[i]) * hidden +
+                                                          ch * 8);
+          const uint32_t w[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[i] = fma(a[2 * j], static_cast<double>(__uint_as_float(w[j] << 16)), acc[i]);
+            acc[i] = fma(a[2 * j + 1], static_cast<double>(__uint_as_float(w[j] & 0xffff0000u)),
+                         acc[i]);
+          }
+        }
       }
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      double v = acc[i];
+      if (i < batch) {
+        double v = acc[i];
 #pragma unroll
-      for (int stride = 16; stride > 0; stride >>= 1) v += __shfl_xor_sync(0xffffffffu, v, stride);
-      if (lane == 0 && base + i < total) {
-        float logit = static_cast<float>(v);
-        if (logit_offset != nullptr) logit = __fadd_rn(logit, logit_offset[e[i]]);
-        row_logits[e[i]] = logit;
+        for (int stride = 16; stride > 0; stride >>= 1) v += __shfl_xor_sync(0xffffffffu, v, stride);
+        if (lane == 0) {
+          float logit = static_cast<float>(v);
+          if (logit_offset != nullptr) logit = __fadd_rn(logit, logit_offset[e[i]]);
+          row_logits[e[i]] = logit;
+        }
       }
     }
   }
