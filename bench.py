@@ -284,7 +284,7 @@ def run_side_workloads(package, synthetic, layer, data, peaks, steps, warmup, fl
     counts = torch.bincount(skew_layer.trace(8192).selected_index.flatten().long(), minlength=E)
     ms = float(np.mean(times))
     tf = 8192 * FLOP_PER_TOKEN_TENSOR / (ms * 1e-3) / 1e12
-    up_tf = 8192 * K * 4 * H * I / (stages["routed_up_gemm"] * 1e-3) / 1e12
+    up_tf = 8192 * K * 2 * H * I / (stages["routed_up_gemm"] * 1e-3) / 1e12
     fp4_peak = 4 * peaks["bf16_tflops_sustained"]
     results.append({
         "workload": "configs[2] skewed prefill T=8192", "tokens_per_s": 8192 / (ms * 1e-3),
@@ -366,7 +366,7 @@ def main():
     e2e_ms = float(np.mean(e2e_times))
     stages = stage_profile(layer, x, out, max(3, args.steps // 2), flush_buf)
 
-    up_flops = tokens * K * 4 * H * I
+    up_flops = tokens * K * 2 * H * I  # one GEMM: 2 * M * N * K
     up_tf = up_flops / (stages["routed_up_gemm"] * 1e-3) / 1e12
     fp4_peak = 4 * peaks["bf16_tflops_sustained"]
     line = {

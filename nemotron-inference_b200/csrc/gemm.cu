@@ -24,6 +24,7 @@
 // tile's columns).  Every mbarrier
 // wait is bounded; on a timeout the CTA records kDevWaitTimeout and unwinds.
 #include <algorithm>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -35,8 +36,11 @@ constexpr int kEpilogueWarps = 8;
 constexpr int kGemmThreads = (2 + kEpilogueWarps) * 32;
 constexpr int kStageStride = 20;  // floats per staged row: 16 + 4 keeps float4 stores conflict-free
 
-template <int BN_, int A_ROWS_, int SFB_GS_, int STAGES_>
+template <int BN_, int A_ROWS_, int SFB_GS_, int STAGES_, int PREFETCH_TILES_ = 0>
 struct TileCfg {
+  // HBM-bound shapes: how many of this CTA's future tiles have their weights
+  // prefetched into L2 while the current tile streams through shared memory
+  static constexpr int PREFETCH_TILES = PREFETCH_TILES_;
   static constexpr int BN = BN_;
   static constexpr int A_ROWS = A_ROWS_;
   static constexpr int SFB_GS = SFB_GS_;  // 32-row scale groups stored per K tile (multiple of 4:
@@ -48,9 +52,13 @@ struct TileCfg {
   static constexpr int SFB_BYTES = SFB_GS * 512;
   static constexpr int STAGE_TX = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int ACC_STRIDE = BN;  // TMEM columns per accumulator
+  // block scales are double-buffered in TMEM so that the copies of K block i+1
+  // do not have to wait for the MMAs of K block i to finish reading theirs
+  static constexpr int SF_BUFS = 2;
+  static constexpr int SF_BUF_COLS = 16 + 4 * SFB_GS;
   static constexpr int SFA_COL = 2 * ACC_STRIDE;
   static constexpr int SFB_COL = SFA_COL + 16;
-  static constexpr int TMEM_USED = SFB_COL + 4 * SFB_GS;
+  static constexpr int TMEM_USED = SFA_COL + SF_BUFS * SF_BUF_COLS;
   static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
   static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
   static constexpr int EPI_STAGE_BYTES = kEpilogueWarps * 32 * kStageStride * 4;
@@ -67,9 +75,9 @@ struct TileCfg {
 };
 
 using CfgPrefillUp = TileCfg<208, 128, 8, 4>;
-using CfgPrefillDown = TileCfg<224, 128, 8, 4>;
-using CfgDecode = TileCfg<128, 32, 4, 8>;
-using CfgDecodeWide = TileCfg<128, 128, 4, 5>;
+using CfgPrefillDown = TileCfg<192, 128, 8, 4>;
+using CfgDecode = TileCfg<128, 32, 4, 8, 0>;
+using CfgDecodeWide = TileCfg<128, 128, 4, 5, 0>;
 
 __device__ __forceinline__ void report_timeout(int32_t* error, volatile int* abort_flag) {
   *abort_flag = 1;
@@ -153,6 +161,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // weights are stored K-block-major: [expert][k block][row][128 B], then the
         // partial last K block as [expert][row][tail bytes]
         const int b_row = nt * C::BN;
+        if constexpr (C::PREFETCH_TILES > 0) {
+          const int ft = t + C::PREFETCH_TILES * static_cast<int>(gridDim.x);
+          if (ft < total_tiles) {
+            const int frt = ft / args.n_tiles;
+            const int fnt = ft - frt * args.n_tiles;
+            const int fe = args.row_tiles != nullptr ? args.row_tiles[frt].expert : 0;
+            const uint8_t* fsf = args.sfb + (static_cast<size_t>(fe) * args.n_tiles + fnt) *
+                                                args.k_blocks * C::SFB_BYTES;
+            bulk_prefetch(fsf, static_cast<uint32_t>(args.k_blocks * C::SFB_BYTES));
+            for (int kb = 0; kb < args.k_blocks; ++kb) {
+              if (kb < args.kb_full) {
+                tma_prefetch_2d(&tmap_b, 0, (fe * args.kb_full + kb) * args.N + fnt * C::BN);
+              } else {
+                tma_prefetch_2d(&tmap_b_tail, 0, fe * args.N + fnt * C::BN);
+              }
+            }
+          }
+        }
         for (int kb = 0; kb < args.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
             report_timeout(args.error, abort_flag);
@@ -186,6 +212,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
+      int sf_buf = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
         const int acc = local & 1;
@@ -207,22 +234,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t b_addr = smem_u32(sB + stage * C::B_BYTES);
           const uint32_t sfa_addr = smem_u32(sSFA + stage * C::SFA_BYTES);
           const uint32_t sfb_addr = smem_u32(sSFB + stage * C::SFB_BYTES);
+          const uint32_t sf_tmem = tmem_base + sf_buf * C::SF_BUF_COLS;
+          sf_buf ^= 1;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            tcgen05_cp_32x128b_warpx4(tmem_base + C::SFA_COL + 4 * c,
+            tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFA_COL + 4 * c,
                                       make_smem_desc(sfa_addr + c * 512, 0, 128, 0));
           }
 #pragma unroll
           for (int c = 0; c < C::SFB_GS; ++c) {
-            tcgen05_cp_32x128b_warpx4(tmem_base + C::SFB_COL + 4 * c,
+            tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFB_COL + 4 * c,
                                       make_smem_desc(sfb_addr + c * 512, 0, 128, 0));
           }
           const int kt_count = min(4, k_mmas - kb * 4);
           for (int kt = 0; kt < kt_count; ++kt) {
             tcgen05_mma_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
                              make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
-                             tmem_base + C::SFA_COL + 4 * kt,
-                             tmem_base + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
+                             sf_tmem + C::SFA_COL + 4 * kt,
+                             sf_tmem + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
           }
           tcgen05_commit(&empty_bar[stage]);
           if (++stage == C::STAGES) {

@@ -71,31 +71,42 @@ class DeviceStages:
         send_counts = _as_tensor(counts.value, (self.world,), torch.int32, self.device)
         return send_records, send_counts
 
-    def experts(self, recv_records: torch.Tensor, count: int) -> torch.Tensor:
-        _check(load_library().nmoe_ep_experts(self.layer._handle, _stream(),
-                                              recv_records.data_ptr(), count,
-                                              self.rows_out.data_ptr(),
-                                              _dtype_code(self.rows_out)),
-               "nmoe_ep_experts", self.layer._last_error())
-        return self.rows_out[:count]
+    def experts(self, recv_records: torch.Tensor, count: int, row_offset: int = 0) -> torch.Tensor:
+        """Local experts over `count` records; row i of the result belongs to record i."""
+        out = self.rows_out[row_offset:row_offset + count]
+        if count > 0:
+            _check(load_library().nmoe_ep_experts(self.layer._handle, _stream(),
+                                                  recv_records.data_ptr(), count, out.data_ptr(),
+                                                  _dtype_code(self.rows_out)),
+                   "nmoe_ep_experts", self.layer._last_error())
+        return out
 
     def shared(self) -> None:
-        """Shared expert on a side stream, ordered after the dispatch stage."""
-        ready = torch.cuda.Event()
-        ready.record()
-        with torch.cuda.stream(self.side_stream):
-            self.side_stream.wait_event(ready)
-            _check(load_library().nmoe_ep_shared(self.layer._handle, _stream()),
-                   "nmoe_ep_shared", self.layer._last_error())
-            self._shared_done = torch.cuda.Event()
-            self._shared_done.record()
+        """Shared expert over the tokens of the last dispatch, on the compute stream: it keeps
+        the GPU busy while the host waits for the split sizes and the records travel."""
+        _check(load_library().nmoe_ep_shared(self.layer._handle, _stream()),
+               "nmoe_ep_shared", self.layer._last_error())
 
     def combine(self, x: torch.Tensor, rows_back: torch.Tensor, out: torch.Tensor) -> None:
-        torch.cuda.current_stream().wait_event(self._shared_done)
         _check(load_library().nmoe_ep_combine(self.layer._handle, _stream(), x.data_ptr(),
                                               _dtype_code(x), rows_back.data_ptr(),
                                               _dtype_code(rows_back), out.data_ptr(),
                                               _dtype_code(out)), "nmoe_ep_combine")
+
+    # -- stream hooks: collectives are issued from a communication stream so that they
+    #    depend only on the kernels that produce their inputs
+    def comm_stream(self):
+        return torch.cuda.stream(self.side_stream)
+
+    def main_to_comm(self) -> None:
+        event = torch.cuda.Event()
+        event.record()
+        self.side_stream.wait_event(event)
+
+    def comm_to_main(self) -> None:
+        event = torch.cuda.Event()
+        event.record(self.side_stream)
+        torch.cuda.current_stream().wait_event(event)
 
     def recv_buffer(self, count: int) -> torch.Tensor:
         if count > self.capacity:
@@ -132,32 +143,51 @@ class ExpertParallelEngine:
     combine plus recv_buffer / back_buffer; tensors may live on any device the process
     group's backend can move (CUDA with NCCL, CPU with gloo)."""
 
-    def __init__(self, stages, group=None):
+    def __init__(self, stages, group=None, chunks: Optional[int] = None):
         self.stages = stages
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
+        self.chunks = max(1, min(chunks if chunks is not None else 2, self.world))
         self.last_send_splits: List[int] = []
         self.last_recv_splits: List[int] = []
 
     def step(self, x: torch.Tensor, out: torch.Tensor) -> None:
         st = self.stages
         send_records, send_counts = st.dispatch(x)
-        recv_counts = torch.empty_like(send_counts)
-        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        st.shared()
-        # the split sizes of the variable-size exchange must be known on the host
-        both = torch.stack([send_counts, recv_counts]).cpu()
-        send_splits = [int(v) for v in both[0]]
-        recv_splits = [int(v) for v in both[1]]
-        if min(send_splits + recv_splits) < 0 or sum(send_splits) != send_records.shape[0]:
-            raise RuntimeError(f"rank {self.rank}: inconsistent dispatch counts {send_splits}")
-        n_recv = sum(recv_splits)
-        recv = st.recv_buffer(n_recv)
-        dist.all_to_all_single(recv, send_records, recv_splits, send_splits, group=self.group)
-        rows = st.experts(recv, n_recv)
+        st.main_to_comm()
+        st.shared()  # overlaps the host's wait for the split sizes and the dispatch exchange
+        with st.comm_stream():
+            recv_counts = torch.empty_like(send_counts)
+            dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+            # the split sizes of the variable-size exchange must be known on the host
+            both = torch.stack([send_counts, recv_counts]).cpu()
+            send_splits = [int(v) for v in both[0]]
+            recv_splits = [int(v) for v in both[1]]
+            if min(send_splits + recv_splits) < 0 or sum(send_splits) != send_records.shape[0]:
+                raise RuntimeError(f"rank {self.rank}: inconsistent dispatch counts {send_splits}")
+            recv = st.recv_buffer(sum(recv_splits))
+            dist.all_to_all_single(recv, send_records, recv_splits, send_splits, group=self.group)
+        st.comm_to_main()
         back = st.back_buffer(sum(send_splits))
-        dist.all_to_all_single(back, rows, send_splits, recv_splits, group=self.group)
+        # Source ranks are served in contiguous groups: while one group's rows travel home,
+        # the next group's records are being computed.
+        bounds = [self.world * c // self.chunks for c in range(self.chunks + 1)]
+        row_offset = 0
+        for c in range(self.chunks):
+            lo, hi = bounds[c], bounds[c + 1]
+            count = sum(recv_splits[lo:hi])
+            rows = st.experts(recv[row_offset:row_offset + count], count, row_offset)
+            st.main_to_comm()
+            with st.comm_stream():
+                in_splits = [recv_splits[r] if lo <= r < hi else 0 for r in range(self.world)]
+                if lo <= self.rank < hi:
+                    dist.all_to_all_single(back, rows, send_splits, in_splits, group=self.group)
+                else:
+                    dist.all_to_all_single(back[:0], rows, [0] * self.world, in_splits,
+                                           group=self.group)
+            row_offset += count
+        st.comm_to_main()
         st.combine(x, back, out)
         self.last_send_splits, self.last_recv_splits = send_splits, recv_splits
 

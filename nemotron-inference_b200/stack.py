@@ -1,0 +1,48 @@
+"""A stack of MoE expert layers applied back to back (the MoE path of the model's layer
+loop, runtime/src/api/single_token_forward_model.cpp:588-656: the caller hands each
+layer's FP32 output to the next and swaps `current` / `next`).  Every layer carries its
+own input RMSNorm and residual add, so the stack is layer(layer(...layer(x))).
+
+Works over single-device layers (`ExpertLayerSlice`) and over expert-parallel engines
+(`ExpertParallelEngine`): both expose "run x -> out" on device buffers.  The hidden state
+stays on the device in FP32 between layers; nothing synchronises with the host except the
+split-size exchange inside an expert-parallel step.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+
+class MoeLayerStack:
+    def __init__(self, layers: Sequence, hidden_size: int, max_tokens: int, device=None):
+        self.layers = list(layers)
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        self._ping = torch.empty((max_tokens, hidden_size), dtype=torch.float32, device=device)
+        self._pong = torch.empty((max_tokens, hidden_size), dtype=torch.float32, device=device)
+
+    @staticmethod
+    def _run_one(layer, x: torch.Tensor, out: torch.Tensor) -> None:
+        if hasattr(layer, "step"):      # ExpertParallelEngine
+            layer.step(x, out)
+        else:                           # ExpertLayerSlice
+            layer.run_async(x, out)
+
+    def run(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        """x: [tokens, hidden] bf16 or FP32; out: same shape, bf16 or FP32 (may not alias x)."""
+        tokens = x.shape[0]
+        current = x
+        buffers = [self._ping[:tokens], self._pong[:tokens]]
+        for index, layer in enumerate(self.layers):
+            last = index == len(self.layers) - 1
+            target = out if last else buffers[index % 2]
+            self._run_one(layer, current, target)
+            current = target
+
+    def sync_status(self) -> int:
+        status = 0
+        for layer in self.layers:
+            owner = layer.stages if hasattr(layer, "stages") else layer
+            status = status or owner.sync_status()
+        return status

@@ -71,7 +71,18 @@ class NumpyStages:
                 self.position[t, k] = pos
         return torch.from_numpy(records), torch.from_numpy(counts)
 
-    def experts(self, recv, count):
+    # no streams on the CPU: the hooks of the device implementation are no-ops here
+    def comm_stream(self):
+        import contextlib
+        return contextlib.nullcontext()
+
+    def main_to_comm(self):
+        pass
+
+    def comm_to_main(self):
+        pass
+
+    def experts(self, recv, count, row_offset=0):
         o, H = self.oracle, self.cfg.hidden
         recs = recv.numpy()
         out = np.zeros((count, H), dtype=np.float32)
