@@ -159,7 +159,7 @@ def cpu_baseline_port(layer_data, cfg, sample_tokens, seed):
                       f"expert), restructured bit-identical host path, gcc -O2 -ffp-contract=off"}
 
 
-def run_reference_arm(args):
+def run_reference_arm(args, real_stdout):
     """Times the reference's own host implementation (literal per-token loop of
     ExpertLayerSlice::Run built from the reference's functions) on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -185,7 +185,7 @@ def run_reference_arm(args):
                 "data": "synthetic", "config": workload, "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        print(json.dumps(line), file=real_stdout, flush=True)
         return
     tokens_per_proc = 1
     sample = cores * tokens_per_proc
@@ -244,7 +244,7 @@ def run_reference_arm(args):
             "reference_equals_port": bool(np.array_equal(ref_out, port_out)),
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
                     "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    print(json.dumps(line), file=real_stdout, flush=True)
 
 
 def run_side_workloads(package, synthetic, layer, data, peaks, steps, warmup, flush_buf):
@@ -298,7 +298,17 @@ def run_side_workloads(package, synthetic, layer, data, peaks, steps, warmup, fl
     return results
 
 
+def _claim_stdout():
+    """Keeps the real stdout for the single JSON line and points file descriptor 1 at
+    stderr, so that libraries that print banners from native code cannot add lines."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
+
+
 def main():
+    real_stdout = _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -311,7 +321,7 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     if args.impl == "reference":
-        run_reference_arm(args)
+        run_reference_arm(args, real_stdout)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -332,7 +342,7 @@ def main():
         ep = importlib.import_module("nemotron_inference_b200.expert_parallel")
         line = ep.bench_main(args, package, synthetic, peaks, flush_buf, dist, sys.modules[__name__])
         if rank == 0:
-            print(json.dumps(line))
+            print(json.dumps(line), file=real_stdout, flush=True)
         dist.destroy_process_group()
         return
 
@@ -398,7 +408,7 @@ def main():
                                           max(5, args.steps), args.warmup, flush_buf)
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline_port(data, cfg, 1024, seed=4001)
-    print(json.dumps(line))
+    print(json.dumps(line), file=real_stdout, flush=True)
 
 
 if __name__ == "__main__":

@@ -204,13 +204,26 @@ NMOE_API nmoe_status nmoe_layer_export_hidden(nmoe_layer* layer, void* stream,
  *   nmoe_ep_combine    output = input + (sum of the returned rows of each token
  *                      in selection order + shared).  returned_rows holds one
  *                      row per pair in the order the records were sent.
+ *
+ * Two record layouts.  capacity_per_rank == 0: records are compact, grouped by
+ * destination rank, and the host must read the counts to size the exchange.
+ * capacity_per_rank > 0: destination rank r owns the fixed segment
+ * [r*capacity, (r+1)*capacity) of the send buffer, so every exchange has equal,
+ * host-known splits and a step needs no host synchronisation (it can be recorded
+ * once and replayed); the receiver passes the device counts it received
+ * (valid_counts[source rank]) and count = world*capacity slots, and returns rows
+ * in the same segmented layout.  A destination that would get more than
+ * `capacity` pairs sets NMOE_ERR_CAPACITY (reported by nmoe_layer_sync_status).
  */
 NMOE_API size_t nmoe_ep_record_bytes(const nmoe_layer* layer);
 NMOE_API nmoe_status nmoe_ep_dispatch(nmoe_layer* layer, void* stream, const void* input,
                                       nmoe_dtype input_dtype, int64_t tokens,
-                                      const void** send_records, const int32_t** send_counts);
+                                      int64_t capacity_per_rank, const void** send_records,
+                                      const int32_t** send_counts);
 NMOE_API nmoe_status nmoe_ep_experts(nmoe_layer* layer, void* stream, const void* recv_records,
-                                     int64_t count, void* out_rows, nmoe_dtype rows_dtype);
+                                     int64_t count, const int32_t* valid_counts,
+                                     int64_t capacity_per_rank, void* out_rows,
+                                     nmoe_dtype rows_dtype);
 NMOE_API nmoe_status nmoe_ep_shared(nmoe_layer* layer, void* stream);
 NMOE_API nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream, const void* input,
                                      nmoe_dtype input_dtype, const void* returned_rows,

@@ -135,9 +135,9 @@ def load_library() -> ctypes.CDLL:
     lib.nmoe_router_topk.argtypes = [vp, vp, vp, i64, i32, i32, i32, i32, i32, f32, vp, vp]
     lib.nmoe_ep_record_bytes.argtypes = [vp]
     lib.nmoe_ep_record_bytes.restype = ctypes.c_size_t
-    lib.nmoe_ep_dispatch.argtypes = [vp, vp, vp, ctypes.c_int, i64, ctypes.POINTER(vp),
+    lib.nmoe_ep_dispatch.argtypes = [vp, vp, vp, ctypes.c_int, i64, i64, ctypes.POINTER(vp),
                                      ctypes.POINTER(vp)]
-    lib.nmoe_ep_experts.argtypes = [vp, vp, vp, i64, vp, ctypes.c_int]
+    lib.nmoe_ep_experts.argtypes = [vp, vp, vp, i64, vp, i64, vp, ctypes.c_int]
     lib.nmoe_ep_shared.argtypes = [vp, vp]
     lib.nmoe_ep_combine.argtypes = [vp, vp, vp, ctypes.c_int, vp, ctypes.c_int, vp, ctypes.c_int]
     lib.nmoe_route_tokens_noalloc.argtypes = [vp, vp, ctypes.c_int, i64, i32, vp, f32, vp, vp, i32,

@@ -55,7 +55,8 @@ pack_records_kernel(const int32_t* __restrict__ top_index, const float* __restri
                     const uint8_t* __restrict__ packed, const uint8_t* __restrict__ sf_row_major,
                     const float* __restrict__ tensor_scale, int cols, int record_bytes,
                     const int32_t* __restrict__ send_offsets, int32_t* __restrict__ rank_cursor,
-                    uint8_t* __restrict__ records, int32_t* __restrict__ send_position) {
+                    int capacity, uint8_t* __restrict__ records,
+                    int32_t* __restrict__ send_position, int32_t* __restrict__ error) {
   const int lane = threadIdx.x & 31;
   const int pair = blockIdx.x * kPackWarps + (threadIdx.x >> 5);
   if (pair >= pairs) return;
@@ -63,8 +64,21 @@ pack_records_kernel(const int32_t* __restrict__ top_index, const float* __restri
   const int expert = top_index[pair];
   const int rank = expert / experts_per_rank;
   int position = 0;
-  if (lane == 0) position = send_offsets[rank] + atomicAdd(&rank_cursor[rank], 1);
+  if (lane == 0) {
+    const int slot = atomicAdd(&rank_cursor[rank], 1);
+    if (capacity > 0) {
+      // fixed-capacity layout: destination rank r owns records [r*capacity, (r+1)*capacity)
+      position = slot < capacity ? rank * capacity + slot : -1;
+      if (position < 0 && error != nullptr) atomicCAS(error, kDevOk, kDevPlanOverflow);
+    } else {
+      position = send_offsets[rank] + slot;
+    }
+  }
   position = __shfl_sync(0xffffffffu, position, 0);
+  if (position < 0) {
+    if (lane == 0) send_position[pair] = 0;
+    return;
+  }
   uint8_t* record = records + static_cast<size_t>(position) * record_bytes;
   const int packed_words = cols / 8;
   const uint32_t* src = reinterpret_cast<const uint32_t*>(packed) + static_cast<size_t>(token) * packed_words;
@@ -86,9 +100,13 @@ pack_records_kernel(const int32_t* __restrict__ top_index, const float* __restri
 
 __global__ void record_histogram_kernel(const uint8_t* __restrict__ records, int count,
                                         int record_bytes, int expert_offset, int local_experts,
+                                        const int32_t* __restrict__ valid_counts, int capacity,
                                         int32_t* __restrict__ expert_counts,
                                         int32_t* __restrict__ error) {
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) {
+    if (valid_counts != nullptr && (i % capacity) >= min(valid_counts[i / capacity], capacity)) {
+      continue;  // an unused slot of a fixed-capacity segment
+    }
     const int e = *reinterpret_cast<const int32_t*>(
         records + static_cast<size_t>(i) * record_bytes + expert_offset);
     if (e >= 0 && e < local_experts) {
@@ -191,24 +209,27 @@ cudaError_t launch_dispatch_plan(const int32_t* expert_counts, int experts, int 
 cudaError_t launch_pack_records(const int32_t* top_index, const float* top_weight, int rows,
                                 int top_k, int experts_per_rank, const uint8_t* packed,
                                 const uint8_t* sf_row_major, const float* tensor_scale, int cols,
-                                const int32_t* send_offsets, int32_t* rank_cursor,
-                                uint8_t* records, int32_t* send_position, cudaStream_t stream) {
+                                const int32_t* send_offsets, int32_t* rank_cursor, int capacity,
+                                uint8_t* records, int32_t* send_position, int32_t* error,
+                                cudaStream_t stream) {
   const int pairs = rows * top_k;
   if (pairs <= 0 || cols % 64 != 0) return cudaErrorInvalidValue;
   pack_records_kernel<<<(pairs + kPackWarps - 1) / kPackWarps, kPackWarps * 32, 0, stream>>>(
       top_index, top_weight, pairs, top_k, experts_per_rank, packed, sf_row_major, tensor_scale,
-      cols, dispatch_record_bytes(cols), send_offsets, rank_cursor, records, send_position);
+      cols, dispatch_record_bytes(cols), send_offsets, rank_cursor, capacity, records,
+      send_position, error);
   return cudaGetLastError();
 }
 
 cudaError_t launch_record_histogram(const uint8_t* records, int count, int cols,
-                                    int local_experts, int32_t* expert_counts, int32_t* error,
-                                    cudaStream_t stream) {
+                                    int local_experts, const int32_t* valid_counts, int capacity,
+                                    int32_t* expert_counts, int32_t* error, cudaStream_t stream) {
   if (count <= 0) return cudaSuccess;
   const int blocks = (count + 255) / 256 < 592 ? (count + 255) / 256 : 592;
   record_histogram_kernel<<<blocks, 256, 0, stream>>>(records, count, dispatch_record_bytes(cols),
                                                       cols / 2 + cols / 16 + 8, local_experts,
-                                                      expert_counts, error);
+                                                      valid_counts, capacity, expert_counts,
+                                                      error);
   return cudaGetLastError();
 }
 

@@ -171,6 +171,10 @@ struct PermuteSource {
   const int32_t* expert;  // index into the LOCAL expert stack
   size_t expert_stride;
   int pairs_per_row;
+  // fixed-capacity receive buffers: pair i is valid iff (i % capacity) <
+  // valid_counts[i / capacity]; nullptr = every pair is valid
+  const int32_t* valid_counts = nullptr;
+  int capacity = 0;
 };
 // Copies each pair's quantised activation row into its expert's row slots and
 // records where it went; sorted_dest[row] = source_row * dest_stride + slot.
@@ -189,10 +193,12 @@ cudaError_t launch_pack_records(const int32_t* top_index, const float* top_weigh
                                 int top_k, int experts_per_rank, const uint8_t* packed,
                                 const uint8_t* sf_row_major, const float* tensor_scale, int cols,
                                 const int32_t* send_offsets, int32_t* rank_cursor,
-                                uint8_t* records, int32_t* send_position, cudaStream_t stream);
+                                int capacity /* per destination rank, 0 = compact */,
+                                uint8_t* records, int32_t* send_position, int32_t* error,
+                                cudaStream_t stream);
 cudaError_t launch_record_histogram(const uint8_t* records, int count, int cols,
-                                    int local_experts, int32_t* expert_counts, int32_t* error,
-                                    cudaStream_t stream);
+                                    int local_experts, const int32_t* valid_counts, int capacity,
+                                    int32_t* expert_counts, int32_t* error, cudaStream_t stream);
 cudaError_t launch_combine_indexed(const void* in, bool in_bf16, const void* returned_rows,
                                    bool rows_bf16, const int32_t* position,
                                    const float* shared_rows, int rows, int hidden, int top_k,

@@ -591,6 +591,7 @@ struct nmoe_layer {
   int ep_world = 1;
   int ep_rank = 0;
   int64_t max_pairs = 0;
+  int64_t send_record_slots = 0;
   int record_bytes = 0;
   DeviceBuffer send_records, send_position, send_counts, send_offsets, rank_cursor, shared_out;
 
@@ -714,7 +715,9 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
   L->pair_row.allocate(pairs * sizeof(int32_t), true);
   if (L->ep_world > 1) {
     L->record_bytes = dispatch_record_bytes(H);
-    L->send_records.allocate(local_pairs * L->record_bytes, true);
+    // room for the compact layout and for fixed-capacity segments up to 2x the mean
+    L->send_record_slots = static_cast<int64_t>(2 * local_pairs + 64 * 16);
+    L->send_records.allocate(static_cast<size_t>(L->send_record_slots) * L->record_bytes, true);
     L->send_position.allocate(local_pairs * sizeof(int32_t), true);
     L->send_counts.allocate(64 * sizeof(int32_t), true);
     L->send_offsets.allocate(64 * sizeof(int32_t), true);
@@ -955,13 +958,17 @@ size_t nmoe_ep_record_bytes(const nmoe_layer* layer) {
 }
 
 nmoe_status nmoe_ep_dispatch(nmoe_layer* layer, void* stream_ptr, const void* input,
-                             nmoe_dtype input_dtype, int64_t tokens, const void** send_records,
-                             const int32_t** send_counts) {
+                             nmoe_dtype input_dtype, int64_t tokens, int64_t capacity_per_rank,
+                             const void** send_records, const int32_t** send_counts) {
   if (layer == nullptr || input == nullptr || send_records == nullptr || send_counts == nullptr ||
       tokens <= 0 || layer->ep_world <= 1) {
     return NMOE_ERR_INVALID_ARGUMENT;
   }
   if (tokens > layer->cfg.max_tokens) return NMOE_ERR_CAPACITY;
+  if (capacity_per_rank < 0 ||
+      capacity_per_rank * layer->ep_world > layer->send_record_slots) {
+    return NMOE_ERR_CAPACITY;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   try {
     const nmoe_config& c = layer->cfg;
@@ -977,8 +984,10 @@ nmoe_status nmoe_ep_dispatch(nmoe_layer* layer, void* stream_ptr, const void* in
                                   layer->y_sf_row_major.as<uint8_t>(), layer->y_ts.as<float>(),
                                   c.hidden_size, layer->send_offsets.as<int32_t>(),
                                   layer->rank_cursor.as<int32_t>(),
+                                  static_cast<int>(capacity_per_rank),
                                   layer->send_records.as<uint8_t>(),
-                                  layer->send_position.as<int32_t>(), stream));
+                                  layer->send_position.as<int32_t>(),
+                                  layer->error.device.as<int32_t>(), stream));
     layer->last_tokens = static_cast<int>(tokens);
   } catch (const Failure& failure) {
     layer->last_error = failure.message;
@@ -990,13 +999,15 @@ nmoe_status nmoe_ep_dispatch(nmoe_layer* layer, void* stream_ptr, const void* in
 }
 
 nmoe_status nmoe_ep_experts(nmoe_layer* layer, void* stream_ptr, const void* recv_records,
-                            int64_t count, void* out_rows, nmoe_dtype rows_dtype) {
+                            int64_t count, const int32_t* valid_counts, int64_t capacity_per_rank,
+                            void* out_rows, nmoe_dtype rows_dtype) {
   if (layer == nullptr || layer->ep_world <= 1 || count < 0 ||
       (count > 0 && (recv_records == nullptr || out_rows == nullptr))) {
     return NMOE_ERR_INVALID_ARGUMENT;
   }
   if (count > layer->max_pairs) return NMOE_ERR_CAPACITY;
   if (count == 0) return NMOE_OK;
+  if (valid_counts != nullptr && capacity_per_rank <= 0) return NMOE_ERR_INVALID_ARGUMENT;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   try {
     const int H = layer->cfg.hidden_size;
@@ -1004,6 +1015,7 @@ nmoe_status nmoe_ep_experts(nmoe_layer* layer, void* stream_ptr, const void* rec
                               layer->local_experts * sizeof(int32_t), stream));
     NMOE_CUDA(launch_record_histogram(static_cast<const uint8_t*>(recv_records),
                                       static_cast<int>(count), H, layer->local_experts,
+                                      valid_counts, static_cast<int>(capacity_per_rank),
                                       layer->counts.as<int32_t>(),
                                       layer->error.device.as<int32_t>(), stream));
     const uint8_t* records = static_cast<const uint8_t*>(recv_records);
@@ -1021,6 +1033,8 @@ nmoe_status nmoe_ep_experts(nmoe_layer* layer, void* stream_ptr, const void* rec
     source.expert = reinterpret_cast<const int32_t*>(records + tail + 8);
     source.expert_stride = stride;
     source.pairs_per_row = 1;
+    source.valid_counts = valid_counts;
+    source.capacity = static_cast<int>(capacity_per_rank);
     routed_experts(layer, stream, source, static_cast<int>(count), 1, out_rows,
                    rows_dtype == NMOE_BF16);
   } catch (const Failure& failure) {

@@ -71,6 +71,10 @@ permute_kernel(PlanBuffers plan, PermuteSource src, int pairs, int tile_rows, in
   const int lane = threadIdx.x & 31;
   const int pair = blockIdx.x * kPermuteWarps + (threadIdx.x >> 5);
   if (pair >= pairs) return;
+  if (src.valid_counts != nullptr &&
+      (pair % src.capacity) >= min(src.valid_counts[pair / src.capacity], src.capacity)) {
+    return;  // an unused slot of a fixed-capacity segment
+  }
   const int source_row = pair / src.pairs_per_row;
   const int slot = pair - source_row * src.pairs_per_row;
   const int expert = *reinterpret_cast<const int32_t*>(

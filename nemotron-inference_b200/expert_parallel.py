@@ -35,6 +35,7 @@ class DeviceStages:
 
     def __init__(self, config: ExpertLayerConfig, bindings: ExpertLayerBindings, rank: int,
                  world: int, rows_dtype: torch.dtype = torch.bfloat16):
+        # config.max_recv_pairs bounds what this rank accepts per step in either layout
         experts_per_rank = config.n_routed_experts // world
         assert len(bindings.routed_experts) == experts_per_rank
         bindings.first_local_expert = rank * experts_per_rank
@@ -55,30 +56,39 @@ class DeviceStages:
         self.recv_records = torch.empty((self.capacity, self.record_bytes), dtype=torch.uint8,
                                         device=self.device)
         self.rows_out = torch.empty((self.capacity, H), dtype=rows_dtype, device=self.device)
-        self.rows_back = torch.empty((pairs, H), dtype=rows_dtype, device=self.device)
+        self.rows_back = torch.empty((max(pairs, self.capacity), H), dtype=rows_dtype,
+                                     device=self.device)
+        self.send_slots = 2 * pairs + 64 * 16  # what the library reserves for send records
         self.side_stream = torch.cuda.Stream()
         self._send_view = None
 
-    def dispatch(self, x: torch.Tensor):
+    def dispatch(self, x: torch.Tensor, capacity: int = 0):
+        """capacity == 0: compact records (one per pair); capacity > 0: world * capacity
+        record slots, destination rank r owning slots [r*capacity, (r+1)*capacity)."""
         lib = load_library()
         records, counts = ctypes.c_void_p(), ctypes.c_void_p()
         _check(lib.nmoe_ep_dispatch(self.layer._handle, _stream(), x.data_ptr(), _dtype_code(x),
-                                    x.shape[0], ctypes.byref(records), ctypes.byref(counts)),
+                                    x.shape[0], capacity, ctypes.byref(records),
+                                    ctypes.byref(counts)),
                "nmoe_ep_dispatch", self.layer._last_error())
-        pairs = x.shape[0] * self.config.top_k
+        pairs = capacity * self.world if capacity > 0 else x.shape[0] * self.config.top_k
         send_records = _as_tensor(records.value, (pairs, self.record_bytes), torch.uint8,
                                   self.device)
         send_counts = _as_tensor(counts.value, (self.world,), torch.int32, self.device)
         return send_records, send_counts
 
-    def experts(self, recv_records: torch.Tensor, count: int, row_offset: int = 0) -> torch.Tensor:
-        """Local experts over `count` records; row i of the result belongs to record i."""
+    def experts(self, recv_records: torch.Tensor, count: int, row_offset: int = 0,
+                valid_counts: Optional[torch.Tensor] = None, capacity: int = 0) -> torch.Tensor:
+        """Local experts over `count` record slots; row i of the result belongs to slot i.
+        With fixed-capacity segments, valid_counts[j] (device int32) says how many of the
+        `capacity` slots of segment j hold a record."""
         out = self.rows_out[row_offset:row_offset + count]
         if count > 0:
-            _check(load_library().nmoe_ep_experts(self.layer._handle, _stream(),
-                                                  recv_records.data_ptr(), count, out.data_ptr(),
-                                                  _dtype_code(self.rows_out)),
-                   "nmoe_ep_experts", self.layer._last_error())
+            _check(load_library().nmoe_ep_experts(
+                self.layer._handle, _stream(), recv_records.data_ptr(), count,
+                valid_counts.data_ptr() if valid_counts is not None else None, capacity,
+                out.data_ptr(), _dtype_code(self.rows_out)),
+                "nmoe_ep_experts", self.layer._last_error())
         return out
 
     def shared(self) -> None:
@@ -107,6 +117,11 @@ class DeviceStages:
         event = torch.cuda.Event()
         event.record(self.side_stream)
         torch.cuda.current_stream().wait_event(event)
+
+    def count_buffer(self) -> torch.Tensor:
+        if not hasattr(self, "_recv_counts"):
+            self._recv_counts = torch.zeros((self.world,), dtype=torch.int32, device=self.device)
+        return self._recv_counts
 
     def recv_buffer(self, count: int) -> torch.Tensor:
         if count > self.capacity:
@@ -143,7 +158,12 @@ class ExpertParallelEngine:
     combine plus recv_buffer / back_buffer; tensors may live on any device the process
     group's backend can move (CUDA with NCCL, CPU with gloo)."""
 
-    def __init__(self, stages, group=None, chunks: Optional[int] = None):
+    def __init__(self, stages, group=None, chunks: Optional[int] = None,
+                 capacity_per_rank: int = 0):
+        """capacity_per_rank > 0 selects fixed-capacity record segments: all exchanges
+        have equal, host-known splits, so a step never synchronises with the host."""
+        self.capacity = capacity_per_rank
+        self._graph = None
         self.stages = stages
         self.group = group
         self.rank = dist.get_rank(group)
@@ -153,6 +173,63 @@ class ExpertParallelEngine:
         self.last_recv_splits: List[int] = []
 
     def step(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        if self.capacity > 0:
+            self._step_fixed(x, out)
+        else:
+            self._step_compact(x, out)
+
+    def _step_fixed(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        st, cap, W = self.stages, self.capacity, self.world
+        send_records, send_counts = st.dispatch(x, cap)
+        st.main_to_comm()
+        st.shared()
+        with st.comm_stream():
+            recv_counts = st.count_buffer()
+            dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+            recv = st.recv_buffer(W * cap)
+            dist.all_to_all_single(recv, send_records, group=self.group)
+        st.comm_to_main()
+        back = st.back_buffer(W * cap)
+        bounds = [W * c // self.chunks for c in range(self.chunks + 1)]
+        for c in range(self.chunks):
+            lo, hi = bounds[c], bounds[c + 1]
+            rows = st.experts(recv[lo * cap:hi * cap], (hi - lo) * cap, lo * cap,
+                              recv_counts[lo:hi], cap)
+            st.main_to_comm()
+            with st.comm_stream():
+                in_splits = [cap if lo <= r < hi else 0 for r in range(W)]
+                if lo <= self.rank < hi:
+                    dist.all_to_all_single(back, rows, [cap] * W, in_splits, group=self.group)
+                else:
+                    dist.all_to_all_single(back[:0], rows, [0] * W, in_splits, group=self.group)
+        st.comm_to_main()
+        st.combine(x, back, out)
+        self.last_send_splits = self.last_recv_splits = [cap] * W
+
+    def capture(self, x: torch.Tensor, out: torch.Tensor) -> bool:
+        """Records one fixed-capacity step on (x, out) as a CUDA graph; `replay` then costs
+        one launch.  Returns False (and stays eager) if the capture is not possible."""
+        if self.capacity <= 0:
+            return False
+        try:
+            for _ in range(2):
+                self._step_fixed(x, out)  # warm up: allocations, NCCL channels
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._step_fixed(x, out)
+            self._graph = graph
+            return True
+        except Exception as error:  # noqa: BLE001 - any capture failure means "stay eager"
+            self.capture_error = str(error)
+            self._graph = None
+            torch.cuda.synchronize()
+            return False
+
+    def replay(self) -> None:
+        self._graph.replay()
+
+    def _step_compact(self, x: torch.Tensor, out: torch.Tensor) -> None:
         st = self.stages
         send_records, send_counts = st.dispatch(x)
         st.main_to_comm()
@@ -211,12 +288,15 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
     tokens = tokens_total // world
     H = synthetic.HIDDEN
     cfg = synthetic.baseline_config(max_tokens=tokens)
-    cfg.max_recv_pairs = int(1.5 * tokens * cfg.top_k) + 1024
+    # fixed record segments, 25 % above the uniform share: equal exchange splits, no host
+    # round trip, and the whole step replays as one CUDA graph
+    capacity = (int(1.25 * tokens * cfg.top_k / world) + 15) // 16 * 16
+    cfg.max_recv_pairs = capacity * world
     data = synthetic.make_layer(cfg, seed=4000, device="cuda")
     stages = DeviceStages(cfg, shard_bindings(data.bindings, rank, world), rank, world)
     del data
     torch.cuda.empty_cache()
-    engine = ExpertParallelEngine(stages)
+    engine = ExpertParallelEngine(stages, capacity_per_rank=capacity)
     x_all = synthetic.make_tokens(tokens_total, H, seed=4001)
     x_host = x_all[rank * tokens:(rank + 1) * tokens].contiguous().pin_memory()
     x = x_host.cuda()
@@ -250,7 +330,12 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
     sampler = ClockSampler(torch.cuda.current_device())
     if rank == 0:
         sampler.start()
-    ms = timed(lambda: engine.step(x, out), args.steps, args.warmup)
+    graphed = engine.capture(x, out)
+    flags = torch.tensor([1 if graphed else 0], device="cuda")
+    dist_module.all_reduce(flags, op=dist_module.ReduceOp.MIN)
+    graphed = bool(flags.item())  # every rank replays, or none does
+    run_step = engine.replay if graphed else (lambda: engine.step(x, out))
+    ms = timed(run_step, args.steps, args.warmup)
     clocks = sampler.stop() if rank == 0 else None
     status = stages.sync_status()
     if status != NMOE_OK:
@@ -258,11 +343,11 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
 
     def e2e_step():
         x.copy_(x_host, non_blocking=True)
-        engine.step(x, out)
+        run_step()
         out_host.copy_(out, non_blocking=True)
 
     e2e_ms = timed(e2e_step, args.steps, args.warmup)
-    sent = sum(engine.last_send_splits) - engine.last_send_splits[rank]
+    sent = capacity * (world - 1)
     return {
         "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -272,8 +357,10 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
                                f"128 experts x 1856 top-6 ({128 // world} per GPU), shared 3712 "
                                "replicated, bf16 in/out",
                    "global_tokens": tokens_total, "parallelism": f"ep{world}",
-                   "dispatch": f"NVFP4 records, {stages.record_bytes} B per pair, NCCL all-to-all-v",
-                   "return": "bf16 rows, NCCL all-to-all-v",
+                   "dispatch": f"NVFP4 records, {stages.record_bytes} B per pair, fixed segments of "
+                               f"{capacity} pairs per (source, destination), NCCL all-to-all",
+                   "return": "bf16 rows, same segments, NCCL all-to-all in two source-rank groups",
+                   "step_launch": "one CUDA graph replay" if graphed else "eager",
                    "l2": "256 MB buffer written between timed steps; working set > L2"},
         "layer_tflops": tokens_total * FLOP_PER_TOKEN_TENSOR / (ms * 1e-3) / 1e12,
         "e2e": {"value": tokens_total / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,

@@ -40,7 +40,10 @@ class NumpyStages:
         p, s, ts = o.pack_nvfp4(h[None, :])
         return sequential_matvec(o.dequant_nvfp4(p, s, ts)[0], down)
 
-    def dispatch(self, x):
+    def count_buffer(self):
+        return torch.zeros((self.world,), dtype=torch.int32)
+
+    def dispatch(self, x, capacity=0):
         o, cfg = self.oracle, self.cfg
         xs = x.to(torch.float32).numpy()
         y = o.rmsnorm(xs, self.w.norm_weight, cfg.rms_eps)
@@ -51,9 +54,14 @@ class NumpyStages:
         T, K, H = xs.shape[0], cfg.top_k, cfg.hidden
         dest = idx // self.per_rank
         counts = np.bincount(dest.ravel(), minlength=self.world).astype(np.int32)
-        offsets = np.concatenate([[0], np.cumsum(counts)[:-1]])
+        if capacity > 0:
+            assert counts.max() <= capacity
+            offsets = np.arange(self.world) * capacity
+            records = np.zeros((self.world * capacity, self.record_bytes), dtype=np.uint8)
+        else:
+            offsets = np.concatenate([[0], np.cumsum(counts)[:-1]])
+            records = np.zeros((T * K, self.record_bytes), dtype=np.uint8)
         cursor = np.zeros(self.world, dtype=np.int64)
-        records = np.zeros((T * K, self.record_bytes), dtype=np.uint8)
         self.position = np.zeros((T, K), dtype=np.int64)
         for t in range(T):
             for k in range(K):
@@ -82,12 +90,14 @@ class NumpyStages:
     def comm_to_main(self):
         pass
 
-    def experts(self, recv, count, row_offset=0):
+    def experts(self, recv, count, row_offset=0, valid_counts=None, capacity=0):
         o, H = self.oracle, self.cfg.hidden
         recs = recv.numpy()
         out = np.zeros((count, H), dtype=np.float32)
         tail = H // 2 + H // 16
         for i in range(count):
+            if valid_counts is not None and (i % capacity) >= int(valid_counts[i // capacity]):
+                continue
             rec = recs[i]
             ts = rec[tail:tail + 4].copy().view(np.float32)[0]
             weight = rec[tail + 4:tail + 8].copy().view(np.float32)[0]

@@ -20,7 +20,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, tokens, result_dir):
+def _worker(rank, world, port, tokens, result_dir, capacity):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -36,11 +36,12 @@ def _worker(rank, world, port, tokens, result_dir):
         x_all = synthetic.make_tokens(tokens, cfg.hidden_size, seed=5)
         per = tokens // world
         x = x_all[rank * per:(rank + 1) * per].contiguous()
-        engine = ep.ExpertParallelEngine(NumpyStages(ocfg, ow, rank, world))
+        engine = ep.ExpertParallelEngine(NumpyStages(ocfg, ow, rank, world),
+                                         capacity_per_rank=capacity)
         out = torch.zeros((per, cfg.hidden_size), dtype=torch.float32)
         engine.step(x, out)
         engine.step(x, out)  # a second step reuses every buffer
-        assert sum(engine.last_send_splits) == per * cfg.top_k
+        assert capacity > 0 or sum(engine.last_send_splits) == per * cfg.top_k
         np.save(os.path.join(result_dir, f"out{rank}.npy"), out.numpy())
         if rank == 0:
             oracle = entry.load_oracle()
@@ -50,9 +51,12 @@ def _worker(rank, world, port, tokens, result_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,tokens", [(2, 12), (4, 8)])
-def test_expert_parallel_protocol_equals_single_process_oracle(tmp_path, world, tokens):
-    mp.spawn(_worker, args=(world, _free_port(), tokens, str(tmp_path)), nprocs=world, join=True)
+@pytest.mark.parametrize("world,tokens,capacity", [(2, 12, 0), (4, 8, 0), (2, 12, 24), (4, 8, 8)])
+def test_expert_parallel_protocol_equals_single_process_oracle(tmp_path, world, tokens, capacity):
+    """capacity == 0: compact records, split sizes read on the host; capacity > 0: fixed
+    segments per destination rank, equal splits, no host round trip."""
+    mp.spawn(_worker, args=(world, _free_port(), tokens, str(tmp_path), capacity), nprocs=world,
+             join=True)
     got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
     expected = np.load(tmp_path / "expected.npy")
     assert np.array_equal(got, expected)

@@ -44,17 +44,31 @@ def _worker(rank, world, port, shape, tokens_per_rank):
         assert single.run(x_all, expected), single.last_error
         mine = slice(rank * tokens_per_rank, (rank + 1) * tokens_per_rank)
         x = x_all[mine].contiguous()
-        for rows_dtype in (torch.float32, torch.bfloat16):
+        # compact records (host reads the split sizes) and fixed-capacity segments (no host
+        # round trip; replayed as a CUDA graph when the capture succeeds)
+        for rows_dtype, capacity in ((torch.float32, 0), (torch.bfloat16, 0),
+                                     (torch.float32, 2 * tokens_per_rank * cfg.top_k // world)):
             ep_cfg = synthetic.baseline_config(tokens_per_rank, experts=experts, hidden=hidden,
                                                routed=routed, shared=shared)
             ep_cfg.max_recv_pairs = total * cfg.top_k
             stages = ep.DeviceStages(ep_cfg, ep.shard_bindings(data.bindings, rank, world), rank,
                                      world, rows_dtype=rows_dtype)
-            engine = ep.ExpertParallelEngine(stages)
+            engine = ep.ExpertParallelEngine(stages, capacity_per_rank=capacity)
             out = torch.empty((tokens_per_rank, hidden), dtype=torch.float32, device="cuda")
             for _ in range(2):
                 engine.step(x, out)
             torch.cuda.synchronize()
+            if capacity > 0:
+                assert torch.equal(out, expected[mine])
+                graphed = engine.capture(x, out)
+                flag = torch.tensor([1 if graphed else 0], device="cuda")
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if flag.item():
+                    out.zero_()
+                    engine.replay()
+                    torch.cuda.synchronize()
+                elif rank == 0:
+                    print("graph capture unavailable:", getattr(engine, "capture_error", ""))
             assert stages.sync_status() == 0
             if rows_dtype == torch.float32:
                 assert torch.equal(out, expected[mine]), (out - expected[mine]).abs().max().item()
