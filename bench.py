@@ -337,6 +337,9 @@ def main():
     flush_buf = torch.zeros(256 * 1024 * 1024 // 4, dtype=torch.float32, device="cuda")
 
     if world > 1:
+        # variable-size all-to-all is made of point-to-point transfers: give them enough
+        # channels to fill NVLink (a library setting of this process only)
+        os.environ.setdefault("NCCL_MIN_P2P_NCHANNELS", "16")
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         ep = importlib.import_module("nemotron_inference_b200.expert_parallel")

@@ -103,6 +103,24 @@ class DeviceStages:
                                               _dtype_code(rows_back), out.data_ptr(),
                                               _dtype_code(out)), "nmoe_ep_combine")
 
+    # -- optional phase timing: `profile = True` makes mark() record a CUDA event on the
+    #    current stream; phase_times_ms() reports them relative to the first mark
+    profile = False
+
+    def mark(self, name: str) -> None:
+        if self.profile:
+            event = torch.cuda.Event(enable_timing=True)
+            event.record()
+            self._marks.append((name, event))
+
+    def reset_marks(self) -> None:
+        self._marks = []
+
+    def phase_times_ms(self) -> dict:
+        torch.cuda.synchronize()
+        start = self._marks[0][1]
+        return {name: start.elapsed_time(event) for name, event in self._marks}
+
     # -- stream hooks: collectives are issued from a communication stream so that they
     #    depend only on the kernels that produce their inputs
     def comm_stream(self):
@@ -180,14 +198,19 @@ class ExpertParallelEngine:
 
     def _step_fixed(self, x: torch.Tensor, out: torch.Tensor) -> None:
         st, cap, W = self.stages, self.capacity, self.world
+        mark = getattr(st, "mark", lambda name: None)
+        mark("start")
         send_records, send_counts = st.dispatch(x, cap)
+        mark("dispatch_done")
         st.main_to_comm()
         st.shared()
+        mark("shared_done")
         with st.comm_stream():
             recv_counts = st.count_buffer()
             dist.all_to_all_single(recv_counts, send_counts, group=self.group)
             recv = st.recv_buffer(W * cap)
             dist.all_to_all_single(recv, send_records, group=self.group)
+            mark("records_arrived")
         st.comm_to_main()
         back = st.back_buffer(W * cap)
         bounds = [W * c // self.chunks for c in range(self.chunks + 1)]
@@ -195,6 +218,7 @@ class ExpertParallelEngine:
             lo, hi = bounds[c], bounds[c + 1]
             rows = st.experts(recv[lo * cap:hi * cap], (hi - lo) * cap, lo * cap,
                               recv_counts[lo:hi], cap)
+            mark(f"experts_{c}_done")
             st.main_to_comm()
             with st.comm_stream():
                 in_splits = [cap if lo <= r < hi else 0 for r in range(W)]
@@ -202,8 +226,10 @@ class ExpertParallelEngine:
                     dist.all_to_all_single(back, rows, [cap] * W, in_splits, group=self.group)
                 else:
                     dist.all_to_all_single(back[:0], rows, [0] * W, in_splits, group=self.group)
+                mark(f"rows_{c}_returned")
         st.comm_to_main()
         st.combine(x, back, out)
+        mark("combine_done")
         self.last_send_splits = self.last_recv_splits = [cap] * W
 
     def capture(self, x: torch.Tensor, out: torch.Tensor) -> bool:
@@ -216,7 +242,8 @@ class ExpertParallelEngine:
                 self._step_fixed(x, out)  # warm up: allocations, NCCL channels
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            # other threads (the NCCL watchdog) make CUDA calls of their own during capture
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 self._step_fixed(x, out)
             self._graph = graph
             return True
@@ -228,6 +255,15 @@ class ExpertParallelEngine:
 
     def replay(self) -> None:
         self._graph.replay()
+
+    def release_graph(self) -> None:
+        """Drops the recorded step.  Do this before the process group is destroyed: a live
+        graph keeps the communicator's kernels referenced and the teardown waits for it."""
+        if self._graph is not None:
+            torch.cuda.synchronize()
+            self._graph = None
+            import gc
+            gc.collect()
 
     def _step_compact(self, x: torch.Tensor, out: torch.Tensor) -> None:
         st = self.stages
@@ -347,6 +383,17 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
         out_host.copy_(out, non_blocking=True)
 
     e2e_ms = timed(e2e_step, args.steps, args.warmup)
+    stages.profile = True
+    phases = {}
+    for i in range(4):
+        stages.reset_marks()
+        flush_buf.add_(1)
+        engine.step(x, out)
+        if i >= 1:
+            for name, ms_at in stages.phase_times_ms().items():
+                phases[name] = phases.get(name, 0.0) + ms_at / 3
+    stages.profile = False
+    engine.release_graph()
     sent = capacity * (world - 1)
     return {
         "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": "tokens/s",
@@ -369,5 +416,6 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
         "gpu_launches": 13 * args.steps * world,
         "clocks": clocks,
         "a2a_bytes_rank0": {"dispatch": sent * stages.record_bytes, "return": sent * H * 2},
+        "ep_phase_end_ms_rank0_eager": {k: round(v, 4) for k, v in phases.items()},
         "roofline": None,
     }

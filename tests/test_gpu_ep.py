@@ -27,8 +27,14 @@ def _worker(rank, world, port, shape, tokens_per_rank):
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
+    import datetime
+    import faulthandler
+    import sys
+    import traceback
+    faulthandler.dump_traceback_later(100, exit=True, file=sys.stderr)  # a hung rank says where
     dist.init_process_group("nccl", rank=rank, world_size=world,
-                            device_id=torch.device("cuda", rank))
+                            device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=90))
     try:
         package = entry.load_package()
         synthetic = importlib.import_module("nemotron_inference_b200.synthetic")
@@ -74,12 +80,18 @@ def _worker(rank, world, port, shape, tokens_per_rank):
                 assert torch.equal(out, expected[mine]), (out - expected[mine]).abs().max().item()
             else:
                 assert (out - expected[mine]).abs().max().item() <= 2e-2
+            engine.release_graph()
             stages.layer.close()
         single.close()
-    finally:
-        dist.destroy_process_group()
+    except BaseException:
+        # leave at once: tearing the process group down while the peer sits in a
+        # collective would block both ranks until the timeout
+        traceback.print_exc()
+        os._exit(1)
+    dist.destroy_process_group()
 
 
+@pytest.mark.timeout(150)
 @pytest.mark.parametrize("tokens_per_rank", [24, 700])
 def test_expert_parallel_equals_single_device(tokens_per_rank):
     world = min(torch.cuda.device_count(), 4)
