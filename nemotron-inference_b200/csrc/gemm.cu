@@ -33,14 +33,13 @@ namespace nmoe {
 namespace {
 
 constexpr int kEpilogueWarps = 8;
-constexpr int kGemmThreads = (2 + kEpilogueWarps) * 32;
-constexpr int kStageStride = 20;  // floats per staged row: 16 + 4 keeps float4 stores conflict-free
+constexpr int kScaleWarp = 2 + kEpilogueWarps;  // issues the block-scale copies into TMEM
+constexpr int kScaleWarps = 2;  // the copies are split between this many issuing threads
+constexpr int kGemmThreads = (2 + kEpilogueWarps + kScaleWarps) * 32;
+constexpr int kStageStride = 36;  // floats per staged row: 32 + 4 keeps float4 accesses conflict-free
 
-template <int BN_, int A_ROWS_, int SFB_GS_, int STAGES_, int PREFETCH_TILES_ = 0>
+template <int BN_, int A_ROWS_, int SFB_GS_, int STAGES_, bool ROW_STAGING_ = true>
 struct TileCfg {
-  // HBM-bound shapes: how many of this CTA's future tiles have their weights
-  // prefetched into L2 while the current tile streams through shared memory
-  static constexpr int PREFETCH_TILES = PREFETCH_TILES_;
   static constexpr int BN = BN_;
   static constexpr int A_ROWS = A_ROWS_;
   static constexpr int SFB_GS = SFB_GS_;  // 32-row scale groups stored per K tile (multiple of 4:
@@ -60,8 +59,10 @@ struct TileCfg {
   static constexpr int SFB_COL = SFA_COL + 16;
   static constexpr int TMEM_USED = SFA_COL + SF_BUFS * SF_BUF_COLS;
   static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
-  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-  static constexpr int EPI_STAGE_BYTES = kEpilogueWarps * 32 * kStageStride * 4;
+  static constexpr int BAR_BYTES = (2 * STAGES + 4 + 2 * SF_BUFS) * 8 + 16;
+  // staging for the row-scattering epilogue of the down projection
+  static constexpr bool ROW_STAGING = ROW_STAGING_;
+  static constexpr int EPI_STAGE_BYTES = ROW_STAGING_ ? kEpilogueWarps * 32 * kStageStride * 4 : 0;
   // The MMA always reads 128 A rows; with a smaller box the tail rows alias the
   // following stages, which is harmless (those output rows are never stored)
   // but must stay inside the allocation: the B region follows the A region.
@@ -74,10 +75,10 @@ struct TileCfg {
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
-using CfgPrefillUp = TileCfg<208, 128, 8, 4>;
+using CfgPrefillUp = TileCfg<208, 128, 8, 4, false>;
 using CfgPrefillDown = TileCfg<192, 128, 8, 4>;
-using CfgDecode = TileCfg<128, 32, 4, 8, 0>;
-using CfgDecodeWide = TileCfg<128, 128, 4, 5, 0>;
+using CfgDecode = TileCfg<128, 32, 4, 7>;
+using CfgDecodeWide = TileCfg<128, 128, 4, 5>;
 
 __device__ __forceinline__ void report_timeout(int32_t* error, volatile int* abort_flag) {
   *abort_flag = 1;
@@ -100,7 +101,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* empty_bar = full_bar + C::STAGES;
   uint64_t* tmem_full_bar = empty_bar + C::STAGES;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+  uint64_t* sf_ready_bar = tmem_empty_bar + 2;
+  uint64_t* sf_free_bar = sf_ready_bar + C::SF_BUFS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_free_bar + C::SF_BUFS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stage_base = reinterpret_cast<float*>(
       reinterpret_cast<uint8_t*>(full_bar) + C::BAR_BYTES);  // down epilogue staging
@@ -116,6 +119,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full_bar[a], 1);
       mbar_init(&tmem_empty_bar[a], kEpilogueWarps);
+    }
+    for (int b = 0; b < C::SF_BUFS; ++b) {
+      mbar_init(&sf_ready_bar[b], kScaleWarps);
+      mbar_init(&sf_free_bar[b], 1);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -143,6 +150,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long prof_wait = 0;
+      const long long prof_start = clock64();
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int rt = t / args.n_tiles;
         const int nt = t - rt * args.n_tiles;
@@ -161,35 +170,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // weights are stored K-block-major: [expert][k block][row][128 B], then the
         // partial last K block as [expert][row][tail bytes]
         const int b_row = nt * C::BN;
-        if constexpr (C::PREFETCH_TILES > 0) {
-          const int ft = t + C::PREFETCH_TILES * static_cast<int>(gridDim.x);
-          if (ft < total_tiles) {
-            const int frt = ft / args.n_tiles;
-            const int fnt = ft - frt * args.n_tiles;
-            const int fe = args.row_tiles != nullptr ? args.row_tiles[frt].expert : 0;
-            const uint8_t* fsf = args.sfb + (static_cast<size_t>(fe) * args.n_tiles + fnt) *
-                                                args.k_blocks * C::SFB_BYTES;
-            bulk_prefetch(fsf, static_cast<uint32_t>(args.k_blocks * C::SFB_BYTES));
-            for (int kb = 0; kb < args.k_blocks; ++kb) {
-              if (kb < args.kb_full) {
-                tma_prefetch_2d(&tmap_b, 0, (fe * args.kb_full + kb) * args.N + fnt * C::BN);
-              } else {
-                tma_prefetch_2d(&tmap_b_tail, 0, fe * args.N + fnt * C::BN);
-              }
-            }
-          }
-        }
         for (int kb = 0; kb < args.k_blocks; ++kb) {
+          const long long w0 = clock64();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
             report_timeout(args.error, abort_flag);
             ok = false;
             break;
           }
+          prof_wait += clock64() - w0;
           mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_TX);
           tma_load_2d(sA + stage * C::A_BYTES, &tmap_a, kb * 128, row0, &full_bar[stage]);
           if (kb < args.kb_full) {
-            tma_load_2d(sB + stage * C::B_BYTES, &tmap_b, 0,
-                        (expert * args.kb_full + kb) * args.N + b_row, &full_bar[stage]);
+            // one contiguous, pre-swizzled panel slice: a single bulk copy
+            bulk_load(sB + stage * C::B_BYTES,
+                      args.b_full + (static_cast<size_t>(expert * args.kb_full + kb) * args.N +
+                                     b_row) * 128,
+                      C::B_BYTES, &full_bar[stage]);
           } else {
             tma_load_2d(sB + stage * C::B_BYTES, &tmap_b_tail, 0, expert * args.N + b_row,
                         &full_bar[stage]);
@@ -204,6 +200,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+      if (args.counters != nullptr) {
+        atomicAdd(&args.counters[0], static_cast<unsigned long long>(clock64() - prof_start));
+        atomicAdd(&args.counters[1], static_cast<unsigned long long>(prof_wait));
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -213,39 +213,42 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       int local = 0;
       int sf_buf = 0;
+      uint32_t sf_phase = 0;
       bool ok = true;
+      long long prof_full = 0, prof_tmem = 0, prof_cp = 0, prof_mma = 0;
+      const long long prof_start = clock64();
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
+        const long long t0 = clock64();
         if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u)) {
           report_timeout(args.error, abort_flag);
           break;
         }
+        prof_tmem += clock64() - t0;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * C::ACC_STRIDE;
         for (int kb = 0; kb < args.k_blocks; ++kb) {
+          const long long f0 = clock64();
           if (!mbar_wait(&full_bar[stage], phase)) {
             report_timeout(args.error, abort_flag);
             ok = false;
             break;
           }
+          const long long f1 = clock64();
+          prof_full += f1 - f0;
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * C::A_BYTES);
           const uint32_t b_addr = smem_u32(sB + stage * C::B_BYTES);
-          const uint32_t sfa_addr = smem_u32(sSFA + stage * C::SFA_BYTES);
-          const uint32_t sfb_addr = smem_u32(sSFB + stage * C::SFB_BYTES);
           const uint32_t sf_tmem = tmem_base + sf_buf * C::SF_BUF_COLS;
-          sf_buf ^= 1;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFA_COL + 4 * c,
-                                      make_smem_desc(sfa_addr + c * 512, 0, 128, 0));
+          if (!mbar_wait(&sf_ready_bar[sf_buf], sf_phase)) {
+            report_timeout(args.error, abort_flag);
+            ok = false;
+            break;
           }
-#pragma unroll
-          for (int c = 0; c < C::SFB_GS; ++c) {
-            tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFB_COL + 4 * c,
-                                      make_smem_desc(sfb_addr + c * 512, 0, 128, 0));
-          }
+          tcgen05_fence_after();
+          const long long f2 = clock64();
+          prof_cp += f2 - f1;
           const int kt_count = min(4, k_mmas - kb * 4);
           for (int kt = 0; kt < kt_count; ++kt) {
             tcgen05_mma_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
@@ -254,12 +257,74 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                              sf_tmem + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
           }
           tcgen05_commit(&empty_bar[stage]);
+          tcgen05_commit(&sf_free_bar[sf_buf]);
+          if (++sf_buf == C::SF_BUFS) {
+            sf_buf = 0;
+            sf_phase ^= 1u;
+          }
+          prof_mma += clock64() - f2;
           if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (ok) tcgen05_commit(&tmem_full_bar[acc]);
+      }
+      if (args.counters != nullptr) {
+        atomicAdd(&args.counters[2], static_cast<unsigned long long>(clock64() - prof_start));
+        atomicAdd(&args.counters[3], static_cast<unsigned long long>(prof_full));
+        atomicAdd(&args.counters[4], static_cast<unsigned long long>(prof_tmem));
+        atomicAdd(&args.counters[5], static_cast<unsigned long long>(prof_cp));
+        atomicAdd(&args.counters[6], static_cast<unsigned long long>(prof_mma));
+      }
+    }
+  } else if (warp >= kScaleWarp) {
+    // ------------------------------------------------------- block-scale copier
+    // The copies of one K block's scales into TMEM take longer to issue than
+    // its MMAs; a thread of their own lets them run ahead of the MMA thread.
+    if (lane == 0) {
+      const int part = warp - kScaleWarp;
+      int stage = 0;
+      uint32_t phase = 0;
+      int sf_buf = 0;
+      uint32_t sf_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < args.k_blocks; ++kb) {
+          if (!mbar_wait(&sf_free_bar[sf_buf], sf_phase ^ 1u) ||
+              !mbar_wait(&full_bar[stage], phase)) {
+            report_timeout(args.error, abort_flag);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sfa_addr = smem_u32(sSFA + stage * C::SFA_BYTES);
+          const uint32_t sfb_addr = smem_u32(sSFB + stage * C::SFB_BYTES);
+          const uint32_t sf_tmem = tmem_base + sf_buf * C::SF_BUF_COLS;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (c % kScaleWarps == part) {
+              tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFA_COL + 4 * c,
+                                        make_smem_desc(sfa_addr + c * 512, 0, 128, 0));
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < C::SFB_GS; ++c) {
+            if (c % kScaleWarps == part) {
+              tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFB_COL + 4 * c,
+                                        make_smem_desc(sfb_addr + c * 512, 0, 128, 0));
+            }
+          }
+          tcgen05_commit(&sf_ready_bar[sf_buf]);
+          if (++sf_buf == C::SF_BUFS) {
+            sf_buf = 0;
+            sf_phase ^= 1u;
+          }
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
       }
     }
   } else {
@@ -288,9 +353,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       float scale = args.w_tensor_scale[expert];
       if (args.a_tensor_scale != nullptr && row_valid) scale *= args.a_tensor_scale[grow];
 
+      const long long e0 = clock64();
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase)) {
         report_timeout(args.error, abort_flag);
         break;
+      }
+      if (args.counters != nullptr && warp == 2 && lane == 0) {
+        atomicAdd(&args.counters[7], static_cast<unsigned long long>(clock64() - e0));
       }
       tcgen05_fence_after();
       const uint32_t t_addr =
@@ -337,39 +406,61 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (args.row_weight != nullptr) wt = args.row_weight[grow];
         }
         // Each thread owns one output row of the tile, but a store instruction
-        // should write whole rows: stage 16 columns of 32 rows in shared memory,
-        // then let half-warps write 64 contiguous bytes of one row each.
+        // should write whole lines: stage 32 columns of 32 rows in shared memory,
+        // then let every 8 lanes write 128 contiguous bytes of one row (4 rows
+        // per instruction).
         float* stage = stage_base + (warp - 2) * (32 * kStageStride);
-        for (int ch = chunk_begin; ch < chunk_end; ++ch) {
+        const int sub = lane >> 3;
+        const int c4 = (lane & 7) * 4;
+        for (int ch = chunk_begin; ch < chunk_end; ch += 2) {
           const int n = n0 + ch * 16;
           if (n >= args.N) break;
-          float v[16];
-          tmem_ld_x16(t_addr + ch * 16, v);
+          const bool wide = ch + 1 < chunk_end && n + 16 < args.N;
+          float va[16], vb[16];
+          tmem_ld_x16(t_addr + ch * 16, va);
+          if (wide) {
+            tmem_ld_x16(t_addr + ch * 16 + 16, vb);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) vb[i] = 0.0f;
+          }
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            v[i] = __fmul_rn(v[i], scale);
-            if (args.row_weight != nullptr) v[i] = __fmul_rn(v[i], wt);
+            va[i] = __fmul_rn(va[i], scale);
+            vb[i] = __fmul_rn(vb[i], scale);
+            if (args.row_weight != nullptr) {
+              va[i] = __fmul_rn(va[i], wt);
+              vb[i] = __fmul_rn(vb[i], wt);
+            }
           }
           __syncwarp();
 #pragma unroll
           for (int i = 0; i < 16; i += 4) {
             *reinterpret_cast<float4*>(stage + lane * kStageStride + i) =
-                make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                make_float4(va[i], va[i + 1], va[i + 2], va[i + 3]);
+            if (wide) {
+              *reinterpret_cast<float4*>(stage + lane * kStageStride + 16 + i) =
+                  make_float4(vb[i], vb[i + 1], vb[i + 2], vb[i + 3]);
+            }
           }
           __syncwarp();
-          const int sub = lane >> 4;
-          const int col = lane & 15;
+          const bool col_ok = c4 < (wide ? 32 : 16);
 #pragma unroll 4
-          for (int it = 0; it < 16; ++it) {
-            const int rr = 2 * it + sub;
+          for (int it = 0; it < 8; ++it) {
+            const int rr = 4 * it + sub;
             const int d = __shfl_sync(0xffffffffu, dest, rr);
-            if (d >= 0) {
-              const size_t at = static_cast<size_t>(d) * args.N + n + col;
-              const float value = stage[rr * kStageStride + col];
+            if (d >= 0 && col_ok) {
+              const size_t at = static_cast<size_t>(d) * args.N + n + c4;
+              const float4 value = *reinterpret_cast<const float4*>(stage + rr * kStageStride + c4);
               if (args.out_bf16) {
-                reinterpret_cast<__nv_bfloat16*>(args.out_rows)[at] = __float2bfloat16_rn(value);
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(value.x, value.y);
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(value.z, value.w);
+                uint2 bits;
+                bits.x = *reinterpret_cast<const uint32_t*>(&lo);
+                bits.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(args.out_rows) + at) = bits;
               } else {
-                args.out_rows[at] = value;
+                *reinterpret_cast<float4*>(args.out_rows + at) = value;
               }
             }
           }
@@ -405,11 +496,13 @@ cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a, const CUtensorM
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (err != cudaSuccess) return err;
     kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, tmap_b_tail, args);
-  } else {
+  } else if constexpr (C::ROW_STAGING) {
     auto kernel = grouped_gemm_kernel<C, kGemmDown>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (err != cudaSuccess) return err;
     kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, tmap_b_tail, args);
+  } else {
+    return cudaErrorInvalidValue;  // this tile shape has no staging for the down epilogue
   }
   return cudaGetLastError();
 }
@@ -469,7 +562,10 @@ __global__ void relayout_weight_packed_kernel(const uint4* __restrict__ src, int
     const size_t e = row / N;
     const int kb = c >> 3;
     if (kb < kb_full) {
-      dst_full[((e * kb_full + kb) * N + n) * 8 + (c & 7)] = src[i];
+      // 16-byte chunk j of row n is stored at position j ^ (n % 8): the 128-byte
+      // shared-memory swizzle, applied here once so that a plain bulk copy of a
+      // panel slice lands in shared memory exactly as a swizzling tensor copy would
+      dst_full[((e * kb_full + kb) * N + n) * 8 + ((c & 7) ^ (n & 7))] = src[i];
     } else {
       dst_tail[row * tail_pitch_chunks + (c - kb_full * 8)] = src[i];
     }

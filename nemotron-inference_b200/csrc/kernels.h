@@ -31,6 +31,7 @@ struct GemmArgs {
   int32_t n_tiles = 0;   // ceil(N / BN)
   int32_t k_blocks = 0;  // ceil(K / 256)
   int32_t kb_full = 0;   // K / 256: K blocks stored in the full-block weight region
+  const uint8_t* b_full = nullptr;  // [expert][kb_full][N][128 B], 16-byte chunks pre-swizzled
   // A-side block scales, tiled: [row slot][k_blocks][2048 bytes]
   const uint8_t* sfa = nullptr;
   // weight block scales, [expert][n_tile][k_block][sfb_bytes] in the layout
@@ -54,6 +55,7 @@ struct GemmArgs {
   int32_t dest_add = 0;
   const float* row_weight = nullptr;  // per activation row routing weight, nullptr => none
   int32_t* error = nullptr;           // device error slot (DeviceError)
+  unsigned long long* counters = nullptr;  // TEMPORARY pipeline cycle counters
 };
 
 // Tile shapes compiled into the library.  The block scales of every MMA must

@@ -216,7 +216,8 @@ struct WeightStack {
     kb_full = cols / 256;
     const int tail_bytes = (cols % 256) / 2;
     const size_t panel_rows = static_cast<size_t>(count) * rows;
-    packed.allocate(panel_rows * kb_full * 128);
+    packed.allocate(panel_rows * kb_full * 128 + 256 * 128, true);  // + one tile of slack: the last
+                                                                    // tile of the last panel over-reads
     // The tail map reads `tail_bytes` per row and lets TMA zero-fill the rest of
     // the 128-byte box; if the driver refuses a box wider than the tensor, the
     // tail rows are padded to 128 bytes instead.
@@ -285,6 +286,8 @@ struct ActivationOperand {
   const CUtensorMap& map(TileClass c) const { return c == kClassDecode ? map_box32 : map_box128; }
 };
 
+unsigned long long* g_debug_counters = nullptr;  // TEMPORARY
+
 struct Schedule {
   const RowTile* row_tiles = nullptr;  // grouped when non-null
   const int32_t* num_row_tiles = nullptr;
@@ -306,6 +309,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   g.n_tiles = (up.n + gemm_variant_info(up_variant).bn - 1) / gemm_variant_info(up_variant).bn;
   g.k_blocks = k_blocks_of(up.k);
   g.kb_full = up.kb_full;
+  g.b_full = up.packed.as<uint8_t>();
   g.sfa = a.sf_tiled;
   g.sfb = up.sf(tile_class);
   g.a_tensor_scale = a_tensor_scale;
@@ -317,6 +321,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   g.out_sf = hidden_sf;
   g.out_k_blocks = k_blocks_of(up.n);
   g.error = error;
+  g.counters = g_debug_counters;
   NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, a.map(tile_class), up.map(tile_class),
                                 up.tail_map(tile_class), g, num_sms, stream));
 
@@ -329,6 +334,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   d.n_tiles = (down.n + gemm_variant_info(down_variant).bn - 1) / gemm_variant_info(down_variant).bn;
   d.k_blocks = k_blocks_of(down.k);
   d.kb_full = down.kb_full;
+  d.b_full = down.packed.as<uint8_t>();
   d.sfa = hidden.sf_tiled;
   d.sfb = down.sf(tile_class);
   d.a_tensor_scale = nullptr;  // the fused quantiser always uses tensor scale 1
@@ -343,6 +349,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   d.dest_add = dest_add;
   d.row_weight = row_weight;
   d.error = error;
+  d.counters = g_debug_counters != nullptr ? g_debug_counters + 8 : nullptr;
   NMOE_CUDA(launch_grouped_gemm(down_variant, kGemmDown, hidden.map(tile_class),
                                 down.map(tile_class), down.tail_map(tile_class), d, num_sms,
                                 stream));
@@ -1071,6 +1078,18 @@ nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream_ptr, const void* inp
       layer->cfg.hidden_size, layer->cfg.top_k, output, output_dtype == NMOE_BF16,
       static_cast<cudaStream_t>(stream_ptr));
   return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
+}
+
+__attribute__((visibility("default"))) int nmoe_debug_counters(int enable, unsigned long long* out16) {
+  if (enable && g_debug_counters == nullptr) {
+    cudaMalloc(&g_debug_counters, 16 * sizeof(unsigned long long));
+  }
+  if (out16 != nullptr && g_debug_counters != nullptr) {
+    cudaDeviceSynchronize();
+    cudaMemcpy(out16, g_debug_counters, 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  }
+  if (g_debug_counters != nullptr) cudaMemset(g_debug_counters, 0, 16 * sizeof(unsigned long long));
+  return 0;
 }
 
 const char* nmoe_layer_last_error(const nmoe_layer* layer) {
