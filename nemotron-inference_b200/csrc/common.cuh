@@ -209,19 +209,6 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
       : "memory");
 }
 
-// L2 prefetches: warm the cache for a tile this CTA will load later without
-// holding shared memory for it.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x),
-               "r"(y)
-               : "memory");
-}
-
-__device__ __forceinline__ void bulk_prefetch(const void* gmem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem_src), "r"(bytes)
-               : "memory");
-}
-
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

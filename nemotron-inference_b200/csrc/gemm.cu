@@ -19,10 +19,14 @@
 // 32-lane x 16-byte form; activations use the reference's 128x4 tile order
 // (runtime/src/backend/nvfp4_scale_layout.cpp:14-28) unchanged.
 //
-// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
+// Warp roles (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
 // owner, warps 2-9 = epilogue (two warps per TMEM lane quarter, splitting the
-// tile's columns).  Every mbarrier
-// wait is bounded; on a timeout the CTA records kDevWaitTimeout and unwinds.
+// tile's columns), warps 10-11 = block-scale copiers.  The twelve scale copies
+// of a K block take longer to issue than its four MMAs and a thread's tcgen05
+// operations execute in order, so the copies have threads of their own and run
+// one K block ahead of the MMAs into double-buffered TMEM columns.  Every
+// mbarrier wait is bounded; on a timeout the CTA records kDevWaitTimeout and
+// unwinds.
 #include <algorithm>
 #include <cstdlib>
 
@@ -59,7 +63,7 @@ struct TileCfg {
   static constexpr int SFB_COL = SFA_COL + 16;
   static constexpr int TMEM_USED = SFA_COL + SF_BUFS * SF_BUF_COLS;
   static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
-  static constexpr int BAR_BYTES = (2 * STAGES + 4 + 2 * SF_BUFS) * 8 + 16;
+  static constexpr int BAR_BYTES = (2 * STAGES + 4 + SF_BUFS) * 8 + 16;
   // staging for the row-scattering epilogue of the down projection
   static constexpr bool ROW_STAGING = ROW_STAGING_;
   static constexpr int EPI_STAGE_BYTES = ROW_STAGING_ ? kEpilogueWarps * 32 * kStageStride * 4 : 0;
@@ -85,6 +89,23 @@ __device__ __forceinline__ void report_timeout(int32_t* error, volatile int* abo
   if (error != nullptr) atomicCAS(error, kDevOk, kDevWaitTimeout);
 }
 
+// All scale copies of one full K block that fall to copier `PART`; compile-time
+// indices only, so that no copy carries a run-time predicate.
+template <class C, int PART>
+__device__ __forceinline__ void issue_scale_copies(uint32_t sf_tmem, uint32_t sfa_addr,
+                                                   uint32_t sfb_addr) {
+#pragma unroll
+  for (int c = PART; c < 4; c += kScaleWarps) {
+    tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFA_COL + 4 * c,
+                              make_smem_desc(sfa_addr + c * 512, 0, 128, 0));
+  }
+#pragma unroll
+  for (int c = PART; c < C::SFB_GS; c += kScaleWarps) {
+    tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFB_COL + 4 * c,
+                              make_smem_desc(sfb_addr + c * 512, 0, 128, 0));
+  }
+}
+
 template <class C, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
@@ -102,8 +123,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint64_t* tmem_full_bar = empty_bar + C::STAGES;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
   uint64_t* sf_ready_bar = tmem_empty_bar + 2;
-  uint64_t* sf_free_bar = sf_ready_bar + C::SF_BUFS;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_free_bar + C::SF_BUFS);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_ready_bar + C::SF_BUFS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* stage_base = reinterpret_cast<float*>(
       reinterpret_cast<uint8_t*>(full_bar) + C::BAR_BYTES);  // down epilogue staging
@@ -122,7 +142,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int b = 0; b < C::SF_BUFS; ++b) {
       mbar_init(&sf_ready_bar[b], kScaleWarps);
-      mbar_init(&sf_free_bar[b], 1);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -150,8 +169,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      long long prof_wait = 0;
-      const long long prof_start = clock64();
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int rt = t / args.n_tiles;
         const int nt = t - rt * args.n_tiles;
@@ -171,13 +188,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // partial last K block as [expert][row][tail bytes]
         const int b_row = nt * C::BN;
         for (int kb = 0; kb < args.k_blocks; ++kb) {
-          const long long w0 = clock64();
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
             report_timeout(args.error, abort_flag);
             ok = false;
             break;
           }
-          prof_wait += clock64() - w0;
           mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_TX);
           tma_load_2d(sA + stage * C::A_BYTES, &tmap_a, kb * 128, row0, &full_bar[stage]);
           if (kb < args.kb_full) {
@@ -200,10 +215,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
-      if (args.counters != nullptr) {
-        atomicAdd(&args.counters[0], static_cast<unsigned long long>(clock64() - prof_start));
-        atomicAdd(&args.counters[1], static_cast<unsigned long long>(prof_wait));
-      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -215,67 +226,56 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int sf_buf = 0;
       uint32_t sf_phase = 0;
       bool ok = true;
-      long long prof_full = 0, prof_tmem = 0, prof_cp = 0, prof_mma = 0;
-      const long long prof_start = clock64();
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        const long long t0 = clock64();
         if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u)) {
           report_timeout(args.error, abort_flag);
           break;
         }
-        prof_tmem += clock64() - t0;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * C::ACC_STRIDE;
         for (int kb = 0; kb < args.k_blocks; ++kb) {
-          const long long f0 = clock64();
-          if (!mbar_wait(&full_bar[stage], phase)) {
+          // the operands have landed and the scale copies of this K block are done
+          if (!mbar_wait(&full_bar[stage], phase) || !mbar_wait(&sf_ready_bar[sf_buf], sf_phase)) {
             report_timeout(args.error, abort_flag);
             ok = false;
             break;
           }
-          const long long f1 = clock64();
-          prof_full += f1 - f0;
           tcgen05_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * C::A_BYTES);
           const uint32_t b_addr = smem_u32(sB + stage * C::B_BYTES);
           const uint32_t sf_tmem = tmem_base + sf_buf * C::SF_BUF_COLS;
-          if (!mbar_wait(&sf_ready_bar[sf_buf], sf_phase)) {
-            report_timeout(args.error, abort_flag);
-            ok = false;
-            break;
-          }
-          tcgen05_fence_after();
-          const long long f2 = clock64();
-          prof_cp += f2 - f1;
           const int kt_count = min(4, k_mmas - kb * 4);
-          for (int kt = 0; kt < kt_count; ++kt) {
-            tcgen05_mma_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
-                             make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
-                             sf_tmem + C::SFA_COL + 4 * kt,
-                             sf_tmem + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
+          if (kt_count == 4) {
+#pragma unroll
+            for (int kt = 0; kt < 4; ++kt) {
+              tcgen05_mma_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
+                               make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
+                               sf_tmem + C::SFA_COL + 4 * kt,
+                               sf_tmem + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
+            }
+          } else {
+            for (int kt = 0; kt < kt_count; ++kt) {
+              tcgen05_mma_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
+                               make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
+                               sf_tmem + C::SFA_COL + 4 * kt,
+                               sf_tmem + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
+            }
           }
+          // frees the stage for the producer and, SF_BUFS K blocks later, this
+          // block's scale columns for the copier
           tcgen05_commit(&empty_bar[stage]);
-          tcgen05_commit(&sf_free_bar[sf_buf]);
           if (++sf_buf == C::SF_BUFS) {
             sf_buf = 0;
             sf_phase ^= 1u;
           }
-          prof_mma += clock64() - f2;
           if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (ok) tcgen05_commit(&tmem_full_bar[acc]);
-      }
-      if (args.counters != nullptr) {
-        atomicAdd(&args.counters[2], static_cast<unsigned long long>(clock64() - prof_start));
-        atomicAdd(&args.counters[3], static_cast<unsigned long long>(prof_full));
-        atomicAdd(&args.counters[4], static_cast<unsigned long long>(prof_tmem));
-        atomicAdd(&args.counters[5], static_cast<unsigned long long>(prof_cp));
-        atomicAdd(&args.counters[6], static_cast<unsigned long long>(prof_mma));
       }
     }
   } else if (warp >= kScaleWarp) {
@@ -287,12 +287,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       int sf_buf = 0;
-      uint32_t sf_phase = 0;
+      // the scale columns written now were last read by the MMAs of the K block
+      // SF_BUFS iterations back; those MMAs also release that block's stage
+      int old_stage = 0;
+      uint32_t old_phase = 0;
+      int iteration = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        for (int kb = 0; kb < args.k_blocks; ++kb) {
-          if (!mbar_wait(&sf_free_bar[sf_buf], sf_phase ^ 1u) ||
-              !mbar_wait(&full_bar[stage], phase)) {
+        for (int kb = 0; kb < args.k_blocks; ++kb, ++iteration) {
+          bool ready = true;
+          if (iteration >= C::SF_BUFS) {
+            ready = mbar_wait(&empty_bar[old_stage], old_phase);
+            if (++old_stage == C::STAGES) {
+              old_stage = 0;
+              old_phase ^= 1u;
+            }
+          }
+          if (!ready || !mbar_wait(&full_bar[stage], phase)) {
             report_timeout(args.error, abort_flag);
             ok = false;
             break;
@@ -301,25 +312,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t sfa_addr = smem_u32(sSFA + stage * C::SFA_BYTES);
           const uint32_t sfb_addr = smem_u32(sSFB + stage * C::SFB_BYTES);
           const uint32_t sf_tmem = tmem_base + sf_buf * C::SF_BUF_COLS;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            if (c % kScaleWarps == part) {
+          // a partial last K block needs the scales of the MMAs it issues only;
+          // the full block keeps its copies free of run-time predicates, which
+          // slow their issue down considerably
+          const int kt_count = min(4, k_mmas - kb * 4);
+          constexpr int kWeightCopiesPerMma = C::SFB_GS / 4;
+          if (kt_count == 4) {
+            static_assert(kScaleWarps == 2, "one branch per copier");
+            if (part == 0) {
+              issue_scale_copies<C, 0>(sf_tmem, sfa_addr, sfb_addr);
+            } else {
+              issue_scale_copies<C, 1>(sf_tmem, sfa_addr, sfb_addr);
+            }
+          } else {
+            for (int c = part; c < kt_count; c += kScaleWarps) {
               tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFA_COL + 4 * c,
                                         make_smem_desc(sfa_addr + c * 512, 0, 128, 0));
             }
-          }
-#pragma unroll
-          for (int c = 0; c < C::SFB_GS; ++c) {
-            if (c % kScaleWarps == part) {
+            for (int c = part; c < kt_count * kWeightCopiesPerMma; c += kScaleWarps) {
               tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFB_COL + 4 * c,
                                         make_smem_desc(sfb_addr + c * 512, 0, 128, 0));
             }
           }
           tcgen05_commit(&sf_ready_bar[sf_buf]);
-          if (++sf_buf == C::SF_BUFS) {
-            sf_buf = 0;
-            sf_phase ^= 1u;
-          }
+          if (++sf_buf == C::SF_BUFS) sf_buf = 0;
           if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -353,13 +369,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       float scale = args.w_tensor_scale[expert];
       if (args.a_tensor_scale != nullptr && row_valid) scale *= args.a_tensor_scale[grow];
 
-      const long long e0 = clock64();
       if (!mbar_wait(&tmem_full_bar[acc], acc_phase)) {
         report_timeout(args.error, abort_flag);
         break;
-      }
-      if (args.counters != nullptr && warp == 2 && lane == 0) {
-        atomicAdd(&args.counters[7], static_cast<unsigned long long>(clock64() - e0));
       }
       tcgen05_fence_after();
       const uint32_t t_addr =

@@ -55,7 +55,6 @@ struct GemmArgs {
   int32_t dest_add = 0;
   const float* row_weight = nullptr;  // per activation row routing weight, nullptr => none
   int32_t* error = nullptr;           // device error slot (DeviceError)
-  unsigned long long* counters = nullptr;  // TEMPORARY pipeline cycle counters
 };
 
 // Tile shapes compiled into the library.  The block scales of every MMA must

@@ -286,7 +286,6 @@ struct ActivationOperand {
   const CUtensorMap& map(TileClass c) const { return c == kClassDecode ? map_box32 : map_box128; }
 };
 
-unsigned long long* g_debug_counters = nullptr;  // TEMPORARY
 
 struct Schedule {
   const RowTile* row_tiles = nullptr;  // grouped when non-null
@@ -321,7 +320,6 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   g.out_sf = hidden_sf;
   g.out_k_blocks = k_blocks_of(up.n);
   g.error = error;
-  g.counters = g_debug_counters;
   NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, a.map(tile_class), up.map(tile_class),
                                 up.tail_map(tile_class), g, num_sms, stream));
 
@@ -349,7 +347,6 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   d.dest_add = dest_add;
   d.row_weight = row_weight;
   d.error = error;
-  d.counters = g_debug_counters != nullptr ? g_debug_counters + 8 : nullptr;
   NMOE_CUDA(launch_grouped_gemm(down_variant, kGemmDown, hidden.map(tile_class),
                                 down.map(tile_class), down.tail_map(tile_class), d, num_sms,
                                 stream));
@@ -1080,17 +1077,6 @@ nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream_ptr, const void* inp
   return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
 }
 
-__attribute__((visibility("default"))) int nmoe_debug_counters(int enable, unsigned long long* out16) {
-  if (enable && g_debug_counters == nullptr) {
-    cudaMalloc(&g_debug_counters, 16 * sizeof(unsigned long long));
-  }
-  if (out16 != nullptr && g_debug_counters != nullptr) {
-    cudaDeviceSynchronize();
-    cudaMemcpy(out16, g_debug_counters, 16 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
-  }
-  if (g_debug_counters != nullptr) cudaMemset(g_debug_counters, 0, 16 * sizeof(unsigned long long));
-  return 0;
-}
 
 const char* nmoe_layer_last_error(const nmoe_layer* layer) {
   return layer == nullptr ? "null layer" : layer->last_error.c_str();
