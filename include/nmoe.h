@@ -152,6 +152,15 @@ NMOE_API nmoe_status nmoe_layer_enable_stage_timing(nmoe_layer* layer, int32_t e
 NMOE_API nmoe_status nmoe_layer_stage_times(nmoe_layer* layer, float* milliseconds,
                                             int32_t count);
 
+/* Expert parallelism runs collectives on a second stream while the grouped
+ * GEMMs execute.  The GEMMs are persistent kernels with one CTA per SM and
+ * nearly all of its shared memory, so a communication kernel launched beside
+ * them would not start before they finish.  This call makes the layer launch
+ * its GEMMs on (SM count - reserved_sms) SMs; 0 restores the default.  No
+ * reference counterpart (the reference runs one GPU per process without
+ * overlap). */
+NMOE_API nmoe_status nmoe_layer_reserve_sms(nmoe_layer* layer, int32_t reserved_sms);
+
 /* The intermediates ExpertLayerRunTrace exposes (expert_layer.h:63-76), for any
  * token count, as device buffers of the LAST run.  A field stays NULL when the
  * layer does not hold it.  Valid until the next run or destroy. */
@@ -228,6 +237,49 @@ NMOE_API nmoe_status nmoe_ep_shared(nmoe_layer* layer, void* stream);
 NMOE_API nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream, const void* input,
                                      nmoe_dtype input_dtype, const void* returned_rows,
                                      nmoe_dtype rows_dtype, void* output, nmoe_dtype output_dtype);
+
+/* --- expert parallelism over peer windows ------------------------------------
+ * The same four stages, with both exchanges done by the stages' own kernels
+ * over NVLink instead of host-issued collectives (fixed-capacity layout only).
+ * Every rank owns a "window": one device allocation holding its receive
+ * segments for records, its segments for returned rows, and flag words.  The
+ * other ranks of the node map it (CUDA IPC) and
+ *   - the record packer stores each record directly into the destination
+ *     rank's window,
+ *   - the down-projection epilogue of the grouped GEMM stores each weighted
+ *     row directly into the window of the rank the record came from, tile by
+ *     tile while the GEMM runs,
+ *   - small kernels raise a per-source flag (the step number) in the peer's
+ *     window after the data, and the consumer's stream waits on its own flags
+ *     with a bounded spin (NMOE_ERR_DEVICE_TIMEOUT after about eight seconds,
+ *     never a hang).
+ * One buffer per direction suffices: a rank overwrites a peer's segment for
+ * step s+1 only after its own combine of step s, which needed that peer's
+ * rows of step s, which the peer produced after reading the segment.
+ * A step records no host synchronisation and launches no collective.
+ *
+ * Setup (host): every rank calls nmoe_ep_window_create and receives a
+ * NMOE_EP_WINDOW_HANDLE_BYTES handle; the host all-gathers the handles in rank
+ * order and passes them to nmoe_ep_window_attach; a host barrier follows.
+ * Teardown: host barrier, nmoe_ep_window_detach on every rank, host barrier,
+ * then nmoe_layer_destroy.  All ranks must be processes on one node whose GPUs
+ * have peer access.  No reference counterpart. */
+#define NMOE_EP_WINDOW_HANDLE_BYTES 64
+NMOE_API nmoe_status nmoe_ep_window_create(nmoe_layer* layer, int64_t capacity_per_rank,
+                                           nmoe_dtype rows_dtype, void* handle_out);
+NMOE_API nmoe_status nmoe_ep_window_attach(nmoe_layer* layer, const void* handles_in_rank_order);
+NMOE_API nmoe_status nmoe_ep_window_detach(nmoe_layer* layer);
+/* route + pack into the peers' windows + raise the record flags */
+NMOE_API nmoe_status nmoe_ep_window_dispatch(nmoe_layer* layer, void* stream, const void* input,
+                                             nmoe_dtype input_dtype, int64_t tokens);
+/* wait for the records of source ranks [first, first+count), run this rank's
+ * experts over them, rows land in those ranks' windows, raise their row flags */
+NMOE_API nmoe_status nmoe_ep_window_experts(nmoe_layer* layer, void* stream,
+                                            int32_t first_source_rank, int32_t source_ranks);
+/* wait for every rank's rows, then combine as nmoe_ep_combine does */
+NMOE_API nmoe_status nmoe_ep_window_combine(nmoe_layer* layer, void* stream, const void* input,
+                                            nmoe_dtype input_dtype, void* output,
+                                            nmoe_dtype output_dtype);
 
 /* --- one expert FFN: down(relu^2(up(x))) with NVFP4 weights ----------------
  * The composition ExpertLayerSlice::Run applies per (token, expert)

@@ -39,7 +39,9 @@ EXPORTED_SYMBOLS = (
     "nmoe_dequant_nvfp4", "nmoe_swizzled_scale_bytes", "nmoe_swizzle_scales", "nmoe_rmsnorm",
     "nmoe_router_logits", "nmoe_router_topk", "nmoe_route_tokens_noalloc",
     "nmoe_ep_record_bytes", "nmoe_ep_dispatch", "nmoe_ep_experts", "nmoe_ep_shared",
-    "nmoe_ep_combine",
+    "nmoe_ep_combine", "nmoe_layer_reserve_sms", "nmoe_ep_window_create",
+    "nmoe_ep_window_attach", "nmoe_ep_window_detach", "nmoe_ep_window_dispatch",
+    "nmoe_ep_window_experts", "nmoe_ep_window_combine",
 )
 
 
@@ -117,6 +119,7 @@ def load_library() -> ctypes.CDLL:
     lib.nmoe_layer_copy_trace_field.argtypes = [vp, vp, i32, vp, ctypes.c_size_t]
     lib.nmoe_layer_export_hidden.argtypes = [vp, vp, vp, vp, vp, vp]
     lib.nmoe_layer_enable_stage_timing.argtypes = [vp, i32]
+    lib.nmoe_layer_reserve_sms.argtypes = [vp, i32]
     lib.nmoe_layer_stage_times.argtypes = [vp, ctypes.POINTER(ctypes.c_float), i32]
     lib.nmoe_ffn_create.argtypes = [ctypes.POINTER(_Nvfp4Matrix), ctypes.POINTER(_Nvfp4Matrix),
                                     i32, ctypes.POINTER(vp)]
@@ -140,6 +143,12 @@ def load_library() -> ctypes.CDLL:
     lib.nmoe_ep_experts.argtypes = [vp, vp, vp, i64, vp, i64, vp, ctypes.c_int]
     lib.nmoe_ep_shared.argtypes = [vp, vp]
     lib.nmoe_ep_combine.argtypes = [vp, vp, vp, ctypes.c_int, vp, ctypes.c_int, vp, ctypes.c_int]
+    lib.nmoe_ep_window_create.argtypes = [vp, i64, ctypes.c_int, vp]
+    lib.nmoe_ep_window_attach.argtypes = [vp, vp]
+    lib.nmoe_ep_window_detach.argtypes = [vp]
+    lib.nmoe_ep_window_dispatch.argtypes = [vp, vp, vp, ctypes.c_int, i64]
+    lib.nmoe_ep_window_experts.argtypes = [vp, vp, i32, i32]
+    lib.nmoe_ep_window_combine.argtypes = [vp, vp, vp, ctypes.c_int, vp, ctypes.c_int]
     lib.nmoe_route_tokens_noalloc.argtypes = [vp, vp, ctypes.c_int, i64, i32, vp, f32, vp, vp, i32,
                                               i32, i32, i32, i32, f32, vp, vp]
     _lib = lib
@@ -358,6 +367,11 @@ class ExpertLayerSlice:
     def enable_stage_timing(self, enable: bool = True) -> None:
         _check(load_library().nmoe_layer_enable_stage_timing(self._handle, 1 if enable else 0),
                "nmoe_layer_enable_stage_timing")
+
+    def reserve_sms(self, reserved: int) -> None:
+        """Keep `reserved` SMs free of the persistent GEMM CTAs (for kernels of other streams)."""
+        _check(load_library().nmoe_layer_reserve_sms(self._handle, int(reserved)),
+               "nmoe_layer_reserve_sms")
 
     def stage_times_ms(self) -> dict:
         """Device time of every stage of the last run (waits for it)."""

@@ -56,6 +56,7 @@ pack_records_kernel(const int32_t* __restrict__ top_index, const float* __restri
                     const float* __restrict__ tensor_scale, int cols, int record_bytes,
                     const int32_t* __restrict__ send_offsets, int32_t* __restrict__ rank_cursor,
                     int capacity, uint8_t* __restrict__ records,
+                    const unsigned long long* __restrict__ windows,
                     int32_t* __restrict__ send_position, int32_t* __restrict__ error) {
   const int lane = threadIdx.x & 31;
   const int pair = blockIdx.x * kPackWarps + (threadIdx.x >> 5);
@@ -64,8 +65,9 @@ pack_records_kernel(const int32_t* __restrict__ top_index, const float* __restri
   const int expert = top_index[pair];
   const int rank = expert / experts_per_rank;
   int position = 0;
+  int slot = 0;
   if (lane == 0) {
-    const int slot = atomicAdd(&rank_cursor[rank], 1);
+    slot = atomicAdd(&rank_cursor[rank], 1);
     if (capacity > 0) {
       // fixed-capacity layout: destination rank r owns records [r*capacity, (r+1)*capacity)
       position = slot < capacity ? rank * capacity + slot : -1;
@@ -79,15 +81,24 @@ pack_records_kernel(const int32_t* __restrict__ top_index, const float* __restri
     if (lane == 0) send_position[pair] = 0;
     return;
   }
-  uint8_t* record = records + static_cast<size_t>(position) * record_bytes;
-  const int packed_words = cols / 8;
-  const uint32_t* src = reinterpret_cast<const uint32_t*>(packed) + static_cast<size_t>(token) * packed_words;
-  uint32_t* dst = reinterpret_cast<uint32_t*>(record);
-  for (int w = lane; w < packed_words; w += 32) dst[w] = src[w];
+  uint8_t* record;
+  if (windows != nullptr) {
+    // the record goes straight into the destination rank's receive window (its
+    // own GPU's memory): windows[rank] is the start of this rank's segment there
+    slot = __shfl_sync(0xffffffffu, slot, 0);
+    record = reinterpret_cast<uint8_t*>(windows[rank]) + static_cast<size_t>(slot) * record_bytes;
+  } else {
+    record = records + static_cast<size_t>(position) * record_bytes;
+  }
+  const int packed_quads = cols / 32;  // 16-byte pieces; cols % 64 == 0
+  const uint4* src = reinterpret_cast<const uint4*>(packed) + static_cast<size_t>(token) * packed_quads;
+  uint4* dst = reinterpret_cast<uint4*>(record);
+  for (int w = lane; w < packed_quads; w += 32) dst[w] = src[w];
   const int sf_bytes = cols / 16;
-  const uint8_t* sf_src = sf_row_major + static_cast<size_t>(token) * sf_bytes;
-  uint8_t* sf_dst = record + cols / 2;
-  for (int b = lane; b < sf_bytes; b += 32) sf_dst[b] = sf_src[b];
+  const uint32_t* sf_src =
+      reinterpret_cast<const uint32_t*>(sf_row_major + static_cast<size_t>(token) * sf_bytes);
+  uint32_t* sf_dst = reinterpret_cast<uint32_t*>(record + cols / 2);
+  for (int b = lane; b < sf_bytes / 4; b += 32) sf_dst[b] = sf_src[b];
   if (lane == 0) {
     // the tail starts at a multiple of 4: cols % 64 == 0 is required
     uint8_t* tail = record + cols / 2 + sf_bytes;
@@ -193,6 +204,53 @@ void launch_combine_indexed_t(const void* in, const void* rows_in, const int32_t
                                                              rows, hidden, top_k, out);
 }
 
+// ---------------------------------------------------------------------------
+// peer windows: flags that ranks raise in each other's memory
+// ---------------------------------------------------------------------------
+
+__global__ void window_epoch_kernel(uint32_t* epoch) { *epoch += 1u; }
+
+// Thread r tells rank first+r that everything this rank's earlier kernels on
+// the stream wrote into that rank's window (for the current step) is there:
+// optionally one 32-bit word of payload (this rank's record count for it), then
+// the step number into this rank's flag slot over there.
+__global__ void window_signal_kernel(const unsigned long long* __restrict__ flag_slots,
+                                     const unsigned long long* __restrict__ word_slots,
+                                     const int32_t* __restrict__ words,
+                                     const uint32_t* __restrict__ epoch, int first, int count) {
+  if (static_cast<int>(threadIdx.x) >= count) return;
+  const int r = first + static_cast<int>(threadIdx.x);
+  if (word_slots != nullptr) {
+    *reinterpret_cast<volatile int32_t*>(word_slots[r]) = words[r];
+  }
+  __threadfence_system();
+  const uint32_t step = *epoch;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag_slots[r]), "r"(step) : "memory");
+}
+
+// Thread r waits until rank first+r has raised its flag for the current step.
+// Bounded: after about eight seconds the thread records kDevWaitTimeout and
+// returns, so a missing peer costs a wrong result and an error status, never a
+// hung GPU.
+__global__ void window_wait_kernel(const uint32_t* __restrict__ flags,
+                                   const uint32_t* __restrict__ epoch, int first, int count,
+                                   int32_t* __restrict__ error) {
+  if (static_cast<int>(threadIdx.x) >= count) return;
+  const uint32_t* flag = flags + first + threadIdx.x;
+  const uint32_t step = *epoch;
+  const long long start = clock64();
+  while (true) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+    if (static_cast<int32_t>(seen - step) >= 0) break;
+    if (clock64() - start > (1ll << 34)) {
+      if (error != nullptr) atomicCAS(error, kDevOk, kDevWaitTimeout);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
 }  // namespace
 
 int dispatch_record_bytes(int cols) { return (cols / 2 + cols / 16 + 12 + 15) / 16 * 16; }
@@ -210,13 +268,14 @@ cudaError_t launch_pack_records(const int32_t* top_index, const float* top_weigh
                                 int top_k, int experts_per_rank, const uint8_t* packed,
                                 const uint8_t* sf_row_major, const float* tensor_scale, int cols,
                                 const int32_t* send_offsets, int32_t* rank_cursor, int capacity,
-                                uint8_t* records, int32_t* send_position, int32_t* error,
-                                cudaStream_t stream) {
+                                uint8_t* records, const unsigned long long* windows,
+                                int32_t* send_position, int32_t* error, cudaStream_t stream) {
   const int pairs = rows * top_k;
   if (pairs <= 0 || cols % 64 != 0) return cudaErrorInvalidValue;
+  if (windows != nullptr && capacity <= 0) return cudaErrorInvalidValue;
   pack_records_kernel<<<(pairs + kPackWarps - 1) / kPackWarps, kPackWarps * 32, 0, stream>>>(
       top_index, top_weight, pairs, top_k, experts_per_rank, packed, sf_row_major, tensor_scale,
-      cols, dispatch_record_bytes(cols), send_offsets, rank_cursor, capacity, records,
+      cols, dispatch_record_bytes(cols), send_offsets, rank_cursor, capacity, records, windows,
       send_position, error);
   return cudaGetLastError();
 }
@@ -251,6 +310,27 @@ cudaError_t launch_combine_indexed(const void* in, bool in_bf16, const void* ret
     case 6: launch_combine_indexed_t<true, true, false>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
     default: launch_combine_indexed_t<true, true, true>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_window_epoch(uint32_t* epoch, cudaStream_t stream) {
+  window_epoch_kernel<<<1, 1, 0, stream>>>(epoch);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_window_signal(const unsigned long long* flag_slots,
+                                 const unsigned long long* word_slots, const int32_t* words,
+                                 const uint32_t* epoch, int first, int count,
+                                 cudaStream_t stream) {
+  if (count <= 0 || count > 64) return cudaErrorInvalidValue;
+  window_signal_kernel<<<1, 64, 0, stream>>>(flag_slots, word_slots, words, epoch, first, count);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_window_wait(const uint32_t* flags, const uint32_t* epoch, int first, int count,
+                               int32_t* error, cudaStream_t stream) {
+  if (count <= 0 || count > 64) return cudaErrorInvalidValue;
+  window_wait_kernel<<<1, 64, 0, stream>>>(flags, epoch, first, count, error);
   return cudaGetLastError();
 }
 

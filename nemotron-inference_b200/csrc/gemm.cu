@@ -410,11 +410,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           atomicCAS(args.error, kDevOk, kDevActivationRange);
         }
       } else {
-        int dest = -1;
+        // byte address of this row's output row (0 = nothing to store); with
+        // out_segments it lies in the memory of the rank the row returns to
+        unsigned long long dest = 0;
         float wt = 1.0f;
         if (row_valid) {
-          dest = args.dest_row != nullptr ? args.dest_row[grow]
-                                          : grow * args.dest_mul + args.dest_add;
+          const int d = args.dest_row != nullptr ? args.dest_row[grow]
+                                                 : grow * args.dest_mul + args.dest_add;
+          const size_t row_bytes = static_cast<size_t>(args.N) * (args.out_bf16 ? 2 : 4);
+          if (d >= 0) {
+            if (args.out_segments != nullptr) {
+              const int slot = d + args.segment_slot0;
+              const int segment = slot / args.segment_rows;
+              dest = args.out_segments[segment] +
+                     static_cast<size_t>(slot - segment * args.segment_rows) * row_bytes;
+            } else {
+              dest = reinterpret_cast<unsigned long long>(args.out_rows) + d * row_bytes;
+            }
+          }
           if (args.row_weight != nullptr) wt = args.row_weight[grow];
         }
         // Each thread owns one output row of the tile, but a store instruction
@@ -460,9 +473,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll 4
           for (int it = 0; it < 8; ++it) {
             const int rr = 4 * it + sub;
-            const int d = __shfl_sync(0xffffffffu, dest, rr);
-            if (d >= 0 && col_ok) {
-              const size_t at = static_cast<size_t>(d) * args.N + n + c4;
+            const unsigned long long d = __shfl_sync(0xffffffffu, dest, rr);
+            if (d != 0 && col_ok) {
               const float4 value = *reinterpret_cast<const float4*>(stage + rr * kStageStride + c4);
               if (args.out_bf16) {
                 const __nv_bfloat162 lo = __floats2bfloat162_rn(value.x, value.y);
@@ -470,9 +482,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 uint2 bits;
                 bits.x = *reinterpret_cast<const uint32_t*>(&lo);
                 bits.y = *reinterpret_cast<const uint32_t*>(&hi);
-                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(args.out_rows) + at) = bits;
+                *reinterpret_cast<uint2*>(d + static_cast<size_t>(n + c4) * 2) = bits;
               } else {
-                *reinterpret_cast<float4*>(args.out_rows + at) = value;
+                *reinterpret_cast<float4*>(d + static_cast<size_t>(n + c4) * 4) = value;
               }
             }
           }

@@ -54,6 +54,12 @@ struct GemmArgs {
   int32_t dest_mul = 1;
   int32_t dest_add = 0;
   const float* row_weight = nullptr;  // per activation row routing weight, nullptr => none
+  // Expert-parallel return straight into the source ranks' memory: destination
+  // index d means row (d + segment_slot0) % segment_rows of the buffer that
+  // out_segments[(d + segment_slot0) / segment_rows] points to (a peer's GPU).
+  const unsigned long long* out_segments = nullptr;
+  int32_t segment_rows = 0;
+  int32_t segment_slot0 = 0;
   int32_t* error = nullptr;           // device error slot (DeviceError)
 };
 
@@ -62,7 +68,7 @@ struct GemmArgs {
 // whole groups of 128 rows; BN = 128 makes that exact for the HBM-bound sizes.
 enum GemmVariant : int {
   kVariantPrefillUp = 0,    // BN 208, 128-row A box
-  kVariantPrefillDown = 1,  // BN 224, 128-row A box
+  kVariantPrefillDown = 1,  // BN 192, 128-row A box
   kVariantDecode = 2,       // BN 128, 32-row A box, deep pipeline
   kVariantDecodeWide = 3,   // BN 128, 128-row A box
   kVariantCount = 4,
@@ -195,8 +201,18 @@ cudaError_t launch_pack_records(const int32_t* top_index, const float* top_weigh
                                 const uint8_t* sf_row_major, const float* tensor_scale, int cols,
                                 const int32_t* send_offsets, int32_t* rank_cursor,
                                 int capacity /* per destination rank, 0 = compact */,
-                                uint8_t* records, int32_t* send_position, int32_t* error,
-                                cudaStream_t stream);
+                                uint8_t* records,
+                                const unsigned long long* windows /* nullable: per destination
+                                rank, where this rank's segment starts in that rank's memory */,
+                                int32_t* send_position, int32_t* error, cudaStream_t stream);
+// Peer windows: a step counter on the device, flags raised in other ranks'
+// memory (one thread per rank first..first+count-1), and a bounded wait.
+cudaError_t launch_window_epoch(uint32_t* epoch, cudaStream_t stream);
+cudaError_t launch_window_signal(const unsigned long long* flag_slots,
+                                 const unsigned long long* word_slots, const int32_t* words,
+                                 const uint32_t* epoch, int first, int count, cudaStream_t stream);
+cudaError_t launch_window_wait(const uint32_t* flags, const uint32_t* epoch, int first, int count,
+                               int32_t* error, cudaStream_t stream);
 cudaError_t launch_record_histogram(const uint8_t* records, int count, int cols,
                                     int local_experts, const int32_t* valid_counts, int capacity,
                                     int32_t* expert_counts, int32_t* error, cudaStream_t stream);

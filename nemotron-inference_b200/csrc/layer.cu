@@ -293,6 +293,14 @@ struct Schedule {
   int dense_rows = 0;
 };
 
+// Where the down projection's rows go when they return straight to the ranks
+// their records came from (GemmArgs::out_segments).
+struct RowSegments {
+  const unsigned long long* bases = nullptr;
+  int rows = 0;
+  int slot0 = 0;
+};
+
 // up GEMM (relu^2 + quantise) followed by down GEMM (scale, weight, scatter).
 void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass tile_class,
                       const ActivationOperand& a, const float* a_tensor_scale,
@@ -300,7 +308,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
                       const ActivationOperand& hidden, void* out_rows, const int32_t* dest_row,
                       int dest_mul, int dest_add, const float* row_weight, int32_t* error,
                       int num_sms, cudaStream_t stream, cudaEvent_t between = nullptr,
-                      bool out_bf16 = false) {
+                      bool out_bf16 = false, RowSegments segments = RowSegments()) {
   GemmArgs g;
   const GemmVariant up_variant = up.variant(tile_class);
   g.K = up.k;
@@ -346,6 +354,9 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   d.dest_mul = dest_mul;
   d.dest_add = dest_add;
   d.row_weight = row_weight;
+  d.out_segments = segments.bases;
+  d.segment_rows = segments.rows;
+  d.segment_slot0 = segments.slot0;
   d.error = error;
   NMOE_CUDA(launch_grouped_gemm(down_variant, kGemmDown, hidden.map(tile_class),
                                 down.map(tile_class), down.tail_map(tile_class), d, num_sms,
@@ -599,6 +610,30 @@ struct nmoe_layer {
   int record_bytes = 0;
   DeviceBuffer send_records, send_position, send_counts, send_offsets, rank_cursor, shared_out;
 
+  // Peer window (nmoe_ep_window_*): one allocation per rank that the other
+  // ranks map and write into: [records][returned rows][flags and counts].
+  struct PeerWindow {
+    bool attached = false;
+    int64_t capacity = 0;  // pairs per (source rank, destination rank)
+    bool rows_bf16 = true;
+    DeviceBuffer local;
+    size_t records_off = 0, rows_off = 0, flags_off = 0;
+    std::vector<void*> peer_base;  // opened mappings, nullptr for this rank
+    // u64[world] tables on the device: where this rank writes in rank r's window
+    DeviceBuffer record_segments, row_segments, record_flag_slots, row_flag_slots, count_slots;
+    DeviceBuffer epoch;  // uint32 step counter
+    uint32_t* record_flags() const { return reinterpret_cast<uint32_t*>(local.as<uint8_t>() + flags_off); }
+    uint32_t* row_flags() const { return record_flags() + 64; }
+    int32_t* counts() const { return reinterpret_cast<int32_t*>(record_flags() + 128); }
+    void close_peers() {
+      for (void*& base : peer_base) {
+        if (base != nullptr) cudaIpcCloseMemHandle(base);
+        base = nullptr;
+      }
+      attached = false;
+    }
+  } window;
+
   ActivationOperand y_op, sh_op, a_op, h_op;
   ErrorSlot error;
   int last_tokens = 0;
@@ -608,6 +643,7 @@ struct nmoe_layer {
   bool stage_timing = false;
   cudaEvent_t stage_events[kStageCount + 1] = {};
   ~nmoe_layer() {
+    window.close_peers();
     for (cudaEvent_t e : stage_events)
       if (e != nullptr) cudaEventDestroy(e);
   }
@@ -789,7 +825,8 @@ void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dt
 // Plan + permute + the two grouped GEMMs over `pairs` (row, slot) pairs whose
 // per-local-expert histogram is already in `counts`.
 void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& source, int pairs,
-                    int dest_stride, void* out_rows, bool out_bf16) {
+                    int dest_stride, void* out_rows, bool out_bf16,
+                    RowSegments segments = RowSegments()) {
   const nmoe_config& c = L->cfg;
   const int H = c.hidden_size;
   int32_t* error = L->error.device.as<int32_t>();
@@ -817,7 +854,7 @@ void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& sou
   run_expert_gemms(L->up, L->down, routed_class, L->a_op, L->a_ts.as<float>(), routed,
                    L->h_packed.as<uint8_t>(), L->h_sf.as<uint8_t>(), L->h_op, out_rows,
                    L->a_dest.as<int32_t>(), 1, 0, L->a_weight.as<float>(), error, L->num_sms,
-                   stream, L->stage_timing ? L->stage_events[6] : nullptr, out_bf16);
+                   stream, L->stage_timing ? L->stage_events[6] : nullptr, out_bf16, segments);
 }
 
 // shared expert (:814-818, :956-964, :981-1005) on the token-order quantised rows
@@ -928,6 +965,14 @@ nmoe_status nmoe_layer_sync_status(nmoe_layer* layer, void* stream) {
   }
 }
 
+nmoe_status nmoe_layer_reserve_sms(nmoe_layer* layer, int32_t reserved_sms) {
+  if (layer == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  const int all = device_sm_count();
+  if (reserved_sms < 0 || reserved_sms >= all) return NMOE_ERR_INVALID_ARGUMENT;
+  layer->num_sms = all - reserved_sms;
+  return NMOE_OK;
+}
+
 nmoe_status nmoe_layer_enable_stage_timing(nmoe_layer* layer, int32_t enable) {
   if (layer == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
   if (enable != 0) {
@@ -989,7 +1034,7 @@ nmoe_status nmoe_ep_dispatch(nmoe_layer* layer, void* stream_ptr, const void* in
                                   c.hidden_size, layer->send_offsets.as<int32_t>(),
                                   layer->rank_cursor.as<int32_t>(),
                                   static_cast<int>(capacity_per_rank),
-                                  layer->send_records.as<uint8_t>(),
+                                  layer->send_records.as<uint8_t>(), nullptr,
                                   layer->send_position.as<int32_t>(),
                                   layer->error.device.as<int32_t>(), stream));
     layer->last_tokens = static_cast<int>(tokens);
@@ -1077,6 +1122,225 @@ nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream_ptr, const void* inp
   return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
 }
 
+
+// --- peer windows: the exchanges done by the stages' own kernels ------------
+
+namespace {
+
+// the part of nmoe_ep_experts after the records are known to be in place
+void experts_over_records(nmoe_layer* layer, cudaStream_t stream, const uint8_t* records,
+                          int count, const int32_t* valid_counts, int capacity, void* out_rows,
+                          bool rows_bf16, RowSegments segments) {
+  const int H = layer->cfg.hidden_size;
+  NMOE_CUDA(cudaMemsetAsync(layer->counts.as<int32_t>(), 0,
+                            layer->local_experts * sizeof(int32_t), stream));
+  NMOE_CUDA(launch_record_histogram(records, count, H, layer->local_experts, valid_counts,
+                                    capacity, layer->counts.as<int32_t>(),
+                                    layer->error.device.as<int32_t>(), stream));
+  const size_t stride = static_cast<size_t>(layer->record_bytes);
+  const size_t tail = static_cast<size_t>(H) / 2 + static_cast<size_t>(H) / 16;
+  PermuteSource source;
+  source.packed = records;
+  source.packed_stride = stride;
+  source.sf = records + H / 2;
+  source.sf_stride = stride;
+  source.tensor_scale = reinterpret_cast<const float*>(records + tail);
+  source.tensor_scale_stride = stride;
+  source.weight = reinterpret_cast<const float*>(records + tail + 4);
+  source.weight_stride = stride;
+  source.expert = reinterpret_cast<const int32_t*>(records + tail + 8);
+  source.expert_stride = stride;
+  source.pairs_per_row = 1;
+  source.valid_counts = valid_counts;
+  source.capacity = capacity;
+  routed_experts(layer, stream, source, count, 1, out_rows, rows_bf16, segments);
+}
+
+}  // namespace
+
+nmoe_status nmoe_ep_window_create(nmoe_layer* layer, int64_t capacity_per_rank,
+                                  nmoe_dtype rows_dtype, void* handle_out) {
+  if (layer == nullptr || handle_out == nullptr || layer->ep_world <= 1 ||
+      layer->ep_world > 64 || capacity_per_rank <= 0) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == NMOE_EP_WINDOW_HANDLE_BYTES, "handle size");
+  const int64_t slots = capacity_per_rank * layer->ep_world;
+  if (slots > layer->max_pairs) return NMOE_ERR_CAPACITY;
+  try {
+    auto& w = layer->window;
+    w.close_peers();
+    w.capacity = capacity_per_rank;
+    w.rows_bf16 = rows_dtype == NMOE_BF16;
+    const size_t H = static_cast<size_t>(layer->cfg.hidden_size);
+    auto round_up = [](size_t v) { return (v + 255) / 256 * 256; };
+    w.records_off = 0;
+    w.rows_off = round_up(static_cast<size_t>(slots) * layer->record_bytes);
+    w.flags_off = w.rows_off + round_up(static_cast<size_t>(slots) * H * (w.rows_bf16 ? 2 : 4));
+    w.local.allocate(w.flags_off + 3 * 64 * sizeof(uint32_t), true);
+    w.epoch.allocate(sizeof(uint32_t), true);
+    NMOE_CUDA(cudaDeviceSynchronize());  // the zeroes are in place before any peer maps it
+    cudaIpcMemHandle_t handle;
+    NMOE_CUDA(cudaIpcGetMemHandle(&handle, w.local.as<void>()));
+    std::memcpy(handle_out, &handle, sizeof(handle));
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_ep_window_attach(nmoe_layer* layer, const void* handles) {
+  if (layer == nullptr || handles == nullptr || layer->ep_world <= 1 ||
+      layer->window.capacity <= 0) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  try {
+    auto& w = layer->window;
+    const int W = layer->ep_world, me = layer->ep_rank;
+    w.close_peers();
+    w.peer_base.assign(W, nullptr);
+    std::vector<unsigned long long> record_segments(W), row_segments(W), record_flags(W),
+        row_flags(W), counts(W);
+    const size_t H = static_cast<size_t>(layer->cfg.hidden_size);
+    const size_t row_bytes = H * (w.rows_bf16 ? 2 : 4);
+    for (int r = 0; r < W; ++r) {
+      uint8_t* base = w.local.as<uint8_t>();
+      if (r != me) {
+        cudaIpcMemHandle_t handle;
+        std::memcpy(&handle, static_cast<const uint8_t*>(handles) + r * sizeof(handle),
+                    sizeof(handle));
+        void* mapped = nullptr;
+        NMOE_CUDA(cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess));
+        w.peer_base[r] = mapped;
+        base = static_cast<uint8_t*>(mapped);
+      }
+      // in rank r's window this rank owns segment `me` of every region
+      const size_t segment = static_cast<size_t>(me) * w.capacity;
+      record_segments[r] = reinterpret_cast<unsigned long long>(
+          base + w.records_off + segment * layer->record_bytes);
+      row_segments[r] =
+          reinterpret_cast<unsigned long long>(base + w.rows_off + segment * row_bytes);
+      uint32_t* flags = reinterpret_cast<uint32_t*>(base + w.flags_off);
+      record_flags[r] = reinterpret_cast<unsigned long long>(flags + me);
+      row_flags[r] = reinterpret_cast<unsigned long long>(flags + 64 + me);
+      counts[r] = reinterpret_cast<unsigned long long>(flags + 128 + me);
+    }
+    auto upload = [&](DeviceBuffer& buffer, const std::vector<unsigned long long>& host) {
+      buffer.allocate(host.size() * sizeof(unsigned long long));
+      NMOE_CUDA(cudaMemcpy(buffer.as<void>(), host.data(),
+                           host.size() * sizeof(unsigned long long), cudaMemcpyHostToDevice));
+    };
+    upload(w.record_segments, record_segments);
+    upload(w.row_segments, row_segments);
+    upload(w.record_flag_slots, record_flags);
+    upload(w.row_flag_slots, row_flags);
+    upload(w.count_slots, counts);
+    w.attached = true;
+  } catch (const Failure& failure) {
+    layer->window.close_peers();
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_ep_window_detach(nmoe_layer* layer) {
+  if (layer == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  cudaDeviceSynchronize();
+  layer->window.close_peers();
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_ep_window_dispatch(nmoe_layer* layer, void* stream_ptr, const void* input,
+                                    nmoe_dtype input_dtype, int64_t tokens) {
+  if (layer == nullptr || input == nullptr || tokens <= 0 || !layer->window.attached) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  if (tokens > layer->cfg.max_tokens) return NMOE_ERR_CAPACITY;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  try {
+    const nmoe_config& c = layer->cfg;
+    auto& w = layer->window;
+    NMOE_CUDA(launch_window_epoch(w.epoch.as<uint32_t>(), stream));
+    route_tokens(layer, stream, input, input_dtype, static_cast<int>(tokens));
+    NMOE_CUDA(launch_dispatch_plan(layer->counts.as<int32_t>(), c.n_routed_experts,
+                                   layer->local_experts, layer->ep_world,
+                                   layer->send_counts.as<int32_t>(),
+                                   layer->send_offsets.as<int32_t>(),
+                                   layer->rank_cursor.as<int32_t>(), stream));
+    NMOE_CUDA(launch_pack_records(layer->top_index.as<int32_t>(), layer->top_weight.as<float>(),
+                                  static_cast<int>(tokens), c.top_k, layer->local_experts,
+                                  layer->y_packed.as<uint8_t>(),
+                                  layer->y_sf_row_major.as<uint8_t>(), layer->y_ts.as<float>(),
+                                  c.hidden_size, layer->send_offsets.as<int32_t>(),
+                                  layer->rank_cursor.as<int32_t>(), static_cast<int>(w.capacity),
+                                  nullptr, w.record_segments.as<unsigned long long>(),
+                                  layer->send_position.as<int32_t>(),
+                                  layer->error.device.as<int32_t>(), stream));
+    // every destination learns its record count and that the records are there
+    NMOE_CUDA(launch_window_signal(w.record_flag_slots.as<unsigned long long>(),
+                                   w.count_slots.as<unsigned long long>(),
+                                   layer->send_counts.as<int32_t>(), w.epoch.as<uint32_t>(), 0,
+                                   layer->ep_world, stream));
+    layer->last_tokens = static_cast<int>(tokens);
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_ep_window_experts(nmoe_layer* layer, void* stream_ptr, int32_t first_source_rank,
+                                   int32_t source_ranks) {
+  if (layer == nullptr || !layer->window.attached || first_source_rank < 0 ||
+      source_ranks <= 0 || first_source_rank + source_ranks > layer->ep_world) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  try {
+    auto& w = layer->window;
+    const int cap = static_cast<int>(w.capacity);
+    NMOE_CUDA(launch_window_wait(w.record_flags(), w.epoch.as<uint32_t>(), first_source_rank,
+                                 source_ranks, layer->error.device.as<int32_t>(), stream));
+    RowSegments segments;
+    segments.bases = w.row_segments.as<unsigned long long>();
+    segments.rows = cap;
+    segments.slot0 = first_source_rank * cap;
+    const uint8_t* records = w.local.as<uint8_t>() + w.records_off +
+                             static_cast<size_t>(first_source_rank) * cap * layer->record_bytes;
+    experts_over_records(layer, stream, records, source_ranks * cap,
+                         w.counts() + first_source_rank, cap, nullptr, w.rows_bf16, segments);
+    NMOE_CUDA(launch_window_signal(w.row_flag_slots.as<unsigned long long>(), nullptr, nullptr,
+                                   w.epoch.as<uint32_t>(), first_source_rank, source_ranks,
+                                   stream));
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_ep_window_combine(nmoe_layer* layer, void* stream_ptr, const void* input,
+                                   nmoe_dtype input_dtype, void* output,
+                                   nmoe_dtype output_dtype) {
+  if (layer == nullptr || !layer->window.attached || layer->last_tokens <= 0 ||
+      input == nullptr || output == nullptr) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  auto& w = layer->window;
+  cudaError_t err = launch_window_wait(w.row_flags(), w.epoch.as<uint32_t>(), 0, layer->ep_world,
+                                       layer->error.device.as<int32_t>(), stream);
+  if (err == cudaSuccess) {
+    err = launch_combine_indexed(input, input_dtype == NMOE_BF16,
+                                 w.local.as<uint8_t>() + w.rows_off, w.rows_bf16,
+                                 layer->send_position.as<int32_t>(), layer->shared_out.as<float>(),
+                                 layer->last_tokens, layer->cfg.hidden_size, layer->cfg.top_k,
+                                 output, output_dtype == NMOE_BF16, stream);
+  }
+  return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
+}
 
 const char* nmoe_layer_last_error(const nmoe_layer* layer) {
   return layer == nullptr ? "null layer" : layer->last_error.c_str();

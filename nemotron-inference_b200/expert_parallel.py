@@ -21,6 +21,7 @@ implementation; `DeviceStages` is the CUDA implementation over the C ABI.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import List, Optional
 
 import torch
@@ -43,6 +44,9 @@ class DeviceStages:
         if self.layer is None:
             raise RuntimeError("expert-parallel layer creation failed: " +
                                ExpertLayerSlice.create_error)
+        # the collectives run beside the persistent GEMMs: leave them some SMs
+        self.reserved_sms = int(os.environ.get("NMOE_EP_RESERVED_SMS", "16")) if world > 1 else 0
+        self.layer.reserve_sms(self.reserved_sms)
         self.config = config
         self.world = world
         self.rows_dtype = rows_dtype
@@ -102,6 +106,47 @@ class DeviceStages:
                                               _dtype_code(x), rows_back.data_ptr(),
                                               _dtype_code(rows_back), out.data_ptr(),
                                               _dtype_code(out)), "nmoe_ep_combine")
+
+    # -- peer windows: the exchanges done by the stages' own kernels over NVLink
+    def attach_windows(self, capacity: int, group=None) -> None:
+        """Creates this rank's window, exchanges the handles and maps the peers' windows."""
+        lib = load_library()
+        handle = (ctypes.c_uint8 * 64)()
+        _check(lib.nmoe_ep_window_create(self.layer._handle, capacity,
+                                         _dtype_code(self.rows_out), handle),
+               "nmoe_ep_window_create", self.layer._last_error())
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, bytes(handle), group=group)
+        table = (ctypes.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(gathered))
+        _check(lib.nmoe_ep_window_attach(self.layer._handle, table),
+               "nmoe_ep_window_attach", self.layer._last_error())
+        self.window_capacity = capacity
+        self.layer.reserve_sms(0)  # no collective kernels run beside the GEMMs in this mode
+        self.reserved_sms = 0
+        dist.barrier(group=group)
+
+    def detach_windows(self, group=None) -> None:
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+        _check(load_library().nmoe_ep_window_detach(self.layer._handle), "nmoe_ep_window_detach")
+        self.window_capacity = 0
+        dist.barrier(group=group)
+
+    def window_dispatch(self, x: torch.Tensor) -> None:
+        _check(load_library().nmoe_ep_window_dispatch(self.layer._handle, _stream(), x.data_ptr(),
+                                                      _dtype_code(x), x.shape[0]),
+               "nmoe_ep_window_dispatch", self.layer._last_error())
+
+    def window_experts(self, first_rank: int, ranks: int) -> None:
+        _check(load_library().nmoe_ep_window_experts(self.layer._handle, _stream(), first_rank,
+                                                     ranks),
+               "nmoe_ep_window_experts", self.layer._last_error())
+
+    def window_combine(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        _check(load_library().nmoe_ep_window_combine(self.layer._handle, _stream(), x.data_ptr(),
+                                                     _dtype_code(x), out.data_ptr(),
+                                                     _dtype_code(out)),
+               "nmoe_ep_window_combine", self.layer._last_error())
 
     # -- optional phase timing: `profile = True` makes mark() record a CUDA event on the
     #    current stream; phase_times_ms() reports them relative to the first mark
@@ -191,10 +236,33 @@ class ExpertParallelEngine:
         self.last_recv_splits: List[int] = []
 
     def step(self, x: torch.Tensor, out: torch.Tensor) -> None:
-        if self.capacity > 0:
+        if getattr(self.stages, "window_capacity", 0) > 0:
+            self._step_window(x, out)
+        elif self.capacity > 0:
             self._step_fixed(x, out)
         else:
             self._step_compact(x, out)
+
+    def _step_window(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        """Peer-window step: one stream, no collective and no host synchronisation.  The
+        shared expert runs while the peers' records are still arriving; the experts run over
+        the source ranks in groups so that the first group's rows travel back while the
+        second group is computed."""
+        st, W = self.stages, self.world
+        mark = getattr(st, "mark", lambda name: None)
+        mark("start")
+        st.window_dispatch(x)
+        mark("dispatch_done")
+        st.shared()
+        mark("shared_done")
+        bounds = [W * c // self.chunks for c in range(self.chunks + 1)]
+        for c in range(self.chunks):
+            st.window_experts(bounds[c], bounds[c + 1] - bounds[c])
+            mark(f"experts_{c}_done")
+        st.window_combine(x, out)
+        mark("combine_done")
+        cap = st.window_capacity
+        self.last_send_splits = self.last_recv_splits = [cap] * W
 
     def _step_fixed(self, x: torch.Tensor, out: torch.Tensor) -> None:
         st, cap, W = self.stages, self.capacity, self.world
@@ -235,16 +303,16 @@ class ExpertParallelEngine:
     def capture(self, x: torch.Tensor, out: torch.Tensor) -> bool:
         """Records one fixed-capacity step on (x, out) as a CUDA graph; `replay` then costs
         one launch.  Returns False (and stays eager) if the capture is not possible."""
-        if self.capacity <= 0:
+        if self.capacity <= 0 and getattr(self.stages, "window_capacity", 0) <= 0:
             return False
         try:
             for _ in range(2):
-                self._step_fixed(x, out)  # warm up: allocations, NCCL channels
+                self.step(x, out)  # warm up: allocations, NCCL channels
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             # other threads (the NCCL watchdog) make CUDA calls of their own during capture
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                self._step_fixed(x, out)
+                self.step(x, out)
             self._graph = graph
             return True
         except Exception as error:  # noqa: BLE001 - any capture failure means "stay eager"
@@ -333,6 +401,11 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
     del data
     torch.cuda.empty_cache()
     engine = ExpertParallelEngine(stages, capacity_per_rank=capacity)
+    # transport: "window" = the stages' own kernels store into the peers' memory (default);
+    # "nccl" = host-issued all-to-all collectives between the stages
+    transport = os.environ.get("NMOE_EP_TRANSPORT", "window")
+    if transport == "window":
+        stages.attach_windows(capacity)
     x_all = synthetic.make_tokens(tokens_total, H, seed=4001)
     x_host = x_all[rank * tokens:(rank + 1) * tokens].contiguous().pin_memory()
     x = x_host.cuda()
@@ -394,7 +467,26 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
                 phases[name] = phases.get(name, 0.0) + ms_at / 3
     stages.profile = False
     engine.release_graph()
+    if transport == "window":
+        stages.detach_windows()
     sent = capacity * (world - 1)
+    if transport == "window":
+        exchange = {
+            "dispatch": f"NVFP4 records, {stages.record_bytes} B per pair, stored by the packing "
+                        f"kernel straight into the destination GPU's window (fixed segments of "
+                        f"{capacity} pairs per (source, destination)); flag words signal arrival",
+            "return": "bf16 rows stored by the down-projection epilogue of the grouped GEMM "
+                      "straight into the source GPU's window, tile by tile; experts run in two "
+                      "source-rank groups",
+        }
+        launches = 10 + 2 + 6 * engine.chunks + 2
+    else:
+        exchange = {
+            "dispatch": f"NVFP4 records, {stages.record_bytes} B per pair, fixed segments of "
+                        f"{capacity} pairs per (source, destination), NCCL all-to-all",
+            "return": "bf16 rows, same segments, NCCL all-to-all in two source-rank groups",
+        }
+        launches = 13 + 6 * engine.chunks
     return {
         "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -404,18 +496,18 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
                                f"128 experts x 1856 top-6 ({128 // world} per GPU), shared 3712 "
                                "replicated, bf16 in/out",
                    "global_tokens": tokens_total, "parallelism": f"ep{world}",
-                   "dispatch": f"NVFP4 records, {stages.record_bytes} B per pair, fixed segments of "
-                               f"{capacity} pairs per (source, destination), NCCL all-to-all",
-                   "return": "bf16 rows, same segments, NCCL all-to-all in two source-rank groups",
+                   "transport": transport, **exchange,
                    "step_launch": "one CUDA graph replay" if graphed else "eager",
+                   "gemm_sms": f"{stages.reserved_sms} SMs kept free of GEMM CTAs for the "
+                               "collectives' kernels",
                    "l2": "256 MB buffer written between timed steps; working set > L2"},
         "layer_tflops": tokens_total * FLOP_PER_TOKEN_TENSOR / (ms * 1e-3) / 1e12,
         "e2e": {"value": tokens_total / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": x_host.numel() * 2 * world,
                 "d2h_bytes_per_step": out_host.numel() * 2 * world},
-        "gpu_launches": 13 * args.steps * world,
+        "gpu_launches": launches * args.steps * world,
         "clocks": clocks,
-        "a2a_bytes_rank0": {"dispatch": sent * stages.record_bytes, "return": sent * H * 2},
+        "exchange_bytes_rank0": {"dispatch": sent * stages.record_bytes, "return": sent * H * 2},
         "ep_phase_end_ms_rank0_eager": {k: round(v, 4) for k, v in phases.items()},
         "roofline": None,
     }

@@ -1,5 +1,5 @@
 """Multi-GPU test of the expert-parallel layer (needs >= 2 GPUs, skipped otherwise): NCCL
-ranks as child processes; every rank also runs the single-device layer over all tokens and
+ranks as child processes, exchanging through collectives and through peer windows; every rank also runs the single-device layer over all tokens and
 checks that its slice of the expert-parallel output is identical (FP32 return rows) or within
 the layer tolerance (bf16 return rows)."""
 import importlib
@@ -52,20 +52,29 @@ def _worker(rank, world, port, shape, tokens_per_rank):
         x = x_all[mine].contiguous()
         # compact records (host reads the split sizes) and fixed-capacity segments (no host
         # round trip; replayed as a CUDA graph when the capture succeeds)
-        for rows_dtype, capacity in ((torch.float32, 0), (torch.bfloat16, 0),
-                                     (torch.float32, 2 * tokens_per_rank * cfg.top_k // world)):
+        # ... and the same fixed segments exchanged through peer windows: the packing kernel
+        # and the GEMM epilogue store into the other GPU's memory, no collective runs
+        fixed = 2 * tokens_per_rank * cfg.top_k // world
+        for rows_dtype, capacity, window in ((torch.float32, 0, False),
+                                             (torch.bfloat16, 0, False),
+                                             (torch.float32, fixed, False),
+                                             (torch.float32, fixed, True),
+                                             (torch.bfloat16, fixed, True)):
             ep_cfg = synthetic.baseline_config(tokens_per_rank, experts=experts, hidden=hidden,
                                                routed=routed, shared=shared)
             ep_cfg.max_recv_pairs = total * cfg.top_k
             stages = ep.DeviceStages(ep_cfg, ep.shard_bindings(data.bindings, rank, world), rank,
                                      world, rows_dtype=rows_dtype)
             engine = ep.ExpertParallelEngine(stages, capacity_per_rank=capacity)
+            if window:
+                stages.attach_windows(capacity)
             out = torch.empty((tokens_per_rank, hidden), dtype=torch.float32, device="cuda")
             for _ in range(2):
                 engine.step(x, out)
             torch.cuda.synchronize()
             if capacity > 0:
-                assert torch.equal(out, expected[mine])
+                if rows_dtype == torch.float32:
+                    assert torch.equal(out, expected[mine])
                 graphed = engine.capture(x, out)
                 flag = torch.tensor([1 if graphed else 0], device="cuda")
                 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
@@ -81,6 +90,8 @@ def _worker(rank, world, port, shape, tokens_per_rank):
             else:
                 assert (out - expected[mine]).abs().max().item() <= 2e-2
             engine.release_graph()
+            if window:
+                stages.detach_windows()
             stages.layer.close()
         single.close()
     except BaseException:
