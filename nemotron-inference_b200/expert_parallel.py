@@ -232,6 +232,7 @@ class ExpertParallelEngine:
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.chunks = max(1, min(chunks if chunks is not None else 2, self.world))
+        self.window_groups = int(os.environ.get("NMOE_EP_WINDOW_GROUPS", "1"))
         self.last_send_splits: List[int] = []
         self.last_recv_splits: List[int] = []
 
@@ -245,9 +246,7 @@ class ExpertParallelEngine:
 
     def _step_window(self, x: torch.Tensor, out: torch.Tensor) -> None:
         """Peer-window step: one stream, no collective and no host synchronisation.  The
-        shared expert runs while the peers' records are still arriving; the experts run over
-        the source ranks in groups so that the first group's rows travel back while the
-        second group is computed."""
+        shared expert runs while the peers' records are still arriving."""
         st, W = self.stages, self.world
         mark = getattr(st, "mark", lambda name: None)
         mark("start")
@@ -255,8 +254,11 @@ class ExpertParallelEngine:
         mark("dispatch_done")
         st.shared()
         mark("shared_done")
-        bounds = [W * c // self.chunks for c in range(self.chunks + 1)]
-        for c in range(self.chunks):
+        # the rows travel inside the GEMM's own epilogue, so splitting the source ranks into
+        # groups buys no overlap here; one group keeps the launch count and GEMM tails low
+        groups = max(1, min(self.window_groups, W))
+        bounds = [W * c // groups for c in range(groups + 1)]
+        for c in range(groups):
             st.window_experts(bounds[c], bounds[c + 1] - bounds[c])
             mark(f"experts_{c}_done")
         st.window_combine(x, out)
@@ -476,10 +478,9 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
                         f"kernel straight into the destination GPU's window (fixed segments of "
                         f"{capacity} pairs per (source, destination)); flag words signal arrival",
             "return": "bf16 rows stored by the down-projection epilogue of the grouped GEMM "
-                      "straight into the source GPU's window, tile by tile; experts run in two "
-                      "source-rank groups",
+                      "straight into the source GPU's window, tile by tile",
         }
-        launches = 10 + 2 + 6 * engine.chunks + 2
+        launches = 10 + 2 + 6 * engine.window_groups + 2
     else:
         exchange = {
             "dispatch": f"NVFP4 records, {stages.record_bytes} B per pair, fixed segments of "
