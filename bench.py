@@ -298,6 +298,24 @@ def run_side_workloads(package, synthetic, layer, data, peaks, steps, warmup, fl
     return results
 
 
+def time_pipelined(pipe, x_host, out_host, steps, warmup, barrier=None):
+    """ms per step of `steps` batches pushed through a HostPipeline, fill and drain included."""
+    for _ in range(warmup):
+        pipe.submit(x_host, out_host)
+    pipe.synchronize()
+    if barrier is not None:
+        barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    pipe.start_after(start)
+    for _ in range(steps):
+        pipe.submit(x_host, out_host)
+    pipe.drain()
+    end.record()
+    end.synchronize()
+    return start.elapsed_time(end) / steps
+
+
 def _claim_stdout():
     """Keeps the real stdout for the single JSON line and points file descriptor 1 at
     stderr, so that libraries that print banners from native code cannot add lines."""
@@ -375,11 +393,21 @@ def main():
         layer.run_async(x, out)
         out_host.copy_(out, non_blocking=True)
 
-    e2e_times = time_steps(e2e_step, args.steps, args.warmup, flush_buf)
-    e2e_ms = float(np.mean(e2e_times))
+    # end to end from pinned host buffers: one batch at a time (upload, compute, download in
+    # turn), and through the package's HostPipeline, which overlaps the transfers of
+    # neighbouring batches with the compute; every step uploads its input and downloads
+    # its result inside the timed region either way
+    serial_ms = float(np.mean(time_steps(e2e_step, args.steps, args.warmup, flush_buf)))
+    host_pipeline = importlib.import_module("nemotron_inference_b200.host_pipeline")
+    pipe = host_pipeline.HostPipeline(lambda a, b: layer.run_async(a, b), tokens, H)
+    e2e_ms = time_pipelined(pipe, x_host, out_host, args.steps, args.warmup)
     stages = stage_profile(layer, x, out, max(3, args.steps // 2), flush_buf)
 
     up_flops = tokens * K * 2 * H * I  # one GEMM: 2 * M * N * K
+    # DRAM traffic of one routed up-GEMM launch, from the ncu capture at T=4096
+    # (profiles/grouped_gemm_prefill_T4096.md): 422,349,568 B read + 23,130,624 B written for
+    # 24576 rows, of which E * UP_BYTES are the weights
+    up_traffic = E * UP_BYTES + (422349568 + 23130624 - E * UP_BYTES) * (tokens * K) / 24576.0
     up_tf = up_flops / (stages["routed_up_gemm"] * 1e-3) / 1e12
     fp4_peak = 4 * peaks["bf16_tflops_sustained"]
     line = {
@@ -393,12 +421,19 @@ def main():
                    "l2": "256 MB buffer written between timed steps; working set > L2"},
         "layer_tflops": tokens * FLOP_PER_TOKEN_TENSOR / (ms * 1e-3) / 1e12,
         "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+                "how": "HostPipeline: pinned host batches, uploads and downloads of neighbouring "
+                       "steps overlap the compute (2 device buffers per direction); working set "
+                       "per step (718 MB weights + 88 MB in + 88 MB out) exceeds L2",
+                "one_batch_at_a_time_ms_per_step": serial_ms},
         "gpu_launches": 10 * args.steps,
         "clocks": clocks,
         "roofline": {"kernel": "grouped_gemm_kernel<BN=208, up: relu^2 + NVFP4 quantise epilogue>",
                      "bound": "tensor", "achieved": up_tf, "peak": fp4_peak, "unit": "TFLOP/s",
-                     "frac": up_tf / fp4_peak, "traffic": None,
+                     "frac": up_tf / fp4_peak, "traffic": up_traffic,
+                     "traffic_note": "ncu dram__bytes_read+write of this kernel at T=4096 "
+                                     "(445.5 MB for 24576 rows), scaled to this launch: the weight "
+                                     "bytes (359.2 MB, read once) stay, the rest grows with the rows",
                      "peak_note": f"4 x {peaks['source']} sustained dense bf16 "
                                   f"({peaks['bf16_tflops_sustained']} TF/s); no FP4 figure is "
                                   "measured on this pool; nominal dense FP4 is 9000 TF/s",

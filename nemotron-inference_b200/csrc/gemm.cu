@@ -39,6 +39,7 @@ namespace {
 constexpr int kEpilogueWarps = 8;
 constexpr int kScaleWarp = 2 + kEpilogueWarps;  // issues the block-scale copies into TMEM
 constexpr int kScaleWarps = 2;  // the copies are split between this many issuing threads
+                                // (four measured no faster than two)
 constexpr int kGemmThreads = (2 + kEpilogueWarps + kScaleWarps) * 32;
 constexpr int kStageStride = 36;  // floats per staged row: 32 + 4 keeps float4 accesses conflict-free
 

@@ -87,10 +87,19 @@ permute_kernel(PlanBuffers plan, PermuteSource src, int pairs, int tile_rows, in
   const int row = tile * 128 + position % tile_rows;
 
   const int words = cols / 8;
-  const uint32_t* from = reinterpret_cast<const uint32_t*>(
-      src.packed + static_cast<size_t>(source_row) * src.packed_stride);
-  uint32_t* dst = reinterpret_cast<uint32_t*>(sorted_packed) + static_cast<size_t>(row) * words;
-  for (int w = lane; w < words; w += 32) dst[w] = from[w];
+  const uint8_t* from_bytes = src.packed + static_cast<size_t>(source_row) * src.packed_stride;
+  uint8_t* dst_bytes = sorted_packed + static_cast<size_t>(row) * (cols / 2);
+  if (((reinterpret_cast<uintptr_t>(from_bytes) | reinterpret_cast<uintptr_t>(dst_bytes)) & 15u) == 0 &&
+      (cols & 31) == 0) {
+    // 16 bytes per lane: a warp moves 512 contiguous bytes per instruction
+    const uint4* from = reinterpret_cast<const uint4*>(from_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(dst_bytes);
+    for (int q = lane; q < words / 4; q += 32) dst[q] = from[q];
+  } else {
+    const uint32_t* from = reinterpret_cast<const uint32_t*>(from_bytes);
+    uint32_t* dst = reinterpret_cast<uint32_t*>(dst_bytes);
+    for (int w = lane; w < words; w += 32) dst[w] = from[w];
+  }
 
   const int blocks = cols / 16;
   const uint8_t* sf_src = src.sf + static_cast<size_t>(source_row) * src.sf_stride;

@@ -209,7 +209,11 @@ __device__ __forceinline__ Pick warp_pick(Pick mine) {
   return mine;
 }
 
-__global__ void __launch_bounds__(kSelectWarps * 32)
+// One warp per token runs a long dependent chain (two top-k searches, the FP64 dot
+// products, their reductions), so the kernel lives on occupancy: at most 64 registers
+// per thread (8 blocks of 4 warps per SM) and four candidates per FP64 batch.
+constexpr int kSelectBatch = 4;
+__global__ void __launch_bounds__(kSelectWarps * 32, 8)
 router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__ normalized,
                            const __nv_bfloat16* __restrict__ gate,
                            const float* __restrict__ logit_offset, const float* __restrict__ bias,
@@ -282,16 +286,17 @@ router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__
   }
   __syncwarp();
 
-  // FP64 logits of the candidates, up to eight at a time; every lane takes
+  // FP64 logits of the candidates, up to kSelectBatch at a time; every lane takes
   // eight consecutive hidden elements per step (16-byte gate loads)
   const float* y = normalized + static_cast<size_t>(row) * hidden;
   const int chunks = hidden / 8;
-  for (int base = 0; base < total; base += 8) {
-    const int batch = min(8, total - base);
-    int e[8];
-    double acc[8];
+  constexpr int kBatch = kSelectBatch;
+  for (int base = 0; base < total; base += kBatch) {
+    const int batch = min(kBatch, total - base);
+    int e[kBatch];
+    double acc[kBatch];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < kBatch; ++i) {
       e[i] = candidate_list[warp][min(base + i, total - 1)];
       acc[i] = 0.0;
     }
@@ -300,7 +305,7 @@ router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__
       const float4 y1 = *reinterpret_cast<const float4*>(y + ch * 8 + 4);
       const double a[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < kBatch; ++i) {
         if (i < batch) {
           const uint4 g = *reinterpret_cast<const uint4*>(gate + static_cast<size_t>(e[i]) * hidden +
                                                           ch * 8);
@@ -315,7 +320,7 @@ router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__
       }
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < kBatch; ++i) {
       if (i < batch) {
         double v = acc[i];
 #pragma unroll
