@@ -22,6 +22,7 @@ CUDA_INCLUDE = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
 PORT_LIB = os.path.join(HERE, "libnmoe_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_BIN = os.path.join(REF_DIR, "ref_driver")
+SHIM_BIN = os.path.join(REF_DIR, "shim_driver")
 
 
 def _newer(target, sources):
@@ -61,6 +62,34 @@ def build_reference(force=False):
     return REF_BIN
 
 
+def build_shim_driver(force=False):
+    """The drop-in shim (nemotron-inference_b200/shim) linked with the reference's own
+    device tensor and cuBLASLt handle classes and libnmoe_b200.so: proves that code written
+    against the reference's headers runs on the new layer.  Returns the binary path, or
+    None when it can be neither built nor found."""
+    backend = os.path.join(REFERENCE_ROOT, "runtime", "src", "backend")
+    package = os.path.join(os.path.dirname(HERE), "nemotron-inference_b200")
+    library = os.path.join(package, "libnmoe_b200.so")
+    if not os.path.isdir(backend) or not os.path.exists(library):
+        return SHIM_BIN if os.path.exists(SHIM_BIN) else None
+    sources = [os.path.join(HERE, "shim_driver.cpp"),
+               os.path.join(package, "shim", "expert_layer_shim.cpp"),
+               os.path.join(backend, "device_tensor.cpp"),
+               os.path.join(backend, "cublaslt_handle.cpp")]
+    if not force and _newer(SHIM_BIN, sources + [os.path.join(os.path.dirname(HERE), "include", "nmoe.h")]):
+        return SHIM_BIN
+    os.makedirs(REF_DIR, exist_ok=True)
+    cuda_lib = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/lib64"
+    cmd = ["g++", "-std=c++20", "-O2", "-I", os.path.join(REFERENCE_ROOT, "runtime", "include"),
+           "-I", os.path.join(os.path.dirname(HERE), "include"), "-I", CUDA_INCLUDE, *sources,
+           "-L", package, "-lnmoe_b200", "-L", cuda_lib, "-lcudart", "-lcublasLt",
+           "-Wl,-rpath,$ORIGIN/../../nemotron-inference_b200", "-Wl,-rpath," + cuda_lib,
+           "-o", SHIM_BIN]
+    subprocess.run(cmd, check=True)
+    return SHIM_BIN
+
+
 if __name__ == "__main__":
     print(build_port(force="--force" in sys.argv))
     print(build_reference(force="--force" in sys.argv))
+    print(build_shim_driver(force="--force" in sys.argv))

@@ -57,3 +57,20 @@ def test_invalid_arguments_are_rejected_without_a_device(package):
     assert lib.nmoe_quantize_nvfp4(None, None, 0, 1, 16, 1, None, None, None, None) == 1
     assert lib.nmoe_layer_run(None, None, None, 0, 1, None, 0) == 1
     assert lib.nmoe_layer_create(None, None, None) == 1
+
+
+def test_cpp_shim_compiles_against_the_reference_headers():
+    """nemotron-inference_b200/shim/expert_layer_shim.cpp defines the members that the
+    reference's expert_layer.h declares; it must compile against that very header."""
+    import shutil
+    import subprocess
+    reference_include = os.path.join(os.environ.get("NMOE_REFERENCE_ROOT", "/root/reference"),
+                                     "runtime", "include")
+    if not os.path.isdir(reference_include) or shutil.which("g++") is None:
+        pytest.skip("needs the reference checkout and g++")
+    cuda_include = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    shim = os.path.join(ROOT, "nemotron-inference_b200", "shim", "expert_layer_shim.cpp")
+    done = subprocess.run(["g++", "-std=c++20", "-fsyntax-only", "-Wall", "-I", reference_include,
+                           "-I", os.path.join(ROOT, "include"), "-I", cuda_include, shim],
+                          capture_output=True, text=True)
+    assert done.returncode == 0, done.stderr
