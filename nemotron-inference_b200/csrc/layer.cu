@@ -639,11 +639,21 @@ struct nmoe_layer {
   int last_tokens = 0;
   std::string last_error;
 
+  // Small batches: the shared expert runs on a stream of the layer's own beside the
+  // router, plan and permute kernels (it needs only the quantised rows) and joins
+  // before the combine.  Its GEMMs use a few dozen SMs at these sizes.
+  cudaStream_t side_stream = nullptr;
+  cudaEvent_t quant_done = nullptr, shared_done = nullptr;
+  int fork_max_tokens = 256;
+
   // optional per-stage CUDA events (nmoe_layer_enable_stage_timing)
   bool stage_timing = false;
   cudaEvent_t stage_events[kStageCount + 1] = {};
   ~nmoe_layer() {
     window.close_peers();
+    if (quant_done != nullptr) cudaEventDestroy(quant_done);
+    if (shared_done != nullptr) cudaEventDestroy(shared_done);
+    if (side_stream != nullptr) cudaStreamDestroy(side_stream);
     for (cudaEvent_t e : stage_events)
       if (e != nullptr) cudaEventDestroy(e);
   }
@@ -682,6 +692,11 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
 
   L->cfg = c;
   L->num_sms = device_sm_count();
+  if (std::getenv("NMOE_NO_SHARED_FORK") == nullptr) {
+    NMOE_CUDA(cudaStreamCreateWithFlags(&L->side_stream, cudaStreamNonBlocking));
+    NMOE_CUDA(cudaEventCreateWithFlags(&L->quant_done, cudaEventDisableTiming));
+    NMOE_CUDA(cudaEventCreateWithFlags(&L->shared_done, cudaEventDisableTiming));
+  }
   L->local_experts = w.n_local_experts;
   L->first_local_expert = w.first_local_expert;
   cudaStream_t stream = nullptr;
@@ -783,7 +798,7 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
 // RMSNorm + activation quantiser + router: fills normalized, y_*, logits,
 // top_index / top_weight and the per-expert histogram `counts` (global ids).
 void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dtype in_dtype,
-                  int tokens) {
+                  int tokens, cudaEvent_t after_quantise = nullptr) {
   const nmoe_config& c = L->cfg;
   const int H = c.hidden_size, E = c.n_routed_experts, K = c.top_k;
   int32_t* error = L->error.device.as<int32_t>();
@@ -797,6 +812,7 @@ void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dt
                               k_blocks_of(H), L->y_ts.as<float>(), stream,
                               two_pass_router ? L->y_split.as<__nv_bfloat16>() : nullptr,
                               static_cast<size_t>(L->split_plane_rows) * H));
+  if (after_quantise != nullptr) NMOE_CUDA(cudaEventRecord(after_quantise, stream));
   L->mark(1, stream);
   // gate projection (:797-799) and top-k (:881)
   NMOE_CUDA(cudaMemsetAsync(L->counts.as<int32_t>(), 0, E * sizeof(int32_t), stream));
@@ -891,11 +907,21 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
                     int tokens, void* output, nmoe_dtype out_dtype) {
   const nmoe_config& c = L->cfg;
   const int H = c.hidden_size, K = c.top_k;
-  route_tokens(L, stream, input, in_dtype, tokens);
+  const bool fork = L->side_stream != nullptr && !L->stage_timing && tokens <= L->fork_max_tokens;
+  route_tokens(L, stream, input, in_dtype, tokens, fork ? L->quant_done : nullptr);
+  if (fork) {
+    NMOE_CUDA(cudaStreamWaitEvent(L->side_stream, L->quant_done, 0));
+    shared_expert(L, L->side_stream, tokens, L->parts.as<float>(), K + 1, K, nullptr);
+    NMOE_CUDA(cudaEventRecord(L->shared_done, L->side_stream));
+  }
   routed_experts(L, stream, local_source(L), tokens * K, K + 1, L->parts.as<float>(), false);
   L->mark(7, stream);
-  shared_expert(L, stream, tokens, L->parts.as<float>(), K + 1, K,
-                L->stage_timing ? L->stage_events[8] : nullptr);
+  if (fork) {
+    NMOE_CUDA(cudaStreamWaitEvent(stream, L->shared_done, 0));
+  } else {
+    shared_expert(L, stream, tokens, L->parts.as<float>(), K + 1, K,
+                  L->stage_timing ? L->stage_events[8] : nullptr);
+  }
   // routed sum in selection order, mixer and residual (:951-953, :1064-1069)
   L->mark(9, stream);
   NMOE_CUDA(launch_combine(input, in_dtype == NMOE_BF16, L->parts.as<float>(), tokens, H, K,
