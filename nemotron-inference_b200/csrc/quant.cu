@@ -71,28 +71,32 @@ norm_quant_kernel(const void* __restrict__ in, int rows, int cols,
 
   float inv_rms = 1.0f;
   if (norm_weight != nullptr) {
-    // partial[t], t = lane + 32 j, accumulates columns t, t+256, ... in order
+    // The reference kernel keeps 256 partial sums, partial[t] accumulating columns
+    // t, t+256, ... in order, and folds them with a halving tree.  Lane L owns
+    // t = 8L .. 8L+7: its it-th 8-element chunk (columns 8(L+32 it) ..) is exactly
+    // columns t + 256 it, so 16-byte loads reproduce the same partial sums.
     float partial[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int base = 0; base < cols; base += 256) {
+    const int row_chunks = cols / 8;
+    for (int ch = lane; ch < row_chunks; ch += 32) {
+      float x[8];
+      load8<BF16>(in, row_base + static_cast<size_t>(ch) * 8, x);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int c = base + lane + 32 * j;
-        if (c < cols) {
-          const float x = load_scalar<BF16>(in, row_base + c);
-          partial[j] = __fmaf_rn(x, x, partial[j]);
-        }
+      for (int i = 0; i < 8; ++i) partial[i] = __fmaf_rn(x[i], x[i], partial[i]);
+    }
+    // halving tree: strides 128, 64, 32, 16, 8 pair lane L with L+16, +8, +4, +2, +1
+    // (same i); strides 4, 2, 1 stay inside the lane
+#pragma unroll
+    for (int stride = 16; stride > 0; stride >>= 1) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        partial[i] = __fadd_rn(partial[i], __shfl_down_sync(0xffffffffu, partial[i], stride));
       }
     }
-    // halving tree over the 256 partials: strides 128, 64, 32 stay inside a lane
 #pragma unroll
-    for (int j = 0; j < 4; ++j) partial[j] = __fadd_rn(partial[j], partial[j + 4]);
+    for (int i = 0; i < 4; ++i) partial[i] = __fadd_rn(partial[i], partial[i + 4]);
     partial[0] = __fadd_rn(partial[0], partial[2]);
     partial[1] = __fadd_rn(partial[1], partial[3]);
     float sum = __fadd_rn(partial[0], partial[1]);
-#pragma unroll
-    for (int stride = 16; stride > 0; stride >>= 1) {
-      sum = __fadd_rn(sum, __shfl_down_sync(0xffffffffu, sum, stride));
-    }
     sum = __shfl_sync(0xffffffffu, sum, 0);
     const float mean = __fdiv_rn(sum, static_cast<float>(cols));
     inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
