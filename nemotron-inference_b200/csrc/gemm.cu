@@ -110,7 +110,6 @@ __device__ __forceinline__ void issue_scale_copies(uint32_t sf_tmem, uint32_t sf
 template <class C, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_b_tail, const GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) &
@@ -147,7 +146,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
-    prefetch_tensormap(&tmap_b);
     prefetch_tensormap(&tmap_b_tail);
   }
   if (warp == 1) {
@@ -506,7 +504,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 template <class C>
-cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a,
                        const CUtensorMap& tmap_b_tail, const GemmArgs& args, int num_sms,
                        cudaStream_t stream) {
   int grid = num_sms;
@@ -520,12 +518,12 @@ cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a, const CUtensorM
     auto kernel = grouped_gemm_kernel<C, kGemmUp>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (err != cudaSuccess) return err;
-    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, tmap_b_tail, args);
+    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b_tail, args);
   } else if constexpr (C::ROW_STAGING) {
     auto kernel = grouped_gemm_kernel<C, kGemmDown>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (err != cudaSuccess) return err;
-    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b, tmap_b_tail, args);
+    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b_tail, args);
   } else {
     return cudaErrorInvalidValue;  // this tile shape has no staging for the down epilogue
   }
@@ -623,13 +621,13 @@ GemmVariantInfo gemm_variant_info(GemmVariant v) {
 }
 
 cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const CUtensorMap& tmap_a,
-                                const CUtensorMap& tmap_b, const CUtensorMap& tmap_b_tail,
+                                const CUtensorMap& tmap_b_tail,
                                 const GemmArgs& args, int num_sms, cudaStream_t stream) {
   switch (v) {
-    case kVariantPrefillUp: return launch_cfg<CfgPrefillUp>(mode, tmap_a, tmap_b, tmap_b_tail, args, num_sms, stream);
-    case kVariantPrefillDown: return launch_cfg<CfgPrefillDown>(mode, tmap_a, tmap_b, tmap_b_tail, args, num_sms, stream);
-    case kVariantDecode: return launch_cfg<CfgDecode>(mode, tmap_a, tmap_b, tmap_b_tail, args, num_sms, stream);
-    case kVariantDecodeWide: return launch_cfg<CfgDecodeWide>(mode, tmap_a, tmap_b, tmap_b_tail, args, num_sms, stream);
+    case kVariantPrefillUp: return launch_cfg<CfgPrefillUp>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
+    case kVariantPrefillDown: return launch_cfg<CfgPrefillDown>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
+    case kVariantDecode: return launch_cfg<CfgDecode>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
+    case kVariantDecodeWide: return launch_cfg<CfgDecodeWide>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
     default: return cudaErrorInvalidValue;
   }
 }

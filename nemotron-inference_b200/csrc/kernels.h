@@ -84,7 +84,7 @@ struct GemmVariantInfo {
 
 GemmVariantInfo gemm_variant_info(GemmVariant v);
 cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const CUtensorMap& tmap_a,
-                                const CUtensorMap& tmap_b, const CUtensorMap& tmap_b_tail,
+                                const CUtensorMap& tmap_b_tail,
                                 const GemmArgs& args, int num_sms, cudaStream_t stream);
 
 // Packed weights [experts][N][K/2] -> K-block-major (device to device): every

@@ -177,8 +177,8 @@ struct WeightStack {
   GemmVariant prefill_variant = kVariantPrefillUp;
   GemmVariant decode_variant = kVariantDecode;
   GemmVariant decode_wide_variant = kVariantDecodeWide;
-  CUtensorMap map_prefill;
-  CUtensorMap map_decode;
+  // tensor maps exist only for the partial last K block; full K blocks are
+  // plain bulk copies of contiguous, pre-swizzled panels
   CUtensorMap tail_prefill;
   CUtensorMap tail_decode;
 
@@ -245,16 +245,10 @@ struct WeightStack {
     NMOE_CUDA(relayout_weight_packed(row_major.as<uint8_t>(), count, rows, cols, tail_pitch,
                                      packed.as<uint8_t>(), packed_tail.as<uint8_t>(), stream));
     NMOE_CUDA(cudaStreamSynchronize(stream));  // the row-major staging copies die here
-    if (kb_full > 0) {
-      map_prefill = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, pi.bn);
-      map_decode = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, di.bn);
-    } else {
-      map_prefill = tail_prefill;
-      map_decode = tail_decode;
-    }
-    if (tail_bytes == 0) {  // never read: k_blocks == kb_full
-      tail_prefill = map_prefill;
-      tail_decode = map_decode;
+    if (tail_bytes == 0) {
+      // never read (k_blocks == kb_full), but the kernel takes a valid map
+      tail_prefill = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, pi.bn);
+      tail_decode = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, di.bn);
     }
   }
 
@@ -262,7 +256,6 @@ struct WeightStack {
     return c == kClassPrefill ? prefill_variant
                               : c == kClassDecode ? decode_variant : decode_wide_variant;
   }
-  const CUtensorMap& map(TileClass c) const { return c == kClassPrefill ? map_prefill : map_decode; }
   const CUtensorMap& tail_map(TileClass c) const {
     return c == kClassPrefill ? tail_prefill : tail_decode;
   }
@@ -328,7 +321,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   g.out_sf = hidden_sf;
   g.out_k_blocks = k_blocks_of(up.n);
   g.error = error;
-  NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, a.map(tile_class), up.map(tile_class),
+  NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, a.map(tile_class),
                                 up.tail_map(tile_class), g, num_sms, stream));
 
   if (between != nullptr) cudaEventRecord(between, stream);
@@ -359,7 +352,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   d.segment_slot0 = segments.slot0;
   d.error = error;
   NMOE_CUDA(launch_grouped_gemm(down_variant, kGemmDown, hidden.map(tile_class),
-                                down.map(tile_class), down.tail_map(tile_class), d, num_sms,
+                                down.tail_map(tile_class), d, num_sms,
                                 stream));
 }
 

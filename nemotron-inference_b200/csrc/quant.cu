@@ -77,6 +77,7 @@ norm_quant_kernel(const void* __restrict__ in, int rows, int cols,
     // columns t + 256 it, so 16-byte loads reproduce the same partial sums.
     float partial[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     const int row_chunks = cols / 8;
+#pragma unroll 4
     for (int ch = lane; ch < row_chunks; ch += 32) {
       float x[8];
       load8<BF16>(in, row_base + static_cast<size_t>(ch) * 8, x);
@@ -106,6 +107,7 @@ norm_quant_kernel(const void* __restrict__ in, int rows, int cols,
   float ts = 1.0f;
   if constexpr (PER_ROW_SCALE) {
     float amax = 0.0f;
+#pragma unroll 4
     for (int ch = lane; ch < chunks; ch += 32) {
       float v[8];
       load8<BF16>(in, row_base + static_cast<size_t>(ch) * 8, v);

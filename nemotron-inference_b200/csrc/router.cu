@@ -39,7 +39,31 @@ router_logits_kernel(const float* __restrict__ y, const float* __restrict__ gate
 #pragma unroll
     for (int j = 0; j < EPW; ++j) acc[i][j] = 0.0;
 
-  for (int k = lane; k < hidden; k += 32) {
+  int k_begin = lane;
+  if constexpr (TPW == 1) {
+    if ((hidden & 127) == 0) {
+      // small batches: 16-byte loads, three steps in flight (the loop is a chain of
+      // load -> FMA otherwise and costs a memory latency per step)
+      const float4* y4 = reinterpret_cast<const float4*>(y + static_cast<size_t>(t0) * hidden);
+      const int quads = hidden / 4;
+#pragma unroll 3
+      for (int q = lane; q < quads; q += 32) {
+        const float4 a4 = y4[q];
+        const double a[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+        for (int j = 0; j < EPW; ++j) {
+          const float4 w4 =
+              reinterpret_cast<const float4*>(gate + static_cast<size_t>(e0 + j) * hidden)[q];
+          acc[0][j] = fma(a[0], static_cast<double>(w4.x), acc[0][j]);
+          acc[0][j] = fma(a[1], static_cast<double>(w4.y), acc[0][j]);
+          acc[0][j] = fma(a[2], static_cast<double>(w4.z), acc[0][j]);
+          acc[0][j] = fma(a[3], static_cast<double>(w4.w), acc[0][j]);
+        }
+      }
+      k_begin = hidden;  // nothing left for the scalar loop
+    }
+  }
+  for (int k = k_begin; k < hidden; k += 32) {
     double a[TPW];
 #pragma unroll
     for (int i = 0; i < TPW; ++i) {

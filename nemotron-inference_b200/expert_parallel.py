@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import sys
 from typing import List, Optional
 
 import torch
@@ -108,22 +109,38 @@ class DeviceStages:
                                               _dtype_code(out)), "nmoe_ep_combine")
 
     # -- peer windows: the exchanges done by the stages' own kernels over NVLink
-    def attach_windows(self, capacity: int, group=None) -> None:
-        """Creates this rank's window, exchanges the handles and maps the peers' windows."""
+    def attach_windows(self, capacity: int, group=None) -> bool:
+        """Creates this rank's window, exchanges the handles and maps the peers' windows.
+        Every rank takes part in every collective of the set-up whether or not its own
+        steps succeeded, so the ranks agree on the outcome: True when all of them are
+        attached, False (and nothing left attached) otherwise; `attach_error` says why."""
         lib = load_library()
         handle = (ctypes.c_uint8 * 64)()
-        _check(lib.nmoe_ep_window_create(self.layer._handle, capacity,
-                                         _dtype_code(self.rows_out), handle),
-               "nmoe_ep_window_create", self.layer._last_error())
+        self.attach_error = ""
+        status = lib.nmoe_ep_window_create(self.layer._handle, capacity,
+                                           _dtype_code(self.rows_out), handle)
+        if status != NMOE_OK:
+            self.attach_error = f"nmoe_ep_window_create: {self.layer._last_error() or status}"
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, bytes(handle), group=group)
-        table = (ctypes.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(gathered))
-        _check(lib.nmoe_ep_window_attach(self.layer._handle, table),
-               "nmoe_ep_window_attach", self.layer._last_error())
+        dist.all_gather_object(gathered, (status == NMOE_OK, bytes(handle)), group=group)
+        everyone = all(ok for ok, _ in gathered)
+        if everyone:
+            table = (ctypes.c_uint8 * (64 * self.world)).from_buffer_copy(
+                b"".join(h for _, h in gathered))
+            status = lib.nmoe_ep_window_attach(self.layer._handle, table)
+            if status != NMOE_OK:
+                self.attach_error = f"nmoe_ep_window_attach: {self.layer._last_error() or status}"
+        outcome = [None] * self.world
+        dist.all_gather_object(outcome, everyone and status == NMOE_OK, group=group)
+        if not all(outcome):
+            lib.nmoe_ep_window_detach(self.layer._handle)
+            dist.barrier(group=group)
+            return False
         self.window_capacity = capacity
         self.layer.reserve_sms(0)  # no collective kernels run beside the GEMMs in this mode
         self.reserved_sms = 0
         dist.barrier(group=group)
+        return True
 
     def detach_windows(self, group=None) -> None:
         torch.cuda.synchronize()
@@ -407,7 +424,12 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
     # "nccl" = host-issued all-to-all collectives between the stages
     transport = os.environ.get("NMOE_EP_TRANSPORT", "window")
     if transport == "window":
-        stages.attach_windows(capacity)
+        # peer windows need CUDA IPC between the ranks' processes; where a rank cannot map
+        # its peers, every rank falls back to the collectives
+        if not stages.attach_windows(capacity):
+            print(f"rank {rank}: peer windows unavailable ({stages.attach_error}); using NCCL",
+                  file=sys.stderr)
+            transport = "nccl"
     x_all = synthetic.make_tokens(tokens_total, H, seed=4001)
     x_host = x_all[rank * tokens:(rank + 1) * tokens].contiguous().pin_memory()
     x = x_host.cuda()

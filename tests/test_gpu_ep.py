@@ -67,7 +67,7 @@ def _worker(rank, world, port, shape, tokens_per_rank):
                                      world, rows_dtype=rows_dtype)
             engine = ep.ExpertParallelEngine(stages, capacity_per_rank=capacity)
             if window:
-                stages.attach_windows(capacity)
+                assert stages.attach_windows(capacity), stages.attach_error
             out = torch.empty((tokens_per_rank, hidden), dtype=torch.float32, device="cuda")
             for _ in range(2):
                 engine.step(x, out)
