@@ -417,6 +417,20 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
     cfg.max_recv_pairs = capacity * world
     data = synthetic.make_layer(cfg, seed=4000, device="cuda")
     stages = DeviceStages(cfg, shard_bindings(data.bindings, rank, world), rank, world)
+    # Efficiency baseline: ONE GPU holding all experts, running the per-GPU token count of
+    # this configuration (tokens / world).  Rank 0 measures it before the ranks start to
+    # exchange; efficiency = aggregate tokens/s / (world x that figure).
+    single_ms = None
+    if rank == 0:
+        single_cfg = synthetic.baseline_config(max_tokens=tokens)
+        single = package.ExpertLayerSlice.create(single_cfg, data.bindings)
+        if single is not None:
+            xs = synthetic.make_tokens(tokens_total, H, seed=4001)[:tokens].cuda()
+            outs = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+            single_ms = float(np.mean(bench_module.time_steps(
+                lambda: single.run_async(xs, outs), args.steps, args.warmup, flush_buf)))
+            single.close()
+            del xs, outs
     del data
     torch.cuda.empty_cache()
     engine = ExpertParallelEngine(stages, capacity_per_rank=capacity)
@@ -548,6 +562,12 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
                 "one_batch_at_a_time_ms_per_step": serial_ms},
         "gpu_launches": launches * args.steps * world,
         "clocks": clocks,
+        "per_gpu_tokens": tokens,
+        "single_gpu_same_tokens": None if single_ms is None else {
+            "what": f"one GPU, all 128 experts, T={tokens} (the per-GPU token count of this run)",
+            "ms_per_step": single_ms, "tokens_per_s": tokens / (single_ms * 1e-3)},
+        "ep_efficiency": None if single_ms is None else
+        (tokens_total / (ms * 1e-3)) / (world * tokens / (single_ms * 1e-3)),
         "exchange_bytes_rank0": {"dispatch": sent * stages.record_bytes, "return": sent * H * 2},
         "ep_phase_end_ms_rank0_eager": {k: round(v, 4) for k, v in phases.items()},
         "roofline": None,
