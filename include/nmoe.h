@@ -269,6 +269,10 @@ NMOE_API nmoe_status nmoe_ep_window_create(nmoe_layer* layer, int64_t capacity_p
                                            nmoe_dtype rows_dtype, void* handle_out);
 NMOE_API nmoe_status nmoe_ep_window_attach(nmoe_layer* layer, const void* handles_in_rank_order);
 NMOE_API nmoe_status nmoe_ep_window_detach(nmoe_layer* layer);
+/* With enable != 0, nmoe_ep_window_dispatch also starts the shared expert, on a
+ * stream of the layer's own, as soon as the rows are quantised, and
+ * nmoe_ep_window_combine joins it: nmoe_ep_shared must then not be called. */
+NMOE_API nmoe_status nmoe_ep_window_fork_shared(nmoe_layer* layer, int32_t enable);
 /* route + pack into the peers' windows + raise the record flags */
 NMOE_API nmoe_status nmoe_ep_window_dispatch(nmoe_layer* layer, void* stream, const void* input,
                                              nmoe_dtype input_dtype, int64_t tokens);

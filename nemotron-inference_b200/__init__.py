@@ -41,7 +41,7 @@ EXPORTED_SYMBOLS = (
     "nmoe_ep_record_bytes", "nmoe_ep_dispatch", "nmoe_ep_experts", "nmoe_ep_shared",
     "nmoe_ep_combine", "nmoe_layer_reserve_sms", "nmoe_ep_window_create",
     "nmoe_ep_window_attach", "nmoe_ep_window_detach", "nmoe_ep_window_dispatch",
-    "nmoe_ep_window_experts", "nmoe_ep_window_combine",
+    "nmoe_ep_window_experts", "nmoe_ep_window_combine", "nmoe_ep_window_fork_shared",
 )
 
 
@@ -146,6 +146,7 @@ def load_library() -> ctypes.CDLL:
     lib.nmoe_ep_window_create.argtypes = [vp, i64, ctypes.c_int, vp]
     lib.nmoe_ep_window_attach.argtypes = [vp, vp]
     lib.nmoe_ep_window_detach.argtypes = [vp]
+    lib.nmoe_ep_window_fork_shared.argtypes = [vp, i32]
     lib.nmoe_ep_window_dispatch.argtypes = [vp, vp, vp, ctypes.c_int, i64]
     lib.nmoe_ep_window_experts.argtypes = [vp, vp, i32, i32]
     lib.nmoe_ep_window_combine.argtypes = [vp, vp, vp, ctypes.c_int, vp, ctypes.c_int]

@@ -638,6 +638,8 @@ struct nmoe_layer {
   cudaStream_t side_stream = nullptr;
   cudaEvent_t quant_done = nullptr, shared_done = nullptr;
   int fork_max_tokens = 256;
+  bool window_fork_shared = false;    // nmoe_ep_window_fork_shared
+  bool window_shared_pending = false;
 
   // optional per-stage CUDA events (nmoe_layer_enable_stage_timing)
   bool stage_timing = false;
@@ -1271,6 +1273,13 @@ nmoe_status nmoe_ep_window_detach(nmoe_layer* layer) {
   return NMOE_OK;
 }
 
+nmoe_status nmoe_ep_window_fork_shared(nmoe_layer* layer, int32_t enable) {
+  if (layer == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  if (enable != 0 && layer->side_stream == nullptr) return NMOE_ERR_UNSUPPORTED;
+  layer->window_fork_shared = enable != 0;
+  return NMOE_OK;
+}
+
 nmoe_status nmoe_ep_window_dispatch(nmoe_layer* layer, void* stream_ptr, const void* input,
                                     nmoe_dtype input_dtype, int64_t tokens) {
   if (layer == nullptr || input == nullptr || tokens <= 0 || !layer->window.attached) {
@@ -1282,7 +1291,19 @@ nmoe_status nmoe_ep_window_dispatch(nmoe_layer* layer, void* stream_ptr, const v
     const nmoe_config& c = layer->cfg;
     auto& w = layer->window;
     NMOE_CUDA(launch_window_epoch(w.epoch.as<uint32_t>(), stream));
-    route_tokens(layer, stream, input, input_dtype, static_cast<int>(tokens));
+    // The shared expert needs only the quantised rows: with `fork_shared` it starts on
+    // the layer's own stream right after the quantiser and runs beside the router and
+    // the packing; nmoe_ep_window_combine joins it.
+    const bool fork = layer->side_stream != nullptr && layer->window_fork_shared;
+    route_tokens(layer, stream, input, input_dtype, static_cast<int>(tokens),
+                 fork ? layer->quant_done : nullptr);
+    if (fork) {
+      NMOE_CUDA(cudaStreamWaitEvent(layer->side_stream, layer->quant_done, 0));
+      shared_expert(layer, layer->side_stream, static_cast<int>(tokens),
+                    layer->shared_out.as<float>(), 1, 0, nullptr);
+      NMOE_CUDA(cudaEventRecord(layer->shared_done, layer->side_stream));
+    }
+    layer->window_shared_pending = fork;
     NMOE_CUDA(launch_dispatch_plan(layer->counts.as<int32_t>(), c.n_routed_experts,
                                    layer->local_experts, layer->ep_world,
                                    layer->send_counts.as<int32_t>(),
@@ -1351,6 +1372,10 @@ nmoe_status nmoe_ep_window_combine(nmoe_layer* layer, void* stream_ptr, const vo
   auto& w = layer->window;
   cudaError_t err = launch_window_wait(w.row_flags(), w.epoch.as<uint32_t>(), 0, layer->ep_world,
                                        layer->error.device.as<int32_t>(), stream);
+  if (err == cudaSuccess && layer->window_shared_pending) {
+    err = cudaStreamWaitEvent(stream, layer->shared_done, 0);
+    layer->window_shared_pending = false;
+  }
   if (err == cudaSuccess) {
     err = launch_combine_indexed(input, input_dtype == NMOE_BF16,
                                  w.local.as<uint8_t>() + w.rows_off, w.rows_bf16,

@@ -137,6 +137,9 @@ class DeviceStages:
             dist.barrier(group=group)
             return False
         self.window_capacity = capacity
+        # the shared expert starts inside the dispatch stage, beside the router kernels
+        self.fork_shared = os.environ.get("NMOE_EP_FORK_SHARED", "1") == "1" and \
+            lib.nmoe_ep_window_fork_shared(self.layer._handle, 1) == NMOE_OK
         self.layer.reserve_sms(0)  # no collective kernels run beside the GEMMs in this mode
         self.reserved_sms = 0
         dist.barrier(group=group)
@@ -269,7 +272,8 @@ class ExpertParallelEngine:
         mark("start")
         st.window_dispatch(x)
         mark("dispatch_done")
-        st.shared()
+        if not getattr(st, "fork_shared", False):
+            st.shared()
         mark("shared_done")
         # the rows travel inside the GEMM's own epilogue, so splitting the source ranks into
         # groups buys no overlap here; one group keeps the launch count and GEMM tails low
