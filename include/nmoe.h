@@ -127,6 +127,8 @@ NMOE_API void nmoe_layer_destroy(nmoe_layer* layer);
 /* ExpertLayerSlice::Run (expert_layer.cpp:752-1092) for `tokens` rows:
  * output = input + routed + shared with the input RMSNorm inside.  input and
  * output are device [tokens][hidden] in the given dtypes and must not alias.
+ * With FP32 output the per-slot rows are summed from FP32, in the reference's
+ * order (:951-953, :1064-1069); with bf16 output they are rounded to bf16 first.
  * Enqueues on `stream` and returns; device-side failures surface through
  * nmoe_layer_sync_status(). */
 NMOE_API nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void* input,
@@ -138,6 +140,21 @@ NMOE_API nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void*
  * returns. */
 NMOE_API nmoe_status nmoe_layer_sync_status(nmoe_layer* layer, void* stream);
 NMOE_API const char* nmoe_layer_last_error(const nmoe_layer* layer);
+
+/* Failure detection.  No reference counterpart (one process, one GPU; every
+ * failure there is `return false`).  Kernels of this library that wait for
+ * another GPU -- the flag waits of the peer-window stages below -- give up after
+ * a limit, leave NMOE_ERR_DEVICE_TIMEOUT in the layer's error slot and return,
+ * so a peer that died or skipped a step costs an error status, never a hung
+ * GPU.  nmoe_layer_set_wait_limit_ms sets that limit (default about eight
+ * seconds; the environment variable NMOE_WAIT_LIMIT_MS sets it at creation).
+ * nmoe_layer_wait_flag enqueues the same bounded wait on a caller-owned device
+ * word: it returns when *flag >= expected (as a wrapping 32-bit step counter) or
+ * when the limit runs out; health checks and tests use it to see the timeout
+ * path without a second GPU. */
+NMOE_API nmoe_status nmoe_layer_set_wait_limit_ms(nmoe_layer* layer, double milliseconds);
+NMOE_API nmoe_status nmoe_layer_wait_flag(nmoe_layer* layer, void* stream, const uint32_t* flag,
+                                          uint32_t expected);
 
 /* Per-stage device timing (the reference has no profiler hooks; its benchmarks
  * time with steady_clock around synchronous calls,
@@ -173,7 +190,10 @@ typedef struct nmoe_trace_view {
   const uint8_t* act_scales;       /* [tokens][hidden/16] row-major E4M3 */
   const float* act_tensor_scale;   /* [tokens] */
   const float* parts;              /* [tokens][top_k+1][hidden]: weighted routed
-                                      contributions in selection order, then shared */
+                                      contributions in selection order, then shared.
+                                      FP32 when the last run's output was FP32; a run
+                                      with bf16 output keeps these rows in bf16 and
+                                      leaves this field NULL */
 } nmoe_trace_view;
 NMOE_API nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out);
 /* Copies one nmoe_trace_view field (index in declaration order, 0 =
@@ -251,8 +271,8 @@ NMOE_API nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream, const void
  *     tile while the GEMM runs,
  *   - small kernels raise a per-source flag (the step number) in the peer's
  *     window after the data, and the consumer's stream waits on its own flags
- *     with a bounded spin (NMOE_ERR_DEVICE_TIMEOUT after about eight seconds,
- *     never a hang).
+ *     with a bounded spin (NMOE_ERR_DEVICE_TIMEOUT after the limit of
+ *     nmoe_layer_set_wait_limit_ms, about eight seconds by default; never a hang).
  * One buffer per direction suffices: a rank overwrites a peer's segment for
  * step s+1 only after its own combine of step s, which needed that peer's
  * rows of step s, which the peer produced after reading the segment.
@@ -368,7 +388,12 @@ NMOE_API nmoe_status nmoe_router_topk(void* stream, const float* logits, const f
  * calls whose kernels can overlap on the GPU -- different streams, no ordering
  * between them -- race; serialise them.
  * The first call on each device looks up the array's device address (the
- * device must be current); make that first call outside any stream capture. */
+ * device must be current); make that first call outside any stream capture.
+ * The address is kept for the life of the process: after a cudaDeviceReset of a
+ * device do not call this entry point on it again.
+ * `input`, `norm_weight` and `gate` must be 16-byte aligned (the kernels read 16
+ * bytes at a time); every argument is validated before the first kernel is
+ * enqueued, so a rejected call leaves no work on the stream. */
 #define NMOE_NOALLOC_MAX_ROWS_X_HIDDEN 1048576
 #define NMOE_NOALLOC_MAX_ROWS_X_EXPERTS 131072
 NMOE_API nmoe_status nmoe_route_tokens_noalloc(

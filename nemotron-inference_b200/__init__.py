@@ -42,6 +42,7 @@ EXPORTED_SYMBOLS = (
     "nmoe_ep_combine", "nmoe_layer_reserve_sms", "nmoe_ep_window_create",
     "nmoe_ep_window_attach", "nmoe_ep_window_detach", "nmoe_ep_window_dispatch",
     "nmoe_ep_window_experts", "nmoe_ep_window_combine", "nmoe_ep_window_fork_shared",
+    "nmoe_layer_set_wait_limit_ms", "nmoe_layer_wait_flag",
 )
 
 
@@ -120,6 +121,8 @@ def load_library() -> ctypes.CDLL:
     lib.nmoe_layer_export_hidden.argtypes = [vp, vp, vp, vp, vp, vp]
     lib.nmoe_layer_enable_stage_timing.argtypes = [vp, i32]
     lib.nmoe_layer_reserve_sms.argtypes = [vp, i32]
+    lib.nmoe_layer_set_wait_limit_ms.argtypes = [vp, ctypes.c_double]
+    lib.nmoe_layer_wait_flag.argtypes = [vp, vp, vp, ctypes.c_uint32]
     lib.nmoe_layer_stage_times.argtypes = [vp, ctypes.POINTER(ctypes.c_float), i32]
     lib.nmoe_ffn_create.argtypes = [ctypes.POINTER(_Nvfp4Matrix), ctypes.POINTER(_Nvfp4Matrix),
                                     i32, ctypes.POINTER(vp)]
@@ -268,7 +271,7 @@ class ExpertLayerTrace:
     act_packed: torch.Tensor
     act_scales: torch.Tensor
     act_tensor_scale: torch.Tensor
-    parts: torch.Tensor
+    parts: Optional[torch.Tensor]  # FP32 [tokens, top_k + 1, hidden]; None after a bf16-output run
     routed_hidden_packed: torch.Tensor
     routed_hidden_scales: torch.Tensor
     shared_hidden_packed: torch.Tensor
@@ -374,6 +377,21 @@ class ExpertLayerSlice:
         _check(load_library().nmoe_layer_reserve_sms(self._handle, int(reserved)),
                "nmoe_layer_reserve_sms")
 
+    def set_wait_limit_ms(self, milliseconds: float) -> None:
+        """How long a kernel of this layer waits for a flag another GPU raises before it
+        gives up with NMOE_ERR_DEVICE_TIMEOUT."""
+        _check(load_library().nmoe_layer_set_wait_limit_ms(self._handle, float(milliseconds)),
+               "nmoe_layer_set_wait_limit_ms")
+
+    def wait_flag(self, flag: torch.Tensor, expected: int) -> None:
+        """Enqueues the bounded wait of the peer-window stages on a caller-owned 32-bit
+        device word: returns (on the device) when flag >= expected or at the limit."""
+        _require_cuda(flag, "flag")
+        if flag.element_size() != 4:
+            raise ValueError("flag must be a 32-bit device word")
+        _check(load_library().nmoe_layer_wait_flag(self._handle, _stream(), flag.data_ptr(),
+                                                   int(expected)), "nmoe_layer_wait_flag")
+
     def stage_times_ms(self) -> dict:
         """Device time of every stage of the last run (waits for it)."""
         buf = (ctypes.c_float * len(self.STAGES))()
@@ -396,11 +414,14 @@ class ExpertLayerSlice:
         fields = ("normalized_input", "router_logits", "selected_index", "selected_weight",
                   "act_packed", "act_scales", "act_tensor_scale", "parts")
 
-        def grab(name, shape, dtype):
+        def grab(name, shape, dtype, optional=False):
             out = torch.empty(shape, dtype=dtype, device=dev)
-            _check(lib.nmoe_layer_copy_trace_field(self._handle, _stream(), fields.index(name),
-                                                   out.data_ptr(), out.numel() * out.element_size()),
-                   "nmoe_layer_copy_trace_field")
+            status = lib.nmoe_layer_copy_trace_field(self._handle, _stream(), fields.index(name),
+                                                     out.data_ptr(),
+                                                     out.numel() * out.element_size())
+            if optional and status != NMOE_OK:
+                return None  # the layer does not hold this field for the last run
+            _check(status, "nmoe_layer_copy_trace_field")
             return out
 
         rp = torch.empty((tokens, K, I // 2), dtype=torch.uint8, device=dev)
@@ -418,7 +439,7 @@ class ExpertLayerSlice:
             act_packed=grab("act_packed", (tokens, H // 2), torch.uint8),
             act_scales=grab("act_scales", (tokens, H // 16), torch.uint8),
             act_tensor_scale=grab("act_tensor_scale", (tokens,), torch.float32),
-            parts=grab("parts", (tokens, K + 1, H), torch.float32),
+            parts=grab("parts", (tokens, K + 1, H), torch.float32, optional=True),
             routed_hidden_packed=rp, routed_hidden_scales=rs,
             shared_hidden_packed=sp, shared_hidden_scales=ss)
         torch.cuda.current_stream().synchronize()

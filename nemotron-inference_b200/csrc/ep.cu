@@ -128,14 +128,25 @@ __global__ void record_histogram_kernel(const uint8_t* __restrict__ records, int
   }
 }
 
+__device__ __forceinline__ float4 load_row4(const void* base, bool bf16, size_t row, int hidden,
+                                            int c) {
+  if (bf16) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(
+        reinterpret_cast<const __nv_bfloat16*>(base) + row * hidden + c);
+    return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                       __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+  }
+  return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + row * hidden + c);
+}
+
 // out[t] = in[t] + ((sum_k routed[position[t][k]]) + shared[t]), routed parts
 // added in selection order (expert_layer.cpp:951-953, :1064-1069).
 template <bool IN_BF16, bool OUT_BF16, bool ROWS_BF16>
 __global__ void combine_indexed_kernel(const void* __restrict__ in,
                                        const void* __restrict__ returned_rows,
                                        const int32_t* __restrict__ position,
-                                       const float* __restrict__ shared_rows, int rows, int hidden,
-                                       int top_k, void* __restrict__ out) {
+                                       const void* __restrict__ shared_rows, bool shared_bf16,
+                                       int rows, int hidden, int top_k, void* __restrict__ out) {
   const int quads = hidden / 4;
   const size_t total = static_cast<size_t>(rows) * quads;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -145,16 +156,7 @@ __global__ void combine_indexed_kernel(const void* __restrict__ in,
     float4 routed = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < top_k; ++k) {
       const size_t row = static_cast<size_t>(position[t * top_k + k]);
-      float4 p;
-      if constexpr (ROWS_BF16) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(
-            reinterpret_cast<const __nv_bfloat16*>(returned_rows) + row * hidden + c);
-        p = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                        __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
-      } else {
-        p = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(returned_rows) +
-                                             row * hidden + c);
-      }
+      const float4 p = load_row4(returned_rows, ROWS_BF16, row, hidden, c);
       if (k == 0) {
         routed = p;
       } else {
@@ -164,24 +166,13 @@ __global__ void combine_indexed_kernel(const void* __restrict__ in,
         routed.w = __fadd_rn(routed.w, p.w);
       }
     }
-    const float4 shared = *reinterpret_cast<const float4*>(shared_rows + t * hidden + c);
-    float x[4];
-    if constexpr (IN_BF16) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(
-          reinterpret_cast<const __nv_bfloat16*>(in) + t * hidden + c);
-      x[0] = __uint_as_float(raw.x << 16);
-      x[1] = __uint_as_float(raw.x & 0xffff0000u);
-      x[2] = __uint_as_float(raw.y << 16);
-      x[3] = __uint_as_float(raw.y & 0xffff0000u);
-    } else {
-      const float4 raw = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(in) + t * hidden + c);
-      x[0] = raw.x; x[1] = raw.y; x[2] = raw.z; x[3] = raw.w;
-    }
+    const float4 shared = load_row4(shared_rows, shared_bf16, t, hidden, c);
+    const float4 x = load_row4(in, IN_BF16, t, hidden, c);
     float r[4];
-    r[0] = __fadd_rn(x[0], __fadd_rn(routed.x, shared.x));
-    r[1] = __fadd_rn(x[1], __fadd_rn(routed.y, shared.y));
-    r[2] = __fadd_rn(x[2], __fadd_rn(routed.z, shared.z));
-    r[3] = __fadd_rn(x[3], __fadd_rn(routed.w, shared.w));
+    r[0] = __fadd_rn(x.x, __fadd_rn(routed.x, shared.x));
+    r[1] = __fadd_rn(x.y, __fadd_rn(routed.y, shared.y));
+    r[2] = __fadd_rn(x.z, __fadd_rn(routed.z, shared.z));
+    r[3] = __fadd_rn(x.w, __fadd_rn(routed.w, shared.w));
     if constexpr (OUT_BF16) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]);
       __nv_bfloat162 hi = __floats2bfloat162_rn(r[2], r[3]);
@@ -198,10 +189,10 @@ __global__ void combine_indexed_kernel(const void* __restrict__ in,
 
 template <bool A, bool B, bool C>
 void launch_combine_indexed_t(const void* in, const void* rows_in, const int32_t* position,
-                              const float* shared_rows, int rows, int hidden, int top_k, void* out,
-                              int blocks, cudaStream_t stream) {
-  combine_indexed_kernel<A, B, C><<<blocks, 256, 0, stream>>>(in, rows_in, position, shared_rows,
-                                                             rows, hidden, top_k, out);
+                              const void* shared_rows, bool shared_bf16, int rows, int hidden,
+                              int top_k, void* out, int blocks, cudaStream_t stream) {
+  combine_indexed_kernel<A, B, C><<<blocks, 256, 0, stream>>>(
+      in, rows_in, position, shared_rows, shared_bf16, rows, hidden, top_k, out);
 }
 
 // ---------------------------------------------------------------------------
@@ -229,12 +220,12 @@ __global__ void window_signal_kernel(const unsigned long long* __restrict__ flag
 }
 
 // Thread r waits until rank first+r has raised its flag for the current step.
-// Bounded: after about eight seconds the thread records kDevWaitTimeout and
-// returns, so a missing peer costs a wrong result and an error status, never a
-// hung GPU.
+// Bounded: after `limit_ticks` of clock64 the thread records kDevWaitTimeout
+// and returns, so a missing peer costs a wrong result and an error status,
+// never a hung GPU.
 __global__ void window_wait_kernel(const uint32_t* __restrict__ flags,
                                    const uint32_t* __restrict__ epoch, int first, int count,
-                                   int32_t* __restrict__ error) {
+                                   long long limit_ticks, int32_t* __restrict__ error) {
   if (static_cast<int>(threadIdx.x) >= count) return;
   const uint32_t* flag = flags + first + threadIdx.x;
   const uint32_t step = *epoch;
@@ -243,7 +234,7 @@ __global__ void window_wait_kernel(const uint32_t* __restrict__ flags,
     uint32_t seen;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
     if (static_cast<int32_t>(seen - step) >= 0) break;
-    if (clock64() - start > (1ll << 34)) {
+    if (clock64() - start > limit_ticks) {
       if (error != nullptr) atomicCAS(error, kDevOk, kDevWaitTimeout);
       break;
     }
@@ -294,21 +285,22 @@ cudaError_t launch_record_histogram(const uint8_t* records, int count, int cols,
 
 cudaError_t launch_combine_indexed(const void* in, bool in_bf16, const void* returned_rows,
                                    bool rows_bf16, const int32_t* position,
-                                   const float* shared_rows, int rows, int hidden, int top_k,
-                                   void* out, bool out_bf16, cudaStream_t stream) {
+                                   const void* shared_rows, bool shared_bf16, int rows,
+                                   int hidden, int top_k, void* out, bool out_bf16,
+                                   cudaStream_t stream) {
   if (rows <= 0 || hidden % 4 != 0 || top_k < 1) return cudaErrorInvalidValue;
   const size_t total = static_cast<size_t>(rows) * (hidden / 4);
   const int blocks = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   const int key = (in_bf16 ? 4 : 0) | (out_bf16 ? 2 : 0) | (rows_bf16 ? 1 : 0);
   switch (key) {
-    case 0: launch_combine_indexed_t<false, false, false>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
-    case 1: launch_combine_indexed_t<false, false, true>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
-    case 2: launch_combine_indexed_t<false, true, false>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
-    case 3: launch_combine_indexed_t<false, true, true>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
-    case 4: launch_combine_indexed_t<true, false, false>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
-    case 5: launch_combine_indexed_t<true, false, true>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
-    case 6: launch_combine_indexed_t<true, true, false>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
-    default: launch_combine_indexed_t<true, true, true>(in, returned_rows, position, shared_rows, rows, hidden, top_k, out, blocks, stream); break;
+    case 0: launch_combine_indexed_t<false, false, false>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
+    case 1: launch_combine_indexed_t<false, false, true>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
+    case 2: launch_combine_indexed_t<false, true, false>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
+    case 3: launch_combine_indexed_t<false, true, true>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
+    case 4: launch_combine_indexed_t<true, false, false>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
+    case 5: launch_combine_indexed_t<true, false, true>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
+    case 6: launch_combine_indexed_t<true, true, false>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
+    default: launch_combine_indexed_t<true, true, true>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
   }
   return cudaGetLastError();
 }
@@ -328,9 +320,9 @@ cudaError_t launch_window_signal(const unsigned long long* flag_slots,
 }
 
 cudaError_t launch_window_wait(const uint32_t* flags, const uint32_t* epoch, int first, int count,
-                               int32_t* error, cudaStream_t stream) {
-  if (count <= 0 || count > 64) return cudaErrorInvalidValue;
-  window_wait_kernel<<<1, 64, 0, stream>>>(flags, epoch, first, count, error);
+                               long long limit_ticks, int32_t* error, cudaStream_t stream) {
+  if (count <= 0 || count > 64 || limit_ticks <= 0) return cudaErrorInvalidValue;
+  window_wait_kernel<<<1, 64, 0, stream>>>(flags, epoch, first, count, limit_ticks, error);
   return cudaGetLastError();
 }
 

@@ -130,6 +130,9 @@ cudaError_t launch_swizzle_scales(const uint8_t* row_major, int rows, int cols, 
 cudaError_t launch_router_logits(const float* normalized, const float* gate,
                                  const float* logit_offset /* nullable [experts] */, int rows,
                                  int experts, int hidden, float* logits, cudaStream_t stream);
+// The argument rules of launch_router_topk, for callers that must know before they
+// enqueue anything.
+bool router_topk_arguments_valid(int rows, int experts, int top_k, int n_group, int topk_group);
 cudaError_t launch_router_topk(const float* logits, const float* bias, int rows, int experts,
                                int top_k, int n_group, int topk_group, bool norm_topk_prob,
                                float routed_scaling, int32_t* top_index, float* top_weight,
@@ -186,7 +189,8 @@ struct PermuteSource {
 // Copies each pair's quantised activation row into its expert's row slots and
 // records where it went; sorted_dest[row] = source_row * dest_stride + slot.
 cudaError_t launch_permute(const PlanBuffers& plan, const PermuteSource& src, int pairs,
-                           int tile_rows, int max_row_tiles, int cols, int k_blocks,
+                           int experts /* size of the local expert stack */, int tile_rows,
+                           int max_row_tiles, int cols, int k_blocks,
                            uint8_t* sorted_packed, uint8_t* sorted_sf_tiled,
                            float* sorted_tensor_scale, float* sorted_weight,
                            int32_t* sorted_dest, int32_t* pair_row /* nullable */,
@@ -211,19 +215,23 @@ cudaError_t launch_window_epoch(uint32_t* epoch, cudaStream_t stream);
 cudaError_t launch_window_signal(const unsigned long long* flag_slots,
                                  const unsigned long long* word_slots, const int32_t* words,
                                  const uint32_t* epoch, int first, int count, cudaStream_t stream);
+// `limit_ticks`: clock64 ticks after which a waiting thread gives up and records
+// kDevWaitTimeout in `error`.
 cudaError_t launch_window_wait(const uint32_t* flags, const uint32_t* epoch, int first, int count,
-                               int32_t* error, cudaStream_t stream);
+                               long long limit_ticks, int32_t* error, cudaStream_t stream);
 cudaError_t launch_record_histogram(const uint8_t* records, int count, int cols,
                                     int local_experts, const int32_t* valid_counts, int capacity,
                                     int32_t* expert_counts, int32_t* error, cudaStream_t stream);
 cudaError_t launch_combine_indexed(const void* in, bool in_bf16, const void* returned_rows,
                                    bool rows_bf16, const int32_t* position,
-                                   const float* shared_rows, int rows, int hidden, int top_k,
-                                   void* out, bool out_bf16, cudaStream_t stream);
+                                   const void* shared_rows, bool shared_bf16, int rows,
+                                   int hidden, int top_k, void* out, bool out_bf16,
+                                   cudaStream_t stream);
 
 // out[t] = in[t] + ((sum_k parts[t][k]) + parts[t][top_k]) with the routed
-// parts added in slot order.
-cudaError_t launch_combine(const void* in, bool in_bf16, const float* parts, int rows, int hidden,
-                           int top_k, void* out, bool out_bf16, cudaStream_t stream);
+// parts (FP32 or bf16 rows, [rows][top_k + 1][hidden]) added in slot order.
+cudaError_t launch_combine(const void* in, bool in_bf16, const void* parts, bool parts_bf16,
+                           int rows, int hidden, int top_k, void* out, bool out_bf16,
+                           cudaStream_t stream);
 
 }  // namespace nmoe

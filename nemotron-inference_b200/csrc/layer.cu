@@ -134,6 +134,15 @@ CUtensorMap make_bf16_map(const void* base, size_t rows, size_t cols, int box_ro
 int k_blocks_of(int k) { return (k + 255) / 256; }
 size_t tiled_sf_bytes(size_t row_slots, int k) { return row_slots * k_blocks_of(k) * 2048; }
 
+// clock64 ticks in `ms` milliseconds at the device's maximum SM clock
+long long ticks_from_ms(double ms) {
+  int device = 0, khz = 0;
+  NMOE_CUDA(cudaGetDevice(&device));
+  NMOE_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device));
+  const double ticks = ms * static_cast<double>(khz);
+  return ticks < 1.0 ? 1 : static_cast<long long>(ticks);
+}
+
 int device_sm_count() {
   int device = 0, sms = 0;
   NMOE_CUDA(cudaGetDevice(&device));
@@ -630,6 +639,12 @@ struct nmoe_layer {
   ActivationOperand y_op, sh_op, a_op, h_op;
   ErrorSlot error;
   int last_tokens = 0;
+  bool last_parts_bf16 = false;
+  bool force_fp32_parts = false;  // NMOE_PARTS_FP32=1: FP32 rows whatever the output type
+  // how long a kernel waits for a flag another GPU raises before it gives up with
+  // kDevWaitTimeout (clock64 ticks; nmoe_layer_set_wait_limit_ms, NMOE_WAIT_LIMIT_MS)
+  long long wait_limit_ticks = 1ll << 34;
+  DeviceBuffer probe_epoch;  // nmoe_layer_wait_flag
   std::string last_error;
 
   // Small batches: the shared expert runs on a stream of the layer's own beside the
@@ -640,6 +655,7 @@ struct nmoe_layer {
   int fork_max_tokens = 256;
   bool window_fork_shared = false;    // nmoe_ep_window_fork_shared
   bool window_shared_pending = false;
+  bool window_shared_bf16 = false;    // type of shared_out for the pending combine
 
   // optional per-stage CUDA events (nmoe_layer_enable_stage_timing)
   bool stage_timing = false;
@@ -687,6 +703,11 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
 
   L->cfg = c;
   L->num_sms = device_sm_count();
+  L->force_fp32_parts = std::getenv("NMOE_PARTS_FP32") != nullptr;
+  if (const char* env = std::getenv("NMOE_WAIT_LIMIT_MS")) {
+    const double ms = std::strtod(env, nullptr);
+    if (ms > 0.0) L->wait_limit_ticks = ticks_from_ms(ms);
+  }
   if (std::getenv("NMOE_NO_SHARED_FORK") == nullptr) {
     NMOE_CUDA(cudaStreamCreateWithFlags(&L->side_stream, cudaStreamNonBlocking));
     NMOE_CUDA(cudaEventCreateWithFlags(&L->quant_done, cudaEventDisableTiming));
@@ -852,7 +873,8 @@ void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& sou
   plan.num_row_tiles = L->num_row_tiles.as<int32_t>();
   NMOE_CUDA(launch_route_plan(plan, L->local_experts, tile_rows, L->max_row_tiles, error, stream));
   L->mark(4, stream);
-  NMOE_CUDA(launch_permute(plan, source, pairs, tile_rows, L->max_row_tiles, H, k_blocks_of(H),
+  NMOE_CUDA(launch_permute(plan, source, pairs, L->local_experts, tile_rows, L->max_row_tiles, H,
+                           k_blocks_of(H),
                            L->a_packed.as<uint8_t>(), L->a_sf.as<uint8_t>(), L->a_ts.as<float>(),
                            L->a_weight.as<float>(), L->a_dest.as<int32_t>(),
                            L->ep_world == 1 ? L->pair_row.as<int32_t>() : nullptr, dest_stride,
@@ -869,8 +891,8 @@ void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& sou
 }
 
 // shared expert (:814-818, :956-964, :981-1005) on the token-order quantised rows
-void shared_expert(nmoe_layer* L, cudaStream_t stream, int tokens, float* out_rows, int dest_mul,
-                   int dest_add, cudaEvent_t between) {
+void shared_expert(nmoe_layer* L, cudaStream_t stream, int tokens, void* out_rows, int dest_mul,
+                   int dest_add, cudaEvent_t between, bool out_bf16 = false) {
   const TileClass shared_class =
       tokens <= 32 ? kClassDecode : tokens <= 256 ? kClassDecodeWide : kClassPrefill;
   Schedule shared;
@@ -878,7 +900,7 @@ void shared_expert(nmoe_layer* L, cudaStream_t stream, int tokens, float* out_ro
   run_expert_gemms(L->shared_up, L->shared_down, shared_class, L->y_op, L->y_ts.as<float>(),
                    shared, L->sh_packed.as<uint8_t>(), L->sh_sf.as<uint8_t>(), L->sh_op, out_rows,
                    nullptr, dest_mul, dest_add, nullptr, L->error.device.as<int32_t>(),
-                   L->num_sms, stream, between, false);
+                   L->num_sms, stream, between, out_bf16);
 }
 
 PermuteSource local_source(nmoe_layer* L) {
@@ -902,27 +924,33 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
                     int tokens, void* output, nmoe_dtype out_dtype) {
   const nmoe_config& c = L->cfg;
   const int H = c.hidden_size, K = c.top_k;
+  // The per-(token, slot) rows of the down projection and the shared expert's row
+  // wait in `parts` for the combine.  They carry the precision of the output: FP32
+  // rows for an FP32 result (the reference's arithmetic, bit for bit in the sums),
+  // bf16 rows for a bf16 result, which halves the largest write and read of the layer.
+  const bool parts_bf16 = out_dtype == NMOE_BF16 && !L->force_fp32_parts;
   const bool fork = L->side_stream != nullptr && !L->stage_timing && tokens <= L->fork_max_tokens;
   route_tokens(L, stream, input, in_dtype, tokens, fork ? L->quant_done : nullptr);
   if (fork) {
     NMOE_CUDA(cudaStreamWaitEvent(L->side_stream, L->quant_done, 0));
-    shared_expert(L, L->side_stream, tokens, L->parts.as<float>(), K + 1, K, nullptr);
+    shared_expert(L, L->side_stream, tokens, L->parts.as<void>(), K + 1, K, nullptr, parts_bf16);
     NMOE_CUDA(cudaEventRecord(L->shared_done, L->side_stream));
   }
-  routed_experts(L, stream, local_source(L), tokens * K, K + 1, L->parts.as<float>(), false);
+  routed_experts(L, stream, local_source(L), tokens * K, K + 1, L->parts.as<void>(), parts_bf16);
   L->mark(7, stream);
   if (fork) {
     NMOE_CUDA(cudaStreamWaitEvent(stream, L->shared_done, 0));
   } else {
-    shared_expert(L, stream, tokens, L->parts.as<float>(), K + 1, K,
-                  L->stage_timing ? L->stage_events[8] : nullptr);
+    shared_expert(L, stream, tokens, L->parts.as<void>(), K + 1, K,
+                  L->stage_timing ? L->stage_events[8] : nullptr, parts_bf16);
   }
   // routed sum in selection order, mixer and residual (:951-953, :1064-1069)
   L->mark(9, stream);
-  NMOE_CUDA(launch_combine(input, in_dtype == NMOE_BF16, L->parts.as<float>(), tokens, H, K,
-                           output, out_dtype == NMOE_BF16, stream));
+  NMOE_CUDA(launch_combine(input, in_dtype == NMOE_BF16, L->parts.as<void>(), parts_bf16, tokens,
+                           H, K, output, out_dtype == NMOE_BF16, stream));
   L->mark(10, stream);
   L->last_tokens = tokens;
+  L->last_parts_bf16 = parts_bf16;
 }
 
 }  // namespace
@@ -991,6 +1019,37 @@ nmoe_status nmoe_layer_reserve_sms(nmoe_layer* layer, int32_t reserved_sms) {
   const int all = device_sm_count();
   if (reserved_sms < 0 || reserved_sms >= all) return NMOE_ERR_INVALID_ARGUMENT;
   layer->num_sms = all - reserved_sms;
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_layer_set_wait_limit_ms(nmoe_layer* layer, double milliseconds) {
+  if (layer == nullptr || !(milliseconds > 0.0) || milliseconds > 60000.0) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  try {
+    layer->wait_limit_ticks = ticks_from_ms(milliseconds);
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_layer_wait_flag(nmoe_layer* layer, void* stream_ptr, const uint32_t* flag,
+                                 uint32_t expected) {
+  if (layer == nullptr || flag == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  try {
+    if (layer->probe_epoch.bytes() == 0) layer->probe_epoch.allocate(sizeof(uint32_t), true);
+    NMOE_CUDA(cudaMemcpyAsync(layer->probe_epoch.as<uint32_t>(), &expected, sizeof(uint32_t),
+                              cudaMemcpyHostToDevice, stream));
+    NMOE_CUDA(launch_window_wait(flag, layer->probe_epoch.as<uint32_t>(), 0, 1,
+                                 layer->wait_limit_ticks, layer->error.device.as<int32_t>(),
+                                 stream));
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    return failure.status;
+  }
   return NMOE_OK;
 }
 
@@ -1137,7 +1196,7 @@ nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream_ptr, const void* inp
   }
   const cudaError_t err = launch_combine_indexed(
       input, input_dtype == NMOE_BF16, returned_rows, rows_dtype == NMOE_BF16,
-      layer->send_position.as<int32_t>(), layer->shared_out.as<float>(), layer->last_tokens,
+      layer->send_position.as<int32_t>(), layer->shared_out.as<void>(), false, layer->last_tokens,
       layer->cfg.hidden_size, layer->cfg.top_k, output, output_dtype == NMOE_BF16,
       static_cast<cudaStream_t>(stream_ptr));
   return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
@@ -1299,11 +1358,14 @@ nmoe_status nmoe_ep_window_dispatch(nmoe_layer* layer, void* stream_ptr, const v
                  fork ? layer->quant_done : nullptr);
     if (fork) {
       NMOE_CUDA(cudaStreamWaitEvent(layer->side_stream, layer->quant_done, 0));
+      // the shared expert's rows take the type of the returned rows, so that the
+      // combine adds what the single-device layer adds for the same output type
       shared_expert(layer, layer->side_stream, static_cast<int>(tokens),
-                    layer->shared_out.as<float>(), 1, 0, nullptr);
+                    layer->shared_out.as<void>(), 1, 0, nullptr, w.rows_bf16);
       NMOE_CUDA(cudaEventRecord(layer->shared_done, layer->side_stream));
     }
     layer->window_shared_pending = fork;
+    layer->window_shared_bf16 = fork && w.rows_bf16;
     NMOE_CUDA(launch_dispatch_plan(layer->counts.as<int32_t>(), c.n_routed_experts,
                                    layer->local_experts, layer->ep_world,
                                    layer->send_counts.as<int32_t>(),
@@ -1342,7 +1404,8 @@ nmoe_status nmoe_ep_window_experts(nmoe_layer* layer, void* stream_ptr, int32_t 
     auto& w = layer->window;
     const int cap = static_cast<int>(w.capacity);
     NMOE_CUDA(launch_window_wait(w.record_flags(), w.epoch.as<uint32_t>(), first_source_rank,
-                                 source_ranks, layer->error.device.as<int32_t>(), stream));
+                                 source_ranks, layer->wait_limit_ticks,
+                                 layer->error.device.as<int32_t>(), stream));
     RowSegments segments;
     segments.bases = w.row_segments.as<unsigned long long>();
     segments.rows = cap;
@@ -1371,6 +1434,7 @@ nmoe_status nmoe_ep_window_combine(nmoe_layer* layer, void* stream_ptr, const vo
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   auto& w = layer->window;
   cudaError_t err = launch_window_wait(w.row_flags(), w.epoch.as<uint32_t>(), 0, layer->ep_world,
+                                       layer->wait_limit_ticks,
                                        layer->error.device.as<int32_t>(), stream);
   if (err == cudaSuccess && layer->window_shared_pending) {
     err = cudaStreamWaitEvent(stream, layer->shared_done, 0);
@@ -1379,8 +1443,8 @@ nmoe_status nmoe_ep_window_combine(nmoe_layer* layer, void* stream_ptr, const vo
   if (err == cudaSuccess) {
     err = launch_combine_indexed(input, input_dtype == NMOE_BF16,
                                  w.local.as<uint8_t>() + w.rows_off, w.rows_bf16,
-                                 layer->send_position.as<int32_t>(), layer->shared_out.as<float>(),
-                                 layer->last_tokens, layer->cfg.hidden_size, layer->cfg.top_k,
+                                 layer->send_position.as<int32_t>(), layer->shared_out.as<void>(),
+                                 layer->window_shared_bf16, layer->last_tokens, layer->cfg.hidden_size, layer->cfg.top_k,
                                  output, output_dtype == NMOE_BF16, stream);
   }
   return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
@@ -1399,7 +1463,7 @@ nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out) {
   out->act_packed = layer->y_packed.as<uint8_t>();
   out->act_scales = layer->y_sf_row_major.as<uint8_t>();
   out->act_tensor_scale = layer->y_ts.as<float>();
-  out->parts = layer->parts.as<float>();
+  out->parts = layer->last_parts_bf16 ? nullptr : layer->parts.as<float>();
   return NMOE_OK;
 }
 
@@ -1411,7 +1475,7 @@ nmoe_status nmoe_layer_copy_trace_field(nmoe_layer* layer, void* stream, int32_t
   const void* sources[8] = {view.normalized_input, view.router_logits, view.selected_index,
                             view.selected_weight,  view.act_packed,    view.act_scales,
                             view.act_tensor_scale, view.parts};
-  if (field < 0 || field >= 8) return NMOE_ERR_INVALID_ARGUMENT;
+  if (field < 0 || field >= 8 || sources[field] == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
   return cudaMemcpyAsync(dst, sources[field], nbytes, cudaMemcpyDefault,
                          static_cast<cudaStream_t>(stream)) == cudaSuccess
              ? NMOE_OK

@@ -63,8 +63,8 @@ __global__ void route_plan_kernel(PlanBuffers plan, int experts, int tile_rows, 
 constexpr int kPermuteWarps = 8;
 
 __global__ void __launch_bounds__(kPermuteWarps * 32)
-permute_kernel(PlanBuffers plan, PermuteSource src, int pairs, int tile_rows, int max_row_tiles,
-               int cols, int k_tiles, uint8_t* __restrict__ sorted_packed,
+permute_kernel(PlanBuffers plan, PermuteSource src, int pairs, int experts, int tile_rows,
+               int max_row_tiles, int cols, int k_tiles, uint8_t* __restrict__ sorted_packed,
                uint8_t* __restrict__ sorted_sf_tiled, float* __restrict__ sorted_tensor_scale,
                float* __restrict__ sorted_weight, int32_t* __restrict__ sorted_dest,
                int32_t* __restrict__ pair_row, int dest_stride) {
@@ -79,9 +79,15 @@ permute_kernel(PlanBuffers plan, PermuteSource src, int pairs, int tile_rows, in
   const int slot = pair - source_row * src.pairs_per_row;
   const int expert = *reinterpret_cast<const int32_t*>(
       reinterpret_cast<const uint8_t*>(src.expert) + static_cast<size_t>(pair) * src.expert_stride);
+  // a record that arrived corrupt or half written (a peer that timed out) names no
+  // expert of this stack: the histogram kernel has reported it, nothing is indexed by it
+  if (expert < 0 || expert >= experts) return;
   int position = 0;
   if (lane == 0) position = atomicAdd(&plan.expert_cursor[expert], 1);
   position = __shfl_sync(0xffffffffu, position, 0);
+  // an expert's rows stay inside the tiles the plan gave it, whatever the histogram said
+  const int own_tiles = (plan.expert_counts[expert] + tile_rows - 1) / tile_rows;
+  if (position / tile_rows >= own_tiles) return;
   const int tile = plan.expert_slot0[expert] + position / tile_rows;
   if (tile >= max_row_tiles) return;  // plan overflow was already reported
   const int row = tile * 128 + position % tile_rows;
@@ -126,53 +132,88 @@ permute_kernel(PlanBuffers plan, PermuteSource src, int pairs, int tile_rows, in
   }
 }
 
-template <bool IN_BF16, bool OUT_BF16>
-__global__ void combine_kernel(const void* __restrict__ in, const float* __restrict__ parts,
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float (&v)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+// Eight consecutive elements of row `row` of a [rows][hidden] FP32 or bf16 matrix.
+template <bool BF16>
+__device__ __forceinline__ void load_row8(const void* base, size_t row, int hidden, int c,
+                                          float (&v)[8]) {
+  if constexpr (BF16) {
+    unpack_bf16x8(*reinterpret_cast<const uint4*>(
+                      reinterpret_cast<const __nv_bfloat16*>(base) + row * hidden + c), v);
+  } else {
+    const float* p = reinterpret_cast<const float*>(base) + row * hidden + c;
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+}
+
+template <bool BF16>
+__device__ __forceinline__ void store_row8(void* base, size_t row, int hidden, int c,
+                                           const float (&v)[8]) {
+  if constexpr (BF16) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(base) + row * hidden + c) =
+        make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    float* p = reinterpret_cast<float*>(base) + row * hidden + c;
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+// out[t] = in[t] + ((sum_k parts[t][k]) + parts[t][top_k]): the routed parts are
+// added in selection order (expert_layer.cpp:951-953), then the shared expert's
+// row and the residual (:1064-1069).  Eight elements per thread, 16- or 32-byte
+// accesses; the parts are FP32 or bf16 rows.
+template <bool IN_BF16, bool OUT_BF16, bool PARTS_BF16>
+__global__ void combine_kernel(const void* __restrict__ in, const void* __restrict__ parts,
                                int rows, int hidden, int top_k, void* __restrict__ out) {
-  const int quads = hidden / 4;
-  const size_t total = static_cast<size_t>(rows) * quads;
+  const int octs = hidden / 8;
+  const size_t total = static_cast<size_t>(rows) * octs;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const size_t t = i / quads;
-    const int c = static_cast<int>(i - t * quads) * 4;
-    const float* base = parts + (t * (top_k + 1)) * hidden + c;
-    float4 routed = *reinterpret_cast<const float4*>(base);
+    const size_t t = i / octs;
+    const int c = static_cast<int>(i - t * octs) * 8;
+    const size_t first = t * (top_k + 1);
+    float routed[8];
+    load_row8<PARTS_BF16>(parts, first, hidden, c, routed);
     for (int k = 1; k < top_k; ++k) {
-      const float4 p = *reinterpret_cast<const float4*>(base + static_cast<size_t>(k) * hidden);
-      routed.x = __fadd_rn(routed.x, p.x);
-      routed.y = __fadd_rn(routed.y, p.y);
-      routed.z = __fadd_rn(routed.z, p.z);
-      routed.w = __fadd_rn(routed.w, p.w);
+      float p[8];
+      load_row8<PARTS_BF16>(parts, first + k, hidden, c, p);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) routed[j] = __fadd_rn(routed[j], p[j]);
     }
-    const float4 shared = *reinterpret_cast<const float4*>(base + static_cast<size_t>(top_k) * hidden);
-    float x[4];
-    if constexpr (IN_BF16) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(
-          reinterpret_cast<const __nv_bfloat16*>(in) + t * hidden + c);
-      x[0] = __uint_as_float(raw.x << 16);
-      x[1] = __uint_as_float(raw.x & 0xffff0000u);
-      x[2] = __uint_as_float(raw.y << 16);
-      x[3] = __uint_as_float(raw.y & 0xffff0000u);
-    } else {
-      const float4 raw = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(in) + t * hidden + c);
-      x[0] = raw.x; x[1] = raw.y; x[2] = raw.z; x[3] = raw.w;
-    }
-    float r[4];
-    r[0] = __fadd_rn(x[0], __fadd_rn(routed.x, shared.x));
-    r[1] = __fadd_rn(x[1], __fadd_rn(routed.y, shared.y));
-    r[2] = __fadd_rn(x[2], __fadd_rn(routed.z, shared.z));
-    r[3] = __fadd_rn(x[3], __fadd_rn(routed.w, shared.w));
-    if constexpr (OUT_BF16) {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]);
-      __nv_bfloat162 hi = __floats2bfloat162_rn(r[2], r[3]);
-      uint2 packed;
-      packed.x = *reinterpret_cast<uint32_t*>(&lo);
-      packed.y = *reinterpret_cast<uint32_t*>(&hi);
-      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + t * hidden + c) = packed;
-    } else {
-      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + t * hidden + c) =
-          make_float4(r[0], r[1], r[2], r[3]);
-    }
+    float shared[8], x[8], r[8];
+    load_row8<PARTS_BF16>(parts, first + top_k, hidden, c, shared);
+    load_row8<IN_BF16>(in, t, hidden, c, x);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = __fadd_rn(x[j], __fadd_rn(routed[j], shared[j]));
+    store_row8<OUT_BF16>(out, t, hidden, c, r);
+  }
+}
+
+template <bool A, bool B>
+void launch_combine_t(const void* in, const void* parts, bool parts_bf16, int rows, int hidden,
+                      int top_k, void* out, int blocks, cudaStream_t stream) {
+  if (parts_bf16) {
+    combine_kernel<A, B, true><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+  } else {
+    combine_kernel<A, B, false><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out);
   }
 }
 
@@ -186,32 +227,32 @@ cudaError_t launch_route_plan(const PlanBuffers& plan, int experts, int tile_row
 }
 
 cudaError_t launch_permute(const PlanBuffers& plan, const PermuteSource& src, int pairs,
-                           int tile_rows, int max_row_tiles, int cols, int k_blocks,
+                           int experts, int tile_rows, int max_row_tiles, int cols, int k_blocks,
                            uint8_t* sorted_packed, uint8_t* sorted_sf_tiled,
                            float* sorted_tensor_scale, float* sorted_weight,
                            int32_t* sorted_dest, int32_t* pair_row, int dest_stride,
                            cudaStream_t stream) {
   if (pairs <= 0 || src.pairs_per_row <= 0) return cudaErrorInvalidValue;
   permute_kernel<<<(pairs + kPermuteWarps - 1) / kPermuteWarps, kPermuteWarps * 32, 0, stream>>>(
-      plan, src, pairs, tile_rows, max_row_tiles, cols, k_blocks * 4, sorted_packed,
+      plan, src, pairs, experts, tile_rows, max_row_tiles, cols, k_blocks * 4, sorted_packed,
       sorted_sf_tiled, sorted_tensor_scale, sorted_weight, sorted_dest, pair_row, dest_stride);
   return cudaGetLastError();
 }
 
-cudaError_t launch_combine(const void* in, bool in_bf16, const float* parts, int rows, int hidden,
-                           int top_k, void* out, bool out_bf16, cudaStream_t stream) {
-  if (rows <= 0 || hidden % 4 != 0 || top_k < 1) return cudaErrorInvalidValue;
-  const size_t total = static_cast<size_t>(rows) * (hidden / 4);
-  const int threads = 256;
-  const int blocks = static_cast<int>(std::min<size_t>((total + threads - 1) / threads, 148 * 16));
+cudaError_t launch_combine(const void* in, bool in_bf16, const void* parts, bool parts_bf16,
+                           int rows, int hidden, int top_k, void* out, bool out_bf16,
+                           cudaStream_t stream) {
+  if (rows <= 0 || hidden % 8 != 0 || top_k < 1) return cudaErrorInvalidValue;
+  const size_t total = static_cast<size_t>(rows) * (hidden / 8);
+  const int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 16));
   if (in_bf16 && out_bf16) {
-    combine_kernel<true, true><<<blocks, threads, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+    launch_combine_t<true, true>(in, parts, parts_bf16, rows, hidden, top_k, out, blocks, stream);
   } else if (in_bf16) {
-    combine_kernel<true, false><<<blocks, threads, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+    launch_combine_t<true, false>(in, parts, parts_bf16, rows, hidden, top_k, out, blocks, stream);
   } else if (out_bf16) {
-    combine_kernel<false, true><<<blocks, threads, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+    launch_combine_t<false, true>(in, parts, parts_bf16, rows, hidden, top_k, out, blocks, stream);
   } else {
-    combine_kernel<false, false><<<blocks, threads, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+    launch_combine_t<false, false>(in, parts, parts_bf16, rows, hidden, top_k, out, blocks, stream);
   }
   return cudaGetLastError();
 }

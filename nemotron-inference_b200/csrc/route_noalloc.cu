@@ -65,6 +65,16 @@ extern "C" nmoe_status nmoe_route_tokens_noalloc(
       hidden % 16 != 0 || experts <= 0 || !(epsilon > 0.0f)) {
     return NMOE_ERR_INVALID_ARGUMENT;
   }
+  // the selection's own argument rules, checked before anything is enqueued
+  if (!nmoe::router_topk_arguments_valid(static_cast<int>(rows), experts, top_k, n_group,
+                                         topk_group)) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  // the kernels read `input`, `norm_weight` and `gate` 16 bytes at a time
+  if (((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(norm_weight) |
+        reinterpret_cast<uintptr_t>(gate)) & 15u) != 0) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
   if (static_cast<size_t>(rows) * static_cast<size_t>(hidden) > kMaxNormalizedFloats ||
       static_cast<size_t>(rows) * static_cast<size_t>(experts) > kMaxLogitFloats) {
     return NMOE_ERR_CAPACITY;  // the fixed scratch cannot hold this many rows
@@ -77,19 +87,21 @@ extern "C" nmoe_status nmoe_route_tokens_noalloc(
   const int r = static_cast<int>(rows);
   // Nothing in the scratch has to start at zero: both regions are fully
   // written for `rows` rows before they are read.
-  if (nmoe::launch_norm_quant(input, dtype == NMOE_BF16, r, hidden, norm_weight, epsilon,
-                              normalized, nullptr, nullptr, nullptr, 0, nullptr,
-                              stream) != cudaSuccess) {
-    return NMOE_ERR_CUDA;
-  }
-  if (nmoe::launch_router_logits(normalized, gate, nullptr, r, experts, hidden, logits, stream) !=
-      cudaSuccess) {
-    return NMOE_ERR_INVALID_ARGUMENT;
-  }
-  if (nmoe::launch_router_topk(logits, bias, r, experts, top_k, n_group, topk_group,
-                               norm_topk_prob != 0, routed_scaling, top_index, top_weight, nullptr,
-                               stream) != cudaSuccess) {
-    return NMOE_ERR_INVALID_ARGUMENT;
-  }
-  return NMOE_OK;
+  // a launcher that rejects its arguments says cudaErrorInvalidValue; anything else
+  // is a failure of the CUDA runtime
+  auto status_of = [](cudaError_t err) {
+    return err == cudaSuccess ? NMOE_OK
+                              : err == cudaErrorInvalidValue ? NMOE_ERR_INVALID_ARGUMENT
+                                                             : NMOE_ERR_CUDA;
+  };
+  nmoe_status status = status_of(nmoe::launch_norm_quant(
+      input, dtype == NMOE_BF16, r, hidden, norm_weight, epsilon, normalized, nullptr, nullptr,
+      nullptr, 0, nullptr, stream));
+  if (status != NMOE_OK) return status;
+  status = status_of(
+      nmoe::launch_router_logits(normalized, gate, nullptr, r, experts, hidden, logits, stream));
+  if (status != NMOE_OK) return status;
+  return status_of(nmoe::launch_router_topk(logits, bias, r, experts, top_k, n_group, topk_group,
+                                            norm_topk_prob != 0, routed_scaling, top_index,
+                                            top_weight, nullptr, stream));
 }

@@ -273,13 +273,17 @@ cudaError_t launch_router_logits(const float* normalized, const float* gate,
   return cudaGetLastError();
 }
 
+bool router_topk_arguments_valid(int rows, int experts, int top_k, int n_group, int topk_group) {
+  return rows > 0 && experts > 0 && experts % 32 == 0 && experts <= 32 * kMaxPerLane &&
+         top_k > 0 && top_k <= 32 && top_k <= experts && n_group > 0 && n_group <= 32 &&
+         topk_group > 0 && experts % n_group == 0;
+}
+
 cudaError_t launch_router_topk(const float* logits, const float* bias, int rows, int experts,
                                int top_k, int n_group, int topk_group, bool norm_topk_prob,
                                float routed_scaling, int32_t* top_index, float* top_weight,
                                int32_t* expert_counts, cudaStream_t stream) {
-  if (rows <= 0 || experts <= 0 || experts % 32 != 0 || experts > 32 * kMaxPerLane ||
-      top_k <= 0 || top_k > 32 || top_k > experts || n_group <= 0 || n_group > 32 ||
-      topk_group <= 0 || experts % n_group != 0) {
+  if (!router_topk_arguments_valid(rows, experts, top_k, n_group, topk_group)) {
     return cudaErrorInvalidValue;
   }
   const size_t smem = n_group > 1 ? sizeof(float) * kTopkWarps * experts : 0;

@@ -218,6 +218,13 @@ class DeviceStages:
     def sync_status(self) -> int:
         return self.layer.sync_status()
 
+    def launches_per_window_step(self, groups: int) -> int:
+        """Kernels one peer-window step launches on this rank: epoch, the routing front end
+        (5), dispatch plan, record packing, flag signal, the shared expert's two GEMMs,
+        then per source-rank group wait + histogram + plan + permute + two GEMMs + signal,
+        and wait + combine."""
+        return 1 + 5 + 3 + 2 + 7 * groups + 2
+
 
 def _as_tensor(address: int, shape, dtype, device) -> torch.Tensor:
     """A torch view of library-owned device memory (no copy, no ownership)."""
@@ -421,21 +428,33 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
     cfg.max_recv_pairs = capacity * world
     data = synthetic.make_layer(cfg, seed=4000, device="cuda")
     stages = DeviceStages(cfg, shard_bindings(data.bindings, rank, world), rank, world)
-    # Efficiency baseline: ONE GPU holding all experts, running the per-GPU token count of
-    # this configuration (tokens / world).  Rank 0 measures it before the ranks start to
-    # exchange; efficiency = aggregate tokens/s / (world x that figure).
-    single_ms = None
+    x_all = synthetic.make_tokens(tokens_total, H, seed=4001)
+    # One GPU holding all experts, for two purposes.  (1) Every rank runs it on its own
+    # token slice after the timed region and compares the expert-parallel result with it.
+    # (2) Rank 0 times it before the ranks start to exchange, on the per-GPU token count
+    # (what the exchange and the smaller batches cost) and on all T tokens (the N = 1
+    # figure of the strong-scaling efficiency).
+    single = package.ExpertLayerSlice.create(synthetic.baseline_config(max_tokens=tokens),
+                                             data.bindings)
+    if single is None:
+        raise SystemExit("single-GPU layer creation failed: " +
+                         package.ExpertLayerSlice.create_error)
+    single_ms = full_ms = None
     if rank == 0:
-        single_cfg = synthetic.baseline_config(max_tokens=tokens)
-        single = package.ExpertLayerSlice.create(single_cfg, data.bindings)
-        if single is not None:
-            xs = synthetic.make_tokens(tokens_total, H, seed=4001)[:tokens].cuda()
-            outs = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
-            single_ms = float(np.mean(bench_module.time_steps(
-                lambda: single.run_async(xs, outs), args.steps, args.warmup, flush_buf)))
-            single.close()
-            del xs, outs
-    del data
+        xs = x_all[:tokens].cuda()
+        outs = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+        single_ms = float(np.mean(bench_module.time_steps(
+            lambda: single.run_async(xs, outs), args.steps, args.warmup, flush_buf)))
+        del xs, outs
+        full = package.ExpertLayerSlice.create(synthetic.baseline_config(max_tokens=tokens_total),
+                                               data.bindings)
+        if full is not None:
+            xf = x_all.cuda()
+            outf = torch.empty((tokens_total, H), dtype=torch.bfloat16, device="cuda")
+            full_ms = float(np.mean(bench_module.time_steps(
+                lambda: full.run_async(xf, outf), args.steps, args.warmup, flush_buf)))
+            full.close()
+            del xf, outf
     torch.cuda.empty_cache()
     engine = ExpertParallelEngine(stages, capacity_per_rank=capacity)
     # transport: "window" = the stages' own kernels store into the peers' memory (default);
@@ -448,7 +467,6 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
             print(f"rank {rank}: peer windows unavailable ({stages.attach_error}); using NCCL",
                   file=sys.stderr)
             transport = "nccl"
-    x_all = synthetic.make_tokens(tokens_total, H, seed=4001)
     x_host = x_all[rank * tokens:(rank + 1) * tokens].contiguous().pin_memory()
     x = x_host.cuda()
     out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
@@ -492,6 +510,14 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
     if status != NMOE_OK:
         raise SystemExit(f"rank {rank}: device error {status}")
 
+    # Correctness of what was just timed, outside the timed region: the output of the
+    # last timed step against the single-GPU layer on the same tokens, on every rank; on
+    # rank 0 the single-GPU layer against the CPU oracle on the first 256 of them.
+    parity = ep_parity_check(package, single, data, x, out, rank, dist_module)
+    single.close()
+    del data
+    torch.cuda.empty_cache()
+
     def e2e_step():
         x.copy_(x_host, non_blocking=True)
         run_step()
@@ -524,8 +550,22 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
                 phases[name] = phases.get(name, 0.0) + ms_at / 3
     stages.profile = False
     engine.release_graph()
+    nccl_arm = None
     if transport == "window":
         stages.detach_windows()
+        # the configuration as the benchmark definition words it: dispatch and return as
+        # NCCL all-to-all, same stages, same fixed segments (eager: collectives between them)
+        try:
+            stages.layer.reserve_sms(int(os.environ.get("NMOE_EP_RESERVED_SMS", "16")))
+            nccl_ms = timed(lambda: engine.step(x, out), max(3, args.steps // 2), 3)
+            nccl_arm = {"ms_per_step": nccl_ms, "tokens_per_s": tokens_total / (nccl_ms * 1e-3),
+                        "how": "same stages with host-issued NCCL all-to-all of the fixed "
+                               "segments between them, eager launches, 16 SMs kept free for "
+                               "NCCL's kernels"}
+            if stages.sync_status() != NMOE_OK:
+                nccl_arm["device_error"] = True
+        except Exception as error:  # noqa: BLE001 - an extra key must not lose the line
+            nccl_arm = {"unavailable": str(error)[:200]}
     sent = capacity * (world - 1)
     if transport == "window":
         exchange = {
@@ -535,7 +575,7 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
             "return": "bf16 rows stored by the down-projection epilogue of the grouped GEMM "
                       "straight into the source GPU's window, tile by tile",
         }
-        launches = 10 + 2 + 6 * engine.window_groups + 2
+        launches = stages.launches_per_window_step(engine.window_groups)
     else:
         exchange = {
             "dispatch": f"NVFP4 records, {stages.record_bytes} B per pair, fixed segments of "
@@ -543,8 +583,9 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
             "return": "bf16 rows, same segments, NCCL all-to-all in two source-rank groups",
         }
         launches = 13 + 6 * engine.chunks
+    value = tokens_total / (ms * 1e-3)
     return {
-        "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": "tokens/s",
+        "metric": METRIC, "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
@@ -566,13 +607,69 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
                 "one_batch_at_a_time_ms_per_step": serial_ms},
         "gpu_launches": launches * args.steps * world,
         "clocks": clocks,
+        "ep_parity": parity,
         "per_gpu_tokens": tokens,
+        "single_gpu_all_tokens": None if full_ms is None else {
+            "what": f"one GPU, all 128 experts, all T={tokens_total} tokens, measured on rank 0 "
+                    "in this run",
+            "ms_per_step": full_ms, "tokens_per_s": tokens_total / (full_ms * 1e-3)},
+        "strong_scaling_efficiency": None if full_ms is None else
+        value / (world * tokens_total / (full_ms * 1e-3)),
         "single_gpu_same_tokens": None if single_ms is None else {
             "what": f"one GPU, all 128 experts, T={tokens} (the per-GPU token count of this run)",
             "ms_per_step": single_ms, "tokens_per_s": tokens / (single_ms * 1e-3)},
-        "ep_efficiency": None if single_ms is None else
-        (tokens_total / (ms * 1e-3)) / (world * tokens / (single_ms * 1e-3)),
+        "ep_overhead_efficiency_same_per_gpu_tokens": None if single_ms is None else
+        value / (world * tokens / (single_ms * 1e-3)),
+        "nccl_transport": nccl_arm,
         "exchange_bytes_rank0": {"dispatch": sent * stages.record_bytes, "return": sent * H * 2},
         "ep_phase_end_ms_rank0_eager": {k: round(v, 4) for k, v in phases.items()},
         "roofline": None,
     }
+
+
+def ep_parity_check(package, single, data, x, out, rank, dist_module) -> dict:
+    """Compares `out`, the expert-parallel result for this rank's tokens `x`, with the
+    single-GPU layer `single` (all experts, same weights) on the same tokens, and on rank 0
+    the single-GPU layer with the CPU oracle on the first 256 tokens.  Returns the record
+    rank 0 prints; every rank takes part in the reductions."""
+    import numpy as np
+    tokens, H = x.shape
+    ref = torch.empty((tokens, H), dtype=out.dtype, device=x.device)
+    single.run_async(x, ref)
+    torch.cuda.synchronize()
+    status = single.sync_status()
+    diff = (out.to(torch.float32) - ref.to(torch.float32)).abs()
+    # bf16 rows: both sides round the same FP32 values, so equality is expected; the gate
+    # is the layer tolerance plus half a bf16 ulp at the reference value
+    mag = ref.to(torch.float32).abs().clamp_min(2.0 ** -126)
+    half_ulp = torch.exp2(torch.floor(torch.log2(mag)) - 8)
+    excess = float((diff - half_ulp).max().item())
+    stats = torch.tensor([float(torch.equal(out, ref)), -float(diff.max().item()), -excess,
+                          float(status == NMOE_OK)], device=x.device, dtype=torch.float64)
+    dist_module.all_reduce(stats, op=dist_module.ReduceOp.MIN)
+    record = {"tokens_checked_per_rank": tokens,
+              "bit_equal_to_single_gpu_on_every_rank": bool(stats[0].item() == 1.0),
+              "max_abs_vs_single_gpu": -float(stats[1].item()),
+              "within_2e-2_of_single_gpu": bool(-float(stats[2].item()) <= 2e-2),
+              "single_gpu_status_ok": bool(stats[3].item() == 1.0)}
+    if rank == 0:
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(
+            os.path.abspath(__file__))), "tests"))
+        try:
+            import helpers  # the test suite's parity report (CPU oracle): checker only
+            sample = min(256, tokens)
+            xs = x[:sample].contiguous()
+            outs = torch.empty((sample, H), dtype=torch.float32, device=x.device)
+            single.run_async(xs, outs)
+            torch.cuda.synchronize()
+            report = helpers.compare_layer_with_oracle(single, data, xs, outs)
+            record["single_gpu_vs_oracle"] = {"tokens": sample, "ok": bool(report.ok()),
+                                              "summary": report.summary()}
+        except Exception as error:  # noqa: BLE001
+            record["single_gpu_vs_oracle"] = {"ok": False, "error": str(error)[:300]}
+    oracle_ok = torch.tensor([1.0 if rank != 0 or record["single_gpu_vs_oracle"]["ok"] else 0.0],
+                             device=x.device)
+    dist_module.all_reduce(oracle_ok, op=dist_module.ReduceOp.MIN)
+    record["ok"] = bool(record["within_2e-2_of_single_gpu"] and record["single_gpu_status_ok"]
+                        and oracle_ok.item() == 1.0)
+    return record

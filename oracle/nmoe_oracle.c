@@ -580,17 +580,33 @@ static void matvec_transposed(const float* a, const float* wt, size_t out_rows,
 
 /* A device result may legitimately differ from this oracle in a quantised
  * intermediate when the FP32 value being quantised sits within rounding
- * noise of a code boundary (the two sides accumulate K products in different
- * orders).  Given the oracle's own row `h` and a candidate (packed, scales)
- * row from the device, adopt the candidate wherever it differs but is what
- * the reference packer would emit for an input perturbed by a relative
- * `eps`; count adopted and inadmissible differences.  Only blocks whose
- * tensor scale is 1.0 are considered (larger rows keep the oracle's codes). */
+ * noise of a code boundary: both sides accumulate the K products of the up
+ * projection in FP32, in different orders.  Given the oracle's own
+ * pre-activation row `u` (h = relu^2(u) is what gets quantised) and a
+ * candidate (packed, scales) row from the device, a differing code or scale
+ * byte is ADOPTED when the smallest shift of the pre-activation that makes the
+ * reference packer emit the device's byte is at most `limit` noise units, and
+ * counted as INADMISSIBLE otherwise.
+ *
+ * Noise unit of output i: 2^-24 * sum_c |a[c] * w[i][c]|.  A sequential FP32
+ * sum of K random-sign terms carries an rms error of about half that unit
+ * (each add rounds at relative 2^-24 of a partial sum that performs a random
+ * walk), so a handful of units covers the largest accumulation error among
+ * ~10^8 outputs, while a systematic error in the GEMM or its epilogue (a wrong
+ * scale, a dropped K block) is thousands of units.  A code is also given the
+ * pre-activation equivalent of the block maximum's noise, because the divisor
+ * of every value of a block derives from that maximum.
+ *
+ * Only rows whose tensor scale is 1.0 are considered (larger rows keep the
+ * oracle's codes).  The largest adopted distance is reported so that a test
+ * can assert how close to the boundary the adopted values really were. */
 typedef struct {
   int64_t adopted_codes;
   int64_t adopted_scales;
   int64_t inadmissible_codes;
   int64_t inadmissible_scales;
+  double max_noise_units; /* largest adopted shift, in noise units */
+  double max_rel_shift;   /* the same shift relative to |u| */
 } nmo_override_stats;
 
 static int e2m1_rank(uint8_t code) {
@@ -598,50 +614,129 @@ static int e2m1_rank(uint8_t code) {
   return (code & 8) ? -mag : mag;
 }
 
-static void apply_override(const float* h, size_t cols, float tensor_scale,
-                           uint8_t* packed, uint8_t* scales,
-                           const uint8_t* cand_packed, const uint8_t* cand_scales,
-                           float eps, nmo_override_stats* stats) {
-  if (tensor_scale != 1.0f) return;
-  for (size_t blk = 0; blk < cols / NMO_BLOCK; ++blk) {
-    const float* b = h + blk * NMO_BLOCK;
-    float block_max = 0.0f;
-    for (int i = 0; i < NMO_BLOCK; ++i) {
-      const float a = fabsf(b[i]);
-      if (a > block_max) block_max = a;
+/* what the packer needs to know about the row being checked */
+typedef struct {
+  const float* u;    /* [cols] pre-activation (before relu^2) */
+  const float* a;    /* [K] dequantised activation row */
+  const float* wt;   /* [K][cols] dequantised up_proj, transposed */
+  size_t k;
+  size_t cols;
+} nmo_override_row;
+
+static double noise_unit(const nmo_override_row* row, size_t i) {
+  double sum = 0.0;
+  for (size_t c = 0; c < row->k; ++c) sum += fabs((double)row->a[c] * (double)row->wt[c * row->cols + i]);
+  return sum * 5.9604644775390625e-08; /* 2^-24 */
+}
+
+static float relu2_shifted(float u, double shift) {
+  const float v = (float)((double)u + shift);
+  return v > 0.0f ? v * v : 0.0f;
+}
+
+/* smallest |shift| (searched up to `bound`, direction `dir`) for which
+ * rank(shifted value) reaches `target`; negative when even `bound` does not. */
+static double code_shift(float u, float bs, int target, int dir, double bound) {
+  const int at_bound = e2m1_rank(nmo_encode_e2m1(relu2_shifted(u, dir * bound) / bs));
+  if (dir > 0 ? at_bound < target : at_bound > target) return -1.0;
+  double lo = 0.0, hi = bound;
+  for (int it = 0; it < 48; ++it) {
+    const double mid = 0.5 * (lo + hi);
+    const int r = e2m1_rank(nmo_encode_e2m1(relu2_shifted(u, dir * mid) / bs));
+    if (dir > 0 ? r >= target : r <= target) hi = mid; else lo = mid;
+  }
+  return hi;
+}
+
+static double scale_shift(float u, int target, int dir, double bound) {
+  float m = relu2_shifted(u, dir * bound);
+  int at_bound = nmo_encode_e4m3(m > 0.0f ? clamp_scale(m / kFp4Max) : 1.0f);
+  if (dir > 0 ? at_bound < target : at_bound > target) return -1.0;
+  double lo = 0.0, hi = bound;
+  for (int it = 0; it < 48; ++it) {
+    const double mid = 0.5 * (lo + hi);
+    m = relu2_shifted(u, dir * mid);
+    const int r = nmo_encode_e4m3(m > 0.0f ? clamp_scale(m / kFp4Max) : 1.0f);
+    if (dir > 0 ? r >= target : r <= target) hi = mid; else lo = mid;
+  }
+  return hi;
+}
+
+static void note_adopted(nmo_override_stats* stats, double shift, double unit, float u) {
+  const double units = shift / unit;
+  if (units > stats->max_noise_units) stats->max_noise_units = units;
+  const double rel = fabs((double)u) > 0.0 ? shift / fabs((double)u) : 0.0;
+  if (rel > stats->max_rel_shift) stats->max_rel_shift = rel;
+}
+
+/* Returns 1 when anything was adopted. */
+static int apply_override(const nmo_override_row* row, float tensor_scale, uint8_t* packed,
+                          uint8_t* scales, const uint8_t* cand_packed,
+                          const uint8_t* cand_scales, float limit, nmo_override_stats* stats) {
+  if (tensor_scale != 1.0f) return 0;
+  int adopted = 0;
+  for (size_t blk = 0; blk < row->cols / NMO_BLOCK; ++blk) {
+    const float* ub = row->u + blk * NMO_BLOCK;
+    const int scale_differs = cand_scales[blk] != scales[blk];
+    int codes_differ = 0;
+    for (size_t j = 0; j < NMO_BLOCK / 2; ++j) {
+      codes_differ |= packed[blk * (NMO_BLOCK / 2) + j] != cand_packed[blk * (NMO_BLOCK / 2) + j];
     }
+    if (!scale_differs && !codes_differ) continue;
+    /* the block maximum decides the block scale */
+    int i_max = 0;
+    for (int i = 1; i < NMO_BLOCK; ++i) {
+      if (ub[i] > ub[i_max]) i_max = i;
+    }
+    const float block_max = relu2(ub[i_max]);
     const float bs = block_max > 0.0f ? clamp_scale(block_max / kFp4Max) : 1.0f;
-    if (cand_scales[blk] != scales[blk]) {
-      const uint8_t lo = nmo_encode_e4m3(bs * (1.0f - eps));
-      const uint8_t hi = nmo_encode_e4m3(bs * (1.0f + eps));
-      if (cand_scales[blk] >= lo && cand_scales[blk] <= hi) {
+    const double unit_max = noise_unit(row, blk * NMO_BLOCK + (size_t)i_max);
+    if (scale_differs) {
+      const int dir = cand_scales[blk] > scales[blk] ? 1 : -1;
+      const double shift = scale_shift(ub[i_max], cand_scales[blk], dir, unit_max * limit);
+      if (shift >= 0.0 && unit_max > 0.0) {
         scales[blk] = cand_scales[blk];
         stats->adopted_scales++;
+        note_adopted(stats, shift, unit_max, ub[i_max]);
+        adopted = 1;
       } else {
         stats->inadmissible_scales++;
       }
     }
     for (int i = 0; i < NMO_BLOCK; ++i) {
       const size_t byte_index = (blk * NMO_BLOCK + (size_t)i) / 2;
-      const int shift = (i & 1) ? 4 : 0;
-      const uint8_t mine = (packed[byte_index] >> shift) & 0x0fu;
-      const uint8_t theirs = (cand_packed[byte_index] >> shift) & 0x0fu;
+      const int shift_bits = (i & 1) ? 4 : 0;
+      const uint8_t mine = (packed[byte_index] >> shift_bits) & 0x0fu;
+      const uint8_t theirs = (cand_packed[byte_index] >> shift_bits) & 0x0fu;
       if (mine == theirs) continue;
-      const float v = b[i] / bs;
-      const float spread = fabsf(v) * 2.0f * eps;
-      const int r_lo = e2m1_rank(nmo_encode_e2m1(v - spread));
-      const int r_hi = e2m1_rank(nmo_encode_e2m1(v + spread));
-      const int r = e2m1_rank(theirs);
-      /* +0 and -0 share rank 0 */
-      if (r >= r_lo && r <= r_hi) {
-        packed[byte_index] = (uint8_t)((packed[byte_index] & ~(0x0fu << shift)) |
-                                       (theirs << shift));
+      const int r_mine = e2m1_rank(mine), r_theirs = e2m1_rank(theirs);
+      if (r_mine == r_theirs) continue; /* +0 and -0 */
+      /* own accumulation noise plus the share of the block maximum's */
+      double unit = noise_unit(row, blk * NMO_BLOCK + (size_t)i);
+      if (ub[i_max] > 0.0f && ub[i] > 0.0f) unit += (double)ub[i] * unit_max / (double)ub[i_max];
+      const double shift =
+          code_shift(ub[i], bs, r_theirs, r_theirs > r_mine ? 1 : -1, unit * limit);
+      if (shift >= 0.0 && unit > 0.0) {
+        packed[byte_index] =
+            (uint8_t)((packed[byte_index] & ~(0x0fu << shift_bits)) | (theirs << shift_bits));
         stats->adopted_codes++;
+        note_adopted(stats, shift, unit, ub[i]);
+        adopted = 1;
       } else {
         stats->inadmissible_codes++;
       }
     }
   }
+  return adopted;
+}
+
+static void merge_override_stats(nmo_override_stats* total, const nmo_override_stats* local) {
+  total->adopted_codes += local->adopted_codes;
+  total->adopted_scales += local->adopted_scales;
+  total->inadmissible_codes += local->inadmissible_codes;
+  total->inadmissible_scales += local->inadmissible_scales;
+  if (local->max_noise_units > total->max_noise_units) total->max_noise_units = local->max_noise_units;
+  if (local->max_rel_shift > total->max_rel_shift) total->max_rel_shift = local->max_rel_shift;
 }
 
 /* ------------------------------------------------------------------------ */
@@ -699,8 +794,9 @@ typedef struct {
   const uint8_t* cand_hid_scales;
   const uint8_t* cand_shid_packed;
   const uint8_t* cand_shid_scales;
-  float override_eps;
+  float override_limit;     /* admissible shift of a pre-activation, in noise units */
   nmo_override_stats stats;
+  uint8_t* adopted_token;   /* optional [T]: 1 where a code or scale of the token was adopted */
 } nmo_layer_trace;
 
 /* One expert FFN on a single activation row that is ALREADY dequantised:
@@ -708,17 +804,19 @@ typedef struct {
  * Follows expert_layer.cpp:913-922 (routed) and :814-818/:956-964/:981-1005
  * (shared, with shared_up taken through the NVFP4 host linear as well). */
 static int expert_row(const float* a_deq, size_t H, size_t I, const float* up_t,
-                      const float* down_t, float* scratch_h /* [I] */,
+                      const float* down_t, float* scratch_u /* [I] */, float* scratch_h /* [I] */,
                       float* scratch_hd /* [I] */, uint8_t* hq /* [I/2] */,
                       uint8_t* hs /* [I/16] */, const uint8_t* cand_q,
-                      const uint8_t* cand_s, float eps, nmo_override_stats* stats,
-                      float* out /* [H] */) {
-  matvec_transposed(a_deq, up_t, I, H, scratch_h);
-  for (size_t i = 0; i < I; ++i) scratch_h[i] = relu2(scratch_h[i]);
+                      const uint8_t* cand_s, float limit, nmo_override_stats* stats,
+                      int* adopted, float* out /* [H] */) {
+  matvec_transposed(a_deq, up_t, I, H, scratch_u);
+  for (size_t i = 0; i < I; ++i) scratch_h[i] = relu2(scratch_u[i]);
   float ts = 1.0f;
   if (nmo_pack_nvfp4(scratch_h, 1, I, 0.0f, hq, hs, &ts) != 0) return -1;
   if (cand_q != NULL && cand_s != NULL) {
-    apply_override(scratch_h, I, ts, hq, hs, cand_q, cand_s, eps, stats);
+    const nmo_override_row row = {scratch_u, a_deq, up_t, H, I};
+    const int any = apply_override(&row, ts, hq, hs, cand_q, cand_s, limit, stats);
+    if (adopted != NULL && any) *adopted = 1;
   }
   nmo_dequant_nvfp4(hq, hs, ts, 1, I, scratch_hd);
   matvec_transposed(scratch_hd, down_t, H, I, out);
@@ -790,16 +888,18 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
       pairs[start[e] + count[e]++] = p;
     }
 
-    nmo_override_stats total = {0, 0, 0, 0};
+    nmo_override_stats total = {0, 0, 0, 0, 0.0, 0.0};
+    if (trace && trace->adopted_token) memset(trace->adopted_token, 0, Tn);
 #pragma omp parallel
     {
       float* up_t = (float*)malloc(sizeof(float) * H * I);
       float* down_t = (float*)malloc(sizeof(float) * H * I);
+      float* u = (float*)malloc(sizeof(float) * I);
       float* h = (float*)malloc(sizeof(float) * I);
       float* hd = (float*)malloc(sizeof(float) * I);
       uint8_t* hq = (uint8_t*)malloc(I / 2);
       uint8_t* hs = (uint8_t*)malloc(I / NMO_BLOCK);
-      nmo_override_stats local = {0, 0, 0, 0};
+      nmo_override_stats local = {0, 0, 0, 0, 0.0, 0.0};
 #pragma omp for schedule(dynamic, 1)
       for (size_t e = 0; e < E; ++e) {
         if (count[e] == 0) continue;
@@ -816,10 +916,16 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
             cq = trace->cand_hid_packed + p * (I / 2);
             cs = trace->cand_hid_scales + p * (I / NMO_BLOCK);
           }
-          if (expert_row(a_deq + t * H, H, I, up_t, down_t, h, hd, hq, hs, cq, cs,
-                         trace ? trace->override_eps : 0.0f, &local, routed + p * H) != 0) {
+          int adopted = 0;
+          if (expert_row(a_deq + t * H, H, I, up_t, down_t, u, h, hd, hq, hs, cq, cs,
+                         trace ? trace->override_limit : 0.0f, &local, &adopted,
+                         routed + p * H) != 0) {
 #pragma omp atomic write
             status = -4;
+          }
+          if (adopted && trace && trace->adopted_token) {
+#pragma omp atomic write
+            trace->adopted_token[t] = 1;
           }
           if (trace && trace->hid_packed) memcpy(trace->hid_packed + p * (I / 2), hq, I / 2);
           if (trace && trace->hid_scales)
@@ -828,17 +934,13 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
       }
       free(up_t);
       free(down_t);
+      free(u);
       free(h);
       free(hd);
       free(hq);
       free(hs);
 #pragma omp critical
-      {
-        total.adopted_codes += local.adopted_codes;
-        total.adopted_scales += local.adopted_scales;
-        total.inadmissible_codes += local.inadmissible_codes;
-        total.inadmissible_scales += local.inadmissible_scales;
-      }
+      merge_override_stats(&total, &local);
     }
 
     /* shared expert, one "expert" over all tokens */
@@ -851,11 +953,12 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
                                 w->shared_down.tensor_scale, H, S, down_t);
 #pragma omp parallel
       {
+        float* u = (float*)malloc(sizeof(float) * S);
         float* h = (float*)malloc(sizeof(float) * S);
         float* hd = (float*)malloc(sizeof(float) * S);
         uint8_t* hq = (uint8_t*)malloc(S / 2);
         uint8_t* hs = (uint8_t*)malloc(S / NMO_BLOCK);
-        nmo_override_stats local = {0, 0, 0, 0};
+        nmo_override_stats local = {0, 0, 0, 0, 0.0, 0.0};
 #pragma omp for schedule(dynamic, 4)
         for (size_t t = 0; t < Tn; ++t) {
           const uint8_t* cq = NULL;
@@ -864,26 +967,28 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
             cq = trace->cand_shid_packed + t * (S / 2);
             cs = trace->cand_shid_scales + t * (S / NMO_BLOCK);
           }
-          if (expert_row(a_deq + t * H, H, S, up_t, down_t, h, hd, hq, hs, cq, cs,
-                         trace ? trace->override_eps : 0.0f, &local, shared + t * H) != 0) {
+          int adopted = 0;
+          if (expert_row(a_deq + t * H, H, S, up_t, down_t, u, h, hd, hq, hs, cq, cs,
+                         trace ? trace->override_limit : 0.0f, &local, &adopted,
+                         shared + t * H) != 0) {
 #pragma omp atomic write
             status = -5;
+          }
+          if (adopted && trace && trace->adopted_token) {
+#pragma omp atomic write
+            trace->adopted_token[t] = 1;
           }
           if (trace && trace->shid_packed) memcpy(trace->shid_packed + t * (S / 2), hq, S / 2);
           if (trace && trace->shid_scales)
             memcpy(trace->shid_scales + t * (S / NMO_BLOCK), hs, S / NMO_BLOCK);
         }
+        free(u);
         free(h);
         free(hd);
         free(hq);
         free(hs);
 #pragma omp critical
-        {
-          total.adopted_codes += local.adopted_codes;
-          total.adopted_scales += local.adopted_scales;
-          total.inadmissible_codes += local.inadmissible_codes;
-          total.inadmissible_scales += local.inadmissible_scales;
-        }
+        merge_override_stats(&total, &local);
       }
       free(up_t);
       free(down_t);
@@ -931,6 +1036,67 @@ done:
   free(aq);
   free(as);
   free(ats);
+  return status;
+}
+
+/* One expert FFN over `rows` FP32 activation rows: pack(row) -> dequant ->
+ * up -> relu^2 -> pack(row) -> [override] -> dequant -> down, i.e. two
+ * RunNvfp4LinearHost calls (expert_layer.cpp:913-922) per row with the weights
+ * dequantised once.  Optional outputs may be NULL. */
+NMO_EXPORT int nmo_expert_ffn_forward(const float* x, int64_t rows, int32_t hidden,
+                                      int32_t inter, const nmo_nvfp4_weight* up,
+                                      const nmo_nvfp4_weight* down, float* out,
+                                      uint8_t* hid_packed, uint8_t* hid_scales,
+                                      const uint8_t* cand_packed, const uint8_t* cand_scales,
+                                      float override_limit, nmo_override_stats* stats,
+                                      uint8_t* adopted_row) {
+  const size_t H = (size_t)hidden, I = (size_t)inter, R = (size_t)rows;
+  if (rows <= 0 || H % NMO_BLOCK || I % NMO_BLOCK) return -1;
+  int status = 0;
+  float* up_t = (float*)malloc(sizeof(float) * H * I);
+  float* down_t = (float*)malloc(sizeof(float) * H * I);
+  dequant_weight_transposed(up->packed, up->scales, up->tensor_scale, I, H, up_t);
+  dequant_weight_transposed(down->packed, down->scales, down->tensor_scale, H, I, down_t);
+  nmo_override_stats total = {0, 0, 0, 0, 0.0, 0.0};
+#pragma omp parallel
+  {
+    float* a = (float*)malloc(sizeof(float) * H);
+    uint8_t* aq = (uint8_t*)malloc(H / 2);
+    uint8_t* as = (uint8_t*)malloc(H / NMO_BLOCK);
+    float* u = (float*)malloc(sizeof(float) * I);
+    float* h = (float*)malloc(sizeof(float) * I);
+    float* hd = (float*)malloc(sizeof(float) * I);
+    uint8_t* hq = (uint8_t*)malloc(I / 2);
+    uint8_t* hs = (uint8_t*)malloc(I / NMO_BLOCK);
+    nmo_override_stats local = {0, 0, 0, 0, 0.0, 0.0};
+#pragma omp for schedule(dynamic, 4)
+    for (size_t r = 0; r < R; ++r) {
+      float ats = 1.0f;
+      int adopted = 0;
+      if (nmo_pack_nvfp4(x + r * H, 1, H, 0.0f, aq, as, &ats) != 0) {
+#pragma omp atomic write
+        status = -3;
+        continue;
+      }
+      nmo_dequant_nvfp4(aq, as, ats, 1, H, a);
+      if (expert_row(a, H, I, up_t, down_t, u, h, hd, hq, hs,
+                     cand_packed ? cand_packed + r * (I / 2) : NULL,
+                     cand_scales ? cand_scales + r * (I / NMO_BLOCK) : NULL, override_limit,
+                     &local, &adopted, out + r * H) != 0) {
+#pragma omp atomic write
+        status = -4;
+      }
+      if (hid_packed) memcpy(hid_packed + r * (I / 2), hq, I / 2);
+      if (hid_scales) memcpy(hid_scales + r * (I / NMO_BLOCK), hs, I / NMO_BLOCK);
+      if (adopted_row) adopted_row[r] = (uint8_t)adopted;
+    }
+    free(a); free(aq); free(as); free(u); free(h); free(hd); free(hq); free(hs);
+#pragma omp critical
+    merge_override_stats(&total, &local);
+  }
+  if (stats) *stats = total;
+  free(up_t);
+  free(down_t);
   return status;
 }
 

@@ -44,7 +44,8 @@ class _LayerWeights(ctypes.Structure):
 
 class _OverrideStats(ctypes.Structure):
     _fields_ = [("adopted_codes", ctypes.c_int64), ("adopted_scales", ctypes.c_int64),
-                ("inadmissible_codes", ctypes.c_int64), ("inadmissible_scales", ctypes.c_int64)]
+                ("inadmissible_codes", ctypes.c_int64), ("inadmissible_scales", ctypes.c_int64),
+                ("max_noise_units", ctypes.c_double), ("max_rel_shift", ctypes.c_double)]
 
 
 class _LayerTrace(ctypes.Structure):
@@ -54,7 +55,8 @@ class _LayerTrace(ctypes.Structure):
                 ("routed_out", _f32p), ("shid_packed", _u8p), ("shid_scales", _u8p),
                 ("shared_out", _f32p), ("cand_hid_packed", _u8p), ("cand_hid_scales", _u8p),
                 ("cand_shid_packed", _u8p), ("cand_shid_scales", _u8p),
-                ("override_eps", ctypes.c_float), ("stats", _OverrideStats)]
+                ("override_limit", ctypes.c_float), ("stats", _OverrideStats),
+                ("adopted_token", _u8p)]
 
 
 _lib = None
@@ -107,6 +109,10 @@ def lib() -> ctypes.CDLL:
         L.nmo_layer_forward_literal.argtypes = [ctypes.POINTER(_LayerConfig),
                                                 ctypes.POINTER(_LayerWeights), _f32p,
                                                 ctypes.c_int64, _f32p]
+        L.nmo_expert_ffn_forward.argtypes = [
+            _f32p, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.POINTER(_Nvfp4Weight),
+            ctypes.POINTER(_Nvfp4Weight), _f32p, _u8p, _u8p, _u8p, _u8p, ctypes.c_float,
+            ctypes.POINTER(_OverrideStats), _u8p]
         L.nmo_num_threads.restype = ctypes.c_int
         _lib = L
     return _lib
@@ -348,13 +354,22 @@ class LayerResult:
     adopted_scales: int = 0
     inadmissible_codes: int = 0
     inadmissible_scales: int = 0
+    max_noise_units: float = 0.0       # largest adopted pre-activation shift, in noise units
+    max_rel_shift: float = 0.0         # the same shift relative to the pre-activation
+    adopted_token: Optional[np.ndarray] = None  # [T] bool: the token owns an adopted byte
+
+
+DEFAULT_OVERRIDE_LIMIT = 6.0
 
 
 def layer_forward(cfg: LayerConfig, w: LayerWeights, x, candidates=None,
-                  override_eps: float = 1e-4, want_routed_out: bool = False) -> LayerResult:
+                  override_limit: float = DEFAULT_OVERRIDE_LIMIT,
+                  want_routed_out: bool = False) -> LayerResult:
     """The whole layer on FP32 input [T, H].  `candidates` = (hid_packed [T,k,I/2],
     hid_scales [T,k,I/16], shid_packed [T,S/2], shid_scales [T,S/16]) from the device
-    turns on the admissible-code override."""
+    turns on the admissible-code override: a differing intermediate byte is adopted when
+    a shift of the pre-activation by at most `override_limit` accumulation-noise units
+    (2^-24 * sum |a_c w_c|) makes the reference packer emit it."""
     x = _f32(x)
     T = x.shape[0]
     H, I, S, E, K = (cfg.hidden, cfg.routed_intermediate, cfg.shared_intermediate, cfg.experts,
@@ -386,7 +401,9 @@ def layer_forward(cfg: LayerConfig, w: LayerWeights, x, candidates=None,
     if want_routed_out:
         tr.routed_out = _p(r.routed_out, _f32p)
     tr.shared_out = _p(r.shared_out, _f32p)
-    tr.override_eps = override_eps
+    tr.override_limit = override_limit
+    adopted_token = np.zeros((T,), np.uint8)
+    tr.adopted_token = _p(adopted_token, _u8p)
     if candidates is not None:
         cands = [_u8(a) for a in candidates]
         keep.extend(cands)
@@ -402,6 +419,9 @@ def layer_forward(cfg: LayerConfig, w: LayerWeights, x, candidates=None,
     r.adopted_scales = tr.stats.adopted_scales
     r.inadmissible_codes = tr.stats.inadmissible_codes
     r.inadmissible_scales = tr.stats.inadmissible_scales
+    r.max_noise_units = tr.stats.max_noise_units
+    r.max_rel_shift = tr.stats.max_rel_shift
+    r.adopted_token = adopted_token.astype(bool)
     return r
 
 
@@ -417,10 +437,55 @@ def layer_forward_literal(cfg: LayerConfig, w: LayerWeights, x) -> np.ndarray:
     return out
 
 
-def expert_ffn(x, up: Nvfp4Weight, down: Nvfp4Weight, candidates=None, override_eps=1e-4):
-    """down(relu^2(up(x))) per row through a one-expert layer-free path: built from
-    the layer's shared-expert branch with a zero-sized routed part is not possible,
-    so this composes the literal row linear (slow, small shapes only)."""
+@dataclass
+class FfnResult:
+    out: np.ndarray
+    hid_packed: np.ndarray
+    hid_scales: np.ndarray
+    adopted_codes: int = 0
+    adopted_scales: int = 0
+    inadmissible_codes: int = 0
+    inadmissible_scales: int = 0
+    max_noise_units: float = 0.0
+    max_rel_shift: float = 0.0
+    adopted_row: Optional[np.ndarray] = None
+
+
+def expert_ffn_forward(x, up: Nvfp4Weight, down: Nvfp4Weight, candidates=None,
+                       override_limit: float = DEFAULT_OVERRIDE_LIMIT) -> FfnResult:
+    """down(relu^2(up(x))) per row, both projections through the NVFP4 host linear with
+    the weights dequantised once (bit-equal to `expert_ffn`, fast).  `candidates` =
+    (hid_packed [R, I/2], hid_scales [R, I/16]) from the device turns on the
+    admissible-code override of `layer_forward`."""
+    x = _f32(x)
+    R, H = x.shape
+    I = up.packed.shape[0]
+    keep: list = []
+    cup, cdown = _cw(up, keep), _cw(down, keep)
+    res = FfnResult(out=np.zeros((R, H), np.float32), hid_packed=np.zeros((R, I // 2), np.uint8),
+                    hid_scales=np.zeros((R, I // 16), np.uint8))
+    stats = _OverrideStats()
+    adopted = np.zeros((R,), np.uint8)
+    cq = cs = None
+    if candidates is not None:
+        cq, cs = _u8(candidates[0]), _u8(candidates[1])
+    rc = lib().nmo_expert_ffn_forward(
+        _p(x, _f32p), R, H, I, ctypes.byref(cup), ctypes.byref(cdown), _p(res.out, _f32p),
+        _p(res.hid_packed, _u8p), _p(res.hid_scales, _u8p),
+        _p(cq, _u8p) if cq is not None else None, _p(cs, _u8p) if cs is not None else None,
+        ctypes.c_float(override_limit), ctypes.byref(stats), _p(adopted, _u8p))
+    if rc != 0:
+        raise RuntimeError(f"nmo_expert_ffn_forward failed with {rc}")
+    for name in ("adopted_codes", "adopted_scales", "inadmissible_codes", "inadmissible_scales",
+                 "max_noise_units", "max_rel_shift"):
+        setattr(res, name, getattr(stats, name))
+    res.adopted_row = adopted.astype(bool)
+    return res
+
+
+def expert_ffn(x, up: Nvfp4Weight, down: Nvfp4Weight):
+    """down(relu^2(up(x))) per row composed from the literal row linear (re-dequantises
+    the weight for every row: slow, small shapes only).  Returns (hidden, out)."""
     x = _f32(x)
     h = nvfp4_linear_literal(x, up.packed, up.scales, up.tensor_scale)
     h = np.where(h > 0, h * h, 0).astype(np.float32)

@@ -11,7 +11,14 @@ import __graft_entry__ as entry
 
 MAX_ABS_TOL = 2e-2      # north-star tolerance on the layer output
 COSINE_TOL = 0.9995
-OVERRIDE_EPS = 1e-4     # relative perturbation that defines an admissible code difference
+# An intermediate FP4 code or scale byte of the device may differ from the oracle's only
+# where a shift of the up-projection's pre-activation by at most this many accumulation-
+# noise units (2^-24 * sum_c |a_c w_c|, see apply_override in oracle/nmoe_oracle.c) makes
+# the reference packer emit the device's byte.  A sequential FP32 sum has an rms error of
+# about half a unit; the largest shift measured on B200 over 1.2e8 codes is reported by
+# every parity run as `max_noise_units`.
+OVERRIDE_LIMIT = 6.0
+ADOPTED_FRACTION_MAX = 1e-5   # adopted bytes / intermediate codes: ties are rare
 
 
 def oracle_config(cfg):
@@ -79,8 +86,12 @@ class ParityReport:
     adopted_scales: int = 0
     inadmissible_codes: int = 0
     inadmissible_scales: int = 0
+    max_noise_units: float = 0.0   # largest pre-activation shift among the adopted bytes
+    max_rel_shift: float = 0.0     # the same, relative to the pre-activation
     raw_max_abs: float = 0.0
     raw_cosine: float = 0.0
+    raw_tokens_over_tol: int = 0           # tokens whose raw error exceeds the tolerance
+    raw_tokens_over_tol_without_tie: int = 0  # ... and that own no adopted byte
     max_abs: float = 0.0      # against the oracle run with admissible device codes adopted
     cosine: float = 0.0
     out_is_bf16: bool = False
@@ -98,8 +109,13 @@ class ParityReport:
         # non-candidate logits of the two-pass router come from the tensor-core pass;
         # its error must stay far inside the tie margin (2e-4 on scores = 8e-4 on logits)
         router = self.logits_max_diff <= 1e-4 and self.weight_max_diff <= 1e-6
-        return (exact and close and router and self.cosine >= COSINE_TOL and
-                self.raw_cosine >= COSINE_TOL)
+        # ties are rare and close: a systematic error would flip codes everywhere
+        adopted = self.adopted_codes + self.adopted_scales
+        rare = adopted <= max(4, int(ADOPTED_FRACTION_MAX * self.hidden_codes_total))
+        # against the oracle as it is: every token off by more than the tolerance owns a tie
+        raw = self.raw_tokens_over_tol_without_tie == 0 and self.raw_cosine >= COSINE_TOL
+        return (exact and close and router and rare and raw and self.cosine >= COSINE_TOL and
+                self.max_noise_units <= OVERRIDE_LIMIT)
 
     def summary(self) -> str:
         return (f"T={self.tokens} idx_set_mismatch={self.index_set_mismatches} "
@@ -108,7 +124,11 @@ class ParityReport:
                 f"hidden_scale_mismatch={self.hidden_scale_mismatches} "
                 f"adopted={self.adopted_codes}+{self.adopted_scales} "
                 f"inadmissible={self.inadmissible_codes}+{self.inadmissible_scales} "
+                f"tie_distance={self.max_noise_units:.3g} noise units "
+                f"(rel {self.max_rel_shift:.3g}) "
                 f"raw_max_abs={self.raw_max_abs:.3g} raw_cos={self.raw_cosine:.6f} "
+                f"raw_tokens_over_tol={self.raw_tokens_over_tol} "
+                f"(without a tie: {self.raw_tokens_over_tol_without_tie}) "
                 f"max_abs={self.max_abs:.3g} cos={self.cosine:.6f} "
                 f"norm_diff={self.norm_max_diff:.3g} logits_diff={self.logits_max_diff:.3g} "
                 f"weight_diff={self.weight_max_diff:.3g}"
@@ -136,7 +156,8 @@ def compare_layer_with_oracle(layer, layer_data, x: torch.Tensor, out: torch.Ten
     rep = ParityReport(tokens=T, out_is_bf16=out.dtype == torch.bfloat16)
     cands = (_np(trace.routed_hidden_packed), _np(trace.routed_hidden_scales),
              _np(trace.shared_hidden_packed), _np(trace.shared_hidden_scales))
-    forced = oracle.layer_forward(ocfg, ow, x_np, candidates=cands, override_eps=OVERRIDE_EPS)
+    forced = oracle.layer_forward(ocfg, ow, x_np, candidates=cands,
+                                  override_limit=OVERRIDE_LIMIT)
     raw = oracle.layer_forward(ocfg, ow, x_np) if raw_run else forced
 
     gi, oi = _np(trace.selected_index), raw.top_index
@@ -157,9 +178,15 @@ def compare_layer_with_oracle(layer, layer_data, x: torch.Tensor, out: torch.Ten
     rep.adopted_codes, rep.adopted_scales = forced.adopted_codes, forced.adopted_scales
     rep.inadmissible_codes = forced.inadmissible_codes
     rep.inadmissible_scales = forced.inadmissible_scales
+    rep.max_noise_units, rep.max_rel_shift = forced.max_noise_units, forced.max_rel_shift
     rep.raw_max_abs, rep.raw_cosine = max_abs_and_cosine(out_np, raw.out)
     rep.max_abs, rep.cosine = max_abs_and_cosine(out_np, forced.out)
+    raw_err = np.abs(out_np.astype(np.float64) - raw.out.astype(np.float64))
     if rep.out_is_bf16:
         err = np.abs(out_np.astype(np.float64) - forced.out.astype(np.float64))
         rep.bf16_excess = float(np.max(err - bf16_half_ulp(forced.out)))
+        raw_err = raw_err - bf16_half_ulp(raw.out)
+    over = raw_err.max(axis=1) > MAX_ABS_TOL
+    rep.raw_tokens_over_tol = int(np.count_nonzero(over))
+    rep.raw_tokens_over_tol_without_tie = int(np.count_nonzero(over & ~forced.adopted_token))
     return rep

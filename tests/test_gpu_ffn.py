@@ -14,46 +14,50 @@ def _run_case(package, oracle, synthetic, rows, hidden, inter, variant, seed=0):
     up, down = synthetic.make_ffn_weights(hidden, inter, seed=seed, device="cuda")
     x = synthetic.make_tokens(rows, hidden, seed=seed + 100, device="cuda")
     ffn = package.ExpertFfn(up, down, max_rows=max(rows, 128))
-    out = ffn.run(x, variant)
+    out = ffn.run(x, variant).cpu().numpy()
     gp, gs = ffn.hidden_codes(rows)
+    gp, gs = gp.cpu().numpy(), gs.cpu().numpy()
     ffn.close()
     x_np = x.to(torch.float32).cpu().numpy()
-    # oracle through a layer-free composition: pack rows, dequantise, sequential FP32 matmul
     oup = oracle.Nvfp4Weight(up.packed.cpu().numpy(), up.block_scales.cpu().numpy(), up.tensor_scale)
     odn = oracle.Nvfp4Weight(down.packed.cpu().numpy(), down.block_scales.cpu().numpy(),
                              down.tensor_scale)
-    hidden_ref, out_ref = oracle.expert_ffn(x_np, oup, odn)
-    hp, hs, hts = oracle.pack_nvfp4_per_row(hidden_ref)
-    code_mismatch = helpers.nibble_mismatches(gp.cpu().numpy(), hp)
-    scale_mismatch = int(np.count_nonzero(gs.cpu().numpy() != hs))
-    # second oracle pass on the device's own intermediate codes isolates the down projection
-    h_dev = oracle.dequant_nvfp4(gp.cpu().numpy(), gs.cpu().numpy(), 1.0)
-    out_forced = np.stack([oracle_row for oracle_row in _down_rows(oracle, h_dev, odn)])
-    max_abs, cosine = helpers.max_abs_and_cosine(out.cpu().numpy(), out_ref)
-    max_abs_forced, _ = helpers.max_abs_and_cosine(out.cpu().numpy(), out_forced)
-    return dict(max_abs=max_abs, cosine=cosine, max_abs_forced=max_abs_forced,
-                code_mismatch=code_mismatch, scale_mismatch=scale_mismatch,
-                total_codes=int(hp.size * 2))
+    # the oracle as it is, and with the device's intermediate bytes adopted where they are
+    # rounding ties (the only admissible difference)
+    raw = oracle.expert_ffn_forward(x_np, oup, odn)
+    tied = oracle.expert_ffn_forward(x_np, oup, odn, candidates=(gp, gs),
+                                     override_limit=helpers.OVERRIDE_LIMIT)
+    raw_max_abs, raw_cosine = helpers.max_abs_and_cosine(out, raw.out)
+    max_abs, cosine = helpers.max_abs_and_cosine(out, tied.out)
+    over = np.abs(out.astype(np.float64) - raw.out).max(axis=1) > helpers.MAX_ABS_TOL
+    return dict(max_abs=max_abs, cosine=cosine, raw_max_abs=raw_max_abs, raw_cosine=raw_cosine,
+                code_mismatch=helpers.nibble_mismatches(gp, raw.hid_packed),
+                scale_mismatch=int(np.count_nonzero(gs != raw.hid_scales)),
+                adopted=tied.adopted_codes + tied.adopted_scales,
+                inadmissible=tied.inadmissible_codes + tied.inadmissible_scales,
+                tie_distance=tied.max_noise_units,
+                rows_over_tol_without_tie=int(np.count_nonzero(over & ~tied.adopted_row)),
+                total_codes=int(gp.size * 2))
 
 
-def _down_rows(oracle, h_deq, down):
-    """Sequential FP32 dot products of already-dequantised rows with the dequantised weight."""
-    w = oracle.dequant_nvfp4(down.packed, down.scales, down.tensor_scale)
-    for row in h_deq:
-        acc = np.zeros(w.shape[0], dtype=np.float32)
-        for c in range(w.shape[1]):
-            acc = (acc + row[c] * w[:, c]).astype(np.float32)
-        yield acc
+def _check(r):
+    # the stated gate (max-abs 2e-2, cosine 0.9995) against the oracle with admissible ties
+    # adopted; nothing but ties may differ, ties are rare and within accumulation noise,
+    # and against the oracle as it is only rows that own a tie may exceed the tolerance
+    assert r["inadmissible"] == 0
+    assert r["adopted"] == r["code_mismatch"] + r["scale_mismatch"]
+    assert r["adopted"] <= max(4, int(helpers.ADOPTED_FRACTION_MAX * r["total_codes"]))
+    assert r["tie_distance"] <= helpers.OVERRIDE_LIMIT
+    assert r["max_abs"] <= 1e-3 <= helpers.MAX_ABS_TOL  # accumulation-order noise only
+    assert r["cosine"] >= helpers.COSINE_TOL and r["raw_cosine"] >= helpers.COSINE_TOL
+    assert r["rows_over_tol_without_tie"] == 0
 
 
 @pytest.mark.parametrize("rows,variant", [(64, 0), (64, 1), (64, 3), (20, 2), (130, 3), (300, 1), (300, 0)])
 def test_single_expert_ffn_baseline_shape(package, oracle, synthetic, rows, variant):
     r = _run_case(package, oracle, synthetic, rows, 2688, 1856, variant)
     print(rows, variant, r)
-    assert r["cosine"] >= helpers.COSINE_TOL
-    assert r["max_abs_forced"] <= 1e-3          # down projection alone: accumulation-order noise
-    assert r["code_mismatch"] <= max(2, r["total_codes"] // 20000)  # rounding ties only
-    assert r["max_abs"] <= helpers.MAX_ABS_TOL or r["code_mismatch"] + r["scale_mismatch"] > 0
+    _check(r)
 
 
 @pytest.mark.parametrize("hidden,inter", [(64, 64), (256, 128), (512, 1024)])
@@ -61,5 +65,4 @@ def test_single_expert_ffn_small_shapes(package, oracle, synthetic, hidden, inte
     for rows, variant in [(3, 1), (3, 2), (40, 1), (40, 3)]:
         r = _run_case(package, oracle, synthetic, rows, hidden, inter, variant, seed=hidden)
         print(hidden, inter, rows, variant, r)
-        assert r["cosine"] >= helpers.COSINE_TOL
-        assert r["max_abs_forced"] <= 1e-3
+        _check(r)

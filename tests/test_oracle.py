@@ -87,6 +87,11 @@ def test_expert_ffn_matches_reference(oracle, golden):
     hidden, out = oracle.expert_ffn(golden["ffn_x"], up, down)
     assert np.array_equal(hidden, golden["ffn_hidden"])
     assert np.array_equal(out, golden["ffn_out"])
+    # the weights-dequantised-once path is the same arithmetic
+    fast = oracle.expert_ffn_forward(golden["ffn_x"], up, down)
+    assert np.array_equal(fast.out, golden["ffn_out"])
+    hp, hs, _ = oracle.pack_nvfp4_per_row(golden["ffn_hidden"])
+    assert np.array_equal(fast.hid_packed, hp) and np.array_equal(fast.hid_scales, hs)
 
 
 def _tiny_layer(synthetic, seed=5, experts=32, hidden=128, routed=64, shared=128, zipf=False):
@@ -124,6 +129,41 @@ def test_override_adopts_only_admissible_codes(oracle, synthetic):
     cands[0][0, 0, 0] ^= 0x07  # a gross code error is not a rounding tie
     bad = oracle.layer_forward(ocfg, ow, x, candidates=cands)
     assert bad.inadmissible_codes >= 1 and np.array_equal(bad.out, base.out)
+    assert not bad.adopted_token.any()
+
+
+def test_override_distance_is_measured_in_accumulation_noise_units(oracle, golden):
+    """A neighbouring code is adopted exactly when the limit reaches the distance that
+    the oracle reports for it; the distance of a real near-tie is a few noise units,
+    that of an arbitrary value thousands."""
+    up = oracle.Nvfp4Weight(golden["ffn_up_p"], golden["ffn_up_s"], float(golden["ffn_up_ts"]))
+    down = oracle.Nvfp4Weight(golden["ffn_down_p"], golden["ffn_down_s"],
+                              float(golden["ffn_down_ts"]))
+    x = golden["ffn_x"]
+    base = oracle.expert_ffn_forward(x, up, down)
+    distances = []
+    for byte in range(0, base.hid_packed.shape[1], 3):
+        cand = base.hid_packed.copy()
+        low = int(cand[0, byte]) & 0x0f
+        if low & 8 or (low & 7) == 7:
+            continue
+        cand[0, byte] = (cand[0, byte] & 0xf0) | (low + 1)  # the next larger magnitude
+        wide = oracle.expert_ffn_forward(x, up, down, candidates=(cand, base.hid_scales),
+                                         override_limit=1e9)
+        assert wide.adopted_codes == 1 and wide.inadmissible_codes == 0 and wide.adopted_row[0]
+        assert not wide.adopted_row[1:].any()
+        d = wide.max_noise_units
+        distances.append(d)
+        below = oracle.expert_ffn_forward(x, up, down, candidates=(cand, base.hid_scales),
+                                          override_limit=float(d) * 0.99)
+        assert below.adopted_codes == 0 and below.inadmissible_codes == 1
+        assert np.array_equal(below.out, base.out)
+        above = oracle.expert_ffn_forward(x, up, down, candidates=(cand, base.hid_scales),
+                                          override_limit=float(d) * 1.01)
+        assert above.adopted_codes == 1
+    assert len(distances) >= 4
+    # arbitrary values are nowhere near a rounding boundary on this scale
+    assert np.median(distances) > 1e3
 
 
 def test_synthetic_weight_quantiser_matches_oracle(oracle, synthetic):

@@ -27,7 +27,7 @@ def _existing_path(package, x, norm, gate, bias, top_k, scaling):
     return package.router_topk(logits, bias, top_k, 1, 1, True, scaling)
 
 
-def test_noalloc_routing_matches_existing_entry_points_twice(package):
+def test_noalloc_routing_matches_existing_entry_points_twice(package, oracle):
     # first call: many rows; second call: fewer rows and another width, so that stale
     # contents of the shared array from the first call lie beside and behind the second's
     for rows, hidden, experts, top_k, dtype, seed in [
@@ -39,6 +39,13 @@ def test_noalloc_routing_matches_existing_entry_points_twice(package):
         torch.cuda.synchronize()
         assert torch.equal(idx, ref_idx)
         assert torch.equal(wt, ref_wt)  # same kernels, same inputs: not merely within 1e-5
+        # and against the CPU restatement of the reference's host path itself
+        y = oracle.rmsnorm(x.to(torch.float32).cpu().numpy(), norm.cpu().numpy(), 1e-5)
+        o_idx, o_wt = oracle.select_top_experts(
+            oracle.router_logits(y, gate.cpu().numpy()), bias.cpu().numpy(), top_k,
+            routed_scaling=2.5)
+        assert (idx.cpu().numpy() == o_idx).all()
+        assert abs(wt.cpu().numpy() - o_wt).max() <= 1.2e-7
 
 
 def test_noalloc_routing_rejects_sizes_beyond_its_fixed_scratch(package):
