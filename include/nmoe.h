@@ -40,7 +40,9 @@ typedef enum nmoe_status {
   NMOE_ERR_CAPACITY = 6         /* more tokens / row tiles than the layer was created for */
 } nmoe_status;
 
-typedef enum nmoe_dtype { NMOE_F32 = 0, NMOE_BF16 = 1 } nmoe_dtype;
+/* NMOE_F16 (binary16) is accepted only for the rows expert-parallel ranks return
+ * (rows_dtype of the nmoe_ep_* entry points); activations are FP32 or bf16. */
+typedef enum nmoe_dtype { NMOE_F32 = 0, NMOE_BF16 = 1, NMOE_F16 = 2 } nmoe_dtype;
 
 /* Mirrors nemotron::ExpertLayerConfig (expert_layer.h:18-31).  The latent
  * projections fc1_latent/fc2_latent of the reference layer
@@ -128,7 +130,8 @@ NMOE_API void nmoe_layer_destroy(nmoe_layer* layer);
  * output = input + routed + shared with the input RMSNorm inside.  input and
  * output are device [tokens][hidden] in the given dtypes and must not alias.
  * With FP32 output the per-slot rows are summed from FP32, in the reference's
- * order (:951-953, :1064-1069); with bf16 output they are rounded to bf16 first.
+ * order (:951-953, :1064-1069); with bf16 output they are rounded to binary16
+ * first (a row beyond 65504 is reported as NMOE_ERR_ACTIVATION_RANGE).
  * Enqueues on `stream` and returns; device-side failures surface through
  * nmoe_layer_sync_status(). */
 NMOE_API nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void* input,
@@ -192,8 +195,8 @@ typedef struct nmoe_trace_view {
   const float* parts;              /* [tokens][top_k+1][hidden]: weighted routed
                                       contributions in selection order, then shared.
                                       FP32 when the last run's output was FP32; a run
-                                      with bf16 output keeps these rows in bf16 and
-                                      leaves this field NULL */
+                                      with bf16 output keeps these rows in binary16
+                                      and leaves this field NULL */
 } nmoe_trace_view;
 NMOE_API nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out);
 /* Copies one nmoe_trace_view field (index in declaration order, 0 =
@@ -226,7 +229,8 @@ NMOE_API nmoe_status nmoe_layer_export_hidden(nmoe_layer* layer, void* stream,
  *   -- exchange counts, then records (all-to-all-v, rows = records) --
  *   nmoe_ep_experts    runs this rank's experts over `count` received records
  *                      and writes one weighted down_proj row per record, in
- *                      arrival order, to out_rows [count][hidden] (FP32 or bf16).
+ *                      arrival order, to out_rows [count][hidden] (FP32, bf16
+ *                      or binary16).
  *   nmoe_ep_shared     shared expert over the tokens of the last dispatch (any
  *                      stream; independent of the exchange).
  *   -- return the rows (all-to-all-v with the splits swapped) --

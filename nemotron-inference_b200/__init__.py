@@ -23,6 +23,7 @@ LIBRARY_PATH = os.path.join(_HERE, "libnmoe_b200.so")
 NMOE_OK = 0
 NMOE_F32 = 0
 NMOE_BF16 = 1
+NMOE_F16 = 2   # only for the rows expert-parallel ranks return
 
 STATUS_NAMES = {
     0: "NMOE_OK", 1: "NMOE_ERR_INVALID_ARGUMENT", 2: "NMOE_ERR_CUDA", 3: "NMOE_ERR_UNSUPPORTED",
@@ -180,6 +181,8 @@ def _dtype_code(t: torch.Tensor) -> int:
         return NMOE_F32
     if t.dtype == torch.bfloat16:
         return NMOE_BF16
+    if t.dtype == torch.float16:
+        return NMOE_F16
     raise ValueError(f"unsupported dtype {t.dtype}: expected float32 or bfloat16")
 
 

@@ -15,6 +15,8 @@
 //   [H/2, H/2 + H/16)   E4M3 block scales, row-major
 //   then FP32 tensor scale, FP32 routing weight, int32 expert index LOCAL to
 //   the destination rank, zero padding.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -128,9 +130,17 @@ __global__ void record_histogram_kernel(const uint8_t* __restrict__ records, int
   }
 }
 
-__device__ __forceinline__ float4 load_row4(const void* base, bool bf16, size_t row, int hidden,
+// Four consecutive elements of a row of RowKind `kind`.
+__device__ __forceinline__ float4 load_row4(const void* base, int kind, size_t row, int hidden,
                                             int c) {
-  if (bf16) {
+  if (kind == kRowF16) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(
+        reinterpret_cast<const __half*>(base) + row * hidden + c);
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+  }
+  if (kind == kRowBf16) {
     const uint2 raw = *reinterpret_cast<const uint2*>(
         reinterpret_cast<const __nv_bfloat16*>(base) + row * hidden + c);
     return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
@@ -141,11 +151,11 @@ __device__ __forceinline__ float4 load_row4(const void* base, bool bf16, size_t 
 
 // out[t] = in[t] + ((sum_k routed[position[t][k]]) + shared[t]), routed parts
 // added in selection order (expert_layer.cpp:951-953, :1064-1069).
-template <bool IN_BF16, bool OUT_BF16, bool ROWS_BF16>
+template <bool IN_BF16, bool OUT_BF16>
 __global__ void combine_indexed_kernel(const void* __restrict__ in,
-                                       const void* __restrict__ returned_rows,
+                                       const void* __restrict__ returned_rows, int rows_kind,
                                        const int32_t* __restrict__ position,
-                                       const void* __restrict__ shared_rows, bool shared_bf16,
+                                       const void* __restrict__ shared_rows, int shared_kind,
                                        int rows, int hidden, int top_k, void* __restrict__ out) {
   const int quads = hidden / 4;
   const size_t total = static_cast<size_t>(rows) * quads;
@@ -156,7 +166,7 @@ __global__ void combine_indexed_kernel(const void* __restrict__ in,
     float4 routed = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < top_k; ++k) {
       const size_t row = static_cast<size_t>(position[t * top_k + k]);
-      const float4 p = load_row4(returned_rows, ROWS_BF16, row, hidden, c);
+      const float4 p = load_row4(returned_rows, rows_kind, row, hidden, c);
       if (k == 0) {
         routed = p;
       } else {
@@ -166,8 +176,8 @@ __global__ void combine_indexed_kernel(const void* __restrict__ in,
         routed.w = __fadd_rn(routed.w, p.w);
       }
     }
-    const float4 shared = load_row4(shared_rows, shared_bf16, t, hidden, c);
-    const float4 x = load_row4(in, IN_BF16, t, hidden, c);
+    const float4 shared = load_row4(shared_rows, shared_kind, t, hidden, c);
+    const float4 x = load_row4(in, IN_BF16 ? kRowBf16 : kRowF32, t, hidden, c);
     float r[4];
     r[0] = __fadd_rn(x.x, __fadd_rn(routed.x, shared.x));
     r[1] = __fadd_rn(x.y, __fadd_rn(routed.y, shared.y));
@@ -185,14 +195,6 @@ __global__ void combine_indexed_kernel(const void* __restrict__ in,
           make_float4(r[0], r[1], r[2], r[3]);
     }
   }
-}
-
-template <bool A, bool B, bool C>
-void launch_combine_indexed_t(const void* in, const void* rows_in, const int32_t* position,
-                              const void* shared_rows, bool shared_bf16, int rows, int hidden,
-                              int top_k, void* out, int blocks, cudaStream_t stream) {
-  combine_indexed_kernel<A, B, C><<<blocks, 256, 0, stream>>>(
-      in, rows_in, position, shared_rows, shared_bf16, rows, hidden, top_k, out);
 }
 
 // ---------------------------------------------------------------------------
@@ -284,23 +286,25 @@ cudaError_t launch_record_histogram(const uint8_t* records, int count, int cols,
 }
 
 cudaError_t launch_combine_indexed(const void* in, bool in_bf16, const void* returned_rows,
-                                   bool rows_bf16, const int32_t* position,
-                                   const void* shared_rows, bool shared_bf16, int rows,
+                                   RowKind rows_kind, const int32_t* position,
+                                   const void* shared_rows, RowKind shared_kind, int rows,
                                    int hidden, int top_k, void* out, bool out_bf16,
                                    cudaStream_t stream) {
   if (rows <= 0 || hidden % 4 != 0 || top_k < 1) return cudaErrorInvalidValue;
   const size_t total = static_cast<size_t>(rows) * (hidden / 4);
   const int blocks = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-  const int key = (in_bf16 ? 4 : 0) | (out_bf16 ? 2 : 0) | (rows_bf16 ? 1 : 0);
-  switch (key) {
-    case 0: launch_combine_indexed_t<false, false, false>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
-    case 1: launch_combine_indexed_t<false, false, true>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
-    case 2: launch_combine_indexed_t<false, true, false>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
-    case 3: launch_combine_indexed_t<false, true, true>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
-    case 4: launch_combine_indexed_t<true, false, false>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
-    case 5: launch_combine_indexed_t<true, false, true>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
-    case 6: launch_combine_indexed_t<true, true, false>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
-    default: launch_combine_indexed_t<true, true, true>(in, returned_rows, position, shared_rows, shared_bf16, rows, hidden, top_k, out, blocks, stream); break;
+  if (in_bf16 && out_bf16) {
+    combine_indexed_kernel<true, true><<<blocks, 256, 0, stream>>>(
+        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out);
+  } else if (in_bf16) {
+    combine_indexed_kernel<true, false><<<blocks, 256, 0, stream>>>(
+        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out);
+  } else if (out_bf16) {
+    combine_indexed_kernel<false, true><<<blocks, 256, 0, stream>>>(
+        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out);
+  } else {
+    combine_indexed_kernel<false, false><<<blocks, 256, 0, stream>>>(
+        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out);
   }
   return cudaGetLastError();
 }

@@ -30,6 +30,8 @@
 #include <algorithm>
 #include <cstdlib>
 
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -416,7 +418,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (row_valid) {
           const int d = args.dest_row != nullptr ? args.dest_row[grow]
                                                  : grow * args.dest_mul + args.dest_add;
-          const size_t row_bytes = static_cast<size_t>(args.N) * (args.out_bf16 ? 2 : 4);
+          const size_t row_bytes = static_cast<size_t>(args.N) * (args.out_kind == kRowF32 ? 4 : 2);
           if (d >= 0) {
             if (args.out_segments != nullptr) {
               const int slot = d + args.segment_slot0;
@@ -475,9 +477,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const unsigned long long d = __shfl_sync(0xffffffffu, dest, rr);
             if (d != 0 && col_ok) {
               const float4 value = *reinterpret_cast<const float4*>(stage + rr * kStageStride + c4);
-              if (args.out_bf16) {
+              if (args.out_kind == kRowBf16) {
                 const __nv_bfloat162 lo = __floats2bfloat162_rn(value.x, value.y);
                 const __nv_bfloat162 hi = __floats2bfloat162_rn(value.z, value.w);
+                uint2 bits;
+                bits.x = *reinterpret_cast<const uint32_t*>(&lo);
+                bits.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(d + static_cast<size_t>(n + c4) * 2) = bits;
+              } else if (args.out_kind == kRowF16) {
+                // binary16 saturates at 65504: a row beyond it is reported, not stored as inf
+                const float top = fmaxf(fmaxf(fabsf(value.x), fabsf(value.y)),
+                                        fmaxf(fabsf(value.z), fabsf(value.w)));
+                if (top > 65504.0f && args.error != nullptr) {
+                  atomicCAS(args.error, kDevOk, kDevActivationRange);
+                }
+                const __half2 lo = __floats2half2_rn(value.x, value.y);
+                const __half2 hi = __floats2half2_rn(value.z, value.w);
                 uint2 bits;
                 bits.x = *reinterpret_cast<const uint32_t*>(&lo);
                 bits.y = *reinterpret_cast<const uint32_t*>(&hi);

@@ -20,6 +20,12 @@ struct RowTile {
   int32_t reserved;
 };
 
+// Element type of the per-(token, slot) rows the down projection produces and the
+// combine kernels add up: FP32, or a 16-bit type that halves the layer's largest
+// write and read.  The numbering is nmoe_dtype's.
+enum RowKind : int { kRowF32 = 0, kRowBf16 = 1, kRowF16 = 2 };
+inline size_t row_kind_bytes(RowKind kind) { return kind == kRowF32 ? 4 : 2; }
+
 enum GemmMode : int {
   kGemmUp = 0,    // D -> *scales -> relu^2 -> NVFP4 (packed + tiled scales)
   kGemmDown = 1,  // D -> *scales [* routing weight] -> FP32 rows scattered by dest_row
@@ -48,8 +54,8 @@ struct GemmArgs {
   uint8_t* out_sf = nullptr;      // tiled [row slot][out_k_blocks][2048]
   int32_t out_k_blocks = 0;       // ceil(N / 256)
   // kGemmDown outputs
-  float* out_rows = nullptr;          // [dest][N], FP32 or (out_bf16) bf16
-  int32_t out_bf16 = 0;
+  void* out_rows = nullptr;           // [dest][N] of out_kind elements
+  int32_t out_kind = kRowF32;         // RowKind
   const int32_t* dest_row = nullptr;  // per activation row; nullptr => row*dest_mul+dest_add
   int32_t dest_mul = 1;
   int32_t dest_add = 0;
@@ -223,14 +229,14 @@ cudaError_t launch_record_histogram(const uint8_t* records, int count, int cols,
                                     int local_experts, const int32_t* valid_counts, int capacity,
                                     int32_t* expert_counts, int32_t* error, cudaStream_t stream);
 cudaError_t launch_combine_indexed(const void* in, bool in_bf16, const void* returned_rows,
-                                   bool rows_bf16, const int32_t* position,
-                                   const void* shared_rows, bool shared_bf16, int rows,
+                                   RowKind rows_kind, const int32_t* position,
+                                   const void* shared_rows, RowKind shared_kind, int rows,
                                    int hidden, int top_k, void* out, bool out_bf16,
                                    cudaStream_t stream);
 
 // out[t] = in[t] + ((sum_k parts[t][k]) + parts[t][top_k]) with the routed
-// parts (FP32 or bf16 rows, [rows][top_k + 1][hidden]) added in slot order.
-cudaError_t launch_combine(const void* in, bool in_bf16, const void* parts, bool parts_bf16,
+// parts (rows of `parts_kind`, [rows][top_k + 1][hidden]) added in slot order.
+cudaError_t launch_combine(const void* in, bool in_bf16, const void* parts, RowKind parts_kind,
                            int rows, int hidden, int top_k, void* out, bool out_bf16,
                            cudaStream_t stream);
 

@@ -310,7 +310,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
                       const ActivationOperand& hidden, void* out_rows, const int32_t* dest_row,
                       int dest_mul, int dest_add, const float* row_weight, int32_t* error,
                       int num_sms, cudaStream_t stream, cudaEvent_t between = nullptr,
-                      bool out_bf16 = false, RowSegments segments = RowSegments()) {
+                      RowKind out_kind = kRowF32, RowSegments segments = RowSegments()) {
   GemmArgs g;
   const GemmVariant up_variant = up.variant(tile_class);
   g.K = up.k;
@@ -350,8 +350,8 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   d.row_tiles = schedule.row_tiles;
   d.num_row_tiles = schedule.num_row_tiles;
   d.dense_rows = schedule.dense_rows;
-  d.out_rows = static_cast<float*>(out_rows);
-  d.out_bf16 = out_bf16 ? 1 : 0;
+  d.out_rows = out_rows;
+  d.out_kind = out_kind;
   d.dest_row = dest_row;
   d.dest_mul = dest_mul;
   d.dest_add = dest_add;
@@ -617,7 +617,7 @@ struct nmoe_layer {
   struct PeerWindow {
     bool attached = false;
     int64_t capacity = 0;  // pairs per (source rank, destination rank)
-    bool rows_bf16 = true;
+    RowKind rows_kind = kRowF16;
     DeviceBuffer local;
     size_t records_off = 0, rows_off = 0, flags_off = 0;
     std::vector<void*> peer_base;  // opened mappings, nullptr for this rank
@@ -639,7 +639,7 @@ struct nmoe_layer {
   ActivationOperand y_op, sh_op, a_op, h_op;
   ErrorSlot error;
   int last_tokens = 0;
-  bool last_parts_bf16 = false;
+  RowKind last_parts_kind = kRowF32;
   bool force_fp32_parts = false;  // NMOE_PARTS_FP32=1: FP32 rows whatever the output type
   // how long a kernel waits for a flag another GPU raises before it gives up with
   // kDevWaitTimeout (clock64 ticks; nmoe_layer_set_wait_limit_ms, NMOE_WAIT_LIMIT_MS)
@@ -655,7 +655,7 @@ struct nmoe_layer {
   int fork_max_tokens = 256;
   bool window_fork_shared = false;    // nmoe_ep_window_fork_shared
   bool window_shared_pending = false;
-  bool window_shared_bf16 = false;    // type of shared_out for the pending combine
+  RowKind window_shared_kind = kRowF32;  // type of shared_out for the pending combine
 
   // optional per-stage CUDA events (nmoe_layer_enable_stage_timing)
   bool stage_timing = false;
@@ -857,7 +857,7 @@ void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dt
 // Plan + permute + the two grouped GEMMs over `pairs` (row, slot) pairs whose
 // per-local-expert histogram is already in `counts`.
 void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& source, int pairs,
-                    int dest_stride, void* out_rows, bool out_bf16,
+                    int dest_stride, void* out_rows, RowKind out_kind,
                     RowSegments segments = RowSegments()) {
   const nmoe_config& c = L->cfg;
   const int H = c.hidden_size;
@@ -887,12 +887,12 @@ void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& sou
   run_expert_gemms(L->up, L->down, routed_class, L->a_op, L->a_ts.as<float>(), routed,
                    L->h_packed.as<uint8_t>(), L->h_sf.as<uint8_t>(), L->h_op, out_rows,
                    L->a_dest.as<int32_t>(), 1, 0, L->a_weight.as<float>(), error, L->num_sms,
-                   stream, L->stage_timing ? L->stage_events[6] : nullptr, out_bf16, segments);
+                   stream, L->stage_timing ? L->stage_events[6] : nullptr, out_kind, segments);
 }
 
 // shared expert (:814-818, :956-964, :981-1005) on the token-order quantised rows
 void shared_expert(nmoe_layer* L, cudaStream_t stream, int tokens, void* out_rows, int dest_mul,
-                   int dest_add, cudaEvent_t between, bool out_bf16 = false) {
+                   int dest_add, cudaEvent_t between, RowKind out_kind = kRowF32) {
   const TileClass shared_class =
       tokens <= 32 ? kClassDecode : tokens <= 256 ? kClassDecodeWide : kClassPrefill;
   Schedule shared;
@@ -900,7 +900,7 @@ void shared_expert(nmoe_layer* L, cudaStream_t stream, int tokens, void* out_row
   run_expert_gemms(L->shared_up, L->shared_down, shared_class, L->y_op, L->y_ts.as<float>(),
                    shared, L->sh_packed.as<uint8_t>(), L->sh_sf.as<uint8_t>(), L->sh_op, out_rows,
                    nullptr, dest_mul, dest_add, nullptr, L->error.device.as<int32_t>(),
-                   L->num_sms, stream, between, out_bf16);
+                   L->num_sms, stream, between, out_kind);
 }
 
 PermuteSource local_source(nmoe_layer* L) {
@@ -925,32 +925,33 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
   const nmoe_config& c = L->cfg;
   const int H = c.hidden_size, K = c.top_k;
   // The per-(token, slot) rows of the down projection and the shared expert's row
-  // wait in `parts` for the combine.  They carry the precision of the output: FP32
+  // wait in `parts` for the combine.  They carry the precision the output needs: FP32
   // rows for an FP32 result (the reference's arithmetic, bit for bit in the sums),
-  // bf16 rows for a bf16 result, which halves the largest write and read of the layer.
-  const bool parts_bf16 = out_dtype == NMOE_BF16 && !L->force_fp32_parts;
+  // binary16 rows for a bf16 result: half the bytes of the layer's largest write and
+  // read, and eight times finer than the bf16 the sum is rounded to in the end.
+  const RowKind parts_kind = out_dtype == NMOE_BF16 && !L->force_fp32_parts ? kRowF16 : kRowF32;
   const bool fork = L->side_stream != nullptr && !L->stage_timing && tokens <= L->fork_max_tokens;
   route_tokens(L, stream, input, in_dtype, tokens, fork ? L->quant_done : nullptr);
   if (fork) {
     NMOE_CUDA(cudaStreamWaitEvent(L->side_stream, L->quant_done, 0));
-    shared_expert(L, L->side_stream, tokens, L->parts.as<void>(), K + 1, K, nullptr, parts_bf16);
+    shared_expert(L, L->side_stream, tokens, L->parts.as<void>(), K + 1, K, nullptr, parts_kind);
     NMOE_CUDA(cudaEventRecord(L->shared_done, L->side_stream));
   }
-  routed_experts(L, stream, local_source(L), tokens * K, K + 1, L->parts.as<void>(), parts_bf16);
+  routed_experts(L, stream, local_source(L), tokens * K, K + 1, L->parts.as<void>(), parts_kind);
   L->mark(7, stream);
   if (fork) {
     NMOE_CUDA(cudaStreamWaitEvent(stream, L->shared_done, 0));
   } else {
     shared_expert(L, stream, tokens, L->parts.as<void>(), K + 1, K,
-                  L->stage_timing ? L->stage_events[8] : nullptr, parts_bf16);
+                  L->stage_timing ? L->stage_events[8] : nullptr, parts_kind);
   }
   // routed sum in selection order, mixer and residual (:951-953, :1064-1069)
   L->mark(9, stream);
-  NMOE_CUDA(launch_combine(input, in_dtype == NMOE_BF16, L->parts.as<void>(), parts_bf16, tokens,
+  NMOE_CUDA(launch_combine(input, in_dtype == NMOE_BF16, L->parts.as<void>(), parts_kind, tokens,
                            H, K, output, out_dtype == NMOE_BF16, stream));
   L->mark(10, stream);
   L->last_tokens = tokens;
-  L->last_parts_bf16 = parts_bf16;
+  L->last_parts_kind = parts_kind;
 }
 
 }  // namespace
@@ -984,7 +985,8 @@ nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void* input,
                            nmoe_dtype input_dtype, int64_t tokens, void* output,
                            nmoe_dtype output_dtype) {
   if (layer == nullptr || input == nullptr || output == nullptr || tokens <= 0 ||
-      input == output) {
+      input == output || (input_dtype != NMOE_F32 && input_dtype != NMOE_BF16) ||
+      (output_dtype != NMOE_F32 && output_dtype != NMOE_BF16)) {
     return NMOE_ERR_INVALID_ARGUMENT;
   }
   if (tokens > layer->cfg.max_tokens) return NMOE_ERR_CAPACITY;
@@ -1134,6 +1136,9 @@ nmoe_status nmoe_ep_experts(nmoe_layer* layer, void* stream_ptr, const void* rec
       (count > 0 && (recv_records == nullptr || out_rows == nullptr))) {
     return NMOE_ERR_INVALID_ARGUMENT;
   }
+  if (rows_dtype != NMOE_F32 && rows_dtype != NMOE_BF16 && rows_dtype != NMOE_F16) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
   if (count > layer->max_pairs) return NMOE_ERR_CAPACITY;
   if (count == 0) return NMOE_OK;
   if (valid_counts != nullptr && capacity_per_rank <= 0) return NMOE_ERR_INVALID_ARGUMENT;
@@ -1165,7 +1170,7 @@ nmoe_status nmoe_ep_experts(nmoe_layer* layer, void* stream_ptr, const void* rec
     source.valid_counts = valid_counts;
     source.capacity = static_cast<int>(capacity_per_rank);
     routed_experts(layer, stream, source, static_cast<int>(count), 1, out_rows,
-                   rows_dtype == NMOE_BF16);
+                   static_cast<RowKind>(rows_dtype));
   } catch (const Failure& failure) {
     layer->last_error = failure.message;
     return failure.status;
@@ -1195,8 +1200,8 @@ nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream_ptr, const void* inp
     return NMOE_ERR_INVALID_ARGUMENT;
   }
   const cudaError_t err = launch_combine_indexed(
-      input, input_dtype == NMOE_BF16, returned_rows, rows_dtype == NMOE_BF16,
-      layer->send_position.as<int32_t>(), layer->shared_out.as<void>(), false, layer->last_tokens,
+      input, input_dtype == NMOE_BF16, returned_rows, static_cast<RowKind>(rows_dtype),
+      layer->send_position.as<int32_t>(), layer->shared_out.as<void>(), kRowF32, layer->last_tokens,
       layer->cfg.hidden_size, layer->cfg.top_k, output, output_dtype == NMOE_BF16,
       static_cast<cudaStream_t>(stream_ptr));
   return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
@@ -1210,7 +1215,7 @@ namespace {
 // the part of nmoe_ep_experts after the records are known to be in place
 void experts_over_records(nmoe_layer* layer, cudaStream_t stream, const uint8_t* records,
                           int count, const int32_t* valid_counts, int capacity, void* out_rows,
-                          bool rows_bf16, RowSegments segments) {
+                          RowKind rows_kind, RowSegments segments) {
   const int H = layer->cfg.hidden_size;
   NMOE_CUDA(cudaMemsetAsync(layer->counts.as<int32_t>(), 0,
                             layer->local_experts * sizeof(int32_t), stream));
@@ -1233,7 +1238,7 @@ void experts_over_records(nmoe_layer* layer, cudaStream_t stream, const uint8_t*
   source.pairs_per_row = 1;
   source.valid_counts = valid_counts;
   source.capacity = capacity;
-  routed_experts(layer, stream, source, count, 1, out_rows, rows_bf16, segments);
+  routed_experts(layer, stream, source, count, 1, out_rows, rows_kind, segments);
 }
 
 }  // namespace
@@ -1241,7 +1246,8 @@ void experts_over_records(nmoe_layer* layer, cudaStream_t stream, const uint8_t*
 nmoe_status nmoe_ep_window_create(nmoe_layer* layer, int64_t capacity_per_rank,
                                   nmoe_dtype rows_dtype, void* handle_out) {
   if (layer == nullptr || handle_out == nullptr || layer->ep_world <= 1 ||
-      layer->ep_world > 64 || capacity_per_rank <= 0) {
+      layer->ep_world > 64 || capacity_per_rank <= 0 ||
+      (rows_dtype != NMOE_F32 && rows_dtype != NMOE_BF16 && rows_dtype != NMOE_F16)) {
     return NMOE_ERR_INVALID_ARGUMENT;
   }
   static_assert(sizeof(cudaIpcMemHandle_t) == NMOE_EP_WINDOW_HANDLE_BYTES, "handle size");
@@ -1251,12 +1257,12 @@ nmoe_status nmoe_ep_window_create(nmoe_layer* layer, int64_t capacity_per_rank,
     auto& w = layer->window;
     w.close_peers();
     w.capacity = capacity_per_rank;
-    w.rows_bf16 = rows_dtype == NMOE_BF16;
+    w.rows_kind = static_cast<RowKind>(rows_dtype);
     const size_t H = static_cast<size_t>(layer->cfg.hidden_size);
     auto round_up = [](size_t v) { return (v + 255) / 256 * 256; };
     w.records_off = 0;
     w.rows_off = round_up(static_cast<size_t>(slots) * layer->record_bytes);
-    w.flags_off = w.rows_off + round_up(static_cast<size_t>(slots) * H * (w.rows_bf16 ? 2 : 4));
+    w.flags_off = w.rows_off + round_up(static_cast<size_t>(slots) * H * row_kind_bytes(w.rows_kind));
     w.local.allocate(w.flags_off + 3 * 64 * sizeof(uint32_t), true);
     w.epoch.allocate(sizeof(uint32_t), true);
     NMOE_CUDA(cudaDeviceSynchronize());  // the zeroes are in place before any peer maps it
@@ -1283,7 +1289,7 @@ nmoe_status nmoe_ep_window_attach(nmoe_layer* layer, const void* handles) {
     std::vector<unsigned long long> record_segments(W), row_segments(W), record_flags(W),
         row_flags(W), counts(W);
     const size_t H = static_cast<size_t>(layer->cfg.hidden_size);
-    const size_t row_bytes = H * (w.rows_bf16 ? 2 : 4);
+    const size_t row_bytes = H * row_kind_bytes(w.rows_kind);
     for (int r = 0; r < W; ++r) {
       uint8_t* base = w.local.as<uint8_t>();
       if (r != me) {
@@ -1361,11 +1367,11 @@ nmoe_status nmoe_ep_window_dispatch(nmoe_layer* layer, void* stream_ptr, const v
       // the shared expert's rows take the type of the returned rows, so that the
       // combine adds what the single-device layer adds for the same output type
       shared_expert(layer, layer->side_stream, static_cast<int>(tokens),
-                    layer->shared_out.as<void>(), 1, 0, nullptr, w.rows_bf16);
+                    layer->shared_out.as<void>(), 1, 0, nullptr, w.rows_kind);
       NMOE_CUDA(cudaEventRecord(layer->shared_done, layer->side_stream));
     }
     layer->window_shared_pending = fork;
-    layer->window_shared_bf16 = fork && w.rows_bf16;
+    layer->window_shared_kind = fork ? w.rows_kind : kRowF32;
     NMOE_CUDA(launch_dispatch_plan(layer->counts.as<int32_t>(), c.n_routed_experts,
                                    layer->local_experts, layer->ep_world,
                                    layer->send_counts.as<int32_t>(),
@@ -1413,7 +1419,7 @@ nmoe_status nmoe_ep_window_experts(nmoe_layer* layer, void* stream_ptr, int32_t 
     const uint8_t* records = w.local.as<uint8_t>() + w.records_off +
                              static_cast<size_t>(first_source_rank) * cap * layer->record_bytes;
     experts_over_records(layer, stream, records, source_ranks * cap,
-                         w.counts() + first_source_rank, cap, nullptr, w.rows_bf16, segments);
+                         w.counts() + first_source_rank, cap, nullptr, w.rows_kind, segments);
     NMOE_CUDA(launch_window_signal(w.row_flag_slots.as<unsigned long long>(), nullptr, nullptr,
                                    w.epoch.as<uint32_t>(), first_source_rank, source_ranks,
                                    stream));
@@ -1442,9 +1448,9 @@ nmoe_status nmoe_ep_window_combine(nmoe_layer* layer, void* stream_ptr, const vo
   }
   if (err == cudaSuccess) {
     err = launch_combine_indexed(input, input_dtype == NMOE_BF16,
-                                 w.local.as<uint8_t>() + w.rows_off, w.rows_bf16,
+                                 w.local.as<uint8_t>() + w.rows_off, w.rows_kind,
                                  layer->send_position.as<int32_t>(), layer->shared_out.as<void>(),
-                                 layer->window_shared_bf16, layer->last_tokens, layer->cfg.hidden_size, layer->cfg.top_k,
+                                 layer->window_shared_kind, layer->last_tokens, layer->cfg.hidden_size, layer->cfg.top_k,
                                  output, output_dtype == NMOE_BF16, stream);
   }
   return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
@@ -1463,7 +1469,7 @@ nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out) {
   out->act_packed = layer->y_packed.as<uint8_t>();
   out->act_scales = layer->y_sf_row_major.as<uint8_t>();
   out->act_tensor_scale = layer->y_ts.as<float>();
-  out->parts = layer->last_parts_bf16 ? nullptr : layer->parts.as<float>();
+  out->parts = layer->last_parts_kind ? nullptr : layer->parts.as<float>();
   return NMOE_OK;
 }
 

@@ -9,6 +9,8 @@
 // per-slot results back in the reference's order.
 #include <algorithm>
 
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -141,13 +143,26 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float (&v)[8]) {
   }
 }
 
-// Eight consecutive elements of row `row` of a [rows][hidden] FP32 or bf16 matrix.
-template <bool BF16>
+__device__ __forceinline__ void unpack_f16x8(const uint4& raw, float (&v)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 pair = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    v[2 * i] = pair.x;
+    v[2 * i + 1] = pair.y;
+  }
+}
+
+// Eight consecutive elements of row `row` of a [rows][hidden] matrix of RowKind KIND.
+template <int KIND>
 __device__ __forceinline__ void load_row8(const void* base, size_t row, int hidden, int c,
                                           float (&v)[8]) {
-  if constexpr (BF16) {
+  if constexpr (KIND == kRowBf16) {
     unpack_bf16x8(*reinterpret_cast<const uint4*>(
                       reinterpret_cast<const __nv_bfloat16*>(base) + row * hidden + c), v);
+  } else if constexpr (KIND == kRowF16) {
+    unpack_f16x8(*reinterpret_cast<const uint4*>(
+                     reinterpret_cast<const __half*>(base) + row * hidden + c), v);
   } else {
     const float* p = reinterpret_cast<const float*>(base) + row * hidden + c;
     const float4 a = *reinterpret_cast<const float4*>(p);
@@ -179,8 +194,8 @@ __device__ __forceinline__ void store_row8(void* base, size_t row, int hidden, i
 // out[t] = in[t] + ((sum_k parts[t][k]) + parts[t][top_k]): the routed parts are
 // added in selection order (expert_layer.cpp:951-953), then the shared expert's
 // row and the residual (:1064-1069).  Eight elements per thread, 16- or 32-byte
-// accesses; the parts are FP32 or bf16 rows.
-template <bool IN_BF16, bool OUT_BF16, bool PARTS_BF16>
+// accesses; the parts are rows of RowKind PARTS.
+template <bool IN_BF16, bool OUT_BF16, int PARTS>
 __global__ void combine_kernel(const void* __restrict__ in, const void* __restrict__ parts,
                                int rows, int hidden, int top_k, void* __restrict__ out) {
   const int octs = hidden / 8;
@@ -191,16 +206,16 @@ __global__ void combine_kernel(const void* __restrict__ in, const void* __restri
     const int c = static_cast<int>(i - t * octs) * 8;
     const size_t first = t * (top_k + 1);
     float routed[8];
-    load_row8<PARTS_BF16>(parts, first, hidden, c, routed);
+    load_row8<PARTS>(parts, first, hidden, c, routed);
     for (int k = 1; k < top_k; ++k) {
       float p[8];
-      load_row8<PARTS_BF16>(parts, first + k, hidden, c, p);
+      load_row8<PARTS>(parts, first + k, hidden, c, p);
 #pragma unroll
       for (int j = 0; j < 8; ++j) routed[j] = __fadd_rn(routed[j], p[j]);
     }
     float shared[8], x[8], r[8];
-    load_row8<PARTS_BF16>(parts, first + top_k, hidden, c, shared);
-    load_row8<IN_BF16>(in, t, hidden, c, x);
+    load_row8<PARTS>(parts, first + top_k, hidden, c, shared);
+    load_row8<IN_BF16 ? kRowBf16 : kRowF32>(in, t, hidden, c, x);
 #pragma unroll
     for (int j = 0; j < 8; ++j) r[j] = __fadd_rn(x[j], __fadd_rn(routed[j], shared[j]));
     store_row8<OUT_BF16>(out, t, hidden, c, r);
@@ -208,12 +223,14 @@ __global__ void combine_kernel(const void* __restrict__ in, const void* __restri
 }
 
 template <bool A, bool B>
-void launch_combine_t(const void* in, const void* parts, bool parts_bf16, int rows, int hidden,
+void launch_combine_t(const void* in, const void* parts, RowKind parts_kind, int rows, int hidden,
                       int top_k, void* out, int blocks, cudaStream_t stream) {
-  if (parts_bf16) {
-    combine_kernel<A, B, true><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+  if (parts_kind == kRowBf16) {
+    combine_kernel<A, B, kRowBf16><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+  } else if (parts_kind == kRowF16) {
+    combine_kernel<A, B, kRowF16><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out);
   } else {
-    combine_kernel<A, B, false><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+    combine_kernel<A, B, kRowF32><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out);
   }
 }
 
@@ -239,20 +256,20 @@ cudaError_t launch_permute(const PlanBuffers& plan, const PermuteSource& src, in
   return cudaGetLastError();
 }
 
-cudaError_t launch_combine(const void* in, bool in_bf16, const void* parts, bool parts_bf16,
+cudaError_t launch_combine(const void* in, bool in_bf16, const void* parts, RowKind parts_kind,
                            int rows, int hidden, int top_k, void* out, bool out_bf16,
                            cudaStream_t stream) {
   if (rows <= 0 || hidden % 8 != 0 || top_k < 1) return cudaErrorInvalidValue;
   const size_t total = static_cast<size_t>(rows) * (hidden / 8);
   const int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 16));
   if (in_bf16 && out_bf16) {
-    launch_combine_t<true, true>(in, parts, parts_bf16, rows, hidden, top_k, out, blocks, stream);
+    launch_combine_t<true, true>(in, parts, parts_kind, rows, hidden, top_k, out, blocks, stream);
   } else if (in_bf16) {
-    launch_combine_t<true, false>(in, parts, parts_bf16, rows, hidden, top_k, out, blocks, stream);
+    launch_combine_t<true, false>(in, parts, parts_kind, rows, hidden, top_k, out, blocks, stream);
   } else if (out_bf16) {
-    launch_combine_t<false, true>(in, parts, parts_bf16, rows, hidden, top_k, out, blocks, stream);
+    launch_combine_t<false, true>(in, parts, parts_kind, rows, hidden, top_k, out, blocks, stream);
   } else {
-    launch_combine_t<false, false>(in, parts, parts_bf16, rows, hidden, top_k, out, blocks, stream);
+    launch_combine_t<false, false>(in, parts, parts_kind, rows, hidden, top_k, out, blocks, stream);
   }
   return cudaGetLastError();
 }

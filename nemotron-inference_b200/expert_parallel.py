@@ -36,7 +36,7 @@ class DeviceStages:
     """The four device stages of one rank, over libnmoe_b200.so."""
 
     def __init__(self, config: ExpertLayerConfig, bindings: ExpertLayerBindings, rank: int,
-                 world: int, rows_dtype: torch.dtype = torch.bfloat16):
+                 world: int, rows_dtype: torch.dtype = torch.float16):
         # config.max_recv_pairs bounds what this rank accepts per step in either layout
         experts_per_rank = config.n_routed_experts // world
         assert len(bindings.routed_experts) == experts_per_rank
@@ -572,15 +572,16 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
             "dispatch": f"NVFP4 records, {stages.record_bytes} B per pair, stored by the packing "
                         f"kernel straight into the destination GPU's window (fixed segments of "
                         f"{capacity} pairs per (source, destination)); flag words signal arrival",
-            "return": "bf16 rows stored by the down-projection epilogue of the grouped GEMM "
-                      "straight into the source GPU's window, tile by tile",
+            "return": "binary16 rows (2 bytes per element, as the bf16 rows of the benchmark "
+                      "definition, eight times finer) stored by the down-projection epilogue "
+                      "of the grouped GEMM straight into the source GPU's window, tile by tile",
         }
         launches = stages.launches_per_window_step(engine.window_groups)
     else:
         exchange = {
             "dispatch": f"NVFP4 records, {stages.record_bytes} B per pair, fixed segments of "
                         f"{capacity} pairs per (source, destination), NCCL all-to-all",
-            "return": "bf16 rows, same segments, NCCL all-to-all in two source-rank groups",
+            "return": "binary16 rows, same segments, NCCL all-to-all in two source-rank groups",
         }
         launches = 13 + 6 * engine.chunks
     value = tokens_total / (ms * 1e-3)

@@ -48,6 +48,8 @@ def _worker(rank, world, port, shape, tokens_per_rank):
         x_all = synthetic.make_tokens(total, hidden, seed=9, device="cuda")
         expected = torch.empty((total, hidden), dtype=torch.float32, device="cuda")
         assert single.run(x_all, expected), single.last_error
+        expected_bf16 = torch.empty((total, hidden), dtype=torch.bfloat16, device="cuda")
+        assert single.run(x_all, expected_bf16), single.last_error
         mine = slice(rank * tokens_per_rank, (rank + 1) * tokens_per_rank)
         x = x_all[mine].contiguous()
         # compact records (host reads the split sizes) and fixed-capacity segments (no host
@@ -55,11 +57,14 @@ def _worker(rank, world, port, shape, tokens_per_rank):
         # ... and the same fixed segments exchanged through peer windows: the packing kernel
         # and the GEMM epilogue store into the other GPU's memory, no collective runs
         fixed = 2 * tokens_per_rank * cfg.top_k // world
-        for rows_dtype, capacity, window in ((torch.float32, 0, False),
-                                             (torch.bfloat16, 0, False),
-                                             (torch.float32, fixed, False),
-                                             (torch.float32, fixed, True),
-                                             (torch.bfloat16, fixed, True)):
+        # binary16 rows with a bf16 result are what the single-device layer keeps for a bf16
+        # result too: that combination must agree bit for bit as well
+        for rows_dtype, capacity, window, out_dtype in (
+                (torch.float32, 0, False, torch.float32), (torch.bfloat16, 0, False, torch.float32),
+                (torch.float32, fixed, False, torch.float32),
+                (torch.float32, fixed, True, torch.float32),
+                (torch.bfloat16, fixed, True, torch.float32),
+                (torch.float16, fixed, True, torch.bfloat16)):
             ep_cfg = synthetic.baseline_config(tokens_per_rank, experts=experts, hidden=hidden,
                                                routed=routed, shared=shared)
             ep_cfg.max_recv_pairs = total * cfg.top_k
@@ -68,13 +73,15 @@ def _worker(rank, world, port, shape, tokens_per_rank):
             engine = ep.ExpertParallelEngine(stages, capacity_per_rank=capacity)
             if window:
                 assert stages.attach_windows(capacity), stages.attach_error
-            out = torch.empty((tokens_per_rank, hidden), dtype=torch.float32, device="cuda")
+            out = torch.empty((tokens_per_rank, hidden), dtype=out_dtype, device="cuda")
+            exact = rows_dtype == torch.float32 or out_dtype == torch.bfloat16
+            want = (expected_bf16 if out_dtype == torch.bfloat16 else expected)[mine]
             for _ in range(2):
                 engine.step(x, out)
             torch.cuda.synchronize()
             if capacity > 0:
-                if rows_dtype == torch.float32:
-                    assert torch.equal(out, expected[mine])
+                if exact:
+                    assert torch.equal(out, want)
                 graphed = engine.capture(x, out)
                 flag = torch.tensor([1 if graphed else 0], device="cuda")
                 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
@@ -85,10 +92,10 @@ def _worker(rank, world, port, shape, tokens_per_rank):
                 elif rank == 0:
                     print("graph capture unavailable:", getattr(engine, "capture_error", ""))
             assert stages.sync_status() == 0
-            if rows_dtype == torch.float32:
-                assert torch.equal(out, expected[mine]), (out - expected[mine]).abs().max().item()
+            if exact:
+                assert torch.equal(out, want), (out.float() - want.float()).abs().max().item()
             else:
-                assert (out - expected[mine]).abs().max().item() <= 2e-2
+                assert (out - want).abs().max().item() <= 2e-2
             engine.release_graph()
             if window:
                 stages.detach_windows()
