@@ -44,10 +44,10 @@ typedef enum nmoe_status {
  * (rows_dtype of the nmoe_ep_* entry points); activations are FP32 or bf16. */
 typedef enum nmoe_dtype { NMOE_F32 = 0, NMOE_BF16 = 1, NMOE_F16 = 2 } nmoe_dtype;
 
-/* Mirrors nemotron::ExpertLayerConfig (expert_layer.h:18-31).  The latent
- * projections fc1_latent/fc2_latent of the reference layer
- * (expert_layer.cpp:809-813, :1047-1048) are the identity here, so
- * moe_latent_size must equal hidden_size. */
+/* Mirrors nemotron::ExpertLayerConfig (expert_layer.h:18-31).  The routed
+ * experts act on rows of moe_latent_size elements: the output of fc1_latent
+ * (expert_layer.cpp:809-813), projected back by fc2_latent (:1047-1053).  With
+ * moe_latent_size == hidden_size both projections may be absent (identity). */
 typedef struct nmoe_config {
   int32_t layer_index;
   int32_t hidden_size;
@@ -95,10 +95,32 @@ typedef struct nmoe_dense_tensor {
   size_t cols;
 } nmoe_dense_tensor;
 
-/* Mirrors nemotron::ExpertLayerBindings (expert_layer.h:38-56) for the
- * all-NVFP4 expert weights.  routed_up/routed_down hold n_local_experts
- * entries: the experts [first_local_expert, first_local_expert +
- * n_local_experts) of the layer. */
+/* A linear of the dense or the scaled-FP8 family, the two families the
+ * reference accepts for fc1_latent, shared_up and (when it is not NVFP4)
+ * shared_down (expert_layer.cpp:534-617), and the dense family of fc2_latent.
+ *   DENSE       weight FP32 or bf16 [out][in]; y = x W^T with DOUBLE accumulation
+ *               (UploadedLinearOp, linear_op.cpp:97-118, :238-271).
+ *   SCALED_FP8  weight E4M3 bytes [out][in] (weight.dtype is ignored, nbytes =
+ *               out * in), dequantised as DecodeFp8(byte) * weight_scale; the
+ *               activations take a round trip through E4M3 at input_scale first
+ *               (ScaledFp8LinearOp, scaled_fp8_linear.cu:121-139, :222-283). */
+typedef enum nmoe_linear_family {
+  NMOE_LINEAR_ABSENT = 0,
+  NMOE_LINEAR_DENSE = 1,
+  NMOE_LINEAR_SCALED_FP8 = 2
+} nmoe_linear_family;
+
+typedef struct nmoe_linear {
+  nmoe_linear_family family;
+  nmoe_dense_tensor weight;
+  float weight_scale; /* SCALED_FP8 only */
+  float input_scale;  /* SCALED_FP8 only */
+} nmoe_linear;
+
+/* Mirrors nemotron::ExpertLayerBindings (expert_layer.h:38-56).
+ * routed_up/routed_down hold n_local_experts entries: the experts
+ * [first_local_expert, first_local_expert + n_local_experts) of the layer,
+ * up_proj [intermediate][latent], down_proj [latent][intermediate]. */
 typedef struct nmoe_weights {
   nmoe_dense_tensor input_norm_weight;
   nmoe_dense_tensor gate_weight;
@@ -112,6 +134,17 @@ typedef struct nmoe_weights {
   /* Optional FP32 [experts] added to the gate logits (NULL = none).  Not in the
    * reference: a hook for synthetic workloads with skewed expert load. */
   const float* gate_logit_offset;
+  /* Latent projections (fc1_latent_*, fc2_latent_weight of the reference's
+   * bindings): fc1 [latent][hidden], fc2 [hidden][latent] (dense only).  Both
+   * ABSENT means identity and requires moe_latent_size == hidden_size. */
+  nmoe_linear fc1_latent;
+  nmoe_linear fc2_latent;
+  /* Shared expert in the dense / scaled-FP8 families the real checkpoint uses
+   * (shared_up_kernel_weight + scales, or a dense shared_up_gemm_weight): when
+   * not ABSENT they replace the NVFP4 shared_up / shared_down above, whose
+   * pointers may then be NULL. */
+  nmoe_linear shared_up_linear;   /* [shared_intermediate][hidden] */
+  nmoe_linear shared_down_linear; /* [hidden][shared_intermediate] */
 } nmoe_weights;
 
 typedef struct nmoe_layer nmoe_layer;
@@ -137,6 +170,37 @@ NMOE_API void nmoe_layer_destroy(nmoe_layer* layer);
 NMOE_API nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void* input,
                                     nmoe_dtype input_dtype, int64_t tokens, void* output,
                                     nmoe_dtype output_dtype);
+
+/* Grows the layer's scratch to `max_tokens` rows per call (no effect when it is
+ * already that large).  Frees and reallocates device memory and synchronises the
+ * device: call it between runs.  The reference allocates its scratch per call
+ * (expert_layer.cpp:782-787) and therefore accepts any token count; a caller
+ * that wants that behaviour calls this when nmoe_layer_run answers
+ * NMOE_ERR_CAPACITY. */
+NMOE_API nmoe_status nmoe_layer_reserve_tokens(nmoe_layer* layer, int32_t max_tokens);
+
+/* The unfused activation path.  By default the up projection's epilogue applies
+ * relu^2 and quantises the row to NVFP4 on the fly, which is the reference's
+ * arithmetic only while the row's tensor scale is 1, i.e. while no activated
+ * value exceeds 6*448 (nvfp4_packing.cpp:119-126); a run that meets a larger
+ * value reports NMOE_ERR_ACTIVATION_RANGE.  With enable != 0 the layer keeps
+ * the activated rows in FP32 and quantises them in a pass of its own with the
+ * per-row tensor scale, as RunNvfp4LinearHost does (expert_layer.cpp:913-922):
+ * any range is handled, at about twice the cost of the expert GEMMs.  It also
+ * retains what ExpertLayerRunTrace needs beyond the fused path's buffers: the
+ * FP32 activated rows and the unweighted down_proj rows
+ * (nmoe_layer_export_unfused).  Allocates on the first enable and synchronises
+ * the device: call it between runs. */
+NMOE_API nmoe_status nmoe_layer_set_unfused_activation(nmoe_layer* layer, int32_t enable);
+/* After a run with the unfused path, in (token, slot) order, any pointer may be
+ * NULL: routed_activated [tokens][top_k][intermediate] FP32 = relu^2(up_proj),
+ * routed_outputs [tokens][top_k][latent] FP32 = down_proj rows before the
+ * routing weight, shared_activated [tokens][shared_intermediate] FP32
+ * (routed_expert_activated_hidden / routed_expert_outputs of
+ * expert_layer.h:63-76). */
+NMOE_API nmoe_status nmoe_layer_export_unfused(nmoe_layer* layer, void* stream,
+                                               float* routed_activated, float* routed_outputs,
+                                               float* shared_activated);
 
 /* Waits for `stream` and reports what the kernels left in the layer's device
  * error slot (and clears it): the boolean the reference's synchronous Run
@@ -196,12 +260,20 @@ typedef struct nmoe_trace_view {
                                       contributions in selection order, then shared.
                                       FP32 when the last run's output was FP32; a run
                                       with bf16 output keeps these rows in binary16
-                                      and leaves this field NULL */
+                                      and leaves this field NULL.  With latent
+                                      projections: [tokens][top_k][latent], routed
+                                      rows only */
+  const float* latent_output;      /* [tokens][latent]: fc1_latent(normalized); NULL when
+                                      the projection is the identity */
+  const float* routed_latent_output; /* [tokens][latent]: the routed sum fed to fc2_latent */
+  const float* projected_routed_output; /* [tokens][hidden]: fc2_latent of it */
+  const float* shared_output;      /* [tokens][hidden] FP32; NULL without latent projections
+                                      (the shared row is parts[t][top_k] there) */
 } nmoe_trace_view;
 NMOE_API nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out);
 /* Copies one nmoe_trace_view field (index in declaration order, 0 =
  * normalized_input) of the last run into `dst` (device or host), `nbytes`
- * bytes, in stream order. */
+ * bytes, in stream order; NMOE_ERR_INVALID_ARGUMENT for a field that is NULL. */
 NMOE_API nmoe_status nmoe_layer_copy_trace_field(nmoe_layer* layer, void* stream, int32_t field,
                                                  void* dst, size_t nbytes);
 

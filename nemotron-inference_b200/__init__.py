@@ -43,7 +43,8 @@ EXPORTED_SYMBOLS = (
     "nmoe_ep_combine", "nmoe_layer_reserve_sms", "nmoe_ep_window_create",
     "nmoe_ep_window_attach", "nmoe_ep_window_detach", "nmoe_ep_window_dispatch",
     "nmoe_ep_window_experts", "nmoe_ep_window_combine", "nmoe_ep_window_fork_shared",
-    "nmoe_layer_set_wait_limit_ms", "nmoe_layer_wait_flag",
+    "nmoe_layer_set_wait_limit_ms", "nmoe_layer_wait_flag", "nmoe_layer_reserve_tokens",
+    "nmoe_layer_set_unfused_activation", "nmoe_layer_export_unfused",
 )
 
 
@@ -78,6 +79,11 @@ class _DenseTensor(ctypes.Structure):
                 ("dtype", ctypes.c_int), ("rows", ctypes.c_size_t), ("cols", ctypes.c_size_t)]
 
 
+class _Linear(ctypes.Structure):
+    _fields_ = [("family", ctypes.c_int), ("weight", _DenseTensor),
+                ("weight_scale", ctypes.c_float), ("input_scale", ctypes.c_float)]
+
+
 class _Weights(ctypes.Structure):
     _fields_ = [("input_norm_weight", _DenseTensor), ("gate_weight", _DenseTensor),
                 ("gate_score_correction_bias", _DenseTensor),
@@ -85,13 +91,16 @@ class _Weights(ctypes.Structure):
                 ("routed_down", ctypes.POINTER(_Nvfp4Matrix)),
                 ("n_local_experts", ctypes.c_int32), ("first_local_expert", ctypes.c_int32),
                 ("shared_up", _Nvfp4Matrix), ("shared_down", _Nvfp4Matrix),
-                ("gate_logit_offset", ctypes.c_void_p)]
+                ("gate_logit_offset", ctypes.c_void_p),
+                ("fc1_latent", _Linear), ("fc2_latent", _Linear),
+                ("shared_up_linear", _Linear), ("shared_down_linear", _Linear)]
 
 
 class _TraceView(ctypes.Structure):
     _fields_ = [(name, ctypes.c_void_p) for name in (
         "normalized_input", "router_logits", "selected_index", "selected_weight", "act_packed",
-        "act_scales", "act_tensor_scale", "parts")]
+        "act_scales", "act_tensor_scale", "parts", "latent_output", "routed_latent_output",
+        "projected_routed_output", "shared_output")]
 
 
 _lib = None
@@ -122,6 +131,9 @@ def load_library() -> ctypes.CDLL:
     lib.nmoe_layer_export_hidden.argtypes = [vp, vp, vp, vp, vp, vp]
     lib.nmoe_layer_enable_stage_timing.argtypes = [vp, i32]
     lib.nmoe_layer_reserve_sms.argtypes = [vp, i32]
+    lib.nmoe_layer_reserve_tokens.argtypes = [vp, i32]
+    lib.nmoe_layer_set_unfused_activation.argtypes = [vp, i32]
+    lib.nmoe_layer_export_unfused.argtypes = [vp, vp, vp, vp, vp]
     lib.nmoe_layer_set_wait_limit_ms.argtypes = [vp, ctypes.c_double]
     lib.nmoe_layer_wait_flag.argtypes = [vp, vp, vp, ctypes.c_uint32]
     lib.nmoe_layer_stage_times.argtypes = [vp, ctypes.POINTER(ctypes.c_float), i32]
@@ -237,6 +249,35 @@ class Nvfp4Matrix:
 
 
 @dataclass
+class DenseLinear:
+    """A linear of the dense family (`weight` FP32 / bf16 [out, in], DOUBLE accumulation:
+    UploadedLinearOp, linear_op.cpp:97-118) or of the scaled-FP8 family (`weight` uint8
+    E4M3 codes [out, in] with per-tensor `weight_scale` and `input_scale`:
+    ScaledFp8LinearOp, scaled_fp8_linear.cu:121-139, :222-283)."""
+    weight: torch.Tensor
+    weight_scale: Optional[float] = None
+    input_scale: Optional[float] = None
+
+    @property
+    def is_fp8(self) -> bool:
+        return self.weight.dtype == torch.uint8
+
+    def _as_c(self, keep: list) -> _Linear:
+        w = self.weight.contiguous()
+        keep.append(w)
+        out = _Linear()
+        if self.is_fp8:
+            out.family = 2
+            out.weight = _DenseTensor(w.data_ptr(), w.numel(), NMOE_F32, w.shape[0], w.shape[1])
+            out.weight_scale = float(self.weight_scale)
+            out.input_scale = float(self.input_scale)
+        else:
+            out.family = 1
+            out.weight = _dense(w, keep)
+        return out
+
+
+@dataclass
 class ExpertWeightPair:
     up_proj: Nvfp4Matrix
     down_proj: Nvfp4Matrix
@@ -244,16 +285,22 @@ class ExpertWeightPair:
 
 @dataclass
 class ExpertLayerBindings:
-    """`nemotron::ExpertLayerBindings` (expert_layer.h:38-56) for all-NVFP4 expert
-    weights and identity latent projections."""
+    """`nemotron::ExpertLayerBindings` (expert_layer.h:38-56).  The latent projections
+    may be absent (identity, moe_latent_size == hidden_size); the shared expert's
+    projections are NVFP4 (`shared_up` / `shared_down`) unless a dense / scaled-FP8
+    `shared_up_linear` / `shared_down_linear` replaces them."""
     input_norm_weight: torch.Tensor            # [hidden] fp32 / bf16
     gate_weight: torch.Tensor                  # [experts, hidden] fp32 / bf16
     gate_score_correction_bias: torch.Tensor   # [experts]
-    shared_up: Nvfp4Matrix
-    shared_down: Nvfp4Matrix
+    shared_up: Optional[Nvfp4Matrix]
+    shared_down: Optional[Nvfp4Matrix]
     routed_experts: List[ExpertWeightPair] = field(default_factory=list)
     gate_logit_offset: Optional[torch.Tensor] = None  # [experts] fp32, synthetic-skew hook
     first_local_expert: int = 0  # expert parallelism: global index of routed_experts[0]
+    fc1_latent: Optional["DenseLinear"] = None   # [latent, hidden]
+    fc2_latent: Optional["DenseLinear"] = None   # [hidden, latent], dense
+    shared_up_linear: Optional["DenseLinear"] = None
+    shared_down_linear: Optional["DenseLinear"] = None
 
 
 def _dense(t: torch.Tensor, keep: list) -> _DenseTensor:
@@ -275,6 +322,10 @@ class ExpertLayerTrace:
     act_scales: torch.Tensor
     act_tensor_scale: torch.Tensor
     parts: Optional[torch.Tensor]  # FP32 [tokens, top_k + 1, hidden]; None after a bf16-output run
+    latent_output: Optional[torch.Tensor]            # [tokens, latent]; None without fc1_latent
+    routed_latent_output: Optional[torch.Tensor]     # [tokens, latent]
+    projected_routed_output: Optional[torch.Tensor]  # [tokens, hidden]
+    shared_output: Optional[torch.Tensor]            # [tokens, hidden]
     routed_hidden_packed: torch.Tensor
     routed_hidden_scales: torch.Tensor
     shared_hidden_packed: torch.Tensor
@@ -289,6 +340,7 @@ class ExpertLayerSlice:
     def __init__(self, handle: int, config: ExpertLayerConfig):
         self._handle = ctypes.c_void_p(handle)
         self._config = config
+        self._has_latent = False
         self.last_error = ""
 
     @staticmethod
@@ -318,8 +370,14 @@ class ExpertLayerSlice:
         w.routed_down = downs
         w.n_local_experts = n
         w.first_local_expert = bindings.first_local_expert
-        w.shared_up = bindings.shared_up._as_c(keep)
-        w.shared_down = bindings.shared_down._as_c(keep)
+        if bindings.shared_up is not None:
+            w.shared_up = bindings.shared_up._as_c(keep)
+        if bindings.shared_down is not None:
+            w.shared_down = bindings.shared_down._as_c(keep)
+        for name in ("fc1_latent", "fc2_latent", "shared_up_linear", "shared_down_linear"):
+            linear = getattr(bindings, name)
+            if linear is not None:
+                setattr(w, name, linear._as_c(keep))
         w.gate_logit_offset = None
         if bindings.gate_logit_offset is not None:
             offset = bindings.gate_logit_offset.to(torch.float32).contiguous()
@@ -330,7 +388,9 @@ class ExpertLayerSlice:
         if status != NMOE_OK or not handle.value:
             ExpertLayerSlice.create_error = STATUS_NAMES.get(status, str(status))
             return None
-        return ExpertLayerSlice(handle.value, config)
+        layer = ExpertLayerSlice(handle.value, config)
+        layer._has_latent = bindings.fc1_latent is not None
+        return layer
 
     create_error = ""
 
@@ -380,6 +440,35 @@ class ExpertLayerSlice:
         _check(load_library().nmoe_layer_reserve_sms(self._handle, int(reserved)),
                "nmoe_layer_reserve_sms")
 
+    def reserve_tokens(self, max_tokens: int) -> None:
+        """Grows the scratch to `max_tokens` rows per run (synchronises the device)."""
+        _check(load_library().nmoe_layer_reserve_tokens(self._handle, int(max_tokens)),
+               "nmoe_layer_reserve_tokens", self._last_error())
+        self._config.max_tokens = max(self._config.max_tokens, int(max_tokens))
+
+    def set_unfused_activation(self, enable: bool = True) -> None:
+        """Two-pass activation path: the activated rows stay FP32 and are quantised with
+        their own tensor scale, as the reference's host linear does; handles activated
+        values beyond 6*448 and keeps what `unfused_trace` returns."""
+        _check(load_library().nmoe_layer_set_unfused_activation(self._handle, 1 if enable else 0),
+               "nmoe_layer_set_unfused_activation", self._last_error())
+
+    def unfused_trace(self, tokens: int):
+        """(routed_activated [tokens, top_k, I], routed_outputs [tokens, top_k, latent],
+        shared_activated [tokens, S]) of the last run, which must have used the unfused path."""
+        cfg = self._config
+        dev = torch.device("cuda", torch.cuda.current_device())
+        ra = torch.empty((tokens, cfg.top_k, cfg.routed_expert_intermediate_size),
+                         dtype=torch.float32, device=dev)
+        ro = torch.empty((tokens, cfg.top_k, cfg.moe_latent_size), dtype=torch.float32, device=dev)
+        sa = torch.empty((tokens, cfg.shared_expert_intermediate_size), dtype=torch.float32,
+                         device=dev)
+        _check(load_library().nmoe_layer_export_unfused(self._handle, _stream(), ra.data_ptr(),
+                                                        ro.data_ptr(), sa.data_ptr()),
+               "nmoe_layer_export_unfused", self._last_error())
+        torch.cuda.current_stream().synchronize()
+        return ra, ro, sa
+
     def set_wait_limit_ms(self, milliseconds: float) -> None:
         """How long a kernel of this layer waits for a flag another GPU raises before it
         gives up with NMOE_ERR_DEVICE_TIMEOUT."""
@@ -415,7 +504,10 @@ class ExpertLayerSlice:
         I, S = cfg.routed_expert_intermediate_size, cfg.shared_expert_intermediate_size
 
         fields = ("normalized_input", "router_logits", "selected_index", "selected_weight",
-                  "act_packed", "act_scales", "act_tensor_scale", "parts")
+                  "act_packed", "act_scales", "act_tensor_scale", "parts", "latent_output",
+                  "routed_latent_output", "projected_routed_output", "shared_output")
+        L = cfg.moe_latent_size
+        latent = L != H or self._has_latent
 
         def grab(name, shape, dtype, optional=False):
             out = torch.empty(shape, dtype=dtype, device=dev)
@@ -439,10 +531,17 @@ class ExpertLayerSlice:
             router_logits=grab("router_logits", (tokens, E), torch.float32),
             selected_index=grab("selected_index", (tokens, K), torch.int32),
             selected_weight=grab("selected_weight", (tokens, K), torch.float32),
-            act_packed=grab("act_packed", (tokens, H // 2), torch.uint8),
-            act_scales=grab("act_scales", (tokens, H // 16), torch.uint8),
+            act_packed=grab("act_packed", (tokens, L // 2), torch.uint8),
+            act_scales=grab("act_scales", (tokens, L // 16), torch.uint8),
             act_tensor_scale=grab("act_tensor_scale", (tokens,), torch.float32),
-            parts=grab("parts", (tokens, K + 1, H), torch.float32, optional=True),
+            parts=grab("parts", (tokens, K, L) if latent else (tokens, K + 1, H), torch.float32,
+                       optional=True),
+            latent_output=grab("latent_output", (tokens, L), torch.float32, optional=True),
+            routed_latent_output=grab("routed_latent_output", (tokens, L), torch.float32,
+                                      optional=True),
+            projected_routed_output=grab("projected_routed_output", (tokens, H), torch.float32,
+                                         optional=True),
+            shared_output=grab("shared_output", (tokens, H), torch.float32, optional=True),
             routed_hidden_packed=rp, routed_hidden_scales=rs,
             shared_hidden_packed=sp, shared_hidden_scales=ss)
         torch.cuda.current_stream().synchronize()

@@ -7,7 +7,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnmoe_b200.so")
 SOURCES = ["gemm.cu", "quant.cu", "router.cu", "router_fast.cu", "plan.cu", "ep.cu", "layer.cu",
-           "route_noalloc.cu"]
+           "route_noalloc.cu", "dense.cu"]
 HEADERS = ["common.cuh", "kernels.h", os.path.join("..", "..", "include", "nmoe.h")]
 NVCC = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -63,6 +63,10 @@ __device__ __forceinline__ float clamp_scale(float v) {
   return (!isfinite(v) || v < kMinScale) ? kMinScale : v;
 }
 
+inline float clamp_scale_host(float v) {
+  return (!(v == v) || v > 3.0e38f || v < kMinScale) ? kMinScale : v;
+}
+
 // Quantise 16 FP32 values that share one block (per-row tensor scale `ts`):
 // returns the E4M3 scale byte, writes 8 packed bytes into two 32-bit words.
 // Follows nvfp4_packing.cpp:130-153 with IEEE divisions.

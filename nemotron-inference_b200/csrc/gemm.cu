@@ -458,6 +458,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               va[i] = __fmul_rn(va[i], wt);
               vb[i] = __fmul_rn(vb[i], wt);
             }
+            if (args.relu2) {  // Relu2 (expert_layer.cpp:138-140): x > 0 ? x * x : 0
+              const float pa = fmaxf(va[i], 0.0f), pb = fmaxf(vb[i], 0.0f);
+              va[i] = __fmul_rn(pa, pa);
+              vb[i] = __fmul_rn(pb, pb);
+            }
           }
           __syncwarp();
 #pragma unroll

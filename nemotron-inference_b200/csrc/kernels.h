@@ -60,6 +60,8 @@ struct GemmArgs {
   int32_t dest_mul = 1;
   int32_t dest_add = 0;
   const float* row_weight = nullptr;  // per activation row routing weight, nullptr => none
+  int32_t relu2 = 0;                  // kGemmDown: store relu^2 of the scaled value (the
+                                      // unfused up projection keeps its rows in FP32)
   // Expert-parallel return straight into the source ranks' memory: destination
   // index d means row (d + segment_slot0) % segment_rows of the buffer that
   // out_segments[(d + segment_slot0) / segment_rows] points to (a peer's GPU).
@@ -160,6 +162,26 @@ cudaError_t launch_router_select_exact(float* logits, const float* normalized,
                                        int top_k, bool norm_topk_prob, float routed_scaling,
                                        float tie_margin, int32_t* top_index, float* top_weight,
                                        int32_t* expert_counts, cudaStream_t stream);
+
+// --- dense and scaled-FP8 linear families, latent-MoE data flow (csrc/dense.cu) -
+// The dense matmul itself is launch_router_logits: out[rows][experts] =
+// a[rows][hidden] x w[experts][hidden]^T, FP64 accumulation, FP32 result.
+// Activation round trip through E4M3 with a per-tensor input scale.
+cudaError_t launch_fp8_round_trip(const float* in, size_t count, float input_scale, float* out,
+                                  cudaStream_t stream);
+// E4M3 weight bytes -> FP32 values times the per-tensor weight scale.
+cudaError_t launch_fp8_weight_dequant(const uint8_t* bytes, size_t count, float weight_scale,
+                                      float* out, cudaStream_t stream);
+cudaError_t launch_relu2(float* values, size_t count, cudaStream_t stream);
+// out[t] = sum_k parts[t][k] in slot order; parts FP32 [rows][top_k][cols].
+cudaError_t launch_sum_parts(const float* parts, int rows, int cols, int top_k, float* out,
+                             cudaStream_t stream);
+// out = in + (projected + shared), all [rows][hidden].
+cudaError_t launch_mixer(const void* in, bool in_bf16, const float* projected, const float* shared,
+                         int rows, int hidden, void* out, bool out_bf16, cudaStream_t stream);
+// out[i] = rows[row_of[i]] (row_of == nullptr: identity), FP32 rows of `cols`.
+cudaError_t launch_gather_rows(const float* rows, const int32_t* row_of, int count, int cols,
+                               float* out, cudaStream_t stream);
 
 // --- plan / permute / combine -------------------------------------------------
 struct PlanBuffers {

@@ -303,6 +303,44 @@ struct RowSegments {
   int slot0 = 0;
 };
 
+// One GEMM with the row-storing epilogue: rows = A x W^T times the tensor scales
+// [x routing weight] [-> relu^2], scattered by dest_row.
+void run_down_gemm(const WeightStack& weights, TileClass tile_class, const ActivationOperand& a,
+                   const float* a_tensor_scale, const Schedule& schedule, void* out_rows,
+                   const int32_t* dest_row, int dest_mul, int dest_add, const float* row_weight,
+                   bool relu2, int32_t* error, int num_sms, cudaStream_t stream, RowKind out_kind,
+                   RowSegments segments) {
+  GemmArgs d;
+  const GemmVariant variant = weights.variant(tile_class);
+  const int bn = gemm_variant_info(variant).bn;
+  d.K = weights.k;
+  d.N = weights.n;
+  d.n_tiles = (weights.n + bn - 1) / bn;
+  d.k_blocks = k_blocks_of(weights.k);
+  d.kb_full = weights.kb_full;
+  d.b_full = weights.packed.as<uint8_t>();
+  d.sfa = a.sf_tiled;
+  d.sfb = weights.sf(tile_class);
+  d.a_tensor_scale = a_tensor_scale;
+  d.w_tensor_scale = weights.tensor_scale.as<float>();
+  d.row_tiles = schedule.row_tiles;
+  d.num_row_tiles = schedule.num_row_tiles;
+  d.dense_rows = schedule.dense_rows;
+  d.out_rows = out_rows;
+  d.out_kind = out_kind;
+  d.dest_row = dest_row;
+  d.dest_mul = dest_mul;
+  d.dest_add = dest_add;
+  d.row_weight = row_weight;
+  d.relu2 = relu2 ? 1 : 0;
+  d.out_segments = segments.bases;
+  d.segment_rows = segments.rows;
+  d.segment_slot0 = segments.slot0;
+  d.error = error;
+  NMOE_CUDA(launch_grouped_gemm(variant, kGemmDown, a.map(tile_class),
+                                weights.tail_map(tile_class), d, num_sms, stream));
+}
+
 // up GEMM (relu^2 + quantise) followed by down GEMM (scale, weight, scatter).
 void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass tile_class,
                       const ActivationOperand& a, const float* a_tensor_scale,
@@ -335,34 +373,9 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
 
   if (between != nullptr) cudaEventRecord(between, stream);
 
-  GemmArgs d;
-  const GemmVariant down_variant = down.variant(tile_class);
-  d.K = down.k;
-  d.N = down.n;
-  d.n_tiles = (down.n + gemm_variant_info(down_variant).bn - 1) / gemm_variant_info(down_variant).bn;
-  d.k_blocks = k_blocks_of(down.k);
-  d.kb_full = down.kb_full;
-  d.b_full = down.packed.as<uint8_t>();
-  d.sfa = hidden.sf_tiled;
-  d.sfb = down.sf(tile_class);
-  d.a_tensor_scale = nullptr;  // the fused quantiser always uses tensor scale 1
-  d.w_tensor_scale = down.tensor_scale.as<float>();
-  d.row_tiles = schedule.row_tiles;
-  d.num_row_tiles = schedule.num_row_tiles;
-  d.dense_rows = schedule.dense_rows;
-  d.out_rows = out_rows;
-  d.out_kind = out_kind;
-  d.dest_row = dest_row;
-  d.dest_mul = dest_mul;
-  d.dest_add = dest_add;
-  d.row_weight = row_weight;
-  d.out_segments = segments.bases;
-  d.segment_rows = segments.rows;
-  d.segment_slot0 = segments.slot0;
-  d.error = error;
-  NMOE_CUDA(launch_grouped_gemm(down_variant, kGemmDown, hidden.map(tile_class),
-                                down.tail_map(tile_class), d, num_sms,
-                                stream));
+  // the fused quantiser always uses tensor scale 1
+  run_down_gemm(down, tile_class, hidden, nullptr, schedule, out_rows, dest_row, dest_mul,
+                dest_add, row_weight, false, error, num_sms, stream, out_kind, segments);
 }
 
 nmoe_status status_from_device(int code) {
@@ -446,6 +459,50 @@ void upload_dense_fp32(const nmoe_dense_tensor& t, size_t count, const char* nam
     NMOE_CUDA(cudaStreamSynchronize(stream));
   }
 }
+
+// A dense or scaled-FP8 linear resident in HBM as FP32 [out][in], the form the
+// reference's UploadedLinearOp / ScaledFp8LinearOp multiply with
+// (linear_op.cpp:274-303, scaled_fp8_linear.cu:121-139).
+struct DenseLinear {
+  bool present = false;
+  bool fp8 = false;
+  int out = 0, in = 0;
+  float input_scale = 1.0f;
+  DeviceBuffer weight;
+
+  void upload(const nmoe_linear& linear, size_t out_rows, size_t in_cols, const char* name,
+              cudaStream_t stream) {
+    const std::string n(name);
+    out = static_cast<int>(out_rows);
+    in = static_cast<int>(in_cols);
+    const size_t count = out_rows * in_cols;
+    if (linear.family == NMOE_LINEAR_DENSE) {
+      nmoe_dense_tensor t = linear.weight;
+      NMOE_REQUIRE(t.rows == out_rows && t.cols == in_cols, n + ": shape mismatch");
+      upload_dense_fp32(t, count, name, &weight, stream);
+    } else if (linear.family == NMOE_LINEAR_SCALED_FP8) {
+      // DequantizeScaledFp8WeightToHostFp32 (scaled_fp8_linear.cu:121-139)
+      NMOE_REQUIRE(linear.weight.data != nullptr && linear.weight.nbytes == count &&
+                       linear.weight.rows == out_rows && linear.weight.cols == in_cols,
+                   n + ": FP8 weight bytes");
+      NMOE_REQUIRE(linear.weight_scale > 0.0f && linear.weight_scale < 3.0e38f,
+                   n + ": weight_scale must be finite and positive");
+      DeviceBuffer staging;
+      staging.allocate(count);
+      NMOE_CUDA(cudaMemcpyAsync(staging.as<void>(), linear.weight.data, count, cudaMemcpyDefault,
+                                stream));
+      weight.allocate(count * sizeof(float));
+      NMOE_CUDA(launch_fp8_weight_dequant(staging.as<uint8_t>(), count, linear.weight_scale,
+                                          weight.as<float>(), stream));
+      NMOE_CUDA(cudaStreamSynchronize(stream));
+      fp8 = true;
+      input_scale = linear.input_scale;
+    } else {
+      throw Failure{NMOE_ERR_INVALID_ARGUMENT, n + ": unknown linear family"};
+    }
+    present = true;
+  }
+};
 
 }  // namespace
 }  // namespace nmoe
@@ -594,6 +651,24 @@ struct nmoe_layer {
   CUtensorMap split_map, gate_map;
   WeightStack up, down, shared_up, shared_down;
 
+  // Latent projections and the dense / scaled-FP8 families (fc1_latent, fc2_latent,
+  // shared_up, shared_down of expert_layer.cpp:534-617).  `latent` is the row length
+  // the routed experts see; without projections it is the hidden size.
+  int latent = 0;
+  bool latent_mode = false;
+  DenseLinear fc1, fc2, shared_up_dense, shared_down_dense;
+  DeviceBuffer latent_rows, lat_packed, lat_sf_row_major, lat_ts;  // fc1 output and its NVFP4 form
+  DeviceBuffer routed_latent, projected, shared_rows;               // [T][latent], [T][H], [T][H]
+  DeviceBuffer fp8_tmp;                                             // activation round trip
+  DeviceBuffer shared_raw;  // [T][S] FP32: shared_up output, activated in place
+  DeviceBuffer sh_ts;       // per-row tensor scale of the quantised shared intermediate
+
+  // The unfused activation path (nmoe_layer_set_unfused_activation): the up
+  // projection's rows stay FP32 and are quantised in a pass of their own.
+  bool unfused = false;
+  DeviceBuffer u_raw, h_ts, unweighted_rows;
+  int unweighted_tokens = 0;  // the unweighted down rows are kept for up to this many tokens
+
   // token-order scratch
   DeviceBuffer normalized, logits, top_index, top_weight;
   DeviceBuffer y_packed, y_sf_row_major, y_sf_tiled, y_ts;
@@ -639,13 +714,14 @@ struct nmoe_layer {
   ActivationOperand y_op, sh_op, a_op, h_op;
   ErrorSlot error;
   int last_tokens = 0;
+  std::string last_error;
   RowKind last_parts_kind = kRowF32;
+  bool last_unfused = false;
   bool force_fp32_parts = false;  // NMOE_PARTS_FP32=1: FP32 rows whatever the output type
   // how long a kernel waits for a flag another GPU raises before it gives up with
   // kDevWaitTimeout (clock64 ticks; nmoe_layer_set_wait_limit_ms, NMOE_WAIT_LIMIT_MS)
   long long wait_limit_ticks = 1ll << 34;
   DeviceBuffer probe_epoch;  // nmoe_layer_wait_flag
-  std::string last_error;
 
   // Small batches: the shared expert runs on a stream of the layer's own beside the
   // router, plan and permute kernels (it needs only the quantised rows) and joins
@@ -675,82 +751,18 @@ struct nmoe_layer {
 
 namespace {
 
-void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& w) {
-  // config checks of expert_layer.cpp:505-528
-  NMOE_REQUIRE(c.hidden_size > 0 && c.routed_expert_intermediate_size > 0 &&
-                   c.shared_expert_intermediate_size > 0 && c.n_routed_experts > 0 &&
-                   c.top_k > 0 && c.top_k <= c.n_routed_experts && c.n_group > 0 &&
-                   c.topk_group > 0 && c.n_routed_experts % c.n_group == 0 &&
-                   c.rms_epsilon > 0.0f && c.max_tokens > 0,
-               "invalid config");
-  if (c.moe_latent_size != c.hidden_size) {
-    throw Failure{NMOE_ERR_UNSUPPORTED, "latent projections are not built: moe_latent_size must equal hidden_size"};
-  }
-  NMOE_REQUIRE(c.n_routed_experts % 32 == 0 && c.n_routed_experts <= 512 && c.top_k <= 32 &&
-                   c.n_group <= 32,
-               "router limits: experts % 32 == 0, experts <= 512, top_k <= 32, n_group <= 32");
-  NMOE_REQUIRE(c.hidden_size % 64 == 0 && c.routed_expert_intermediate_size % 64 == 0 &&
-                   c.shared_expert_intermediate_size % 64 == 0,
-               "hidden and intermediate sizes must be multiples of 64");
-  // Expert parallelism: this device holds experts [first_local_expert,
-  // first_local_expert + n_local_experts), an equal share of all of them.
-  NMOE_REQUIRE(w.n_local_experts > 0 && c.n_routed_experts % w.n_local_experts == 0 &&
-                   w.first_local_expert >= 0 && w.first_local_expert % w.n_local_experts == 0 &&
-                   w.first_local_expert + w.n_local_experts <= c.n_routed_experts &&
-                   c.n_routed_experts / w.n_local_experts <= 64,
-               "local experts must be an equal, aligned share of the routed experts");
-  NMOE_REQUIRE(w.routed_up != nullptr && w.routed_down != nullptr, "missing routed expert weights");
-
-  L->cfg = c;
-  L->num_sms = device_sm_count();
-  L->force_fp32_parts = std::getenv("NMOE_PARTS_FP32") != nullptr;
-  if (const char* env = std::getenv("NMOE_WAIT_LIMIT_MS")) {
-    const double ms = std::strtod(env, nullptr);
-    if (ms > 0.0) L->wait_limit_ticks = ticks_from_ms(ms);
-  }
-  if (std::getenv("NMOE_NO_SHARED_FORK") == nullptr) {
-    NMOE_CUDA(cudaStreamCreateWithFlags(&L->side_stream, cudaStreamNonBlocking));
-    NMOE_CUDA(cudaEventCreateWithFlags(&L->quant_done, cudaEventDisableTiming));
-    NMOE_CUDA(cudaEventCreateWithFlags(&L->shared_done, cudaEventDisableTiming));
-  }
-  L->local_experts = w.n_local_experts;
-  L->first_local_expert = w.first_local_expert;
-  cudaStream_t stream = nullptr;
+// Everything whose size follows the token capacity.  Called at creation and by
+// nmoe_layer_reserve_tokens; weights are not touched.
+void allocate_scratch(nmoe_layer* L, size_t T) {
+  const nmoe_config& c = L->cfg;
   const int H = c.hidden_size, I = c.routed_expert_intermediate_size,
             S = c.shared_expert_intermediate_size, E = c.n_routed_experts, K = c.top_k;
-  const int EL = w.n_local_experts;
-  L->ep_world = E / EL;
-  L->ep_rank = w.first_local_expert / EL;
-  const size_t T = static_cast<size_t>(c.max_tokens);
-
-  upload_dense_fp32(w.input_norm_weight, H, "input_norm_weight", &L->norm_weight, stream);
-  upload_dense_fp32(w.gate_weight, static_cast<size_t>(E) * H, "gate_weight", &L->gate, stream);
-  upload_dense_fp32(w.gate_score_correction_bias, E, "gate_score_correction_bias", &L->bias, stream);
-  if (w.gate_logit_offset != nullptr) {
-    L->logit_offset.allocate(E * sizeof(float));
-    NMOE_CUDA(cudaMemcpyAsync(L->logit_offset.as<float>(), w.gate_logit_offset,
-                              E * sizeof(float), cudaMemcpyDefault, stream));
-    L->has_logit_offset = true;
-  }
-  L->up.upload(w.routed_up, EL, I, H, true, "routed up_proj", stream);
-  L->down.upload(w.routed_down, EL, H, I, false, "routed down_proj", stream);
-  L->shared_up.upload(&w.shared_up, 1, S, H, true, "shared up_proj", stream);
-  L->shared_down.upload(&w.shared_down, 1, H, S, false, "shared down_proj", stream);
-
+  const int EL = L->local_experts, Lr = L->latent;
   const size_t token_slots = (T + 127) / 128;
-  // The tensor-core pass needs the gate exactly in bf16.
-  L->fast_router = w.gate_weight.dtype == NMOE_BF16 && c.n_group == 1 && E % 32 == 0 &&
-                   E <= 256 && H % 64 == 0 && std::getenv("NMOE_ROUTER_FP64_ONLY") == nullptr;
   if (L->fast_router) {
-    L->gate_bf16.allocate(static_cast<size_t>(E) * H * 2);
-    NMOE_CUDA(cudaMemcpyAsync(L->gate_bf16.as<void>(), w.gate_weight.data,
-                              static_cast<size_t>(E) * H * 2, cudaMemcpyDefault, stream));
     L->split_plane_rows = static_cast<int>(token_slots * 128);
     L->y_split.allocate(3 * token_slots * 128 * H * 2, true);
     L->split_map = make_bf16_map(L->y_split.as<void>(), 3 * token_slots * 128, H, 128);
-    L->gate_map = make_bf16_map(L->gate_bf16.as<void>(), E, H, E);
-    if (const char* env = std::getenv("NMOE_ROUTER_TIE_MARGIN")) L->router_tie_margin = std::strtof(env, nullptr);
-    if (const char* env = std::getenv("NMOE_ROUTER_FAST_MIN_TOKENS")) L->fast_router_min_tokens = std::atoi(env);
   }
   L->normalized.allocate(T * H * sizeof(float));
   L->logits.allocate(T * E * sizeof(float));
@@ -762,7 +774,25 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
   L->y_ts.allocate(token_slots * 128 * sizeof(float), true);
   L->sh_packed.allocate(token_slots * 128 * S / 2, true);
   L->sh_sf.allocate(tiled_sf_bytes(token_slots, S), true);
-  if (L->ep_world == 1) L->parts.allocate(T * (K + 1) * H * sizeof(float));
+  L->sh_ts.allocate(token_slots * 128 * sizeof(float), true);
+  if (L->latent_mode) {
+    L->latent_rows.allocate(T * Lr * sizeof(float));
+    L->lat_packed.allocate(T * Lr / 2);
+    L->lat_sf_row_major.allocate(T * (Lr / 16));
+    L->lat_ts.allocate(T * sizeof(float));
+    L->routed_latent.allocate(T * Lr * sizeof(float));
+    L->projected.allocate(T * H * sizeof(float));
+    L->shared_rows.allocate(T * H * sizeof(float));
+  }
+  if (L->fc1.fp8 || L->shared_up_dense.fp8 || L->shared_down_dense.fp8) {
+    L->fp8_tmp.allocate(T * static_cast<size_t>(std::max(H, S)) * sizeof(float));
+  }
+  if (L->shared_up_dense.present || L->shared_down_dense.present || L->unfused) {
+    L->shared_raw.allocate(T * S * sizeof(float));
+  }
+  if (L->ep_world == 1) {
+    L->parts.allocate(T * (K + 1) * static_cast<size_t>(std::max(H, Lr)) * sizeof(float));
+  }
 
   // Row tiles: every expert may leave one partly filled slot.  Small batches
   // use 32-row tiles (decode tile class), large ones 128-row tiles.
@@ -795,20 +825,147 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
     L->rank_cursor.allocate(64 * sizeof(int32_t), true);
     L->shared_out.allocate(T * H * sizeof(float));
   }
-  L->a_packed.allocate(slots * 128 * H / 2, true);
-  L->a_sf.allocate(tiled_sf_bytes(slots, H), true);
+  L->a_packed.allocate(slots * 128 * Lr / 2, true);
+  L->a_sf.allocate(tiled_sf_bytes(slots, Lr), true);
   L->a_ts.allocate(slots * 128 * sizeof(float), true);
   L->a_weight.allocate(slots * 128 * sizeof(float), true);
   L->a_dest.allocate(slots * 128 * sizeof(int32_t), true);
   L->h_packed.allocate(slots * 128 * I / 2, true);
   L->h_sf.allocate(tiled_sf_bytes(slots, I), true);
+  L->h_ts.allocate(slots * 128 * sizeof(float), true);
+  if (L->unfused) {
+    L->u_raw.allocate(slots * 128 * I * sizeof(float), true);
+    L->unweighted_tokens = static_cast<int>(std::min<size_t>(T, 64));
+    L->unweighted_rows.allocate(static_cast<size_t>(L->unweighted_tokens) * (K + 1) *
+                                std::max(H, Lr) * sizeof(float), true);
+  }
 
   L->y_op.bind(L->y_packed.as<uint8_t>(), L->y_sf_tiled.as<uint8_t>(), token_slots * 128, H);
   L->sh_op.bind(L->sh_packed.as<uint8_t>(), L->sh_sf.as<uint8_t>(), token_slots * 128, S);
-  L->a_op.bind(L->a_packed.as<uint8_t>(), L->a_sf.as<uint8_t>(), slots * 128, H);
+  L->a_op.bind(L->a_packed.as<uint8_t>(), L->a_sf.as<uint8_t>(), slots * 128, Lr);
   L->h_op.bind(L->h_packed.as<uint8_t>(), L->h_sf.as<uint8_t>(), slots * 128, I);
+  L->cfg.max_tokens = static_cast<int32_t>(T);
+  L->last_tokens = 0;
+}
+
+void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& w) {
+  // config checks of expert_layer.cpp:505-528
+  NMOE_REQUIRE(c.hidden_size > 0 && c.moe_latent_size > 0 &&
+                   c.routed_expert_intermediate_size > 0 &&
+                   c.shared_expert_intermediate_size > 0 && c.n_routed_experts > 0 &&
+                   c.top_k > 0 && c.top_k <= c.n_routed_experts && c.n_group > 0 &&
+                   c.topk_group > 0 && c.n_routed_experts % c.n_group == 0 &&
+                   c.rms_epsilon > 0.0f && c.max_tokens > 0,
+               "invalid config");
+  const bool has_fc1 = w.fc1_latent.family != NMOE_LINEAR_ABSENT;
+  const bool has_fc2 = w.fc2_latent.family != NMOE_LINEAR_ABSENT;
+  NMOE_REQUIRE(has_fc1 == has_fc2, "fc1_latent and fc2_latent come together");
+  NMOE_REQUIRE(has_fc1 || c.moe_latent_size == c.hidden_size,
+               "moe_latent_size != hidden_size needs the fc1_latent / fc2_latent projections");
+  NMOE_REQUIRE(w.fc2_latent.family != NMOE_LINEAR_SCALED_FP8,
+               "fc2_latent is a dense projection (expert_layer.cpp:617-626)");
+  NMOE_REQUIRE(c.n_routed_experts % 32 == 0 && c.n_routed_experts <= 512 && c.top_k <= 32 &&
+                   c.n_group <= 32,
+               "router limits: experts % 32 == 0, experts <= 512, top_k <= 32, n_group <= 32");
+  NMOE_REQUIRE(c.hidden_size % 64 == 0 && c.moe_latent_size % 64 == 0 &&
+                   c.routed_expert_intermediate_size % 64 == 0 &&
+                   c.shared_expert_intermediate_size % 64 == 0,
+               "hidden, latent and intermediate sizes must be multiples of 64");
+  // Expert parallelism: this device holds experts [first_local_expert,
+  // first_local_expert + n_local_experts), an equal share of all of them.
+  NMOE_REQUIRE(w.n_local_experts > 0 && c.n_routed_experts % w.n_local_experts == 0 &&
+                   w.first_local_expert >= 0 && w.first_local_expert % w.n_local_experts == 0 &&
+                   w.first_local_expert + w.n_local_experts <= c.n_routed_experts &&
+                   c.n_routed_experts / w.n_local_experts <= 64,
+               "local experts must be an equal, aligned share of the routed experts");
+  NMOE_REQUIRE(w.routed_up != nullptr && w.routed_down != nullptr, "missing routed expert weights");
+
+  L->cfg = c;
+  L->num_sms = device_sm_count();
+  L->force_fp32_parts = std::getenv("NMOE_PARTS_FP32") != nullptr;
+  if (const char* env = std::getenv("NMOE_WAIT_LIMIT_MS")) {
+    const double ms = std::strtod(env, nullptr);
+    if (ms > 0.0) L->wait_limit_ticks = ticks_from_ms(ms);
+  }
+  if (std::getenv("NMOE_NO_SHARED_FORK") == nullptr) {
+    NMOE_CUDA(cudaStreamCreateWithFlags(&L->side_stream, cudaStreamNonBlocking));
+    NMOE_CUDA(cudaEventCreateWithFlags(&L->quant_done, cudaEventDisableTiming));
+    NMOE_CUDA(cudaEventCreateWithFlags(&L->shared_done, cudaEventDisableTiming));
+  }
+  L->local_experts = w.n_local_experts;
+  L->first_local_expert = w.first_local_expert;
+  cudaStream_t stream = nullptr;
+  const int H = c.hidden_size, I = c.routed_expert_intermediate_size,
+            S = c.shared_expert_intermediate_size, E = c.n_routed_experts;
+  const int EL = w.n_local_experts;
+  L->ep_world = E / EL;
+  L->ep_rank = w.first_local_expert / EL;
+  L->latent = c.moe_latent_size;
+  L->latent_mode = has_fc1;
+  const int Lr = L->latent;
+  const bool dense_shared = w.shared_up_linear.family != NMOE_LINEAR_ABSENT ||
+                            w.shared_down_linear.family != NMOE_LINEAR_ABSENT;
+  if (L->ep_world > 1 && (L->latent_mode || dense_shared)) {
+    throw Failure{NMOE_ERR_UNSUPPORTED,
+                  "expert parallelism is built for the all-NVFP4 layer without latent projections"};
+  }
+
+  upload_dense_fp32(w.input_norm_weight, H, "input_norm_weight", &L->norm_weight, stream);
+  upload_dense_fp32(w.gate_weight, static_cast<size_t>(E) * H, "gate_weight", &L->gate, stream);
+  upload_dense_fp32(w.gate_score_correction_bias, E, "gate_score_correction_bias", &L->bias, stream);
+  if (w.gate_logit_offset != nullptr) {
+    L->logit_offset.allocate(E * sizeof(float));
+    NMOE_CUDA(cudaMemcpyAsync(L->logit_offset.as<float>(), w.gate_logit_offset,
+                              E * sizeof(float), cudaMemcpyDefault, stream));
+    L->has_logit_offset = true;
+  }
+  // routed experts act on latent rows: up_proj [I][latent], down_proj [latent][I]
+  // (shape checks of expert_layer.cpp:646-689)
+  L->up.upload(w.routed_up, EL, I, Lr, true, "routed up_proj", stream);
+  L->down.upload(w.routed_down, EL, Lr, I, false, "routed down_proj", stream);
+  if (L->latent_mode) {
+    L->fc1.upload(w.fc1_latent, Lr, H, "fc1_latent", stream);
+    L->fc2.upload(w.fc2_latent, H, Lr, "fc2_latent", stream);
+  }
+  if (w.shared_up_linear.family != NMOE_LINEAR_ABSENT) {
+    L->shared_up_dense.upload(w.shared_up_linear, S, H, "shared up_proj", stream);
+  } else {
+    L->shared_up.upload(&w.shared_up, 1, S, H, true, "shared up_proj", stream);
+  }
+  if (w.shared_down_linear.family != NMOE_LINEAR_ABSENT) {
+    L->shared_down_dense.upload(w.shared_down_linear, H, S, "shared down_proj", stream);
+  } else {
+    L->shared_down.upload(&w.shared_down, 1, H, S, false, "shared down_proj", stream);
+  }
+
+  // The tensor-core pass needs the gate exactly in bf16.
+  L->fast_router = w.gate_weight.dtype == NMOE_BF16 && c.n_group == 1 && E % 32 == 0 &&
+                   E <= 256 && H % 64 == 0 && std::getenv("NMOE_ROUTER_FP64_ONLY") == nullptr;
+  if (L->fast_router) {
+    L->gate_bf16.allocate(static_cast<size_t>(E) * H * 2);
+    NMOE_CUDA(cudaMemcpyAsync(L->gate_bf16.as<void>(), w.gate_weight.data,
+                              static_cast<size_t>(E) * H * 2, cudaMemcpyDefault, stream));
+    L->gate_map = make_bf16_map(L->gate_bf16.as<void>(), E, H, E);
+    if (const char* env = std::getenv("NMOE_ROUTER_TIE_MARGIN")) L->router_tie_margin = std::strtof(env, nullptr);
+    if (const char* env = std::getenv("NMOE_ROUTER_FAST_MIN_TOKENS")) L->fast_router_min_tokens = std::atoi(env);
+  }
+  L->unfused = std::getenv("NMOE_UNFUSED_ACTIVATION") != nullptr;
+  allocate_scratch(L, static_cast<size_t>(c.max_tokens));
   L->error.create();
   NMOE_CUDA(cudaDeviceSynchronize());
+}
+
+// y = x W^T of a dense / scaled-FP8 linear, FP64 accumulation.
+void run_linear(nmoe_layer* L, const DenseLinear& linear, const float* in_rows, int rows,
+                float* out_rows, cudaStream_t stream) {
+  const float* source = in_rows;
+  if (linear.fp8) {
+    NMOE_CUDA(launch_fp8_round_trip(in_rows, static_cast<size_t>(rows) * linear.in,
+                                    linear.input_scale, L->fp8_tmp.as<float>(), stream));
+    source = L->fp8_tmp.as<float>();
+  }
+  NMOE_CUDA(launch_router_logits(source, linear.weight.as<float>(), nullptr, rows, linear.out,
+                                 linear.in, out_rows, stream));
 }
 
 // RMSNorm + activation quantiser + router: fills normalized, y_*, logits,
@@ -854,13 +1011,50 @@ void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dt
   L->mark(3, stream);
 }
 
+// One expert FFN over rows that are already quantised, fused or unfused.
+//   fused:   up GEMM (relu^2 + NVFP4 quantise in the epilogue, tensor scale 1) -> down GEMM
+//   unfused: up GEMM keeps relu^2 rows in FP32 (`raw_rows`) -> per-row quantiser with
+//            the row's own tensor scale (nvfp4_packing.cpp:119-153) -> down GEMM
+struct FfnBuffers {
+  uint8_t* hidden_packed;
+  uint8_t* hidden_sf;
+  float* hidden_ts;
+  const ActivationOperand* hidden;
+  float* raw_rows;  // unfused only: [row slots * 128][intermediate] FP32
+  int raw_row_count;
+};
+
+void run_ffn(nmoe_layer* L, bool unfused, const WeightStack& up, const WeightStack& down,
+             TileClass tile_class, const ActivationOperand& a, const float* a_ts,
+             const Schedule& schedule, const FfnBuffers& buffers, void* out_rows,
+             const int32_t* dest_row, int dest_mul, int dest_add, const float* row_weight,
+             cudaStream_t stream, cudaEvent_t between, RowKind out_kind, RowSegments segments) {
+  int32_t* error = L->error.device.as<int32_t>();
+  if (!unfused) {
+    run_expert_gemms(up, down, tile_class, a, a_ts, schedule, buffers.hidden_packed,
+                     buffers.hidden_sf, *buffers.hidden, out_rows, dest_row, dest_mul, dest_add,
+                     row_weight, error, L->num_sms, stream, between, out_kind, segments);
+    return;
+  }
+  // the row-storing epilogue exists for the BN = 128 tile shapes
+  const TileClass raw_class = tile_class == kClassPrefill ? kClassDecodeWide : tile_class;
+  run_down_gemm(up, raw_class, a, a_ts, schedule, buffers.raw_rows, nullptr, 1, 0, nullptr,
+                /*relu2=*/true, error, L->num_sms, stream, kRowF32, RowSegments());
+  NMOE_CUDA(launch_norm_quant(buffers.raw_rows, false, buffers.raw_row_count, up.n, nullptr, 0.0f,
+                              nullptr, buffers.hidden_packed, nullptr, buffers.hidden_sf,
+                              k_blocks_of(up.n), buffers.hidden_ts, stream));
+  if (between != nullptr) cudaEventRecord(between, stream);
+  run_down_gemm(down, tile_class, *buffers.hidden, buffers.hidden_ts, schedule, out_rows, dest_row,
+                dest_mul, dest_add, row_weight, /*relu2=*/false, error, L->num_sms, stream,
+                out_kind, segments);
+}
+
 // Plan + permute + the two grouped GEMMs over `pairs` (row, slot) pairs whose
 // per-local-expert histogram is already in `counts`.
 void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& source, int pairs,
                     int dest_stride, void* out_rows, RowKind out_kind,
                     RowSegments segments = RowSegments()) {
-  const nmoe_config& c = L->cfg;
-  const int H = c.hidden_size;
+  const int Lr = L->latent;
   int32_t* error = L->error.device.as<int32_t>();
   const bool decode = static_cast<long long>(pairs) <= L->decode_pairs_limit / 2;
   const TileClass routed_class = decode ? kClassDecode : kClassPrefill;
@@ -873,8 +1067,8 @@ void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& sou
   plan.num_row_tiles = L->num_row_tiles.as<int32_t>();
   NMOE_CUDA(launch_route_plan(plan, L->local_experts, tile_rows, L->max_row_tiles, error, stream));
   L->mark(4, stream);
-  NMOE_CUDA(launch_permute(plan, source, pairs, L->local_experts, tile_rows, L->max_row_tiles, H,
-                           k_blocks_of(H),
+  NMOE_CUDA(launch_permute(plan, source, pairs, L->local_experts, tile_rows, L->max_row_tiles, Lr,
+                           k_blocks_of(Lr),
                            L->a_packed.as<uint8_t>(), L->a_sf.as<uint8_t>(), L->a_ts.as<float>(),
                            L->a_weight.as<float>(), L->a_dest.as<int32_t>(),
                            L->ep_world == 1 ? L->pair_row.as<int32_t>() : nullptr, dest_stride,
@@ -884,23 +1078,63 @@ void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& sou
   Schedule routed;
   routed.row_tiles = L->row_tiles.as<RowTile>();
   routed.num_row_tiles = L->num_row_tiles.as<int32_t>();
-  run_expert_gemms(L->up, L->down, routed_class, L->a_op, L->a_ts.as<float>(), routed,
-                   L->h_packed.as<uint8_t>(), L->h_sf.as<uint8_t>(), L->h_op, out_rows,
-                   L->a_dest.as<int32_t>(), 1, 0, L->a_weight.as<float>(), error, L->num_sms,
-                   stream, L->stage_timing ? L->stage_events[6] : nullptr, out_kind, segments);
+  FfnBuffers buffers{L->h_packed.as<uint8_t>(), L->h_sf.as<uint8_t>(), L->h_ts.as<float>(),
+                     &L->h_op, L->u_raw.as<float>(), L->max_row_tiles * 128};
+  run_ffn(L, L->unfused, L->up, L->down, routed_class, L->a_op, L->a_ts.as<float>(), routed,
+          buffers, out_rows, L->a_dest.as<int32_t>(), 1, 0, L->a_weight.as<float>(), stream,
+          L->stage_timing ? L->stage_events[6] : nullptr, out_kind, segments);
+  if (L->unfused && L->ep_world == 1 && pairs <= L->unweighted_tokens * L->cfg.top_k) {
+    // the down_proj rows before the routing weight (routed_expert_outputs of the trace)
+    run_down_gemm(L->down, routed_class, L->h_op, L->h_ts.as<float>(), routed,
+                  L->unweighted_rows.as<float>(), L->a_dest.as<int32_t>(), 1, 0, nullptr, false,
+                  error, L->num_sms, stream, kRowF32, RowSegments());
+  }
 }
 
-// shared expert (:814-818, :956-964, :981-1005) on the token-order quantised rows
+// shared expert (:814-818, :956-964, :981-1005) on the token-order rows
 void shared_expert(nmoe_layer* L, cudaStream_t stream, int tokens, void* out_rows, int dest_mul,
                    int dest_add, cudaEvent_t between, RowKind out_kind = kRowF32) {
+  const int H = L->cfg.hidden_size, S = L->cfg.shared_expert_intermediate_size;
   const TileClass shared_class =
       tokens <= 32 ? kClassDecode : tokens <= 256 ? kClassDecodeWide : kClassPrefill;
   Schedule shared;
   shared.dense_rows = tokens;
-  run_expert_gemms(L->shared_up, L->shared_down, shared_class, L->y_op, L->y_ts.as<float>(),
-                   shared, L->sh_packed.as<uint8_t>(), L->sh_sf.as<uint8_t>(), L->sh_op, out_rows,
-                   nullptr, dest_mul, dest_add, nullptr, L->error.device.as<int32_t>(),
-                   L->num_sms, stream, between, out_kind);
+  int32_t* error = L->error.device.as<int32_t>();
+  if (!L->shared_up_dense.present && !L->shared_down_dense.present) {
+    FfnBuffers buffers{L->sh_packed.as<uint8_t>(), L->sh_sf.as<uint8_t>(), L->sh_ts.as<float>(),
+                       &L->sh_op, L->shared_raw.as<float>(), tokens};
+    run_ffn(L, L->unfused, L->shared_up, L->shared_down, shared_class, L->y_op,
+            L->y_ts.as<float>(), shared, buffers, out_rows, nullptr, dest_mul, dest_add, nullptr,
+            stream, between, out_kind, RowSegments());
+    return;
+  }
+  // shared_up -> FP32 rows -> relu^2 in place (:956-964)
+  float* raw = L->shared_raw.as<float>();
+  if (L->shared_up_dense.present) {
+    run_linear(L, L->shared_up_dense, L->normalized.as<float>(), tokens, raw, stream);
+    NMOE_CUDA(launch_relu2(raw, static_cast<size_t>(tokens) * S, stream));
+  } else {
+    run_down_gemm(L->shared_up, shared_class == kClassPrefill ? kClassDecodeWide : shared_class,
+                  L->y_op, L->y_ts.as<float>(), shared, raw, nullptr, 1, 0, nullptr, true, error,
+                  L->num_sms, stream, kRowF32, RowSegments());
+  }
+  if (between != nullptr) cudaEventRecord(between, stream);
+  if (L->shared_down_dense.present) {
+    // dense / scaled-FP8 down projection (:1006-1045) straight from the FP32 rows;
+    // only the latent data flow (FP32 rows of `hidden` per token) reaches this
+    NMOE_REQUIRE(dest_mul == 1 && dest_add == 0 && out_kind == kRowF32,
+                 "a dense shared_down writes FP32 token rows");
+    run_linear(L, L->shared_down_dense, raw, tokens, static_cast<float*>(out_rows), stream);
+    (void)H;
+    return;
+  }
+  // NVFP4 down projection through the host linear's own packing step (:981-1005)
+  NMOE_CUDA(launch_norm_quant(raw, false, tokens, S, nullptr, 0.0f, nullptr,
+                              L->sh_packed.as<uint8_t>(), nullptr, L->sh_sf.as<uint8_t>(),
+                              k_blocks_of(S), L->sh_ts.as<float>(), stream));
+  run_down_gemm(L->shared_down, shared_class, L->sh_op, L->sh_ts.as<float>(), shared, out_rows,
+                nullptr, dest_mul, dest_add, nullptr, false, error, L->num_sms, stream, out_kind,
+                RowSegments());
 }
 
 PermuteSource local_source(nmoe_layer* L) {
@@ -923,15 +1157,51 @@ PermuteSource local_source(nmoe_layer* L) {
 void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dtype in_dtype,
                     int tokens, void* output, nmoe_dtype out_dtype) {
   const nmoe_config& c = L->cfg;
-  const int H = c.hidden_size, K = c.top_k;
+  const int H = c.hidden_size, K = c.top_k, Lr = L->latent;
+  const bool dense_shared = L->shared_up_dense.present || L->shared_down_dense.present;
   // The per-(token, slot) rows of the down projection and the shared expert's row
   // wait in `parts` for the combine.  They carry the precision the output needs: FP32
   // rows for an FP32 result (the reference's arithmetic, bit for bit in the sums),
   // binary16 rows for a bf16 result: half the bytes of the layer's largest write and
   // read, and eight times finer than the bf16 the sum is rounded to in the end.
-  const RowKind parts_kind = out_dtype == NMOE_BF16 && !L->force_fp32_parts ? kRowF16 : kRowF32;
-  const bool fork = L->side_stream != nullptr && !L->stage_timing && tokens <= L->fork_max_tokens;
+  const RowKind parts_kind = out_dtype == NMOE_BF16 && !L->force_fp32_parts && !L->latent_mode
+                                 ? kRowF16 : kRowF32;
+  const bool fork = L->side_stream != nullptr && !L->stage_timing &&
+                    tokens <= L->fork_max_tokens && !L->latent_mode && !dense_shared;
   route_tokens(L, stream, input, in_dtype, tokens, fork ? L->quant_done : nullptr);
+  L->last_tokens = tokens;
+  L->last_parts_kind = parts_kind;
+  L->last_unfused = L->unfused;
+  if (L->latent_mode) {
+    // latent = fc1_latent(normalized) (:809-813); every routed expert's up_proj packs
+    // the same latent row (:913 -> nvfp4_packing.cpp:90)
+    run_linear(L, L->fc1, L->normalized.as<float>(), tokens, L->latent_rows.as<float>(), stream);
+    NMOE_CUDA(launch_norm_quant(L->latent_rows.as<float>(), false, tokens, Lr, nullptr, 0.0f,
+                                nullptr, L->lat_packed.as<uint8_t>(),
+                                L->lat_sf_row_major.as<uint8_t>(), nullptr, 0,
+                                L->lat_ts.as<float>(), stream));
+    PermuteSource source = local_source(L);
+    source.packed = L->lat_packed.as<uint8_t>();
+    source.packed_stride = static_cast<size_t>(Lr) / 2;
+    source.sf = L->lat_sf_row_major.as<uint8_t>();
+    source.sf_stride = static_cast<size_t>(Lr) / 16;
+    source.tensor_scale = L->lat_ts.as<float>();
+    routed_experts(L, stream, source, tokens * K, K, L->parts.as<void>(), kRowF32);
+    L->mark(7, stream);
+    shared_expert(L, stream, tokens, L->shared_rows.as<void>(), 1, 0,
+                  L->stage_timing ? L->stage_events[8] : nullptr, kRowF32);
+    L->mark(9, stream);
+    // routed sum in selection order (:951-953), fc2_latent (:1047-1053), mixer and
+    // residual (:1064-1069)
+    NMOE_CUDA(launch_sum_parts(L->parts.as<float>(), tokens, Lr, K, L->routed_latent.as<float>(),
+                               stream));
+    run_linear(L, L->fc2, L->routed_latent.as<float>(), tokens, L->projected.as<float>(), stream);
+    NMOE_CUDA(launch_mixer(input, in_dtype == NMOE_BF16, L->projected.as<float>(),
+                           L->shared_rows.as<float>(), tokens, H, output, out_dtype == NMOE_BF16,
+                           stream));
+    L->mark(10, stream);
+    return;
+  }
   if (fork) {
     NMOE_CUDA(cudaStreamWaitEvent(L->side_stream, L->quant_done, 0));
     shared_expert(L, L->side_stream, tokens, L->parts.as<void>(), K + 1, K, nullptr, parts_kind);
@@ -950,8 +1220,6 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
   NMOE_CUDA(launch_combine(input, in_dtype == NMOE_BF16, L->parts.as<void>(), parts_kind, tokens,
                            H, K, output, out_dtype == NMOE_BF16, stream));
   L->mark(10, stream);
-  L->last_tokens = tokens;
-  L->last_parts_kind = parts_kind;
 }
 
 }  // namespace
@@ -1466,10 +1734,15 @@ nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out) {
   out->router_logits = layer->logits.as<float>();
   out->selected_index = layer->top_index.as<int32_t>();
   out->selected_weight = layer->top_weight.as<float>();
-  out->act_packed = layer->y_packed.as<uint8_t>();
-  out->act_scales = layer->y_sf_row_major.as<uint8_t>();
-  out->act_tensor_scale = layer->y_ts.as<float>();
-  out->parts = layer->last_parts_kind ? nullptr : layer->parts.as<float>();
+  const bool lat = layer->latent_mode;
+  out->act_packed = lat ? layer->lat_packed.as<uint8_t>() : layer->y_packed.as<uint8_t>();
+  out->act_scales = lat ? layer->lat_sf_row_major.as<uint8_t>() : layer->y_sf_row_major.as<uint8_t>();
+  out->act_tensor_scale = lat ? layer->lat_ts.as<float>() : layer->y_ts.as<float>();
+  out->parts = layer->last_parts_kind != kRowF32 ? nullptr : layer->parts.as<float>();
+  out->latent_output = lat ? layer->latent_rows.as<float>() : nullptr;
+  out->routed_latent_output = lat ? layer->routed_latent.as<float>() : nullptr;
+  out->projected_routed_output = lat ? layer->projected.as<float>() : nullptr;
+  out->shared_output = lat ? layer->shared_rows.as<float>() : nullptr;
   return NMOE_OK;
 }
 
@@ -1478,14 +1751,86 @@ nmoe_status nmoe_layer_copy_trace_field(nmoe_layer* layer, void* stream, int32_t
   if (layer == nullptr || dst == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
   nmoe_trace_view view;
   nmoe_layer_trace_view(layer, &view);
-  const void* sources[8] = {view.normalized_input, view.router_logits, view.selected_index,
-                            view.selected_weight,  view.act_packed,    view.act_scales,
-                            view.act_tensor_scale, view.parts};
-  if (field < 0 || field >= 8 || sources[field] == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  const void* sources[12] = {view.normalized_input, view.router_logits, view.selected_index,
+                             view.selected_weight,  view.act_packed,    view.act_scales,
+                             view.act_tensor_scale, view.parts,         view.latent_output,
+                             view.routed_latent_output, view.projected_routed_output,
+                             view.shared_output};
+  if (field < 0 || field >= 12 || sources[field] == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
   return cudaMemcpyAsync(dst, sources[field], nbytes, cudaMemcpyDefault,
                          static_cast<cudaStream_t>(stream)) == cudaSuccess
              ? NMOE_OK
              : NMOE_ERR_CUDA;
+}
+
+nmoe_status nmoe_layer_reserve_tokens(nmoe_layer* layer, int32_t max_tokens) {
+  if (layer == nullptr || max_tokens <= 0) return NMOE_ERR_INVALID_ARGUMENT;
+  if (max_tokens <= layer->cfg.max_tokens) return NMOE_OK;
+  if (layer->window.attached) return NMOE_ERR_INVALID_ARGUMENT;  // peers hold the old window
+  try {
+    NMOE_CUDA(cudaDeviceSynchronize());
+    allocate_scratch(layer, static_cast<size_t>(max_tokens));
+    NMOE_CUDA(cudaDeviceSynchronize());
+  } catch (const Failure& failure) {
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_layer_set_unfused_activation(nmoe_layer* layer, int32_t enable) {
+  if (layer == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  const bool want = enable != 0;
+  if (want == layer->unfused) return NMOE_OK;
+  if (want && layer->ep_world > 1) return NMOE_ERR_UNSUPPORTED;
+  try {
+    NMOE_CUDA(cudaDeviceSynchronize());
+    layer->unfused = want;
+    if (want && layer->u_raw.bytes() == 0) {
+      allocate_scratch(layer, static_cast<size_t>(layer->cfg.max_tokens));
+      NMOE_CUDA(cudaDeviceSynchronize());
+    }
+  } catch (const Failure& failure) {
+    layer->unfused = false;
+    layer->last_error = failure.message;
+    return failure.status;
+  }
+  return NMOE_OK;
+}
+
+nmoe_status nmoe_layer_export_unfused(nmoe_layer* layer, void* stream_ptr, float* routed_activated,
+                                      float* routed_outputs, float* shared_activated) {
+  if (layer == nullptr || layer->last_tokens <= 0 || !layer->last_unfused) {
+    return NMOE_ERR_INVALID_ARGUMENT;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  const nmoe_config& c = layer->cfg;
+  const int tokens = layer->last_tokens, pairs = tokens * c.top_k;
+  cudaError_t err = cudaSuccess;
+  if (routed_activated != nullptr) {
+    err = launch_gather_rows(layer->u_raw.as<float>(), layer->pair_row.as<int32_t>(), pairs,
+                             c.routed_expert_intermediate_size, routed_activated, stream);
+  }
+  if (err == cudaSuccess && routed_outputs != nullptr) {
+    if (tokens > layer->unweighted_tokens) return NMOE_ERR_CAPACITY;
+    // kept in the layout of `parts`: [token][top_k (+1 unless latent)][row]
+    const int stride = layer->latent_mode ? c.top_k : c.top_k + 1;
+    const int cols = layer->latent;
+    for (int t = 0; t < tokens && err == cudaSuccess; ++t) {
+      err = cudaMemcpyAsync(routed_outputs + static_cast<size_t>(t) * c.top_k * cols,
+                            layer->unweighted_rows.as<float>() +
+                                static_cast<size_t>(t) * stride * cols,
+                            static_cast<size_t>(c.top_k) * cols * sizeof(float),
+                            cudaMemcpyDefault, stream);
+    }
+  }
+  if (err == cudaSuccess && shared_activated != nullptr) {
+    err = cudaMemcpyAsync(shared_activated, layer->shared_raw.as<float>(),
+                          static_cast<size_t>(tokens) * c.shared_expert_intermediate_size *
+                              sizeof(float),
+                          cudaMemcpyDefault, stream);
+  }
+  return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
 }
 
 nmoe_status nmoe_layer_export_hidden(nmoe_layer* layer, void* stream_ptr, uint8_t* routed_packed,

@@ -16,7 +16,8 @@ from typing import List, Optional
 
 import torch
 
-from . import ExpertLayerBindings, ExpertLayerConfig, ExpertWeightPair, Nvfp4Matrix
+from . import (DenseLinear, ExpertLayerBindings, ExpertLayerConfig, ExpertWeightPair,
+               Nvfp4Matrix)
 
 HIDDEN = 2688
 ROUTED_INTERMEDIATE = 1856
@@ -28,8 +29,8 @@ ROUTED_SCALING = 2.5
 
 def baseline_config(max_tokens: int, experts: int = EXPERTS, hidden: int = HIDDEN,
                     routed: int = ROUTED_INTERMEDIATE, shared: int = SHARED_INTERMEDIATE,
-                    top_k: int = TOP_K) -> ExpertLayerConfig:
-    return ExpertLayerConfig(layer_index=0, hidden_size=hidden, moe_latent_size=hidden,
+                    top_k: int = TOP_K, latent: int = 0) -> ExpertLayerConfig:
+    return ExpertLayerConfig(layer_index=0, hidden_size=hidden, moe_latent_size=latent or hidden,
                              routed_expert_intermediate_size=routed,
                              shared_expert_intermediate_size=shared, n_routed_experts=experts,
                              top_k=top_k, n_group=1, topk_group=1, rms_epsilon=1e-5,
@@ -101,20 +102,62 @@ def zipf_logit_offset(experts: int, seed: int, head: float = 0.2, tail: float = 
     return torch.where(centred > 0, head * centred, tail * centred).to(torch.float32)
 
 
+def checkpoint_shape_config(max_tokens: int) -> ExpertLayerConfig:
+    """The latent-MoE shape of the reference's checkpoint
+    (runtime/src/api/single_token_forward_model.cpp:116-126)."""
+    return ExpertLayerConfig(layer_index=0, hidden_size=4096, moe_latent_size=1024,
+                             routed_expert_intermediate_size=2688,
+                             shared_expert_intermediate_size=5376, n_routed_experts=512,
+                             top_k=22, n_group=1, topk_group=1, rms_epsilon=1e-5,
+                             routed_scaling_factor=5.0, norm_topk_prob=True,
+                             max_tokens=max_tokens)
+
+
+def quantize_fp8(w: torch.Tensor):
+    """Per-tensor E4M3 weight of the scaled-FP8 family: (codes uint8, weight_scale)."""
+    scale = float(w.abs().max().item()) / 448.0
+    codes = (w.to(torch.float32) / scale).to(torch.float8_e4m3fn).view(torch.uint8)
+    return codes.contiguous(), scale
+
+
+def _make_linear(shape, family: str, generator, device) -> DenseLinear:
+    w = _normal(shape, 0.02, generator, device)
+    if family == "fp8":
+        codes, scale = quantize_fp8(w)
+        return DenseLinear(codes, weight_scale=scale, input_scale=8.0 / 448.0)
+    if family == "fp32":
+        return DenseLinear(w)
+    return DenseLinear(w.to(torch.bfloat16))
+
+
 def make_layer(config: ExpertLayerConfig, seed: int, device="cpu", norm_weight_uniform=False,
-               skewed: bool = False, chunk: int = 16) -> SyntheticLayer:
+               skewed: bool = False, chunk: int = 16, latent_family: str = "bf16",
+               shared_up_family: str = "nvfp4", shared_down_family: str = "nvfp4"
+               ) -> SyntheticLayer:
     """Seeded layer weights.  Generation runs on `device` (the stream of random
-    numbers depends on the device type); the quantised bytes stay there."""
+    numbers depends on the device type); the quantised bytes stay there.
+    With config.moe_latent_size != hidden_size the layer gets fc1_latent / fc2_latent
+    (fc1 in `latent_family`: "bf16", "fp32" or "fp8"; fc2 dense); the shared expert's
+    projections are "nvfp4", "bf16", "fp32" or "fp8"."""
     dev = torch.device(device)
     g = torch.Generator(device=dev).manual_seed(seed)
-    H, I, S, E = (config.hidden_size, config.routed_expert_intermediate_size,
+    H, I, S, E = (config.moe_latent_size, config.routed_expert_intermediate_size,
                   config.shared_expert_intermediate_size, config.n_routed_experts)
-    gate = _normal((E, H), 0.02, g, dev).to(torch.bfloat16)
+    full_hidden = config.hidden_size
+    latent_mode = H != full_hidden
+    return _make_layer(config, g, dev, H, full_hidden, I, S, E, latent_mode, norm_weight_uniform,
+                       skewed, chunk, seed, latent_family, shared_up_family, shared_down_family)
+
+
+def _make_layer(config, g, dev, H, full_hidden, I, S, E, latent_mode, norm_weight_uniform, skewed,
+                chunk, seed, latent_family, shared_up_family, shared_down_family):
+    # H is the row length the routed experts see (the latent size, or the hidden size)
+    gate = _normal((E, full_hidden), 0.02, g, dev).to(torch.bfloat16)
     bias = (torch.rand((E,), generator=g, device=dev) * 0.02 - 0.01).to(torch.float32)
     if norm_weight_uniform:
-        norm = (torch.rand((H,), generator=g, device=dev) * 0.2 + 0.9).to(torch.float32)
+        norm = (torch.rand((full_hidden,), generator=g, device=dev) * 0.2 + 0.9).to(torch.float32)
     else:
-        norm = torch.ones((H,), dtype=torch.float32, device=dev)
+        norm = torch.ones((full_hidden,), dtype=torch.float32, device=dev)
     ups, downs = [], []
     for e0 in range(0, E, chunk):
         n = min(chunk, E - e0)
@@ -122,8 +165,8 @@ def make_layer(config: ExpertLayerConfig, seed: int, device="cpu", norm_weight_u
         downs.append(quantize_weight(_normal((n, H, I), 0.02, g, dev)))
     up_p, up_s, up_t = (torch.cat([u[i] for u in ups]) for i in range(3))
     dn_p, dn_s, dn_t = (torch.cat([d[i] for d in downs]) for i in range(3))
-    su = quantize_weight(_normal((S, H), 0.02, g, dev))
-    sd = quantize_weight(_normal((H, S), 0.02, g, dev))
+    su = quantize_weight(_normal((S, full_hidden), 0.02, g, dev))
+    sd = quantize_weight(_normal((full_hidden, S), 0.02, g, dev))
     up_t_host, dn_t_host = up_t.cpu(), dn_t.cpu()
     routed = [ExpertWeightPair(Nvfp4Matrix(up_p[e], up_s[e], float(up_t_host[e])),
                                Nvfp4Matrix(dn_p[e], dn_s[e], float(dn_t_host[e])))
@@ -136,6 +179,16 @@ def make_layer(config: ExpertLayerConfig, seed: int, device="cpu", norm_weight_u
         shared_up=Nvfp4Matrix(su[0], su[1], float(su[2])),
         shared_down=Nvfp4Matrix(sd[0], sd[1], float(sd[2])),
         routed_experts=routed, gate_logit_offset=offset)
+    # drawn after everything else so that the layers without them keep their weights
+    if latent_mode:
+        bindings.fc1_latent = _make_linear((H, full_hidden), latent_family, g, dev)
+        bindings.fc2_latent = _make_linear((full_hidden, H), "bf16", g, dev)
+    if shared_up_family != "nvfp4":
+        bindings.shared_up_linear = _make_linear((S, full_hidden), shared_up_family, g, dev)
+        bindings.shared_up = None
+    if shared_down_family != "nvfp4":
+        bindings.shared_down_linear = _make_linear((full_hidden, S), shared_down_family, g, dev)
+        bindings.shared_down = None
     return SyntheticLayer(config, bindings, up_p, up_s, up_t, dn_p, dn_s, dn_t)
 
 

@@ -760,6 +760,7 @@ typedef struct {
   int32_t norm_topk_prob;
   float rms_eps;
   float routed_scaling;
+  int32_t latent;  /* moe_latent_size; 0 = hidden (no latent projections) */
 } nmo_layer_config;
 
 typedef struct {
@@ -772,6 +773,17 @@ typedef struct {
   nmo_nvfp4_weight shared_down; /* [H][S] */
   const float* logit_offset;    /* optional [E] added to the FP32 logits (not in the
                                    reference: synthetic skewed-load hook) */
+  /* Dense / scaled-FP8 linears as the FP32 matrices the reference multiplies with
+   * (UploadedLinearOp, linear_op.cpp:274-303; DequantizeScaledFp8WeightToHostFp32,
+   * scaled_fp8_linear.cu:121-139).  NULL = absent.  *_input_scale > 0 selects the
+   * scaled-FP8 family's activation round trip (scaled_fp8_linear.cu:231-236). */
+  const float* fc1;             /* [latent][H] */
+  float fc1_input_scale;
+  const float* fc2;             /* [H][latent] */
+  const float* shared_up_dense; /* [S][H]; replaces shared_up */
+  float shared_up_input_scale;
+  const float* shared_down_dense; /* [H][S]; replaces shared_down */
+  float shared_down_input_scale;
 } nmo_layer_weights;
 
 /* Optional outputs (NULL to skip) and optional device candidates for the
@@ -797,6 +809,11 @@ typedef struct {
   float override_limit;     /* admissible shift of a pre-activation, in noise units */
   nmo_override_stats stats;
   uint8_t* adopted_token;   /* optional [T]: 1 where a code or scale of the token was adopted */
+  float* latent;            /* optional [T][latent]: fc1_latent output */
+  float* routed_latent;     /* optional [T][latent]: routed sum */
+  float* projected;         /* optional [T][H]: fc2_latent of it */
+  float* hid_values;        /* optional [T][k][I]: relu^2(up_proj) before quantisation */
+  float* shid_values;       /* optional [T][S]: the same for the shared expert */
 } nmo_layer_trace;
 
 /* One expert FFN on a single activation row that is ALREADY dequantised:
@@ -823,17 +840,43 @@ static int expert_row(const float* a_deq, size_t H, size_t I, const float* up_t,
   return 0;
 }
 
+/* ScaledFp8LinearOp::Run's activation round trip (scaled_fp8_linear.cu:231-236):
+ * value / scale -> E4M3 satfinite -> decode -> * scale, scale clamped as in :27-33. */
+NMO_EXPORT void nmo_fp8_round_trip(const float* in, size_t count, float input_scale, float* out) {
+  const float scale = clamp_scale(input_scale);
+  for (size_t i = 0; i < count; ++i) {
+    out[i] = nmo_decode_e4m3(nmo_encode_e4m3(in[i] / scale)) * scale;
+  }
+}
+
+/* A dense or scaled-FP8 linear over `rows` rows: DOUBLE accumulation
+ * (linear_op.cpp:97-118, scaled_fp8_linear.cu:40-62). */
+static void dense_linear(const float* in, size_t rows, size_t in_cols, const float* weight,
+                         size_t out_rows, float input_scale, float* out) {
+  if (input_scale > 0.0f) {
+    float* tmp = (float*)malloc(sizeof(float) * rows * in_cols);
+    nmo_fp8_round_trip(in, rows * in_cols, input_scale, tmp);
+    nmo_router_logits(tmp, weight, rows, out_rows, in_cols, out);
+    free(tmp);
+  } else {
+    nmo_router_logits(in, weight, rows, out_rows, in_cols, out);
+  }
+}
+
 /* The whole layer for T tokens of FP32 input, restructured for speed but
  * arithmetically identical per (token, expert) to the reference's loop
- * (expert_layer.cpp:871-1069): identity latent projections, all five expert
- * weight families NVFP4.  Returns 0 on success. */
+ * (expert_layer.cpp:795-1069).  Latent projections fc1 / fc2 dense or scaled
+ * FP8 or absent (identity); routed experts NVFP4 on latent rows; shared_up and
+ * shared_down NVFP4, dense or scaled FP8.  Returns 0 on success. */
 NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_weights* w,
                                  const float* x, int64_t T, float* out,
                                  nmo_layer_trace* trace) {
   const size_t H = (size_t)cfg->hidden, I = (size_t)cfg->routed_intermediate,
                S = (size_t)cfg->shared_intermediate, E = (size_t)cfg->experts,
                K = (size_t)cfg->top_k;
-  if (T <= 0 || H % NMO_BLOCK || I % NMO_BLOCK || S % NMO_BLOCK) return -1;
+  const size_t L = cfg->latent > 0 ? (size_t)cfg->latent : H;
+  if (T <= 0 || H % NMO_BLOCK || I % NMO_BLOCK || S % NMO_BLOCK || L % NMO_BLOCK) return -1;
+  if ((w->fc1 == NULL) != (w->fc2 == NULL) || (w->fc1 == NULL && L != H)) return -1;
   const size_t Tn = (size_t)T;
   int status = 0;
 
@@ -841,11 +884,15 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
   float* logits = (float*)malloc(sizeof(float) * Tn * E);
   int32_t* top_index = (int32_t*)malloc(sizeof(int32_t) * Tn * K);
   float* top_weight = (float*)malloc(sizeof(float) * Tn * K);
-  float* a_deq = (float*)malloc(sizeof(float) * Tn * H);
-  float* routed = (float*)malloc(sizeof(float) * Tn * K * H);
+  float* lat = w->fc1 ? (float*)malloc(sizeof(float) * Tn * L) : y;
+  float* a_deq = (float*)malloc(sizeof(float) * Tn * L);  /* what the routed up_proj sees */
+  float* y_deq = NULL;                                     /* what an NVFP4 shared_up sees */
+  float* routed = (float*)malloc(sizeof(float) * Tn * K * L);
+  float* routed_sum = (float*)malloc(sizeof(float) * Tn * L);
+  float* projected = w->fc2 ? (float*)malloc(sizeof(float) * Tn * H) : routed_sum;
   float* shared = (float*)malloc(sizeof(float) * Tn * H);
-  uint8_t* aq = (uint8_t*)malloc(Tn * H / 2);
-  uint8_t* as = (uint8_t*)malloc(Tn * H / NMO_BLOCK);
+  uint8_t* aq = (uint8_t*)malloc(Tn * L / 2);
+  uint8_t* as = (uint8_t*)malloc(Tn * L / NMO_BLOCK);
   float* ats = (float*)malloc(sizeof(float) * Tn);
 
   /* :795-799 RMSNorm + gate projection */
@@ -854,6 +901,8 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
   if (w->logit_offset != NULL) {
     for (size_t i = 0; i < Tn * E; ++i) logits[i] = logits[i] + w->logit_offset[i % E];
   }
+  /* :809-813 latent = fc1_latent(normalized) */
+  if (w->fc1) dense_linear(y, Tn, H, w->fc1, L, w->fc1_input_scale, lat);
 
   /* :881 top-k per token; :913 activation pack per row (rows == 1) */
 #pragma omp parallel for schedule(static)
@@ -866,14 +915,28 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
 #pragma omp atomic write
       status = -2;
     }
-    if (nmo_pack_nvfp4(y + t * H, 1, H, 0.0f, aq + t * H / 2, as + t * H / NMO_BLOCK,
+    if (nmo_pack_nvfp4(lat + t * L, 1, L, 0.0f, aq + t * L / 2, as + t * L / NMO_BLOCK,
                        ats + t) != 0) {
 #pragma omp atomic write
       status = -3;
     }
-    nmo_dequant_nvfp4(aq + t * H / 2, as + t * H / NMO_BLOCK, ats[t], 1, H, a_deq + t * H);
+    nmo_dequant_nvfp4(aq + t * L / 2, as + t * L / NMO_BLOCK, ats[t], 1, L, a_deq + t * L);
   }
   if (status != 0) goto done;
+  if (w->fc1 && w->shared_up_dense == NULL) {
+    /* an NVFP4 shared_up packs the normalised hidden row itself */
+    y_deq = (float*)malloc(sizeof(float) * Tn * H);
+#pragma omp parallel for schedule(static)
+    for (size_t t = 0; t < Tn; ++t) {
+      uint8_t* q = (uint8_t*)malloc(H / 2);
+      uint8_t* sc = (uint8_t*)malloc(H / NMO_BLOCK);
+      float ts = 1.0f;
+      nmo_pack_nvfp4(y + t * H, 1, H, 0.0f, q, sc, &ts);
+      nmo_dequant_nvfp4(q, sc, ts, 1, H, y_deq + t * H);
+      free(q);
+      free(sc);
+    }
+  }
 
   /* bucket (token, slot) pairs by expert */
   {
@@ -892,8 +955,8 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
     if (trace && trace->adopted_token) memset(trace->adopted_token, 0, Tn);
 #pragma omp parallel
     {
-      float* up_t = (float*)malloc(sizeof(float) * H * I);
-      float* down_t = (float*)malloc(sizeof(float) * H * I);
+      float* up_t = (float*)malloc(sizeof(float) * L * I);
+      float* down_t = (float*)malloc(sizeof(float) * L * I);
       float* u = (float*)malloc(sizeof(float) * I);
       float* h = (float*)malloc(sizeof(float) * I);
       float* hd = (float*)malloc(sizeof(float) * I);
@@ -904,9 +967,9 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
       for (size_t e = 0; e < E; ++e) {
         if (count[e] == 0) continue;
         dequant_weight_transposed(w->up[e].packed, w->up[e].scales, w->up[e].tensor_scale,
-                                  I, H, up_t);
+                                  I, L, up_t);
         dequant_weight_transposed(w->down[e].packed, w->down[e].scales,
-                                  w->down[e].tensor_scale, H, I, down_t);
+                                  w->down[e].tensor_scale, L, I, down_t);
         for (size_t j = 0; j < count[e]; ++j) {
           const size_t p = pairs[start[e] + j];
           const size_t t = p / K;
@@ -917,9 +980,9 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
             cs = trace->cand_hid_scales + p * (I / NMO_BLOCK);
           }
           int adopted = 0;
-          if (expert_row(a_deq + t * H, H, I, up_t, down_t, u, h, hd, hq, hs, cq, cs,
+          if (expert_row(a_deq + t * L, L, I, up_t, down_t, u, h, hd, hq, hs, cq, cs,
                          trace ? trace->override_limit : 0.0f, &local, &adopted,
-                         routed + p * H) != 0) {
+                         routed + p * L) != 0) {
 #pragma omp atomic write
             status = -4;
           }
@@ -930,6 +993,7 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
           if (trace && trace->hid_packed) memcpy(trace->hid_packed + p * (I / 2), hq, I / 2);
           if (trace && trace->hid_scales)
             memcpy(trace->hid_scales + p * (I / NMO_BLOCK), hs, I / NMO_BLOCK);
+          if (trace && trace->hid_values) memcpy(trace->hid_values + p * I, h, sizeof(float) * I);
         }
       }
       free(up_t);
@@ -943,8 +1007,9 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
       merge_override_stats(&total, &local);
     }
 
-    /* shared expert, one "expert" over all tokens */
-    {
+    /* shared expert, one "expert" over all tokens (:814-818, :956-964, :981-1045) */
+    if (w->shared_up_dense == NULL && w->shared_down_dense == NULL) {
+      const float* shared_in = y_deq ? y_deq : a_deq;
       float* up_t = (float*)malloc(sizeof(float) * H * S);
       float* down_t = (float*)malloc(sizeof(float) * H * S);
       dequant_weight_transposed(w->shared_up.packed, w->shared_up.scales,
@@ -968,7 +1033,7 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
             cs = trace->cand_shid_scales + t * (S / NMO_BLOCK);
           }
           int adopted = 0;
-          if (expert_row(a_deq + t * H, H, S, up_t, down_t, u, h, hd, hq, hs, cq, cs,
+          if (expert_row(shared_in + t * H, H, S, up_t, down_t, u, h, hd, hq, hs, cq, cs,
                          trace ? trace->override_limit : 0.0f, &local, &adopted,
                          shared + t * H) != 0) {
 #pragma omp atomic write
@@ -981,6 +1046,7 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
           if (trace && trace->shid_packed) memcpy(trace->shid_packed + t * (S / 2), hq, S / 2);
           if (trace && trace->shid_scales)
             memcpy(trace->shid_scales + t * (S / NMO_BLOCK), hs, S / NMO_BLOCK);
+          if (trace && trace->shid_values) memcpy(trace->shid_values + t * S, h, sizeof(float) * S);
         }
         free(u);
         free(h);
@@ -992,6 +1058,52 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
       }
       free(up_t);
       free(down_t);
+    } else {
+      /* dense / scaled-FP8 shared_up (:814-818) and relu^2 (:956-964); an NVFP4
+       * shared_up beside a dense shared_down goes through the host linear too */
+      float* su = (float*)malloc(sizeof(float) * Tn * S);
+      if (w->shared_up_dense) {
+        dense_linear(y, Tn, H, w->shared_up_dense, S, w->shared_up_input_scale, su);
+      } else {
+        const float* shared_in = y_deq ? y_deq : a_deq;
+        float* up_t = (float*)malloc(sizeof(float) * H * S);
+        dequant_weight_transposed(w->shared_up.packed, w->shared_up.scales,
+                                  w->shared_up.tensor_scale, S, H, up_t);
+#pragma omp parallel for schedule(static)
+        for (size_t t = 0; t < Tn; ++t) matvec_transposed(shared_in + t * H, up_t, S, H, su + t * S);
+        free(up_t);
+      }
+      for (size_t i = 0; i < Tn * S; ++i) su[i] = relu2(su[i]);
+      if (trace && trace->shid_values) memcpy(trace->shid_values, su, sizeof(float) * Tn * S);
+      if (w->shared_down_dense) {
+        dense_linear(su, Tn, S, w->shared_down_dense, H, w->shared_down_input_scale, shared);
+      } else {
+        /* NVFP4 shared_down through RunNvfp4LinearHost per row (:981-1005) */
+        float* down_t = (float*)malloc(sizeof(float) * H * S);
+        dequant_weight_transposed(w->shared_down.packed, w->shared_down.scales,
+                                  w->shared_down.tensor_scale, H, S, down_t);
+#pragma omp parallel
+        {
+          float* hd = (float*)malloc(sizeof(float) * S);
+          uint8_t* hq = (uint8_t*)malloc(S / 2);
+          uint8_t* hs = (uint8_t*)malloc(S / NMO_BLOCK);
+#pragma omp for schedule(dynamic, 4)
+          for (size_t t = 0; t < Tn; ++t) {
+            float ts = 1.0f;
+            nmo_pack_nvfp4(su + t * S, 1, S, 0.0f, hq, hs, &ts);
+            nmo_dequant_nvfp4(hq, hs, ts, 1, S, hd);
+            matvec_transposed(hd, down_t, H, S, shared + t * H);
+            if (trace && trace->shid_packed) memcpy(trace->shid_packed + t * (S / 2), hq, S / 2);
+            if (trace && trace->shid_scales)
+              memcpy(trace->shid_scales + t * (S / NMO_BLOCK), hs, S / NMO_BLOCK);
+          }
+          free(hd);
+          free(hq);
+          free(hs);
+        }
+        free(down_t);
+      }
+      free(su);
     }
     if (trace) trace->stats = total;
     free(count);
@@ -999,16 +1111,23 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
     free(pairs);
   }
 
-  /* :951-953 weighted accumulate in selection order; :1064-1069 mixer and
-   * residual.  The identity fc2_latent projection returns `routed` exactly. */
+  /* :951-953 weighted accumulate in selection order */
+#pragma omp parallel for schedule(static)
+  for (size_t t = 0; t < Tn; ++t) {
+    for (size_t i = 0; i < L; ++i) {
+      float acc = 0.0f;
+      for (size_t k = 0; k < K; ++k) {
+        acc += routed[(t * K + k) * L + i] * top_weight[t * K + k];
+      }
+      routed_sum[t * L + i] = acc;
+    }
+  }
+  /* :1047-1053 fc2_latent; :1064-1069 mixer and residual */
+  if (w->fc2) dense_linear(routed_sum, Tn, L, w->fc2, H, 0.0f, projected);
 #pragma omp parallel for schedule(static)
   for (size_t t = 0; t < Tn; ++t) {
     for (size_t i = 0; i < H; ++i) {
-      float acc = 0.0f;
-      for (size_t k = 0; k < K; ++k) {
-        acc += routed[(t * K + k) * H + i] * top_weight[t * K + k];
-      }
-      const float mixer = acc + shared[t * H + i];
+      const float mixer = projected[t * H + i] + shared[t * H + i];
       out[t * H + i] = x[t * H + i] + mixer;
     }
   }
@@ -1018,11 +1137,14 @@ NMO_EXPORT int nmo_layer_forward(const nmo_layer_config* cfg, const nmo_layer_we
     if (trace->logits) memcpy(trace->logits, logits, sizeof(float) * Tn * E);
     if (trace->top_index) memcpy(trace->top_index, top_index, sizeof(int32_t) * Tn * K);
     if (trace->top_weight) memcpy(trace->top_weight, top_weight, sizeof(float) * Tn * K);
-    if (trace->act_packed) memcpy(trace->act_packed, aq, Tn * H / 2);
-    if (trace->act_scales) memcpy(trace->act_scales, as, Tn * H / NMO_BLOCK);
+    if (trace->act_packed) memcpy(trace->act_packed, aq, Tn * L / 2);
+    if (trace->act_scales) memcpy(trace->act_scales, as, Tn * L / NMO_BLOCK);
     if (trace->act_tensor_scale) memcpy(trace->act_tensor_scale, ats, sizeof(float) * Tn);
-    if (trace->routed_out) memcpy(trace->routed_out, routed, sizeof(float) * Tn * K * H);
+    if (trace->routed_out) memcpy(trace->routed_out, routed, sizeof(float) * Tn * K * L);
     if (trace->shared_out) memcpy(trace->shared_out, shared, sizeof(float) * Tn * H);
+    if (trace->latent) memcpy(trace->latent, lat, sizeof(float) * Tn * L);
+    if (trace->routed_latent) memcpy(trace->routed_latent, routed_sum, sizeof(float) * Tn * L);
+    if (trace->projected) memcpy(trace->projected, projected, sizeof(float) * Tn * H);
   }
 
 done:
@@ -1030,8 +1152,12 @@ done:
   free(logits);
   free(top_index);
   free(top_weight);
+  if (w->fc1) free(lat);
   free(a_deq);
+  free(y_deq);
   free(routed);
+  free(routed_sum);
+  if (w->fc2) free(projected);
   free(shared);
   free(aq);
   free(as);

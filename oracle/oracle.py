@@ -32,14 +32,18 @@ class _LayerConfig(ctypes.Structure):
                 ("shared_intermediate", ctypes.c_int32), ("experts", ctypes.c_int32),
                 ("top_k", ctypes.c_int32), ("n_group", ctypes.c_int32),
                 ("topk_group", ctypes.c_int32), ("norm_topk_prob", ctypes.c_int32),
-                ("rms_eps", ctypes.c_float), ("routed_scaling", ctypes.c_float)]
+                ("rms_eps", ctypes.c_float), ("routed_scaling", ctypes.c_float),
+                ("latent", ctypes.c_int32)]
 
 
 class _LayerWeights(ctypes.Structure):
     _fields_ = [("norm_weight", _f32p), ("gate", _f32p), ("bias", _f32p),
                 ("up", ctypes.POINTER(_Nvfp4Weight)), ("down", ctypes.POINTER(_Nvfp4Weight)),
                 ("shared_up", _Nvfp4Weight), ("shared_down", _Nvfp4Weight),
-                ("logit_offset", _f32p)]
+                ("logit_offset", _f32p),
+                ("fc1", _f32p), ("fc1_input_scale", ctypes.c_float), ("fc2", _f32p),
+                ("shared_up_dense", _f32p), ("shared_up_input_scale", ctypes.c_float),
+                ("shared_down_dense", _f32p), ("shared_down_input_scale", ctypes.c_float)]
 
 
 class _OverrideStats(ctypes.Structure):
@@ -56,7 +60,8 @@ class _LayerTrace(ctypes.Structure):
                 ("shared_out", _f32p), ("cand_hid_packed", _u8p), ("cand_hid_scales", _u8p),
                 ("cand_shid_packed", _u8p), ("cand_shid_scales", _u8p),
                 ("override_limit", ctypes.c_float), ("stats", _OverrideStats),
-                ("adopted_token", _u8p)]
+                ("adopted_token", _u8p), ("latent", _f32p), ("routed_latent", _f32p),
+                ("projected", _f32p), ("hid_values", _f32p), ("shid_values", _f32p)]
 
 
 _lib = None
@@ -286,9 +291,18 @@ class LayerWeights:
     bias: np.ndarray                 # [E]
     up: List[Nvfp4Weight]
     down: List[Nvfp4Weight]
-    shared_up: Nvfp4Weight
-    shared_down: Nvfp4Weight
+    shared_up: Optional[Nvfp4Weight]
+    shared_down: Optional[Nvfp4Weight]
     logit_offset: Optional[np.ndarray] = None
+    # dense / scaled-FP8 linears as the FP32 matrices the reference multiplies with; an
+    # input scale > 0 selects the scaled-FP8 family's activation round trip
+    fc1: Optional[np.ndarray] = None               # [latent, H]
+    fc1_input_scale: float = 0.0
+    fc2: Optional[np.ndarray] = None               # [H, latent]
+    shared_up_dense: Optional[np.ndarray] = None   # [S, H]
+    shared_up_input_scale: float = 0.0
+    shared_down_dense: Optional[np.ndarray] = None  # [H, S]
+    shared_down_input_scale: float = 0.0
 
 
 @dataclass
@@ -303,6 +317,7 @@ class LayerConfig:
     norm_topk_prob: bool = True
     rms_eps: float = 1e-5
     routed_scaling: float = 1.0
+    latent: int = 0   # moe_latent_size; 0 = hidden (no latent projections)
 
 
 def _cw(w: Nvfp4Weight, keep: list) -> _Nvfp4Weight:
@@ -314,7 +329,7 @@ def _cw(w: Nvfp4Weight, keep: list) -> _Nvfp4Weight:
 def _c_args(cfg: LayerConfig, w: LayerWeights, keep: list):
     c = _LayerConfig(cfg.hidden, cfg.routed_intermediate, cfg.shared_intermediate, cfg.experts,
                      cfg.top_k, cfg.n_group, cfg.topk_group, 1 if cfg.norm_topk_prob else 0,
-                     cfg.rms_eps, cfg.routed_scaling)
+                     cfg.rms_eps, cfg.routed_scaling, cfg.latent)
     ups = (_Nvfp4Weight * cfg.experts)(*[_cw(x, keep) for x in w.up])
     downs = (_Nvfp4Weight * cfg.experts)(*[_cw(x, keep) for x in w.down])
     norm, gate, bias = _f32(w.norm_weight), _f32(w.gate), _f32(w.bias)
@@ -325,8 +340,19 @@ def _c_args(cfg: LayerConfig, w: LayerWeights, keep: list):
     cw.bias = _p(bias, _f32p)
     cw.up = ups
     cw.down = downs
-    cw.shared_up = _cw(w.shared_up, keep)
-    cw.shared_down = _cw(w.shared_down, keep)
+    if w.shared_up is not None:
+        cw.shared_up = _cw(w.shared_up, keep)
+    if w.shared_down is not None:
+        cw.shared_down = _cw(w.shared_down, keep)
+    for name in ("fc1", "fc2", "shared_up_dense", "shared_down_dense"):
+        matrix = getattr(w, name)
+        if matrix is not None:
+            matrix = _f32(matrix)
+            keep.append(matrix)
+            setattr(cw, name, _p(matrix, _f32p))
+    cw.fc1_input_scale = w.fc1_input_scale
+    cw.shared_up_input_scale = w.shared_up_input_scale
+    cw.shared_down_input_scale = w.shared_down_input_scale
     if w.logit_offset is not None:
         off = _f32(w.logit_offset)
         keep.append(off)
@@ -357,6 +383,11 @@ class LayerResult:
     max_noise_units: float = 0.0       # largest adopted pre-activation shift, in noise units
     max_rel_shift: float = 0.0         # the same shift relative to the pre-activation
     adopted_token: Optional[np.ndarray] = None  # [T] bool: the token owns an adopted byte
+    latent: Optional[np.ndarray] = None         # [T, latent] fc1_latent output
+    routed_latent: Optional[np.ndarray] = None  # [T, latent] routed sum
+    projected: Optional[np.ndarray] = None      # [T, H] fc2_latent of it
+    hid_values: Optional[np.ndarray] = None     # [T, k, I] relu^2(up_proj) before quantisation
+    shid_values: Optional[np.ndarray] = None    # [T, S]
 
 
 DEFAULT_OVERRIDE_LIMIT = 6.0
@@ -374,18 +405,20 @@ def layer_forward(cfg: LayerConfig, w: LayerWeights, x, candidates=None,
     T = x.shape[0]
     H, I, S, E, K = (cfg.hidden, cfg.routed_intermediate, cfg.shared_intermediate, cfg.experts,
                      cfg.top_k)
+    L = cfg.latent or H
     keep: list = []
     c, cw = _c_args(cfg, w, keep)
     out = np.zeros((T, H), dtype=np.float32)
     r = LayerResult(
         out=out, normalized=np.zeros((T, H), np.float32), logits=np.zeros((T, E), np.float32),
         top_index=np.zeros((T, K), np.int32), top_weight=np.zeros((T, K), np.float32),
-        act_packed=np.zeros((T, H // 2), np.uint8), act_scales=np.zeros((T, H // 16), np.uint8),
+        act_packed=np.zeros((T, L // 2), np.uint8), act_scales=np.zeros((T, L // 16), np.uint8),
         act_tensor_scale=np.zeros((T,), np.float32),
         hid_packed=np.zeros((T, K, I // 2), np.uint8), hid_scales=np.zeros((T, K, I // 16), np.uint8),
         shid_packed=np.zeros((T, S // 2), np.uint8), shid_scales=np.zeros((T, S // 16), np.uint8),
-        routed_out=np.zeros((T, K, H), np.float32) if want_routed_out else None,
-        shared_out=np.zeros((T, H), np.float32))
+        routed_out=np.zeros((T, K, L), np.float32) if want_routed_out else None,
+        shared_out=np.zeros((T, H), np.float32), latent=np.zeros((T, L), np.float32),
+        routed_latent=np.zeros((T, L), np.float32), projected=np.zeros((T, H), np.float32))
     tr = _LayerTrace()
     tr.normalized = _p(r.normalized, _f32p)
     tr.logits = _p(r.logits, _f32p)
@@ -401,6 +434,14 @@ def layer_forward(cfg: LayerConfig, w: LayerWeights, x, candidates=None,
     if want_routed_out:
         tr.routed_out = _p(r.routed_out, _f32p)
     tr.shared_out = _p(r.shared_out, _f32p)
+    tr.latent = _p(r.latent, _f32p)
+    tr.routed_latent = _p(r.routed_latent, _f32p)
+    tr.projected = _p(r.projected, _f32p)
+    if want_routed_out:
+        r.hid_values = np.zeros((T, K, I), np.float32)
+        r.shid_values = np.zeros((T, S), np.float32)
+        tr.hid_values = _p(r.hid_values, _f32p)
+        tr.shid_values = _p(r.shid_values, _f32p)
     tr.override_limit = override_limit
     adopted_token = np.zeros((T,), np.uint8)
     tr.adopted_token = _p(adopted_token, _u8p)
@@ -423,6 +464,22 @@ def layer_forward(cfg: LayerConfig, w: LayerWeights, x, candidates=None,
     r.max_rel_shift = tr.stats.max_rel_shift
     r.adopted_token = adopted_token.astype(bool)
     return r
+
+
+def fp8_round_trip(x, input_scale: float) -> np.ndarray:
+    """The scaled-FP8 family's activation round trip (scaled_fp8_linear.cu:231-236)."""
+    x = _f32(x)
+    out = np.zeros_like(x)
+    L = lib()
+    L.nmo_fp8_round_trip.argtypes = [_f32p, ctypes.c_size_t, ctypes.c_float, _f32p]
+    L.nmo_fp8_round_trip.restype = None
+    L.nmo_fp8_round_trip(_p(x, _f32p), x.size, ctypes.c_float(input_scale), _p(out, _f32p))
+    return out
+
+
+def decode_e4m3_array(codes) -> np.ndarray:
+    """E4M3 bytes -> FP32 values (DecodeFp8, scaled_fp8_linear.cu:35-39)."""
+    return decode_e4m3_table()[np.asarray(codes, dtype=np.uint8)]
 
 
 def layer_forward_literal(cfg: LayerConfig, w: LayerWeights, x) -> np.ndarray:

@@ -191,6 +191,25 @@ int main(int argc, char** argv) {
     std::fwrite(&index, sizeof(index), 1, out);
     std::fwrite(&s.weight, sizeof(float), 1, out);
   }
+  if (T == 1) {
+    // every vector of ExpertLayerRunTrace (expert_layer.h:63-76): int64 length, then values
+    const std::vector<float>* fields[10] = {
+        &trace.normalized_input, &trace.router_logits, &trace.latent_output,
+        &trace.routed_latent_output, &trace.routed_expert_activated_hidden,
+        &trace.routed_expert_outputs, &trace.routed_expert_weighted_contributions,
+        &trace.projected_routed_output, &trace.shared_output, &trace.mixer_output};
+    for (const std::vector<float>* field : fields) {
+      const std::int64_t n = static_cast<std::int64_t>(field->size());
+      std::fwrite(&n, sizeof(n), 1, out);
+      std::fwrite(field->data(), sizeof(float), field->size(), out);
+    }
+    const std::int64_t n = static_cast<std::int64_t>(trace.routed_expert_order.size());
+    std::fwrite(&n, sizeof(n), 1, out);
+    for (std::size_t e : trace.routed_expert_order) {
+      const std::int64_t index = static_cast<std::int64_t>(e);
+      std::fwrite(&index, sizeof(index), 1, out);
+    }
+  }
   std::fclose(out);
   return 0;
 }

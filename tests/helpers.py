@@ -28,7 +28,8 @@ def oracle_config(cfg):
         shared_intermediate=cfg.shared_expert_intermediate_size, experts=cfg.n_routed_experts,
         top_k=cfg.top_k, n_group=cfg.n_group, topk_group=cfg.topk_group,
         norm_topk_prob=cfg.norm_topk_prob, rms_eps=cfg.rms_epsilon,
-        routed_scaling=cfg.routed_scaling_factor)
+        routed_scaling=cfg.routed_scaling_factor,
+        latent=0 if cfg.moe_latent_size == cfg.hidden_size else cfg.moe_latent_size)
 
 
 def _np(t: torch.Tensor) -> np.ndarray:
@@ -37,9 +38,25 @@ def _np(t: torch.Tensor) -> np.ndarray:
     return t.detach().cpu().numpy()
 
 
+def _dense_matrix(linear):
+    """(FP32 matrix the reference multiplies with, input scale or 0) of a DenseLinear."""
+    if linear is None:
+        return None, 0.0
+    oracle = entry.load_oracle()
+    if linear.is_fp8:
+        # DecodeFp8(byte) * weight_scale in FP32 (scaled_fp8_linear.cu:121-139)
+        values = oracle.decode_e4m3_array(_np(linear.weight)) * np.float32(linear.weight_scale)
+        return values.astype(np.float32), float(linear.input_scale)
+    return _np(linear.weight).astype(np.float32), 0.0
+
+
 def oracle_weights(layer_data):
     oracle = entry.load_oracle()
     b = layer_data.bindings
+    fc1, fc1_scale = _dense_matrix(b.fc1_latent)
+    fc2, _ = _dense_matrix(b.fc2_latent)
+    sup, sup_scale = _dense_matrix(b.shared_up_linear)
+    sdown, sdown_scale = _dense_matrix(b.shared_down_linear)
     up_p, up_s, up_t = _np(layer_data.up_packed), _np(layer_data.up_scales), _np(layer_data.up_ts)
     dn_p, dn_s, dn_t = (_np(layer_data.down_packed), _np(layer_data.down_scales),
                         _np(layer_data.down_ts))
@@ -49,11 +66,15 @@ def oracle_weights(layer_data):
         bias=_np(b.gate_score_correction_bias),
         up=[oracle.Nvfp4Weight(up_p[e], up_s[e], float(up_t[e])) for e in range(E)],
         down=[oracle.Nvfp4Weight(dn_p[e], dn_s[e], float(dn_t[e])) for e in range(E)],
-        shared_up=oracle.Nvfp4Weight(_np(b.shared_up.packed), _np(b.shared_up.block_scales),
-                                     b.shared_up.tensor_scale),
-        shared_down=oracle.Nvfp4Weight(_np(b.shared_down.packed), _np(b.shared_down.block_scales),
-                                       b.shared_down.tensor_scale),
-        logit_offset=None if b.gate_logit_offset is None else _np(b.gate_logit_offset))
+        shared_up=None if b.shared_up is None else oracle.Nvfp4Weight(
+            _np(b.shared_up.packed), _np(b.shared_up.block_scales), b.shared_up.tensor_scale),
+        shared_down=None if b.shared_down is None else oracle.Nvfp4Weight(
+            _np(b.shared_down.packed), _np(b.shared_down.block_scales),
+            b.shared_down.tensor_scale),
+        logit_offset=None if b.gate_logit_offset is None else _np(b.gate_logit_offset),
+        fc1=fc1, fc1_input_scale=fc1_scale, fc2=fc2, shared_up_dense=sup,
+        shared_up_input_scale=sup_scale, shared_down_dense=sdown,
+        shared_down_input_scale=sdown_scale)
 
 
 def max_abs_and_cosine(a: np.ndarray, b: np.ndarray):
@@ -75,6 +96,7 @@ class ParityReport:
     index_order_mismatches: int = 0
     min_margin: float = 0.0
     norm_max_diff: float = 0.0
+    latent_max_diff: float = 0.0   # fc1_latent output (0 when the layer has no projection)
     logits_max_diff: float = 0.0
     weight_max_diff: float = 0.0
     act_code_mismatches: int = 0
@@ -101,7 +123,7 @@ class ParityReport:
     def ok(self) -> bool:
         exact = (self.index_set_mismatches == 0 and self.act_code_mismatches == 0 and
                  self.act_scale_mismatches == 0 and self.inadmissible_codes == 0 and
-                 self.inadmissible_scales == 0)
+                 self.inadmissible_scales == 0 and self.latent_max_diff == 0.0)
         if self.out_is_bf16:
             close = self.bf16_excess <= MAX_ABS_TOL
         else:
@@ -130,7 +152,8 @@ class ParityReport:
                 f"raw_tokens_over_tol={self.raw_tokens_over_tol} "
                 f"(without a tie: {self.raw_tokens_over_tol_without_tie}) "
                 f"max_abs={self.max_abs:.3g} cos={self.cosine:.6f} "
-                f"norm_diff={self.norm_max_diff:.3g} logits_diff={self.logits_max_diff:.3g} "
+                f"norm_diff={self.norm_max_diff:.3g} latent_diff={self.latent_max_diff:.3g} "
+                f"logits_diff={self.logits_max_diff:.3g} "
                 f"weight_diff={self.weight_max_diff:.3g}"
                 + (f" bf16_excess={self.bf16_excess:.3g}" if self.out_is_bf16 else ""))
 
@@ -156,6 +179,9 @@ def compare_layer_with_oracle(layer, layer_data, x: torch.Tensor, out: torch.Ten
     rep = ParityReport(tokens=T, out_is_bf16=out.dtype == torch.bfloat16)
     cands = (_np(trace.routed_hidden_packed), _np(trace.routed_hidden_scales),
              _np(trace.shared_hidden_packed), _np(trace.shared_hidden_scales))
+    b = layer_data.bindings
+    shared_up_dense = b.shared_up_linear is not None
+    shared_down_dense = b.shared_down_linear is not None
     forced = oracle.layer_forward(ocfg, ow, x_np, candidates=cands,
                                   override_limit=OVERRIDE_LIMIT)
     raw = oracle.layer_forward(ocfg, ow, x_np) if raw_run else forced
@@ -170,14 +196,25 @@ def compare_layer_with_oracle(layer, layer_data, x: torch.Tensor, out: torch.Ten
     rep.weight_max_diff = float(np.max(np.abs(_np(trace.selected_weight) - raw.top_weight)))
     rep.act_code_mismatches = nibble_mismatches(_np(trace.act_packed), raw.act_packed)
     rep.act_scale_mismatches = int(np.count_nonzero(_np(trace.act_scales) != raw.act_scales))
-    rep.hidden_code_mismatches = (nibble_mismatches(cands[0], raw.hid_packed) +
-                                  nibble_mismatches(cands[2], raw.shid_packed))
-    rep.hidden_scale_mismatches = int(np.count_nonzero(cands[1] != raw.hid_scales) +
-                                      np.count_nonzero(cands[3] != raw.shid_scales))
-    rep.hidden_codes_total = int(cands[0].size * 2 + cands[2].size * 2)
+    if trace.latent_output is not None:
+        rep.latent_max_diff = float(np.max(np.abs(_np(trace.latent_output) - raw.latent)))
+    rep.hidden_code_mismatches = nibble_mismatches(cands[0], raw.hid_packed)
+    rep.hidden_scale_mismatches = int(np.count_nonzero(cands[1] != raw.hid_scales))
+    rep.hidden_codes_total = int(cands[0].size * 2)
     rep.adopted_codes, rep.adopted_scales = forced.adopted_codes, forced.adopted_scales
     rep.inadmissible_codes = forced.inadmissible_codes
     rep.inadmissible_scales = forced.inadmissible_scales
+    if not shared_down_dense:
+        # the quantised relu^2 rows of the shared expert; behind a dense or scaled-FP8
+        # shared_up both sides accumulate in FP64, so there are no ties to adopt there
+        shared_codes = nibble_mismatches(cands[2], raw.shid_packed)
+        shared_scales = int(np.count_nonzero(cands[3] != raw.shid_scales))
+        rep.hidden_code_mismatches += shared_codes
+        rep.hidden_scale_mismatches += shared_scales
+        rep.hidden_codes_total += int(cands[2].size * 2)
+        if shared_up_dense:
+            rep.inadmissible_codes += shared_codes
+            rep.inadmissible_scales += shared_scales
     rep.max_noise_units, rep.max_rel_shift = forced.max_noise_units, forced.max_rel_shift
     rep.raw_max_abs, rep.raw_cosine = max_abs_and_cosine(out_np, raw.out)
     rep.max_abs, rep.cosine = max_abs_and_cosine(out_np, forced.out)

@@ -26,7 +26,10 @@ def _nvfp4(m) -> bytes:
 
 
 @pytest.mark.parametrize("tokens", [1, 37])
-def test_reference_typed_cpp_caller_gets_the_same_rows(package, synthetic, tmp_path, tokens):
+def test_reference_typed_cpp_caller_gets_the_same_rows(package, synthetic, oracle, tmp_path,
+                                                       tokens, monkeypatch):
+    import helpers
+    monkeypatch.setenv("NMOE_SHIM_MAX_TOKENS", "8")  # 37 tokens make the scratch grow
     if not os.path.exists(DRIVER):
         pytest.skip("oracle/_ref/shim_driver was not built (needs the reference checkout)")
     experts, hidden, routed, shared = 32, 512, 256, 512
@@ -48,7 +51,8 @@ def test_reference_typed_cpp_caller_gets_the_same_rows(package, synthetic, tmp_p
     blob += _bytes(x)
     src, dst = tmp_path / "layer.bin", tmp_path / "rows.bin"
     src.write_bytes(blob)
-    done = subprocess.run([DRIVER, str(src), str(dst)], capture_output=True, text=True, timeout=300)
+    done = subprocess.run([DRIVER, str(src), str(dst)], capture_output=True, text=True,
+                          timeout=300, env=dict(os.environ))
     assert done.returncode == 0, done.stderr
 
     raw = dst.read_bytes()
@@ -72,6 +76,38 @@ def test_reference_typed_cpp_caller_gets_the_same_rows(package, synthetic, tmp_p
             at += 12
             assert index == int(trace.selected_index[0, slot])
             assert weight == float(trace.selected_weight[0, slot])
+        # every vector of the trace against the CPU oracle, at the tolerances of the
+        # reference's own layer test (testing/backend/expert_layer_oracle_test.cpp:1061-1077)
+        names = ("normalized_input", "router_logits", "latent_output", "routed_latent_output",
+                 "routed_expert_activated_hidden", "routed_expert_outputs",
+                 "routed_expert_weighted_contributions", "projected_routed_output",
+                 "shared_output", "mixer_output")
+        fields = {}
+        for name in names:
+            (n,) = struct.unpack("<q", raw[at:at + 8])
+            fields[name] = np.frombuffer(raw, dtype=np.float32, count=n, offset=at + 8)
+            at += 8 + 4 * n
+        (n,) = struct.unpack("<q", raw[at:at + 8])
+        order = np.frombuffer(raw, dtype=np.int64, count=n, offset=at + 8)
+        ref = oracle.layer_forward(helpers.oracle_config(cfg), helpers.oracle_weights(data),
+                                   x.cpu().numpy(), want_routed_out=True)
+        K = cfg.top_k
+        assert list(order) == list(ref.top_index[0])
+        weighted = ref.routed_out[0] * ref.top_weight[0][:, None]
+        expect = {
+            "normalized_input": (ref.normalized[0], 1e-5), "router_logits": (ref.logits[0], 2e-5),
+            "latent_output": (ref.normalized[0], 1e-5),
+            "routed_latent_output": (ref.routed_latent[0], 1e-3),
+            "routed_expert_activated_hidden": (ref.hid_values[0].ravel(), 1e-3),
+            "routed_expert_outputs": (ref.routed_out[0].ravel(), 1e-3),
+            "routed_expert_weighted_contributions": (weighted.ravel(), 1e-3),
+            "projected_routed_output": (ref.projected[0], 1e-3),
+            "shared_output": (ref.shared_out[0], 1e-3),
+            "mixer_output": (ref.projected[0] + ref.shared_out[0], 1e-3)}
+        for name, (want_values, tol) in expect.items():
+            assert fields[name].shape == want_values.shape, name
+            assert np.abs(fields[name] - want_values).max() <= tol, name
+        assert K * hidden == fields["routed_expert_outputs"].size
     else:
         assert selected == 0
     layer.close()

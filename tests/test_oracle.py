@@ -186,3 +186,62 @@ def test_router_near_tie_margin_is_reported(oracle):
     assert oracle.selection_margins(logits, bias, 6)[0] == 0.0
     idx, _ = oracle.select_top_experts(logits, bias, 6)
     assert list(idx[0]) == [0, 1, 2, 3, 4, 5]  # ties resolve to the lower index
+
+
+def test_identity_latent_projections_change_nothing(oracle, synthetic):
+    """fc1_latent = fc2_latent = identity: the double-accumulated dense linear returns its
+    input bit for bit, so the layer equals the one without projections (how the literal
+    reference, which insists on the projections, is driven at the benchmark shapes)."""
+    import helpers
+    cfg, data = _tiny_layer(synthetic)
+    x = synthetic.make_tokens(5, cfg.hidden_size, seed=2).to(torch.float32).numpy()
+    ocfg, ow = helpers.oracle_config(cfg), helpers.oracle_weights(data)
+    base = oracle.layer_forward(ocfg, ow, x)
+    ow.fc1 = np.eye(cfg.hidden_size, dtype=np.float32)
+    ow.fc2 = np.eye(cfg.hidden_size, dtype=np.float32)
+    same = oracle.layer_forward(ocfg, ow, x)
+    assert np.array_equal(same.out, base.out)
+    assert np.array_equal(same.latent, base.normalized)
+    assert np.array_equal(same.projected, same.routed_latent)
+
+
+def test_latent_layer_composes_the_documented_steps(oracle, synthetic):
+    """The latent data flow restated with the oracle's own unit operators: fc1 (scaled FP8),
+    routed sum, fc2, mixer, residual (expert_layer.cpp:809-813, :951-953, :1047-1069)."""
+    import helpers
+    cfg = synthetic.baseline_config(64, experts=32, hidden=128, routed=64, shared=128, top_k=4,
+                                    latent=64)
+    data = synthetic.make_layer(cfg, seed=8, device="cpu", norm_weight_uniform=True,
+                                latent_family="fp8", shared_up_family="bf16",
+                                shared_down_family="fp8")
+    x = synthetic.make_tokens(6, cfg.hidden_size, seed=4).to(torch.float32).numpy()
+    ocfg, ow = helpers.oracle_config(cfg), helpers.oracle_weights(data)
+    r = oracle.layer_forward(ocfg, ow, x, want_routed_out=True)
+    y = oracle.rmsnorm(x, ow.norm_weight, cfg.rms_epsilon)
+    latent = oracle.router_logits(oracle.fp8_round_trip(y, ow.fc1_input_scale), ow.fc1)
+    assert np.array_equal(r.latent, latent)
+    p, s, ts = oracle.pack_nvfp4_per_row(latent)
+    assert np.array_equal(p, r.act_packed) and np.array_equal(s, r.act_scales)
+    routed = np.zeros_like(latent)
+    for k in range(cfg.top_k):
+        routed = (routed + r.routed_out[:, k, :] * r.top_weight[:, k:k + 1]).astype(np.float32)
+    assert np.array_equal(routed, r.routed_latent)
+    assert np.array_equal(r.projected, oracle.router_logits(routed, ow.fc2))
+    su = oracle.router_logits(y, ow.shared_up_dense)
+    su = np.where(su > 0, su * su, 0).astype(np.float32)
+    assert np.array_equal(su, r.shid_values)
+    shared = oracle.router_logits(oracle.fp8_round_trip(su, ow.shared_down_input_scale),
+                                  ow.shared_down_dense)
+    assert np.array_equal(shared, r.shared_out)
+    assert np.array_equal(r.out, (x + (r.projected + shared)).astype(np.float32))
+
+
+def test_fp8_round_trip_matches_torch_e4m3(oracle):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn((4, 64), generator=g) * 3.0
+    scale = 8.0 / 448.0
+    expect = ((x / scale).to(torch.float8_e4m3fn).to(torch.float32) * scale).numpy()
+    inside = (x.abs() / scale <= 448.0).numpy()  # torch does not saturate; the reference does
+    got = oracle.fp8_round_trip(x.numpy(), scale)
+    assert np.array_equal(got[inside], expect[inside])
+    assert np.all(np.abs(got[~inside]) == np.float32(448.0 * scale)) or inside.all()
