@@ -270,10 +270,16 @@ def run_reference_arm(args, real_stdout):
 def run_side_workloads(package, synthetic, layer, data, peaks, steps, warmup, flush_buf):
     """configs[1] decode sizes on the main layer's weights and configs[2] skewed prefill."""
     results = []
+    # a stream of the caller's own, as a serving loop has: there the layer replays its
+    # small batches as recorded CUDA graphs (the legacy default stream cannot be captured)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
     for tokens in (1, 8, 32, 64):
         x = synthetic.make_tokens(tokens, H, seed=5000 + tokens, device="cuda")
         out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
-        times = time_steps(lambda: layer.run_async(x, out), steps, warmup, flush_buf)
+        with torch.cuda.stream(side):
+            times = time_steps(lambda: layer.run_async(x, out), steps, warmup, flush_buf)
+        side.synchronize()
         stages = stage_profile(layer, x, out, max(3, steps // 2), flush_buf)
         idx = layer.trace(tokens).selected_index
         distinct = int(torch.unique(idx).numel())
@@ -297,6 +303,7 @@ def run_side_workloads(package, synthetic, layer, data, peaks, steps, warmup, fl
     cfg = synthetic.baseline_config(max_tokens=8192)
     skew = synthetic.make_layer(cfg, seed=3000, device="cuda", skewed=True)
     skew_layer = package.ExpertLayerSlice.create(cfg, skew.bindings)
+    skew_layer.keep_trace(False)
     x = synthetic.make_tokens(8192, H, seed=3001, device="cuda")
     out = torch.empty((8192, H), dtype=torch.bfloat16, device="cuda")
     times = time_steps(lambda: skew_layer.run_async(x, out), steps, warmup, flush_buf)
@@ -394,6 +401,7 @@ def main():
     layer = package.ExpertLayerSlice.create(cfg, data.bindings)
     if layer is None:
         raise SystemExit("layer creation failed: " + package.ExpertLayerSlice.create_error)
+    layer.keep_trace(False)  # what the drop-in shim sets: nothing is kept for a trace
     x_host = synthetic.make_tokens(tokens, H, seed=4001).pin_memory()
     x = x_host.cuda()
     out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")

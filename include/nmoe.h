@@ -166,7 +166,10 @@ NMOE_API void nmoe_layer_destroy(nmoe_layer* layer);
  * order (:951-953, :1064-1069); with bf16 output they are rounded to binary16
  * first (a row beyond 65504 is reported as NMOE_ERR_ACTIVATION_RANGE).
  * Enqueues on `stream` and returns; device-side failures surface through
- * nmoe_layer_sync_status(). */
+ * nmoe_layer_sync_status().  Batches of up to 256 tokens (NMOE_GRAPH_MAX_TOKENS)
+ * on a capturable stream are recorded once per (token count, buffers, types) as a
+ * CUDA graph and replayed by later calls with the same arguments; the legacy
+ * default stream, and a stream the caller is capturing itself, run eagerly. */
 NMOE_API nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void* input,
                                     nmoe_dtype input_dtype, int64_t tokens, void* output,
                                     nmoe_dtype output_dtype);
@@ -192,8 +195,8 @@ NMOE_API nmoe_status nmoe_layer_reserve_tokens(nmoe_layer* layer, int32_t max_to
  * (nmoe_layer_export_unfused).  Allocates on the first enable and synchronises
  * the device: call it between runs. */
 NMOE_API nmoe_status nmoe_layer_set_unfused_activation(nmoe_layer* layer, int32_t enable);
-/* After a run with the unfused path, in (token, slot) order, any pointer may be
- * NULL: routed_activated [tokens][top_k][intermediate] FP32 = relu^2(up_proj),
+/* After a run with the unfused path, in (token, slot) order, DEVICE pointers, any of
+ * which may be NULL: routed_activated [tokens][top_k][intermediate] FP32 = relu^2(up_proj),
  * routed_outputs [tokens][top_k][latent] FP32 = down_proj rows before the
  * routing weight, shared_activated [tokens][shared_intermediate] FP32
  * (routed_expert_activated_hidden / routed_expert_outputs of
@@ -249,7 +252,8 @@ NMOE_API nmoe_status nmoe_layer_reserve_sms(nmoe_layer* layer, int32_t reserved_
  * token count, as device buffers of the LAST run.  A field stays NULL when the
  * layer does not hold it.  Valid until the next run or destroy. */
 typedef struct nmoe_trace_view {
-  const float* normalized_input;   /* [tokens][hidden] */
+  const float* normalized_input;   /* [tokens][hidden]; NULL after a large-batch run with
+                                      nmoe_layer_keep_trace off */
   const float* router_logits;      /* [tokens][experts] */
   const int32_t* selected_index;   /* [tokens][top_k], selection order */
   const float* selected_weight;    /* [tokens][top_k] */
@@ -271,6 +275,12 @@ typedef struct nmoe_trace_view {
                                       (the shared row is parts[t][top_k] there) */
 } nmoe_trace_view;
 NMOE_API nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out);
+/* A layer keeps everything a trace may ask for (the default).  With enable == 0 it
+ * stops writing the FP32 normalised rows where nothing but a trace reads them --
+ * batches large enough for the two-pass router, whose kernels rebuild the rows
+ * from the input -- which removes the largest write of the routing front end.
+ * The reference captures a trace for one token only (expert_layer.cpp:775). */
+NMOE_API nmoe_status nmoe_layer_keep_trace(nmoe_layer* layer, int32_t enable);
 /* Copies one nmoe_trace_view field (index in declaration order, 0 =
  * normalized_input) of the last run into `dst` (device or host), `nbytes`
  * bytes, in stream order; NMOE_ERR_INVALID_ARGUMENT for a field that is NULL. */
@@ -390,7 +400,9 @@ NMOE_API nmoe_status nmoe_ffn_create(const nmoe_nvfp4_matrix* up, const nmoe_nvf
                                      int32_t max_rows, nmoe_ffn** out_ffn);
 NMOE_API void nmoe_ffn_destroy(nmoe_ffn* ffn);
 /* input [rows][hidden] device FP32/bf16 -> output [rows][hidden] device FP32.
- * gemm_variant: 0 = choose by size, otherwise 1 + a tile-shape index (for tests). */
+ * gemm_variant: 0 = choose by size, otherwise 1 + a tile-shape class (for tests):
+ * 1 prefill tiles, 2 decode tiles (rows <= 32), 3 wide decode tiles, 4 prefill tiles
+ * over CTA pairs. */
 NMOE_API nmoe_status nmoe_ffn_run(nmoe_ffn* ffn, void* stream, const void* input,
                                   nmoe_dtype input_dtype, int64_t rows, float* output,
                                   int32_t gemm_variant);

@@ -44,7 +44,7 @@ EXPORTED_SYMBOLS = (
     "nmoe_ep_window_attach", "nmoe_ep_window_detach", "nmoe_ep_window_dispatch",
     "nmoe_ep_window_experts", "nmoe_ep_window_combine", "nmoe_ep_window_fork_shared",
     "nmoe_layer_set_wait_limit_ms", "nmoe_layer_wait_flag", "nmoe_layer_reserve_tokens",
-    "nmoe_layer_set_unfused_activation", "nmoe_layer_export_unfused",
+    "nmoe_layer_set_unfused_activation", "nmoe_layer_export_unfused", "nmoe_layer_keep_trace",
 )
 
 
@@ -131,6 +131,7 @@ def load_library() -> ctypes.CDLL:
     lib.nmoe_layer_export_hidden.argtypes = [vp, vp, vp, vp, vp, vp]
     lib.nmoe_layer_enable_stage_timing.argtypes = [vp, i32]
     lib.nmoe_layer_reserve_sms.argtypes = [vp, i32]
+    lib.nmoe_layer_keep_trace.argtypes = [vp, i32]
     lib.nmoe_layer_reserve_tokens.argtypes = [vp, i32]
     lib.nmoe_layer_set_unfused_activation.argtypes = [vp, i32]
     lib.nmoe_layer_export_unfused.argtypes = [vp, vp, vp, vp, vp]
@@ -314,7 +315,7 @@ def _dense(t: torch.Tensor, keep: list) -> _DenseTensor:
 class ExpertLayerTrace:
     """Device views of the intermediates of the last run (`ExpertLayerRunTrace`,
     expert_layer.h:63-76, for any token count)."""
-    normalized_input: torch.Tensor
+    normalized_input: Optional[torch.Tensor]  # None after a large batch with keep_trace off
     router_logits: torch.Tensor
     selected_index: torch.Tensor
     selected_weight: torch.Tensor
@@ -440,6 +441,12 @@ class ExpertLayerSlice:
         _check(load_library().nmoe_layer_reserve_sms(self._handle, int(reserved)),
                "nmoe_layer_reserve_sms")
 
+    def keep_trace(self, enable: bool) -> None:
+        """False: stop writing intermediates that only `trace` reads (the FP32 normalised
+        rows of large batches); `trace` then returns None for them."""
+        _check(load_library().nmoe_layer_keep_trace(self._handle, 1 if enable else 0),
+               "nmoe_layer_keep_trace")
+
     def reserve_tokens(self, max_tokens: int) -> None:
         """Grows the scratch to `max_tokens` rows per run (synchronises the device)."""
         _check(load_library().nmoe_layer_reserve_tokens(self._handle, int(max_tokens)),
@@ -527,7 +534,7 @@ class ExpertLayerSlice:
                                             sp.data_ptr(), ss.data_ptr()),
                "nmoe_layer_export_hidden")
         trace = ExpertLayerTrace(
-            normalized_input=grab("normalized_input", (tokens, H), torch.float32),
+            normalized_input=grab("normalized_input", (tokens, H), torch.float32, optional=True),
             router_logits=grab("router_logits", (tokens, E), torch.float32),
             selected_index=grab("selected_index", (tokens, K), torch.int32),
             selected_weight=grab("selected_weight", (tokens, K), torch.float32),

@@ -312,4 +312,108 @@ __device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, float (&v)[16]) {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
 
+// --- CTA pairs (cta_group::2) -------------------------------------------------
+// Two CTAs of a cluster of size 2 drive one tcgen05.mma with M = 256: each CTA
+// holds 128 rows of A and half of B's rows in its own shared memory (at the same
+// offsets), each accumulates its own 128 rows in its own TMEM.  One thread of the
+// leader (cluster rank 0) issues the MMAs and the scale copies for both.
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\t"
+               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Arrive on the mbarrier at the same shared-memory offset in CTA `target_rank`
+// of this cluster.
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, uint32_t target_rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote)
+               : "r"(smem_u32(bar)), "r"(target_rank));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote)
+               : "memory");
+}
+
+// try_wait that acquires at cluster scope: pairs with mbar_arrive_remote.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (clock64() - start > (1ll << 31)) return false;
+  }
+  return true;
+}
+
+// TMEM allocation for a pair: one warp of EACH CTA executes it, the same columns
+// are allocated in both.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_result)),
+               "r"(columns)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns)
+               : "memory");
+}
+
+// Arrive, once every tcgen05 operation this thread issued so far has completed, on
+// the mbarrier at this offset in every CTA of `cta_mask` (bit i = cluster rank i).
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;" ::"r"(smem_u32(bar)),
+      "h"(cta_mask)
+      : "memory");
+}
+
+// Scale copy in both CTAs of the pair: each copies from its own shared memory (same
+// offset) into its own TMEM.
+__device__ __forceinline__ void tcgen05_cp_pair_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc)
+               : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_mma_pair_nvf4(uint32_t d_tmem, uint64_t a_desc,
+                                                      uint64_t b_desc, uint32_t idesc,
+                                                      uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                                      uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X"
+      " [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
+      "r"(sfb_tmem)
+      : "memory");
+}
+
+// Instruction descriptor of make_idesc_nvf4 with M = 256 (a CTA pair).
+__host__ __device__ constexpr uint32_t make_idesc_nvf4_pair(uint32_t n) {
+  return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (0u << 23) | ((256u >> 4) << 24);
+}
+
 }  // namespace nmoe

@@ -156,7 +156,8 @@ __global__ void combine_indexed_kernel(const void* __restrict__ in,
                                        const void* __restrict__ returned_rows, int rows_kind,
                                        const int32_t* __restrict__ position,
                                        const void* __restrict__ shared_rows, int shared_kind,
-                                       int rows, int hidden, int top_k, void* __restrict__ out) {
+                                       int rows, int hidden, int top_k, void* __restrict__ out,
+                                       int32_t* __restrict__ error) {
   const int quads = hidden / 4;
   const size_t total = static_cast<size_t>(rows) * quads;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -179,10 +180,17 @@ __global__ void combine_indexed_kernel(const void* __restrict__ in,
     const float4 shared = load_row4(shared_rows, shared_kind, t, hidden, c);
     const float4 x = load_row4(in, IN_BF16 ? kRowBf16 : kRowF32, t, hidden, c);
     float r[4];
-    r[0] = __fadd_rn(x.x, __fadd_rn(routed.x, shared.x));
-    r[1] = __fadd_rn(x.y, __fadd_rn(routed.y, shared.y));
-    r[2] = __fadd_rn(x.z, __fadd_rn(routed.z, shared.z));
-    r[3] = __fadd_rn(x.w, __fadd_rn(routed.w, shared.w));
+    const float m0 = __fadd_rn(routed.x, shared.x), m1 = __fadd_rn(routed.y, shared.y),
+                m2 = __fadd_rn(routed.z, shared.z), m3 = __fadd_rn(routed.w, shared.w);
+    // a row that left binary16's range on its way here (the GEMM stores an infinity)
+    if (rows_kind == kRowF16 && error != nullptr &&
+        !(isfinite(m0) && isfinite(m1) && isfinite(m2) && isfinite(m3))) {
+      atomicCAS(error, kDevOk, kDevActivationRange);
+    }
+    r[0] = __fadd_rn(x.x, m0);
+    r[1] = __fadd_rn(x.y, m1);
+    r[2] = __fadd_rn(x.z, m2);
+    r[3] = __fadd_rn(x.w, m3);
     if constexpr (OUT_BF16) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]);
       __nv_bfloat162 hi = __floats2bfloat162_rn(r[2], r[3]);
@@ -289,22 +297,26 @@ cudaError_t launch_combine_indexed(const void* in, bool in_bf16, const void* ret
                                    RowKind rows_kind, const int32_t* position,
                                    const void* shared_rows, RowKind shared_kind, int rows,
                                    int hidden, int top_k, void* out, bool out_bf16,
-                                   cudaStream_t stream) {
+                                   int32_t* error, cudaStream_t stream) {
   if (rows <= 0 || hidden % 4 != 0 || top_k < 1) return cudaErrorInvalidValue;
   const size_t total = static_cast<size_t>(rows) * (hidden / 4);
   const int blocks = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   if (in_bf16 && out_bf16) {
     combine_indexed_kernel<true, true><<<blocks, 256, 0, stream>>>(
-        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out);
+        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out,
+        error);
   } else if (in_bf16) {
     combine_indexed_kernel<true, false><<<blocks, 256, 0, stream>>>(
-        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out);
+        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out,
+        error);
   } else if (out_bf16) {
     combine_indexed_kernel<false, true><<<blocks, 256, 0, stream>>>(
-        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out);
+        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out,
+        error);
   } else {
     combine_indexed_kernel<false, false><<<blocks, 256, 0, stream>>>(
-        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out);
+        in, returned_rows, rows_kind, position, shared_rows, shared_kind, rows, hidden, top_k, out,
+        error);
   }
   return cudaGetLastError();
 }

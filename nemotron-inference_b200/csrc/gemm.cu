@@ -45,15 +45,20 @@ constexpr int kScaleWarps = 2;  // the copies are split between this many issuin
 constexpr int kGemmThreads = (2 + kEpilogueWarps + kScaleWarps) * 32;
 constexpr int kStageStride = 36;  // floats per staged row: 32 + 4 keeps float4 accesses conflict-free
 
-template <int BN_, int A_ROWS_, int SFB_GS_, int STAGES_, bool ROW_STAGING_ = true>
+template <int BN_, int A_ROWS_, int SFB_GS_, int STAGES_, bool ROW_STAGING_ = true,
+          bool PAIR_ = false>
 struct TileCfg {
   static constexpr int BN = BN_;
   static constexpr int A_ROWS = A_ROWS_;
   static constexpr int SFB_GS = SFB_GS_;  // 32-row scale groups stored per K tile (multiple of 4:
                                           // an MMA's scale address must be 4-column aligned)
   static constexpr int STAGES = STAGES_;
+  // A CTA pair (cta_group::2, M = 256): each CTA stages its own 128 activation rows
+  // and HALF of the weight tile's rows; both hold the scales of all BN weight rows.
+  static constexpr bool PAIR = PAIR_;
+  static constexpr int B_ROWS = PAIR_ ? BN_ / 2 : BN_;
   static constexpr int A_BYTES = A_ROWS * 128;
-  static constexpr int B_BYTES = BN * 128;
+  static constexpr int B_BYTES = B_ROWS * 128;
   static constexpr int SFA_BYTES = 2048;
   static constexpr int SFB_BYTES = SFB_GS * 512;
   static constexpr int STAGE_TX = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
@@ -66,7 +71,9 @@ struct TileCfg {
   static constexpr int SFB_COL = SFA_COL + 16;
   static constexpr int TMEM_USED = SFA_COL + SF_BUFS * SF_BUF_COLS;
   static constexpr int TMEM_COLS = TMEM_USED <= 32 ? 32 : TMEM_USED <= 64 ? 64 : TMEM_USED <= 128 ? 128 : TMEM_USED <= 256 ? 256 : 512;
-  static constexpr int BAR_BYTES = (2 * STAGES + 4 + SF_BUFS) * 8 + 16;
+  // full, empty and peer-full per stage; accumulator full / empty; scale-ready
+  // (rounded up: the epilogue's staging area behind it is accessed 16 bytes at a time)
+  static constexpr int BAR_BYTES = ((3 * STAGES + 4 + SF_BUFS) * 8 + 16 + 15) / 16 * 16;
   // staging for the row-scattering epilogue of the down projection
   static constexpr bool ROW_STAGING = ROW_STAGING_;
   static constexpr int EPI_STAGE_BYTES = ROW_STAGING_ ? kEpilogueWarps * 32 * kStageStride * 4 : 0;
@@ -76,6 +83,8 @@ struct TileCfg {
   static constexpr int SMEM_BYTES =
       STAGES * (A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES) + BAR_BYTES + EPI_STAGE_BYTES + 1024;
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "BN");
+  static_assert(!PAIR_ || (BN_ % 32 == 0 || (BN_ / 2) % 8 == 0), "half a weight tile is whole 8-row groups");
+  static_assert(!PAIR_ || A_ROWS_ == 128, "a pair stages full 128-row boxes");
   static_assert(SFB_GS % 4 == 0 && SFB_GS * 32 >= BN, "weight scale groups");
   static_assert(TMEM_USED <= 512, "TMEM budget");
   static_assert(STAGES * B_BYTES >= 128 * 128, "A over-read must stay inside shared memory");
@@ -86,6 +95,8 @@ using CfgPrefillUp = TileCfg<208, 128, 8, 4, false>;
 using CfgPrefillDown = TileCfg<192, 128, 8, 4>;
 using CfgDecode = TileCfg<128, 32, 4, 7>;
 using CfgDecodeWide = TileCfg<128, 128, 4, 5>;
+using CfgPairUp = TileCfg<208, 128, 8, 6, false, true>;
+using CfgPairDown = TileCfg<192, 128, 8, 5, true, true>;
 
 __device__ __forceinline__ void report_timeout(int32_t* error, volatile int* abort_flag) {
   *abort_flag = 1;
@@ -94,19 +105,55 @@ __device__ __forceinline__ void report_timeout(int32_t* error, volatile int* abo
 
 // All scale copies of one full K block that fall to copier `PART`; compile-time
 // indices only, so that no copy carries a run-time predicate.
+template <class C>
+__device__ __forceinline__ void scale_copy(uint32_t taddr, uint64_t desc) {
+  if constexpr (C::PAIR) {
+    tcgen05_cp_pair_32x128b_warpx4(taddr, desc);
+  } else {
+    tcgen05_cp_32x128b_warpx4(taddr, desc);
+  }
+}
+
 template <class C, int PART>
 __device__ __forceinline__ void issue_scale_copies(uint32_t sf_tmem, uint32_t sfa_addr,
                                                    uint32_t sfb_addr) {
 #pragma unroll
   for (int c = PART; c < 4; c += kScaleWarps) {
-    tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFA_COL + 4 * c,
-                              make_smem_desc(sfa_addr + c * 512, 0, 128, 0));
+    scale_copy<C>(sf_tmem + C::SFA_COL + 4 * c, make_smem_desc(sfa_addr + c * 512, 0, 128, 0));
   }
 #pragma unroll
   for (int c = PART; c < C::SFB_GS; c += kScaleWarps) {
-    tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFB_COL + 4 * c,
-                              make_smem_desc(sfb_addr + c * 512, 0, 128, 0));
+    scale_copy<C>(sf_tmem + C::SFB_COL + 4 * c, make_smem_desc(sfb_addr + c * 512, 0, 128, 0));
   }
+}
+
+// The row tile a CTA works on in tile unit `rt` (a row tile, or a pair of them).
+struct TileRows {
+  int row0;      // first row of the 128-row slot
+  int rows;      // valid rows in it
+  int load_row0; // where the operands are read from (a valid slot even when rows == 0)
+  int expert;
+};
+
+template <class C>
+__device__ __forceinline__ TileRows tile_rows_of(const GemmArgs& args, int rt, int num_row_tiles,
+                                                 uint32_t cta_rank) {
+  TileRows t;
+  const int index = C::PAIR ? 2 * rt + static_cast<int>(cta_rank) : rt;
+  if (args.row_tiles != nullptr) {
+    // the plan gives every expert an even number of tiles when pairs consume them
+    const int safe = min(index, num_row_tiles - 1);
+    t.row0 = args.row_tiles[safe].row0;
+    t.rows = index < num_row_tiles ? args.row_tiles[safe].rows : 0;
+    t.expert = args.row_tiles[safe].expert;
+    t.load_row0 = t.row0;
+  } else {
+    t.row0 = index * 128;
+    t.rows = max(0, min(128, args.dense_rows - t.row0));
+    t.expert = 0;
+    t.load_row0 = min(t.row0, ((args.dense_rows - 1) >> 7) << 7);
+  }
+  return t;
 }
 
 template <class C, int MODE>
@@ -122,7 +169,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t* sSFB = sSFA + C::STAGES * C::SFA_BYTES;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(sSFB + C::STAGES * C::SFB_BYTES);
   uint64_t* empty_bar = full_bar + C::STAGES;
-  uint64_t* tmem_full_bar = empty_bar + C::STAGES;
+  uint64_t* peer_full_bar = empty_bar + C::STAGES;  // pairs: the other CTA's operands landed
+  uint64_t* tmem_full_bar = peer_full_bar + C::STAGES;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
   uint64_t* sf_ready_bar = tmem_empty_bar + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_ready_bar + C::SF_BUFS);
@@ -132,15 +180,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  constexpr bool P = C::PAIR;
+  // In a pair, cluster rank 0 leads: its warp 1 issues every MMA and its scale warps
+  // every scale copy, for both CTAs.  Rank 1 loads its own operands, tells the leader
+  // when they have landed and runs the epilogue of its own 128 rows.
+  const uint32_t cta_rank = P ? cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0u;
+  const int unit = P ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int units = P ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      mbar_init(&peer_full_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full_bar[a], 1);
-      mbar_init(&tmem_empty_bar[a], kEpilogueWarps);
+      mbar_init(&tmem_empty_bar[a], P ? 2 * kEpilogueWarps : kEpilogueWarps);
     }
     for (int b = 0; b < C::SF_BUFS; ++b) {
       mbar_init(&sf_ready_bar[b], kScaleWarps);
@@ -151,17 +208,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     prefetch_tensormap(&tmap_b_tail);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, C::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (P) {
+      tmem_alloc_pair(tmem_slot, C::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, C::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (P) cluster_sync_all();  // the partner's barriers exist before anything arrives
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_row_tiles =
       args.row_tiles != nullptr ? *args.num_row_tiles : (args.dense_rows + 127) / 128;
-  const int total_tiles = num_row_tiles * args.n_tiles;
+  const int row_units = P ? (num_row_tiles + 1) / 2 : num_row_tiles;
+  const int total_tiles = row_units * args.n_tiles;
   const int k_mmas = args.K / 64;
 
   if (warp == 0) {
@@ -170,24 +234,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += units) {
         const int rt = t / args.n_tiles;
         const int nt = t - rt * args.n_tiles;
-        int row0, expert;
-        if (args.row_tiles != nullptr) {
-          row0 = args.row_tiles[rt].row0;
-          expert = args.row_tiles[rt].expert;
-        } else {
-          row0 = rt * 128;
-          expert = 0;
-        }
+        const TileRows rows = tile_rows_of<C>(args, rt, num_row_tiles, cta_rank);
+        const int expert = rows.expert;
         const uint8_t* sfa_src =
-            args.sfa + static_cast<size_t>(row0 >> 7) * args.k_blocks * C::SFA_BYTES;
+            args.sfa + static_cast<size_t>(rows.load_row0 >> 7) * args.k_blocks * C::SFA_BYTES;
         const uint8_t* sfb_src = args.sfb + (static_cast<size_t>(expert) * args.n_tiles + nt) *
                                                 args.k_blocks * C::SFB_BYTES;
         // weights are stored K-block-major: [expert][k block][row][128 B], then the
-        // partial last K block as [expert][row][tail bytes]
-        const int b_row = nt * C::BN;
+        // partial last K block as [expert][row][tail bytes]; a pair's CTA takes the
+        // half of the tile's rows that belongs to its rank
+        const int b_row = nt * C::BN + static_cast<int>(cta_rank) * C::B_ROWS;
         for (int kb = 0; kb < args.k_blocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
             report_timeout(args.error, abort_flag);
@@ -195,7 +254,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             break;
           }
           mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_TX);
-          tma_load_2d(sA + stage * C::A_BYTES, &tmap_a, kb * 128, row0, &full_bar[stage]);
+          tma_load_2d(sA + stage * C::A_BYTES, &tmap_a, kb * 128, rows.load_row0,
+                      &full_bar[stage]);
           if (kb < args.kb_full) {
             // one contiguous, pre-swizzled panel slice: a single bulk copy
             bulk_load(sB + stage * C::B_BYTES,
@@ -219,26 +279,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_nvf4(C::BN);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = P ? make_idesc_nvf4_pair(C::BN) : make_idesc_nvf4(C::BN);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
       int sf_buf = 0;
       uint32_t sf_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+      for (int t = unit; t < total_tiles && ok; t += units, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u)) {
+        // both CTAs' epilogues have drained this accumulator
+        if (!(P ? mbar_wait_cluster(&tmem_empty_bar[acc], acc_phase ^ 1u)
+                : mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1u))) {
           report_timeout(args.error, abort_flag);
           break;
         }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * C::ACC_STRIDE;
         for (int kb = 0; kb < args.k_blocks; ++kb) {
-          // the operands have landed and the scale copies of this K block are done
-          if (!mbar_wait(&full_bar[stage], phase) || !mbar_wait(&sf_ready_bar[sf_buf], sf_phase)) {
+          // the operands have landed (in both CTAs) and the scale copies of this K
+          // block are done
+          bool landed = mbar_wait(&full_bar[stage], phase);
+          if constexpr (P) landed = landed && mbar_wait_cluster(&peer_full_bar[stage], phase);
+          if (!landed || !mbar_wait(&sf_ready_bar[sf_buf], sf_phase)) {
             report_timeout(args.error, abort_flag);
             ok = false;
             break;
@@ -251,22 +316,42 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (kt_count == 4) {
 #pragma unroll
             for (int kt = 0; kt < 4; ++kt) {
-              tcgen05_mma_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
-                               make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
-                               sf_tmem + C::SFA_COL + 4 * kt,
-                               sf_tmem + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
+              if constexpr (P) {
+                tcgen05_mma_pair_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
+                                      make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
+                                      sf_tmem + C::SFA_COL + 4 * kt,
+                                      sf_tmem + C::SFB_COL + C::SFB_GS * kt,
+                                      (kb | kt) != 0 ? 1u : 0u);
+              } else {
+                tcgen05_mma_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
+                                 make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
+                                 sf_tmem + C::SFA_COL + 4 * kt,
+                                 sf_tmem + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
+              }
             }
           } else {
             for (int kt = 0; kt < kt_count; ++kt) {
-              tcgen05_mma_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
-                               make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
-                               sf_tmem + C::SFA_COL + 4 * kt,
-                               sf_tmem + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
+              if constexpr (P) {
+                tcgen05_mma_pair_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
+                                      make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
+                                      sf_tmem + C::SFA_COL + 4 * kt,
+                                      sf_tmem + C::SFB_COL + C::SFB_GS * kt,
+                                      (kb | kt) != 0 ? 1u : 0u);
+              } else {
+                tcgen05_mma_nvf4(d_tmem, make_smem_desc(a_addr + kt * 32, 0, 1024, 2),
+                                 make_smem_desc(b_addr + kt * 32, 0, 1024, 2), idesc,
+                                 sf_tmem + C::SFA_COL + 4 * kt,
+                                 sf_tmem + C::SFB_COL + C::SFB_GS * kt, (kb | kt) != 0 ? 1u : 0u);
+              }
             }
           }
-          // frees the stage for the producer and, SF_BUFS K blocks later, this
+          // frees the stage for the producer(s) and, SF_BUFS K blocks later, this
           // block's scale columns for the copier
-          tcgen05_commit(&empty_bar[stage]);
+          if constexpr (P) {
+            tcgen05_commit_pair(&empty_bar[stage], 3);
+          } else {
+            tcgen05_commit(&empty_bar[stage]);
+          }
           if (++sf_buf == C::SF_BUFS) {
             sf_buf = 0;
             sf_phase ^= 1u;
@@ -276,14 +361,43 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             phase ^= 1u;
           }
         }
-        if (ok) tcgen05_commit(&tmem_full_bar[acc]);
+        if (ok) {
+          if constexpr (P) {
+            tcgen05_commit_pair(&tmem_full_bar[acc], 3);
+          } else {
+            tcgen05_commit(&tmem_full_bar[acc]);
+          }
+        }
       }
     }
   } else if (warp >= kScaleWarp) {
+    if (lane == 0 && !leader) {
+      // ------------------------------------------- partner: operands-landed relay
+      // The leader's MMAs read this CTA's shared memory; one thread here watches the
+      // local full barrier and raises the leader's peer-full barrier of that stage.
+      if (warp == kScaleWarp) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int t = unit; t < total_tiles && ok; t += units) {
+          for (int kb = 0; kb < args.k_blocks; ++kb) {
+            if (!mbar_wait(&full_bar[stage], phase)) {
+              report_timeout(args.error, abort_flag);
+              ok = false;
+              break;
+            }
+            mbar_arrive_remote(&peer_full_bar[stage], 0);
+            if (++stage == C::STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
     // ------------------------------------------------------- block-scale copier
     // The copies of one K block's scales into TMEM take longer to issue than
     // its MMAs; a thread of their own lets them run ahead of the MMA thread.
-    if (lane == 0) {
       const int part = warp - kScaleWarp;
       int stage = 0;
       uint32_t phase = 0;
@@ -294,7 +408,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t old_phase = 0;
       int iteration = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += units) {
         for (int kb = 0; kb < args.k_blocks; ++kb, ++iteration) {
           bool ready = true;
           if (iteration >= C::SF_BUFS) {
@@ -304,7 +418,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               old_phase ^= 1u;
             }
           }
-          if (!ready || !mbar_wait(&full_bar[stage], phase)) {
+          ready = ready && mbar_wait(&full_bar[stage], phase);
+          if constexpr (P) ready = ready && mbar_wait_cluster(&peer_full_bar[stage], phase);
+          if (!ready) {
             report_timeout(args.error, abort_flag);
             ok = false;
             break;
@@ -327,15 +443,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
           } else {
             for (int c = part; c < kt_count; c += kScaleWarps) {
-              tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFA_COL + 4 * c,
-                                        make_smem_desc(sfa_addr + c * 512, 0, 128, 0));
+              scale_copy<C>(sf_tmem + C::SFA_COL + 4 * c,
+                            make_smem_desc(sfa_addr + c * 512, 0, 128, 0));
             }
             for (int c = part; c < kt_count * kWeightCopiesPerMma; c += kScaleWarps) {
-              tcgen05_cp_32x128b_warpx4(sf_tmem + C::SFB_COL + 4 * c,
-                                        make_smem_desc(sfb_addr + c * 512, 0, 128, 0));
+              scale_copy<C>(sf_tmem + C::SFB_COL + 4 * c,
+                            make_smem_desc(sfb_addr + c * 512, 0, 128, 0));
             }
           }
-          tcgen05_commit(&sf_ready_bar[sf_buf]);
+          if constexpr (P) {
+            tcgen05_commit_pair(&sf_ready_bar[sf_buf], 1);  // the leader's barrier only
+          } else {
+            tcgen05_commit(&sf_ready_bar[sf_buf]);
+          }
           if (++sf_buf == C::SF_BUFS) sf_buf = 0;
           if (++stage == C::STAGES) {
             stage = 0;
@@ -350,21 +470,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int half = (warp - 2) >> 2;       // which half of the tile's columns
     const int r = quarter * 32 + lane;      // row inside the tile == TMEM lane
     int local = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+    for (int t = unit; t < total_tiles; t += units, ++local) {
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
       const int rt = t / args.n_tiles;
       const int nt = t - rt * args.n_tiles;
-      int row0, rows, expert;
-      if (args.row_tiles != nullptr) {
-        row0 = args.row_tiles[rt].row0;
-        rows = args.row_tiles[rt].rows;
-        expert = args.row_tiles[rt].expert;
-      } else {
-        row0 = rt * 128;
-        rows = min(128, args.dense_rows - row0);
-        expert = 0;
-      }
+      const TileRows tile = tile_rows_of<C>(args, rt, num_row_tiles, cta_rank);
+      const int row0 = tile.row0, rows = tile.rows, expert = tile.expert;
       const bool row_valid = r < rows;
       const int grow = row0 + r;
       float scale = args.w_tensor_scale[expert];
@@ -490,12 +602,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 bits.y = *reinterpret_cast<const uint32_t*>(&hi);
                 *reinterpret_cast<uint2*>(d + static_cast<size_t>(n + c4) * 2) = bits;
               } else if (args.out_kind == kRowF16) {
-                // binary16 saturates at 65504: a row beyond it is reported, not stored as inf
-                const float top = fmaxf(fmaxf(fabsf(value.x), fabsf(value.y)),
-                                        fmaxf(fabsf(value.z), fabsf(value.w)));
-                if (top > 65504.0f && args.error != nullptr) {
-                  atomicCAS(args.error, kDevOk, kDevActivationRange);
-                }
+                // a value beyond binary16's 65504 becomes an infinity here; the combine
+                // kernel reports it
                 const __half2 lo = __floats2half2_rn(value.x, value.y);
                 const __half2 hi = __floats2half2_rn(value.z, value.w);
                 uint2 bits;
@@ -511,15 +619,56 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      if (lane == 0) {
+        if (P && !leader) {
+          mbar_arrive_remote(&tmem_empty_bar[acc], 0);  // the leader waits for both CTAs
+        } else {
+          mbar_arrive(&tmem_empty_bar[acc]);
+        }
+      }
     }
   }
 
   tcgen05_fence_before();
   __syncthreads();
+  // neither CTA of a pair leaves while the other may still read its shared memory
+  // or signal its barriers
+  if constexpr (P) cluster_sync_all();
   if (warp == 1) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if constexpr (P) {
+      tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+    } else {
+      tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+  }
+}
+
+template <class C, int MODE>
+cudaError_t launch_kernel(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b_tail,
+                          const GemmArgs& args, int grid, cudaStream_t stream) {
+  auto kernel = grouped_gemm_kernel<C, MODE>;
+  cudaError_t err =
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  if (err != cudaSuccess) return err;
+  if constexpr (C::PAIR) {
+    // two CTAs per cluster: the pair that shares one tcgen05.mma
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    config.blockDim = dim3(kGemmThreads, 1, 1);
+    config.dynamicSmemBytes = C::SMEM_BYTES;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, tmap_a, tmap_b_tail, args);
+  } else {
+    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b_tail, args);
+    return cudaGetLastError();
   }
 }
 
@@ -527,32 +676,27 @@ template <class C>
 cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a,
                        const CUtensorMap& tmap_b_tail, const GemmArgs& args, int num_sms,
                        cudaStream_t stream) {
-  int grid = num_sms;
+  // one persistent CTA (or CTA pair) per SM (pair of SMs), fewer when there is less work
+  int units = C::PAIR ? num_sms / 2 : num_sms;
   if (args.row_tiles == nullptr) {
-    const int tiles = ((args.dense_rows + 127) / 128) * args.n_tiles;
-    if (tiles < grid) grid = tiles;
-    if (grid < 1) grid = 1;
+    const int row_tiles = (args.dense_rows + 127) / 128;
+    const int tiles = (C::PAIR ? (row_tiles + 1) / 2 : row_tiles) * args.n_tiles;
+    if (tiles < units) units = tiles;
   }
-  cudaError_t err;
+  if (units < 1) units = 1;
+  const int grid = C::PAIR ? 2 * units : units;
   if (mode == kGemmUp) {
-    auto kernel = grouped_gemm_kernel<C, kGemmUp>;
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-    if (err != cudaSuccess) return err;
-    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b_tail, args);
+    return launch_kernel<C, kGemmUp>(tmap_a, tmap_b_tail, args, grid, stream);
   } else if constexpr (C::ROW_STAGING) {
-    auto kernel = grouped_gemm_kernel<C, kGemmDown>;
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-    if (err != cudaSuccess) return err;
-    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b_tail, args);
+    return launch_kernel<C, kGemmDown>(tmap_a, tmap_b_tail, args, grid, stream);
   } else {
     return cudaErrorInvalidValue;  // this tile shape has no staging for the down epilogue
   }
-  return cudaGetLastError();
 }
 
 template <class C>
 GemmVariantInfo info_of() {
-  return GemmVariantInfo{C::BN, C::A_ROWS, C::SFB_GS, C::SFB_BYTES, C::SMEM_BYTES};
+  return GemmVariantInfo{C::BN, C::A_ROWS, C::SFB_GS, C::SFB_BYTES, C::SMEM_BYTES, C::B_ROWS};
 }
 
 __global__ void relayout_weight_scales_kernel(const uint8_t* __restrict__ src, int experts, int N,
@@ -636,7 +780,9 @@ GemmVariantInfo gemm_variant_info(GemmVariant v) {
     case kVariantPrefillDown: return info_of<CfgPrefillDown>();
     case kVariantDecode: return info_of<CfgDecode>();
     case kVariantDecodeWide: return info_of<CfgDecodeWide>();
-    default: return GemmVariantInfo{0, 0, 0, 0, 0};
+    case kVariantPairUp: return info_of<CfgPairUp>();
+    case kVariantPairDown: return info_of<CfgPairDown>();
+    default: return GemmVariantInfo{0, 0, 0, 0, 0, 0};
   }
 }
 
@@ -648,6 +794,8 @@ cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const CUtensorMap&
     case kVariantPrefillDown: return launch_cfg<CfgPrefillDown>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
     case kVariantDecode: return launch_cfg<CfgDecode>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
     case kVariantDecodeWide: return launch_cfg<CfgDecodeWide>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
+    case kVariantPairUp: return launch_cfg<CfgPairUp>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
+    case kVariantPairDown: return launch_cfg<CfgPairDown>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -79,7 +79,9 @@ enum GemmVariant : int {
   kVariantPrefillDown = 1,  // BN 192, 128-row A box
   kVariantDecode = 2,       // BN 128, 32-row A box, deep pipeline
   kVariantDecodeWide = 3,   // BN 128, 128-row A box
-  kVariantCount = 4,
+  kVariantPairUp = 4,       // BN 208 over a CTA pair (M = 256, cta_group::2)
+  kVariantPairDown = 5,     // BN 192 over a CTA pair
+  kVariantCount = 6,
 };
 
 struct GemmVariantInfo {
@@ -88,6 +90,7 @@ struct GemmVariantInfo {
   int sfb_groups;    // 32-row groups of weight scales stored per K-tile
   int sfb_bytes;     // bytes of weight scales per (n_tile, k_block)
   int smem_bytes;    // dynamic shared memory of the kernel
+  int b_rows;        // weight rows one CTA stages per K block (half a tile in a pair)
 };
 
 GemmVariantInfo gemm_variant_info(GemmVariant v);
@@ -115,13 +118,12 @@ size_t weight_scale_layout_bytes(int experts, int N, int K, int bn, int sfb_grou
 //   normalized (optional) fp32 [rows][cols]
 //   packed [rows][cols/2]; sf_row_major (optional) [rows][cols/16];
 //   sf_tiled (optional) tiled layout with k_blocks*4 K-tiles per 128-row slot;
-//   tensor_scale (optional) [rows]
+//   tensor_scale (optional) [rows]; inv_rms (optional) [rows]: 1/sqrt(mean(x^2)+eps)
 cudaError_t launch_norm_quant(const void* in, bool in_bf16, int rows, int cols,
                               const float* norm_weight, float eps, float* normalized,
                               uint8_t* packed, uint8_t* sf_row_major, uint8_t* sf_tiled,
                               int k_blocks, float* tensor_scale, cudaStream_t stream,
-                              __nv_bfloat16* split = nullptr, size_t split_plane = 0);
-// `split` (optional): three bf16 planes [3][split_plane] with y = hi + mid + lo.
+                              float* inv_rms = nullptr);
 // Whole-matrix dynamic quantisation with ONE tensor scale (the reference
 // packer's semantics for rows > 1).  `amax_scratch` is one float of device
 // memory; it is overwritten.
@@ -147,16 +149,19 @@ cudaError_t launch_router_topk(const float* logits, const float* bias, int rows,
                                int32_t* expert_counts /* nullable, += histogram */,
                                cudaStream_t stream);
 
-// Two-pass router for large batches.  Pass 1: logits from the three bf16 planes
-// of the normalised activations and the bf16 gate on the tensor cores (FP32
-// accumulate).  Pass 2, per token: every expert whose pass-1 choice score is
-// within `tie_margin` of the top_k-th is re-evaluated in FP64 (and written back
-// into `logits`), then top-k runs on the exact values.  Requires n_group == 1,
+// Two-pass router for large batches.  Pass 1: logits on the tensor cores (FP32
+// accumulate) from the bf16 gate and the normalised activations, which the kernel
+// rebuilds from the layer input `x` as (x * inv_rms) * norm_weight and splits into
+// three bf16 terms on the fly.  Pass 2, per token: every expert whose pass-1 choice
+// score is within `tie_margin` of the top_k-th is re-evaluated in FP64 (and written
+// back into `logits`), then top-k runs on the exact values.  Requires n_group == 1,
 // experts % 32 == 0, experts <= 256, hidden % 64 == 0.
-cudaError_t launch_router_fast_logits(const CUtensorMap& tmap_split, const CUtensorMap& tmap_gate,
-                                      int rows, int split_plane_rows, int experts, int hidden,
-                                      float* logits, int32_t* error, cudaStream_t stream);
-cudaError_t launch_router_select_exact(float* logits, const float* normalized,
+cudaError_t launch_router_fast_logits(const void* x, bool x_bf16, const float* inv_rms,
+                                      const float* norm_weight, const CUtensorMap& tmap_gate,
+                                      int rows, int experts, int hidden, float* logits,
+                                      int32_t* error, cudaStream_t stream);
+cudaError_t launch_router_select_exact(float* logits, const void* x, bool x_bf16,
+                                       const float* inv_rms, const float* norm_weight,
                                        const __nv_bfloat16* gate, const float* logit_offset,
                                        const float* bias, int rows, int experts, int hidden,
                                        int top_k, bool norm_topk_prob, float routed_scaling,
@@ -191,8 +196,11 @@ struct PlanBuffers {
   RowTile* row_tiles;       // [max_row_tiles]
   int32_t* num_row_tiles;   // [1]
 };
+// `tile_multiple`: every expert gets a multiple of this many row tiles (2 when CTA
+// pairs consume them: the second tile of an odd expert is left empty).
 cudaError_t launch_route_plan(const PlanBuffers& plan, int experts, int tile_rows,
-                              int max_row_tiles, int32_t* error, cudaStream_t stream);
+                              int tile_multiple, int max_row_tiles, int32_t* error,
+                              cudaStream_t stream);
 // Where permute reads a (row, slot) pair from.  Quantised rows are indexed by
 // source row = pair / pairs_per_row, routing weight and expert id by pair; all
 // strides are in bytes.  Local routing: pairs_per_row = top_k over the token
@@ -254,12 +262,13 @@ cudaError_t launch_combine_indexed(const void* in, bool in_bf16, const void* ret
                                    RowKind rows_kind, const int32_t* position,
                                    const void* shared_rows, RowKind shared_kind, int rows,
                                    int hidden, int top_k, void* out, bool out_bf16,
-                                   cudaStream_t stream);
+                                   int32_t* error, cudaStream_t stream);
 
 // out[t] = in[t] + ((sum_k parts[t][k]) + parts[t][top_k]) with the routed
 // parts (rows of `parts_kind`, [rows][top_k + 1][hidden]) added in slot order.
+// `error` (nullable): kDevActivationRange when a binary16 part arrived as an infinity.
 cudaError_t launch_combine(const void* in, bool in_bf16, const void* parts, RowKind parts_kind,
                            int rows, int hidden, int top_k, void* out, bool out_bf16,
-                           cudaStream_t stream);
+                           int32_t* error, cudaStream_t stream);
 
 }  // namespace nmoe

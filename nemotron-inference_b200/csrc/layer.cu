@@ -168,7 +168,9 @@ void validate_matrix(const nmoe_nvfp4_matrix& m, size_t rows, size_t cols, const
 // A stack of same-shaped NVFP4 matrices resident in HBM with the scale layouts
 // and tensor maps of every GEMM tile shape that may consume it.
 // ---------------------------------------------------------------------------
-enum TileClass : int { kClassPrefill = 0, kClassDecode = 1, kClassDecodeWide = 2 };
+// kClassPair: the prefill tile shapes over CTA pairs (cta_group::2): each CTA stages
+// half of the weight tile, which is what the load pipeline of a single CTA runs out of.
+enum TileClass : int { kClassPrefill = 0, kClassDecode = 1, kClassDecodeWide = 2, kClassPair = 3 };
 
 struct WeightStack {
   int experts = 0;
@@ -186,10 +188,12 @@ struct WeightStack {
   GemmVariant prefill_variant = kVariantPrefillUp;
   GemmVariant decode_variant = kVariantDecode;
   GemmVariant decode_wide_variant = kVariantDecodeWide;
+  GemmVariant pair_variant = kVariantPairUp;
   // tensor maps exist only for the partial last K block; full K blocks are
   // plain bulk copies of contiguous, pre-swizzled panels
   CUtensorMap tail_prefill;
   CUtensorMap tail_decode;
+  CUtensorMap tail_pair;
 
   void upload(const nmoe_nvfp4_matrix* matrices, int count, int rows, int cols, bool is_up,
               const char* name, cudaStream_t stream) {
@@ -197,6 +201,7 @@ struct WeightStack {
     n = rows;
     k = cols;
     prefill_variant = is_up ? kVariantPrefillUp : kVariantPrefillDown;
+    pair_variant = is_up ? kVariantPairUp : kVariantPairDown;  // same BN and scale layout
     const size_t packed_each = static_cast<size_t>(rows) * cols / 2;
     const size_t sf_each = static_cast<size_t>(rows) * (cols / 16);
     DeviceBuffer row_major;
@@ -216,6 +221,7 @@ struct WeightStack {
     }
     const GemmVariantInfo pi = gemm_variant_info(prefill_variant);
     const GemmVariantInfo di = gemm_variant_info(decode_variant);
+    const int pair_rows = gemm_variant_info(pair_variant).b_rows;
     sf_prefill.allocate(weight_scale_layout_bytes(count, rows, cols, pi.bn, pi.sfb_groups));
     sf_decode.allocate(weight_scale_layout_bytes(count, rows, cols, di.bn, di.sfb_groups));
     NMOE_CUDA(relayout_weight_scales(sf_row_major.as<uint8_t>(), count, rows, cols, pi.bn,
@@ -237,6 +243,7 @@ struct WeightStack {
       try {
         tail_prefill = make_packed_map(packed_tail.as<uint8_t>(), panel_rows, tail_pitch, pi.bn);
         tail_decode = make_packed_map(packed_tail.as<uint8_t>(), panel_rows, tail_pitch, di.bn);
+        tail_pair = make_packed_map(packed_tail.as<uint8_t>(), panel_rows, tail_pitch, pair_rows);
       } catch (const Failure&) {
         narrow_tail = false;
       }
@@ -246,6 +253,7 @@ struct WeightStack {
       packed_tail.allocate(panel_rows * tail_pitch, true);
       tail_prefill = make_packed_map(packed_tail.as<uint8_t>(), panel_rows, tail_pitch, pi.bn);
       tail_decode = make_packed_map(packed_tail.as<uint8_t>(), panel_rows, tail_pitch, di.bn);
+      tail_pair = make_packed_map(packed_tail.as<uint8_t>(), panel_rows, tail_pitch, pair_rows);
     }
     if (tail_bytes == 0) {
       tail_pitch = 16;
@@ -258,18 +266,20 @@ struct WeightStack {
       // never read (k_blocks == kb_full), but the kernel takes a valid map
       tail_prefill = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, pi.bn);
       tail_decode = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, di.bn);
+      tail_pair = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, pair_rows);
     }
   }
 
   GemmVariant variant(TileClass c) const {
     return c == kClassPrefill ? prefill_variant
-                              : c == kClassDecode ? decode_variant : decode_wide_variant;
+           : c == kClassPair  ? pair_variant
+           : c == kClassDecode ? decode_variant : decode_wide_variant;
   }
   const CUtensorMap& tail_map(TileClass c) const {
-    return c == kClassPrefill ? tail_prefill : tail_decode;
+    return c == kClassPrefill ? tail_prefill : c == kClassPair ? tail_pair : tail_decode;
   }
   const uint8_t* sf(TileClass c) const {
-    return (c == kClassPrefill ? sf_prefill : sf_decode).as<uint8_t>();
+    return (c == kClassPrefill || c == kClassPair ? sf_prefill : sf_decode).as<uint8_t>();
   }
 };
 
@@ -586,7 +596,7 @@ nmoe_status nmoe_ffn_run(nmoe_ffn* ffn, void* stream_ptr, const void* input,
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   try {
     TileClass tile_class = rows <= 32 ? kClassDecode : rows <= 256 ? kClassDecodeWide : kClassPrefill;
-    if (gemm_variant >= 1 && gemm_variant <= 3) tile_class = static_cast<TileClass>(gemm_variant - 1);
+    if (gemm_variant >= 1 && gemm_variant <= 4) tile_class = static_cast<TileClass>(gemm_variant - 1);
     if (tile_class == kClassDecode && rows > 32) return NMOE_ERR_INVALID_ARGUMENT;
     NMOE_CUDA(launch_norm_quant(input, input_dtype == NMOE_BF16, static_cast<int>(rows),
                                 ffn->hidden, nullptr, 0.0f, nullptr, ffn->a_packed.as<uint8_t>(),
@@ -646,9 +656,13 @@ struct nmoe_layer {
   bool fast_router = false;
   int fast_router_min_tokens = 256;
   float router_tie_margin = 2.0e-4f;
-  int split_plane_rows = 0;
-  DeviceBuffer gate_bf16, y_split;
-  CUtensorMap split_map, gate_map;
+  DeviceBuffer gate_bf16, inv_rms;
+  CUtensorMap gate_map;
+  // The FP32 normalised rows are needed by the FP64 logits kernel of small batches,
+  // by the dense / scaled-FP8 linears and by the trace; the two-pass router of large
+  // batches rebuilds them on the fly, so they are only written there while a trace may
+  // be asked for (nmoe_layer_keep_trace).
+  bool keep_trace = true;
   WeightStack up, down, shared_up, shared_down;
 
   // Latent projections and the dense / scaled-FP8 families (fc1_latent, fc2_latent,
@@ -717,7 +731,13 @@ struct nmoe_layer {
   std::string last_error;
   RowKind last_parts_kind = kRowF32;
   bool last_unfused = false;
+  bool last_normalized = true;
   bool force_fp32_parts = false;  // NMOE_PARTS_FP32=1: FP32 rows whatever the output type
+  // CTA pairs for the prefill GEMMs (NMOE_GEMM_PAIR=1 turns them on), used once an
+  // expert has this many rows on average.  Off by default: with the partner CTA's
+  // "operands landed" relayed through a thread they measured slower than single CTAs.
+  bool pair_gemms = false;
+  int pair_min_rows = 640;
   // how long a kernel waits for a flag another GPU raises before it gives up with
   // kDevWaitTimeout (clock64 ticks; nmoe_layer_set_wait_limit_ms, NMOE_WAIT_LIMIT_MS)
   long long wait_limit_ticks = 1ll << 34;
@@ -733,10 +753,32 @@ struct nmoe_layer {
   bool window_shared_pending = false;
   RowKind window_shared_kind = kRowF32;  // type of shared_out for the pending combine
 
+  // Small batches are bound by launch overhead: the whole run is recorded once per
+  // (token count, buffers, types) as a CUDA graph and replayed afterwards.
+  // NMOE_GRAPH_MAX_TOKENS sets the largest batch handled this way (0 = never).
+  struct RecordedRun {
+    const void* input;
+    void* output;
+    int tokens;
+    int in_dtype, out_dtype;
+    RowKind parts_kind;
+    bool normalized;
+    cudaGraphExec_t exec;
+    uint64_t last_use;
+  };
+  std::vector<RecordedRun> recorded;
+  int graph_max_tokens = 256;
+  uint64_t run_counter = 0;
+  void drop_recorded() {
+    for (RecordedRun& r : recorded) cudaGraphExecDestroy(r.exec);
+    recorded.clear();
+  }
+
   // optional per-stage CUDA events (nmoe_layer_enable_stage_timing)
   bool stage_timing = false;
   cudaEvent_t stage_events[kStageCount + 1] = {};
   ~nmoe_layer() {
+    drop_recorded();
     window.close_peers();
     if (quant_done != nullptr) cudaEventDestroy(quant_done);
     if (shared_done != nullptr) cudaEventDestroy(shared_done);
@@ -754,16 +796,13 @@ namespace {
 // Everything whose size follows the token capacity.  Called at creation and by
 // nmoe_layer_reserve_tokens; weights are not touched.
 void allocate_scratch(nmoe_layer* L, size_t T) {
+  L->drop_recorded();  // recorded runs hold the old buffers' addresses
   const nmoe_config& c = L->cfg;
   const int H = c.hidden_size, I = c.routed_expert_intermediate_size,
             S = c.shared_expert_intermediate_size, E = c.n_routed_experts, K = c.top_k;
   const int EL = L->local_experts, Lr = L->latent;
   const size_t token_slots = (T + 127) / 128;
-  if (L->fast_router) {
-    L->split_plane_rows = static_cast<int>(token_slots * 128);
-    L->y_split.allocate(3 * token_slots * 128 * H * 2, true);
-    L->split_map = make_bf16_map(L->y_split.as<void>(), 3 * token_slots * 128, H, 128);
-  }
+  L->inv_rms.allocate(T * sizeof(float));
   L->normalized.allocate(T * H * sizeof(float));
   L->logits.allocate(T * E * sizeof(float));
   L->top_index.allocate(T * K * sizeof(int32_t));
@@ -804,7 +843,8 @@ void allocate_scratch(nmoe_layer* L, size_t T) {
                        : c.max_recv_pairs > 0 ? static_cast<size_t>(c.max_recv_pairs)
                                               : 2 * local_pairs;
   L->max_pairs = static_cast<int64_t>(pairs);
-  const size_t tiles_prefill = EL + (pairs + 127) / 128;
+  // (an expert may leave a partly filled slot, and an empty one when pairs consume them)
+  const size_t tiles_prefill = 2 * static_cast<size_t>(EL) + (pairs + 127) / 128;
   const size_t tiles_decode = EL + (std::min<size_t>(pairs, L->decode_pairs_limit) + 31) / 32;
   L->max_row_tiles = static_cast<int>(std::max(tiles_prefill, tiles_decode));
   const size_t slots = static_cast<size_t>(L->max_row_tiles);
@@ -883,6 +923,9 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
   L->cfg = c;
   L->num_sms = device_sm_count();
   L->force_fp32_parts = std::getenv("NMOE_PARTS_FP32") != nullptr;
+  if (const char* env = std::getenv("NMOE_GEMM_PAIR")) L->pair_gemms = std::atoi(env) != 0;
+  if (const char* env = std::getenv("NMOE_GRAPH_MAX_TOKENS")) L->graph_max_tokens = std::atoi(env);
+  if (const char* env = std::getenv("NMOE_GEMM_PAIR_MIN_ROWS")) L->pair_min_rows = std::atoi(env);
   if (const char* env = std::getenv("NMOE_WAIT_LIMIT_MS")) {
     const double ms = std::strtod(env, nullptr);
     if (ms > 0.0) L->wait_limit_ticks = ticks_from_ms(ms);
@@ -977,25 +1020,30 @@ void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dt
   int32_t* error = L->error.device.as<int32_t>();
   L->mark(0, stream);
   const bool two_pass_router = L->fast_router && tokens >= L->fast_router_min_tokens;
+  const bool in_bf16 = in_dtype == NMOE_BF16;
+  const bool want_normalized = !two_pass_router || L->keep_trace || L->latent_mode ||
+                               L->shared_up_dense.present;
   // RMSNorm (:795-796) fused with the activation quantiser every expert's
   // up_proj applies to the same normalised row (:913 -> nvfp4_packing.cpp:90)
-  NMOE_CUDA(launch_norm_quant(input, in_dtype == NMOE_BF16, tokens, H, L->norm_weight.as<float>(),
-                              c.rms_epsilon, L->normalized.as<float>(), L->y_packed.as<uint8_t>(),
-                              L->y_sf_row_major.as<uint8_t>(), L->y_sf_tiled.as<uint8_t>(),
-                              k_blocks_of(H), L->y_ts.as<float>(), stream,
-                              two_pass_router ? L->y_split.as<__nv_bfloat16>() : nullptr,
-                              static_cast<size_t>(L->split_plane_rows) * H));
+  NMOE_CUDA(launch_norm_quant(input, in_bf16, tokens, H, L->norm_weight.as<float>(),
+                              c.rms_epsilon, want_normalized ? L->normalized.as<float>() : nullptr,
+                              L->y_packed.as<uint8_t>(), L->y_sf_row_major.as<uint8_t>(),
+                              L->y_sf_tiled.as<uint8_t>(), k_blocks_of(H), L->y_ts.as<float>(),
+                              stream, L->inv_rms.as<float>()));
+  L->last_normalized = want_normalized;
   if (after_quantise != nullptr) NMOE_CUDA(cudaEventRecord(after_quantise, stream));
   L->mark(1, stream);
   // gate projection (:797-799) and top-k (:881)
   NMOE_CUDA(cudaMemsetAsync(L->counts.as<int32_t>(), 0, E * sizeof(int32_t), stream));
   const float* offset = L->has_logit_offset ? L->logit_offset.as<float>() : nullptr;
   if (two_pass_router) {
-    NMOE_CUDA(launch_router_fast_logits(L->split_map, L->gate_map, tokens, L->split_plane_rows, E,
-                                        H, L->logits.as<float>(), error, stream));
+    NMOE_CUDA(launch_router_fast_logits(input, in_bf16, L->inv_rms.as<float>(),
+                                        L->norm_weight.as<float>(), L->gate_map, tokens, E, H,
+                                        L->logits.as<float>(), error, stream));
     L->mark(2, stream);
     NMOE_CUDA(launch_router_select_exact(
-        L->logits.as<float>(), L->normalized.as<float>(), L->gate_bf16.as<__nv_bfloat16>(), offset,
+        L->logits.as<float>(), input, in_bf16, L->inv_rms.as<float>(),
+        L->norm_weight.as<float>(), L->gate_bf16.as<__nv_bfloat16>(), offset,
         L->bias.as<float>(), tokens, E, H, K, c.norm_topk_prob != 0, c.routed_scaling_factor,
         L->router_tie_margin, L->top_index.as<int32_t>(), L->top_weight.as<float>(),
         L->counts.as<int32_t>(), stream));
@@ -1037,7 +1085,8 @@ void run_ffn(nmoe_layer* L, bool unfused, const WeightStack& up, const WeightSta
     return;
   }
   // the row-storing epilogue exists for the BN = 128 tile shapes
-  const TileClass raw_class = tile_class == kClassPrefill ? kClassDecodeWide : tile_class;
+  const TileClass raw_class =
+      tile_class == kClassPrefill || tile_class == kClassPair ? kClassDecodeWide : tile_class;
   run_down_gemm(up, raw_class, a, a_ts, schedule, buffers.raw_rows, nullptr, 1, 0, nullptr,
                 /*relu2=*/true, error, L->num_sms, stream, kRowF32, RowSegments());
   NMOE_CUDA(launch_norm_quant(buffers.raw_rows, false, buffers.raw_row_count, up.n, nullptr, 0.0f,
@@ -1057,7 +1106,9 @@ void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& sou
   const int Lr = L->latent;
   int32_t* error = L->error.device.as<int32_t>();
   const bool decode = static_cast<long long>(pairs) <= L->decode_pairs_limit / 2;
-  const TileClass routed_class = decode ? kClassDecode : kClassPrefill;
+  const bool pair = !decode && L->pair_gemms && !L->unfused && (L->num_sms & 1) == 0 &&
+                    pairs / L->local_experts >= L->pair_min_rows;
+  const TileClass routed_class = decode ? kClassDecode : pair ? kClassPair : kClassPrefill;
   const int tile_rows = decode ? 32 : 128;
   PlanBuffers plan;
   plan.expert_counts = L->counts.as<int32_t>();
@@ -1065,7 +1116,8 @@ void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& sou
   plan.expert_slot0 = L->slot0.as<int32_t>();
   plan.row_tiles = L->row_tiles.as<RowTile>();
   plan.num_row_tiles = L->num_row_tiles.as<int32_t>();
-  NMOE_CUDA(launch_route_plan(plan, L->local_experts, tile_rows, L->max_row_tiles, error, stream));
+  NMOE_CUDA(launch_route_plan(plan, L->local_experts, tile_rows, pair ? 2 : 1, L->max_row_tiles,
+                              error, stream));
   L->mark(4, stream);
   NMOE_CUDA(launch_permute(plan, source, pairs, L->local_experts, tile_rows, L->max_row_tiles, Lr,
                            k_blocks_of(Lr),
@@ -1095,8 +1147,11 @@ void routed_experts(nmoe_layer* L, cudaStream_t stream, const PermuteSource& sou
 void shared_expert(nmoe_layer* L, cudaStream_t stream, int tokens, void* out_rows, int dest_mul,
                    int dest_add, cudaEvent_t between, RowKind out_kind = kRowF32) {
   const int H = L->cfg.hidden_size, S = L->cfg.shared_expert_intermediate_size;
-  const TileClass shared_class =
-      tokens <= 32 ? kClassDecode : tokens <= 256 ? kClassDecodeWide : kClassPrefill;
+  const bool pair = L->pair_gemms && (L->num_sms & 1) == 0 && tokens >= 1024;
+  const TileClass shared_class = tokens <= 32    ? kClassDecode
+                                 : tokens <= 256 ? kClassDecodeWide
+                                 : pair          ? kClassPair
+                                                 : kClassPrefill;
   Schedule shared;
   shared.dense_rows = tokens;
   int32_t* error = L->error.device.as<int32_t>();
@@ -1114,7 +1169,9 @@ void shared_expert(nmoe_layer* L, cudaStream_t stream, int tokens, void* out_row
     run_linear(L, L->shared_up_dense, L->normalized.as<float>(), tokens, raw, stream);
     NMOE_CUDA(launch_relu2(raw, static_cast<size_t>(tokens) * S, stream));
   } else {
-    run_down_gemm(L->shared_up, shared_class == kClassPrefill ? kClassDecodeWide : shared_class,
+    run_down_gemm(L->shared_up,
+                  shared_class == kClassPrefill || shared_class == kClassPair ? kClassDecodeWide
+                                                                              : shared_class,
                   L->y_op, L->y_ts.as<float>(), shared, raw, nullptr, 1, 0, nullptr, true, error,
                   L->num_sms, stream, kRowF32, RowSegments());
   }
@@ -1218,8 +1275,75 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
   // routed sum in selection order, mixer and residual (:951-953, :1064-1069)
   L->mark(9, stream);
   NMOE_CUDA(launch_combine(input, in_dtype == NMOE_BF16, L->parts.as<void>(), parts_kind, tokens,
-                           H, K, output, out_dtype == NMOE_BF16, stream));
+                           H, K, output, out_dtype == NMOE_BF16, L->error.device.as<int32_t>(),
+                           stream));
   L->mark(10, stream);
+}
+
+// nmoe_layer_run: small batches replay a recorded CUDA graph of the same run.
+void run_recorded_or_eager(nmoe_layer* L, cudaStream_t stream, const void* input,
+                           nmoe_dtype in_dtype, int tokens, void* output, nmoe_dtype out_dtype) {
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  const bool can_query = cudaStreamIsCapturing(stream, &capturing) == cudaSuccess;
+  if (!can_query) cudaGetLastError();
+  const bool eligible = tokens <= L->graph_max_tokens && !L->stage_timing && !L->unfused &&
+                        can_query && capturing == cudaStreamCaptureStatusNone &&
+                        stream != nullptr && stream != cudaStreamLegacy;
+  if (!eligible) {
+    layer_run_impl(L, stream, input, in_dtype, tokens, output, out_dtype);
+    return;
+  }
+  ++L->run_counter;
+  for (nmoe_layer::RecordedRun& r : L->recorded) {
+    if (r.input == input && r.output == output && r.tokens == tokens &&
+        r.in_dtype == in_dtype && r.out_dtype == out_dtype) {
+      r.last_use = L->run_counter;
+      NMOE_CUDA(cudaGraphLaunch(r.exec, stream));
+      L->last_tokens = tokens;
+      L->last_parts_kind = r.parts_kind;
+      L->last_normalized = r.normalized;
+      L->last_unfused = false;
+      return;
+    }
+  }
+  // record: the launches below go into a graph instead of onto the stream
+  if (cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    cudaGetLastError();      // this stream cannot be captured (e.g. the legacy default stream)
+    L->graph_max_tokens = 0;  // stay eager from now on
+    layer_run_impl(L, stream, input, in_dtype, tokens, output, out_dtype);
+    return;
+  }
+  cudaGraph_t graph = nullptr;
+  try {
+    layer_run_impl(L, stream, input, in_dtype, tokens, output, out_dtype);
+  } catch (...) {
+    cudaStreamEndCapture(stream, &graph);
+    if (graph != nullptr) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    throw;
+  }
+  NMOE_CUDA(cudaStreamEndCapture(stream, &graph));
+  cudaGraphExec_t exec = nullptr;
+  const cudaError_t made = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (made != cudaSuccess) {
+    cudaGetLastError();
+    L->graph_max_tokens = 0;
+    layer_run_impl(L, stream, input, in_dtype, tokens, output, out_dtype);
+    return;
+  }
+  if (L->recorded.size() >= 16) {  // forget the run that was used longest ago
+    size_t oldest = 0;
+    for (size_t i = 1; i < L->recorded.size(); ++i) {
+      if (L->recorded[i].last_use < L->recorded[oldest].last_use) oldest = i;
+    }
+    cudaGraphExecDestroy(L->recorded[oldest].exec);
+    L->recorded.erase(L->recorded.begin() + static_cast<long>(oldest));
+  }
+  L->recorded.push_back(nmoe_layer::RecordedRun{input, output, tokens, in_dtype, out_dtype,
+                                                L->last_parts_kind, L->last_normalized, exec,
+                                                L->run_counter});
+  NMOE_CUDA(cudaGraphLaunch(exec, stream));
 }
 
 }  // namespace
@@ -1260,8 +1384,8 @@ nmoe_status nmoe_layer_run(nmoe_layer* layer, void* stream, const void* input,
   if (tokens > layer->cfg.max_tokens) return NMOE_ERR_CAPACITY;
   if (layer->ep_world != 1) return NMOE_ERR_INVALID_ARGUMENT;  // use the nmoe_ep_* stages
   try {
-    layer_run_impl(layer, static_cast<cudaStream_t>(stream), input, input_dtype,
-                   static_cast<int>(tokens), output, output_dtype);
+    run_recorded_or_eager(layer, static_cast<cudaStream_t>(stream), input, input_dtype,
+                          static_cast<int>(tokens), output, output_dtype);
   } catch (const Failure& failure) {
     layer->last_error = failure.message;
     if (std::getenv("NEMOTRON_FORWARD_DEBUG") != nullptr) {
@@ -1288,6 +1412,7 @@ nmoe_status nmoe_layer_reserve_sms(nmoe_layer* layer, int32_t reserved_sms) {
   if (layer == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
   const int all = device_sm_count();
   if (reserved_sms < 0 || reserved_sms >= all) return NMOE_ERR_INVALID_ARGUMENT;
+  layer->drop_recorded();
   layer->num_sms = all - reserved_sms;
   return NMOE_OK;
 }
@@ -1471,7 +1596,7 @@ nmoe_status nmoe_ep_combine(nmoe_layer* layer, void* stream_ptr, const void* inp
       input, input_dtype == NMOE_BF16, returned_rows, static_cast<RowKind>(rows_dtype),
       layer->send_position.as<int32_t>(), layer->shared_out.as<void>(), kRowF32, layer->last_tokens,
       layer->cfg.hidden_size, layer->cfg.top_k, output, output_dtype == NMOE_BF16,
-      static_cast<cudaStream_t>(stream_ptr));
+      layer->error.device.as<int32_t>(), static_cast<cudaStream_t>(stream_ptr));
   return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
 }
 
@@ -1719,7 +1844,8 @@ nmoe_status nmoe_ep_window_combine(nmoe_layer* layer, void* stream_ptr, const vo
                                  w.local.as<uint8_t>() + w.rows_off, w.rows_kind,
                                  layer->send_position.as<int32_t>(), layer->shared_out.as<void>(),
                                  layer->window_shared_kind, layer->last_tokens, layer->cfg.hidden_size, layer->cfg.top_k,
-                                 output, output_dtype == NMOE_BF16, stream);
+                                 output, output_dtype == NMOE_BF16,
+                                 layer->error.device.as<int32_t>(), stream);
   }
   return err == cudaSuccess ? NMOE_OK : NMOE_ERR_CUDA;
 }
@@ -1730,7 +1856,7 @@ const char* nmoe_layer_last_error(const nmoe_layer* layer) {
 
 nmoe_status nmoe_layer_trace_view(nmoe_layer* layer, nmoe_trace_view* out) {
   if (layer == nullptr || out == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
-  out->normalized_input = layer->normalized.as<float>();
+  out->normalized_input = layer->last_normalized ? layer->normalized.as<float>() : nullptr;
   out->router_logits = layer->logits.as<float>();
   out->selected_index = layer->top_index.as<int32_t>();
   out->selected_weight = layer->top_weight.as<float>();
@@ -1761,6 +1887,13 @@ nmoe_status nmoe_layer_copy_trace_field(nmoe_layer* layer, void* stream, int32_t
                          static_cast<cudaStream_t>(stream)) == cudaSuccess
              ? NMOE_OK
              : NMOE_ERR_CUDA;
+}
+
+nmoe_status nmoe_layer_keep_trace(nmoe_layer* layer, int32_t enable) {
+  if (layer == nullptr) return NMOE_ERR_INVALID_ARGUMENT;
+  if (layer->keep_trace != (enable != 0)) layer->drop_recorded();
+  layer->keep_trace = enable != 0;
+  return NMOE_OK;
 }
 
 nmoe_status nmoe_layer_reserve_tokens(nmoe_layer* layer, int32_t max_tokens) {

@@ -17,8 +17,8 @@
 namespace nmoe {
 namespace {
 
-__global__ void route_plan_kernel(PlanBuffers plan, int experts, int tile_rows, int max_row_tiles,
-                                  int32_t* error) {
+__global__ void route_plan_kernel(PlanBuffers plan, int experts, int tile_rows, int tile_multiple,
+                                  int max_row_tiles, int32_t* error) {
   __shared__ int32_t first_tile[513];
   const int e = threadIdx.x;
   int tiles = 0;
@@ -26,6 +26,7 @@ __global__ void route_plan_kernel(PlanBuffers plan, int experts, int tile_rows, 
   if (e < experts) {
     count = plan.expert_counts[e];
     tiles = (count + tile_rows - 1) / tile_rows;
+    tiles = (tiles + tile_multiple - 1) / tile_multiple * tile_multiple;
     first_tile[e + 1] = tiles;
   }
   if (e == 0) first_tile[0] = 0;
@@ -54,7 +55,7 @@ __global__ void route_plan_kernel(PlanBuffers plan, int experts, int tile_rows, 
       if (base + i >= max_row_tiles) break;
       RowTile tile;
       tile.row0 = (base + i) * 128;
-      tile.rows = min(tile_rows, count - i * tile_rows);
+      tile.rows = max(0, min(tile_rows, count - i * tile_rows));
       tile.expert = e;
       tile.reserved = 0;
       plan.row_tiles[base + i] = tile;
@@ -197,7 +198,8 @@ __device__ __forceinline__ void store_row8(void* base, size_t row, int hidden, i
 // accesses; the parts are rows of RowKind PARTS.
 template <bool IN_BF16, bool OUT_BF16, int PARTS>
 __global__ void combine_kernel(const void* __restrict__ in, const void* __restrict__ parts,
-                               int rows, int hidden, int top_k, void* __restrict__ out) {
+                               int rows, int hidden, int top_k, void* __restrict__ out,
+                               int32_t* __restrict__ error) {
   const int octs = hidden / 8;
   const size_t total = static_cast<size_t>(rows) * octs;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -216,30 +218,44 @@ __global__ void combine_kernel(const void* __restrict__ in, const void* __restri
     float shared[8], x[8], r[8];
     load_row8<PARTS>(parts, first + top_k, hidden, c, shared);
     load_row8<IN_BF16 ? kRowBf16 : kRowF32>(in, t, hidden, c, x);
+    bool finite = true;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) r[j] = __fadd_rn(x[j], __fadd_rn(routed[j], shared[j]));
+    for (int j = 0; j < 8; ++j) {
+      const float mixer = __fadd_rn(routed[j], shared[j]);
+      finite = finite && isfinite(mixer);
+      r[j] = __fadd_rn(x[j], mixer);
+    }
+    if constexpr (PARTS == kRowF16) {
+      // a row that left binary16's range on its way here (the GEMM stores an infinity)
+      if (!finite && error != nullptr) atomicCAS(error, kDevOk, kDevActivationRange);
+    }
     store_row8<OUT_BF16>(out, t, hidden, c, r);
   }
 }
 
 template <bool A, bool B>
 void launch_combine_t(const void* in, const void* parts, RowKind parts_kind, int rows, int hidden,
-                      int top_k, void* out, int blocks, cudaStream_t stream) {
+                      int top_k, void* out, int32_t* error, int blocks, cudaStream_t stream) {
   if (parts_kind == kRowBf16) {
-    combine_kernel<A, B, kRowBf16><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+    combine_kernel<A, B, kRowBf16><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out,
+                                                               error);
   } else if (parts_kind == kRowF16) {
-    combine_kernel<A, B, kRowF16><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+    combine_kernel<A, B, kRowF16><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out,
+                                                              error);
   } else {
-    combine_kernel<A, B, kRowF32><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out);
+    combine_kernel<A, B, kRowF32><<<blocks, 256, 0, stream>>>(in, parts, rows, hidden, top_k, out,
+                                                              error);
   }
 }
 
 }  // namespace
 
 cudaError_t launch_route_plan(const PlanBuffers& plan, int experts, int tile_rows,
-                              int max_row_tiles, int32_t* error, cudaStream_t stream) {
-  if (experts <= 0 || experts > 512) return cudaErrorInvalidValue;
-  route_plan_kernel<<<1, 512, 0, stream>>>(plan, experts, tile_rows, max_row_tiles, error);
+                              int tile_multiple, int max_row_tiles, int32_t* error,
+                              cudaStream_t stream) {
+  if (experts <= 0 || experts > 512 || tile_multiple < 1) return cudaErrorInvalidValue;
+  route_plan_kernel<<<1, 512, 0, stream>>>(plan, experts, tile_rows, tile_multiple, max_row_tiles,
+                                           error);
   return cudaGetLastError();
 }
 
@@ -258,18 +274,18 @@ cudaError_t launch_permute(const PlanBuffers& plan, const PermuteSource& src, in
 
 cudaError_t launch_combine(const void* in, bool in_bf16, const void* parts, RowKind parts_kind,
                            int rows, int hidden, int top_k, void* out, bool out_bf16,
-                           cudaStream_t stream) {
+                           int32_t* error, cudaStream_t stream) {
   if (rows <= 0 || hidden % 8 != 0 || top_k < 1) return cudaErrorInvalidValue;
   const size_t total = static_cast<size_t>(rows) * (hidden / 8);
   const int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 16));
   if (in_bf16 && out_bf16) {
-    launch_combine_t<true, true>(in, parts, parts_kind, rows, hidden, top_k, out, blocks, stream);
+    launch_combine_t<true, true>(in, parts, parts_kind, rows, hidden, top_k, out, error, blocks, stream);
   } else if (in_bf16) {
-    launch_combine_t<true, false>(in, parts, parts_kind, rows, hidden, top_k, out, blocks, stream);
+    launch_combine_t<true, false>(in, parts, parts_kind, rows, hidden, top_k, out, error, blocks, stream);
   } else if (out_bf16) {
-    launch_combine_t<false, true>(in, parts, parts_kind, rows, hidden, top_k, out, blocks, stream);
+    launch_combine_t<false, true>(in, parts, parts_kind, rows, hidden, top_k, out, error, blocks, stream);
   } else {
-    launch_combine_t<false, false>(in, parts, parts_kind, rows, hidden, top_k, out, blocks, stream);
+    launch_combine_t<false, false>(in, parts, parts_kind, rows, hidden, top_k, out, error, blocks, stream);
   }
   return cudaGetLastError();
 }

@@ -62,7 +62,7 @@ norm_quant_kernel(const void* __restrict__ in, int rows, int cols,
                   float* __restrict__ normalized, uint8_t* __restrict__ packed,
                   uint8_t* __restrict__ sf_row_major, uint8_t* __restrict__ sf_tiled, int k_tiles,
                   float* __restrict__ tensor_scale, const float* __restrict__ global_amax,
-                  __nv_bfloat16* __restrict__ split, size_t split_plane) {
+                  float* __restrict__ inv_rms_out) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * kWarpsPerBlock + warp;
@@ -101,6 +101,7 @@ norm_quant_kernel(const void* __restrict__ in, int rows, int cols,
     sum = __shfl_sync(0xffffffffu, sum, 0);
     const float mean = __fdiv_rn(sum, static_cast<float>(cols));
     inv_rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+    if (lane == 0 && inv_rms_out != nullptr) inv_rms_out[row] = inv_rms;
   }
 
   const int chunks = cols / 8;
@@ -151,30 +152,6 @@ norm_quant_kernel(const void* __restrict__ in, int rows, int cols,
         float* dst = normalized + row_base + static_cast<size_t>(ch) * 8;
         *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
         *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
-      }
-      if (split != nullptr) {
-        // y = hi + mid + lo with three bf16 terms (24 significand bits): the
-        // operand of the tensor-core pass of the router
-        uint32_t w[3][4];
-#pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          float rem[2] = {v[i], v[i + 1]};
-#pragma unroll
-          for (int term = 0; term < 3; ++term) {
-            const __nv_bfloat16 a = __float2bfloat16_rn(rem[0]);
-            const __nv_bfloat16 b = __float2bfloat16_rn(rem[1]);
-            rem[0] = __fsub_rn(rem[0], __bfloat162float(a));
-            rem[1] = __fsub_rn(rem[1], __bfloat162float(b));
-            w[term][i / 2] = static_cast<uint32_t>(__bfloat16_as_ushort(a)) |
-                             (static_cast<uint32_t>(__bfloat16_as_ushort(b)) << 16);
-          }
-        }
-#pragma unroll
-        for (int term = 0; term < 3; ++term) {
-          *reinterpret_cast<uint4*>(split + term * split_plane + row_base +
-                                    static_cast<size_t>(ch) * 8) =
-              make_uint4(w[term][0], w[term][1], w[term][2], w[term][3]);
-        }
       }
     }
     // a 16-block is shared by lanes (2i, 2i+1)
@@ -264,18 +241,18 @@ cudaError_t launch_norm_quant(const void* in, bool in_bf16, int rows, int cols,
                               const float* norm_weight, float eps, float* normalized,
                               uint8_t* packed, uint8_t* sf_row_major, uint8_t* sf_tiled,
                               int k_blocks, float* tensor_scale, cudaStream_t stream,
-                              __nv_bfloat16* split, size_t split_plane) {
+                              float* inv_rms) {
   if (rows <= 0 || cols <= 0 || cols % 16 != 0) return cudaErrorInvalidValue;
   const int grid = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   const int threads = kWarpsPerBlock * 32;
   if (in_bf16) {
     norm_quant_kernel<true, true><<<grid, threads, 0, stream>>>(
         in, rows, cols, norm_weight, eps, normalized, packed, sf_row_major, sf_tiled,
-        k_blocks * 4, tensor_scale, nullptr, split, split_plane);
+        k_blocks * 4, tensor_scale, nullptr, inv_rms);
   } else {
     norm_quant_kernel<false, true><<<grid, threads, 0, stream>>>(
         in, rows, cols, norm_weight, eps, normalized, packed, sf_row_major, sf_tiled,
-        k_blocks * 4, tensor_scale, nullptr, split, split_plane);
+        k_blocks * 4, tensor_scale, nullptr, inv_rms);
   }
   return cudaGetLastError();
 }
@@ -291,7 +268,7 @@ cudaError_t launch_quant_matrix(const float* in, int rows, int cols, uint8_t* pa
   const int grid = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock;
   norm_quant_kernel<false, false><<<grid, kWarpsPerBlock * 32, 0, stream>>>(
       in, rows, cols, nullptr, 0.0f, nullptr, packed, sf_row_major, nullptr, 0, tensor_scale,
-      amax_scratch, nullptr, 0);
+      amax_scratch, nullptr);
   return cudaGetLastError();
 }
 

@@ -261,11 +261,14 @@ cudaError_t launch_router_logits(const float* normalized, const float* gate,
     const int warps = ((rows + 1) / 2) * (experts / 16);
     router_logits_kernel<2, 16><<<(warps + kWarps - 1) / kWarps, kWarps * 32, 0, stream>>>(
         normalized, gate, logit_offset, rows, experts, hidden, logits);
-  } else if (experts % 4 == 0) {
+  } else if (experts % 4 == 0 && rows * (experts / 4) >= 148 * kWarps) {
+    // four experts per warp once that still gives every SM a block
     const int warps = rows * (experts / 4);
     router_logits_kernel<1, 4><<<(warps + kWarps - 1) / kWarps, kWarps * 32, 0, stream>>>(
         normalized, gate, logit_offset, rows, experts, hidden, logits);
   } else {
+    // a handful of rows: one (row, expert) pair per warp, so that the gate streams
+    // through all SMs instead of a few
     const int warps = rows * experts;
     router_logits_kernel<1, 1><<<(warps + kWarps - 1) / kWarps, kWarps * 32, 0, stream>>>(
         normalized, gate, logit_offset, rows, experts, hidden, logits);

@@ -6,10 +6,14 @@
 // index sets bit for bit needs logits that round like an FP64 sum, but FP64 for
 // every (token, expert) pair costs more than the expert GEMMs.  So:
 //
-//  pass 1  all logits on the tensor cores: the FP32 normalised activations are
-//          split into three bf16 terms (hi + mid + lo carries the full 24-bit
-//          significand), the gate is bf16, products are exact and accumulate in
-//          FP32 (tcgen05.mma.kind::f16, TMA-fed, accumulator in TMEM);
+//  pass 1  all logits on the tensor cores.  The FP32 normalised activation
+//          y = (x * inv_rms) * w is recomputed in the kernel from the layer input
+//          (the same two roundings as the RMSNorm kernel), split into three bf16
+//          terms (hi + mid + lo carries the full 24-bit significand) that go
+//          straight into shared memory in the tensor core's 128-byte swizzle;
+//          the gate is bf16, products are exact and accumulate in FP32
+//          (tcgen05.mma.kind::f16, accumulator in TMEM).  Nothing but the layer
+//          input is read per token: no FP32 copy of y, no bf16 planes in HBM;
 //  pass 2  per token, every expert whose pass-1 choice score lies within
 //          `tie_margin` of the top_k-th score is re-evaluated with the FP64 sum
 //          and the selection runs on those exact values.
@@ -29,7 +33,8 @@ namespace {
 constexpr int kFastStages = 3;
 constexpr int kFastBlockK = 64;                 // bf16 elements per 128-byte row
 constexpr int kFastABytes = 3 * 128 * 128;      // three planes of 128 rows x 128 B
-constexpr int kFastThreads = 192;
+constexpr int kSplitWarps = 8;                  // warps that build the planes, then store
+constexpr int kFastThreads = (2 + kSplitWarps) * 32;
 
 __device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                                  uint32_t idesc, uint32_t accumulate) {
@@ -46,11 +51,32 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
+// Eight consecutive input elements of one row as FP32.
+template <bool BF16>
+__device__ __forceinline__ void load_x8(const void* x, size_t index, float (&v)[8]) {
+  if constexpr (BF16) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(
+        reinterpret_cast<const __nv_bfloat16*>(x) + index);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  } else {
+    const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + index);
+    const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + index + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+}
+
+template <bool IN_BF16>
 __global__ void __launch_bounds__(kFastThreads, 1)
-router_fast_logits_kernel(const __grid_constant__ CUtensorMap tmap_split,
-                          const __grid_constant__ CUtensorMap tmap_gate, int rows,
-                          int split_plane_rows, int experts, int hidden, float* __restrict__ logits,
-                          int32_t* error) {
+router_fast_logits_kernel(const void* __restrict__ x, const float* __restrict__ inv_rms,
+                          const float* __restrict__ norm_weight,
+                          const __grid_constant__ CUtensorMap tmap_gate, int rows, int experts,
+                          int hidden, float* __restrict__ logits, int32_t* error) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) &
                                              ~static_cast<uintptr_t>(1023u));
@@ -70,12 +96,13 @@ router_fast_logits_kernel(const __grid_constant__ CUtensorMap tmap_split,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kFastStages; ++s) {
-      mbar_init(&full_bar[s], 1);
+      // the gate tile arrives by TMA (one arrive + bytes), the planes are written by
+      // the split warps (one arrive each)
+      mbar_init(&full_bar[s], 1 + kSplitWarps);
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(done_bar, 1);
     fence_barrier_init();
-    prefetch_tensormap(&tmap_split);
     prefetch_tensormap(&tmap_gate);
   }
   if (warp == 1) {
@@ -96,11 +123,7 @@ router_fast_logits_kernel(const __grid_constant__ CUtensorMap tmap_split,
           if (error != nullptr) atomicCAS(error, kDevOk, kDevWaitTimeout);
           break;
         }
-        mbar_arrive_expect_tx(&full_bar[stage], kFastABytes + b_bytes);
-        for (int plane = 0; plane < 3; ++plane) {
-          tma_load_2d(sA + stage * kFastABytes + plane * (128 * 128), &tmap_split,
-                      kb * kFastBlockK, plane * split_plane_rows + row0, &full_bar[stage]);
-        }
+        mbar_arrive_expect_tx(&full_bar[stage], b_bytes);
         tma_load_2d(sB + stage * b_bytes, &tmap_gate, kb * kFastBlockK, 0, &full_bar[stage]);
         if (++stage == kFastStages) {
           stage = 0;
@@ -142,24 +165,105 @@ router_fast_logits_kernel(const __grid_constant__ CUtensorMap tmap_split,
       if (ok) tcgen05_commit(done_bar);
     }
   } else {
-    const int quarter = warp & 3;
-    const int row = row0 + quarter * 32 + lane;
-    if (mbar_wait(done_bar, 0)) {
-      tcgen05_fence_after();
-      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-      for (int c = 0; c < experts; c += 16) {
-        float v[16];
-        tmem_ld_x16(t_addr + c, v);
-        if (row < rows) {
-          float* dst = logits + static_cast<size_t>(row) * experts + c;
+    // ------------------------------------------------- split warps, then epilogue
+    // Thread s of the 256 owns 16-byte chunk (s % 8) of rows (s / 8) + 32 j, j = 0..3,
+    // of every K block: eight threads read one row's 128 (bf16) or 256 (FP32) bytes
+    // together and write the row's three 128-byte plane rows, chunk c of row r at
+    // position c ^ (r % 8) (the tensor core's 128-byte swizzle).
+    const int s = threadIdx.x - 64;
+    const int chunk = s & 7;
+    float rinv[4];
+    int row_of[4];
 #pragma unroll
-          for (int i = 0; i < 16; i += 4) {
-            *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    for (int j = 0; j < 4; ++j) {
+      row_of[j] = (s >> 3) + 32 * j;
+      const int row = row0 + row_of[j];
+      rinv[j] = row < rows ? inv_rms[row] : 0.0f;
+    }
+    float xv[4][8];
+    auto fetch = [&](int kb) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int row = min(row0 + row_of[j], rows - 1);
+        load_x8<IN_BF16>(x, static_cast<size_t>(row) * hidden + kb * kFastBlockK + chunk * 8, xv[j]);
+      }
+    };
+    fetch(0);
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int kb = 0; kb < k_blocks; ++kb) {
+      const float4 w0 = *reinterpret_cast<const float4*>(norm_weight + kb * kFastBlockK + chunk * 8);
+      const float4 w1 =
+          *reinterpret_cast<const float4*>(norm_weight + kb * kFastBlockK + chunk * 8 + 4);
+      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      uint32_t words[4][3][4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+          // y exactly as the RMSNorm kernel rounds it: (x * inv_rms) * w
+          float rem[2] = {__fmul_rn(__fmul_rn(xv[j][i], rinv[j]), w[i]),
+                          __fmul_rn(__fmul_rn(xv[j][i + 1], rinv[j]), w[i + 1])};
+#pragma unroll
+          for (int term = 0; term < 3; ++term) {
+            const __nv_bfloat16 a = __float2bfloat16_rn(rem[0]);
+            const __nv_bfloat16 b = __float2bfloat16_rn(rem[1]);
+            rem[0] = __fsub_rn(rem[0], __bfloat162float(a));
+            rem[1] = __fsub_rn(rem[1], __bfloat162float(b));
+            words[j][term][i / 2] = static_cast<uint32_t>(__bfloat16_as_ushort(a)) |
+                                    (static_cast<uint32_t>(__bfloat16_as_ushort(b)) << 16);
           }
         }
       }
-    } else if (error != nullptr) {
-      atomicCAS(error, kDevOk, kDevWaitTimeout);
+      if (kb + 1 < k_blocks) fetch(kb + 1);  // in flight while this block is stored
+      if (ok && !mbar_wait(&empty_bar[stage], phase ^ 1u)) {
+        if (error != nullptr) atomicCAS(error, kDevOk, kDevWaitTimeout);
+        ok = false;
+      }
+      if (ok) {
+        uint8_t* planes = sA + stage * kFastABytes;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = row_of[j];
+          const int offset = r * 128 + ((chunk ^ (r & 7)) << 4);
+#pragma unroll
+          for (int term = 0; term < 3; ++term) {
+            *reinterpret_cast<uint4*>(planes + term * (128 * 128) + offset) =
+                make_uint4(words[j][term][0], words[j][term][1], words[j][term][2],
+                           words[j][term][3]);
+          }
+        }
+        fence_proxy_async_smem();  // the tensor core reads these stores
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_bar[stage]);
+      }
+      if (++stage == kFastStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+    // epilogue: the first four split warps own one TMEM lane quarter each
+    if (warp < 6) {
+      const int quarter = warp & 3;
+      const int row = row0 + quarter * 32 + lane;
+      if (ok && mbar_wait(done_bar, 0)) {
+        tcgen05_fence_after();
+        const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        for (int c = 0; c < experts; c += 16) {
+          float v[16];
+          tmem_ld_x16(t_addr + c, v);
+          if (row < rows) {
+            float* dst = logits + static_cast<size_t>(row) * experts + c;
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            }
+          }
+        }
+      } else if (error != nullptr) {
+        atomicCAS(error, kDevOk, kDevWaitTimeout);
+      }
     }
   }
   tcgen05_fence_before();
@@ -186,35 +290,29 @@ __device__ __forceinline__ float sigmoid_exact(float v) {
   return __fdiv_rn(e, __fadd_rn(1.0f, e));
 }
 
-struct Pick {
-  float value;
-  int index;
-};
-
-__device__ __forceinline__ Pick better_pick(Pick a, Pick b) {
-  if (b.index < 0) return a;
-  if (a.index < 0) return b;
-  if (b.value > a.value || (b.value == a.value && b.index < a.index)) return b;
-  return a;
+// Order-preserving map of a float onto unsigned integers (0 is below every value), so
+// that a warp-wide maximum is one redux instruction.
+__device__ __forceinline__ uint32_t ordered_bits(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
-__device__ __forceinline__ Pick warp_pick(Pick mine) {
-#pragma unroll
-  for (int stride = 16; stride > 0; stride >>= 1) {
-    Pick other;
-    other.value = __shfl_xor_sync(0xffffffffu, mine.value, stride);
-    other.index = __shfl_xor_sync(0xffffffffu, mine.index, stride);
-    mine = better_pick(mine, other);
-  }
-  return mine;
+// The largest key of the warp and, among its holders, the smallest index
+// (SelectTopExperts ranks by value; ties resolve to the lower expert index).
+__device__ __forceinline__ void warp_arg_max(uint32_t key, uint32_t index, uint32_t& best_key,
+                                             uint32_t& best_index) {
+  best_key = __reduce_max_sync(0xffffffffu, key);
+  best_index = __reduce_min_sync(0xffffffffu, key == best_key ? index : 0xffffffffu);
 }
 
-// One warp per token runs a long dependent chain (two top-k searches, the FP64 dot
-// products, their reductions), so the kernel lives on occupancy: at most 64 registers
-// per thread (8 blocks of 4 warps per SM) and four candidates per FP64 batch.
+// One warp per token.  The FP64 dot products dominate; everything around them is kept
+// to a few warp-wide redux steps per selected expert.
 constexpr int kSelectBatch = 4;
+template <bool IN_BF16>
 __global__ void __launch_bounds__(kSelectWarps * 32, 8)
-router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__ normalized,
+router_select_exact_kernel(float* __restrict__ logits, const void* __restrict__ x,
+                           const float* __restrict__ inv_rms,
+                           const float* __restrict__ norm_weight,
                            const __nv_bfloat16* __restrict__ gate,
                            const float* __restrict__ logit_offset, const float* __restrict__ bias,
                            int rows, int experts, int hidden, int top_k, bool norm_topk_prob,
@@ -229,42 +327,51 @@ router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__
   const int per_lane = experts / 32;
   float* row_logits = logits + static_cast<size_t>(row) * experts;
 
-  // pass-1 scores (single precision is enough here: the margin covers it)
-  float fast_logit[kSelectPerLane];
+  // pass-1 choice scores (single precision is enough here: the margin covers it);
+  // lane L holds experts L, L + 32, ...
   float choice[kSelectPerLane];
+  uint32_t key[kSelectPerLane];
 #pragma unroll
   for (int j = 0; j < kSelectPerLane; ++j) {
-    fast_logit[j] = 0.0f;
     choice[j] = -INFINITY;
+    key[j] = 0u;
     if (j < per_lane) {
       const int e = lane + 32 * j;
       float l = row_logits[e];
-      if (logit_offset != nullptr) l = __fadd_rn(l, logit_offset[e]);
-      fast_logit[j] = l;
+      if (logit_offset != nullptr) {
+        l = __fadd_rn(l, logit_offset[e]);
+        row_logits[e] = l;  // what the trace shows for experts that are not re-evaluated
+      }
       choice[j] = __fdividef(1.0f, 1.0f + __expf(-l)) + bias[e];
+      key[j] = ordered_bits(choice[j]);
     }
   }
-  // top_k-th largest pass-1 choice
-  uint32_t taken = 0;
-  float kth = 0.0f;
+  // the top_k-th largest pass-1 choice
+  uint32_t kth_key = 0u;
   for (int r = 0; r < top_k; ++r) {
-    Pick local;
-    local.index = -1;
-    local.value = 0.0f;
+    uint32_t local_key = 0u, local_index = 0xffffffffu;
 #pragma unroll
     for (int j = 0; j < kSelectPerLane; ++j) {
-      if (j < per_lane && ((taken >> j) & 1u) == 0u) {
-        Pick cand;
-        cand.value = choice[j];
-        cand.index = lane + 32 * j;
-        local = better_pick(local, cand);
+      if (key[j] > local_key) {  // ascending j is ascending expert index: first maximum wins
+        local_key = key[j];
+        local_index = static_cast<uint32_t>(lane + 32 * j);
       }
     }
-    const Pick b = warp_pick(local);
-    if ((b.index & 31) == lane) taken |= 1u << (b.index >> 5);
-    kth = b.value;
+    uint32_t best_index;
+    warp_arg_max(local_key, local_index, kth_key, best_index);
+    if ((best_index & 31u) == static_cast<uint32_t>(lane)) {
+#pragma unroll
+      for (int j = 0; j < kSelectPerLane; ++j) {
+        if (j == static_cast<int>(best_index >> 5)) key[j] = 0u;  // taken
+      }
+    }
   }
   // candidates: everything that could still be in the exact top-k
+  float kth = 0.0f;
+  {
+    const uint32_t b = (kth_key & 0x80000000u) ? (kth_key & 0x7fffffffu) : ~kth_key;
+    kth = __uint_as_float(b);
+  }
   const float threshold = kth - tie_margin;
   uint32_t mine = 0;
 #pragma unroll
@@ -287,8 +394,9 @@ router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__
   __syncwarp();
 
   // FP64 logits of the candidates, up to kSelectBatch at a time; every lane takes
-  // eight consecutive hidden elements per step (16-byte gate loads)
-  const float* y = normalized + static_cast<size_t>(row) * hidden;
+  // eight consecutive hidden elements per step.  y is rebuilt from the layer input with
+  // the RMSNorm kernel's own two roundings: (x * inv_rms) * w.
+  const float rinv = inv_rms[row];
   const int chunks = hidden / 8;
   constexpr int kBatch = kSelectBatch;
   for (int base = 0; base < total; base += kBatch) {
@@ -301,19 +409,26 @@ router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__
       acc[i] = 0.0;
     }
     for (int ch = lane; ch < chunks; ch += 32) {
-      const float4 y0 = *reinterpret_cast<const float4*>(y + ch * 8);
-      const float4 y1 = *reinterpret_cast<const float4*>(y + ch * 8 + 4);
-      const double a[8] = {y0.x, y0.y, y0.z, y0.w, y1.x, y1.y, y1.z, y1.w};
+      float xv[8];
+      load_x8<IN_BF16>(x, static_cast<size_t>(row) * hidden + ch * 8, xv);
+      const float4 w0 = *reinterpret_cast<const float4*>(norm_weight + ch * 8);
+      const float4 w1 = *reinterpret_cast<const float4*>(norm_weight + ch * 8 + 4);
+      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      double a[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        a[i] = static_cast<double>(__fmul_rn(__fmul_rn(xv[i], rinv), w[i]));
+      }
 #pragma unroll
       for (int i = 0; i < kBatch; ++i) {
         if (i < batch) {
           const uint4 g = *reinterpret_cast<const uint4*>(gate + static_cast<size_t>(e[i]) * hidden +
                                                           ch * 8);
-          const uint32_t w[4] = {g.x, g.y, g.z, g.w};
+          const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            acc[i] = fma(a[2 * j], static_cast<double>(__uint_as_float(w[j] << 16)), acc[i]);
-            acc[i] = fma(a[2 * j + 1], static_cast<double>(__uint_as_float(w[j] & 0xffff0000u)),
+            acc[i] = fma(a[2 * j], static_cast<double>(__uint_as_float(gw[j] << 16)), acc[i]);
+            acc[i] = fma(a[2 * j + 1], static_cast<double>(__uint_as_float(gw[j] & 0xffff0000u)),
                          acc[i]);
           }
         }
@@ -335,49 +450,58 @@ router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__
   }
   __syncwarp();
 
-  // exact scores of the candidates; everything else is out of the running
+  // exact scores, compacted: lane L takes candidates L, L + 32, ... of the list, so the
+  // double-precision exponential runs once per lane instead of once per expert slot
   float score[kSelectPerLane];
+  uint32_t cand_key[kSelectPerLane];
+  int cand_expert[kSelectPerLane];
+  const int rounds = (total + 31) / 32;
 #pragma unroll
   for (int j = 0; j < kSelectPerLane; ++j) {
     score[j] = 0.0f;
-    if (j < per_lane) {
-      const int ex = lane + 32 * j;
-      if ((mine >> j) & 1u) {
+    cand_key[j] = 0u;
+    cand_expert[j] = -1;
+    if (j < rounds) {
+      const int slot = lane + 32 * j;
+      if (slot < total) {
+        const int ex = candidate_list[warp][slot];
         const float l = *reinterpret_cast<volatile float*>(row_logits + ex);
         score[j] = sigmoid_exact(l);
-        choice[j] = __fadd_rn(score[j], bias[ex]);
-      } else {
-        row_logits[ex] = fast_logit[j];  // pass-1 value (with the offset) for the trace
+        cand_key[j] = ordered_bits(__fadd_rn(score[j], bias[ex]));
+        cand_expert[j] = ex;
       }
     }
   }
-  taken = ~mine;  // non-candidates are never picked
   int my_index = -1;
   float my_score = 0.0f;
   for (int r = 0; r < top_k; ++r) {
-    Pick local;
-    local.index = -1;
-    local.value = 0.0f;
+    uint32_t local_key = 0u, local_index = 0xffffffffu;
+    float local_score = 0.0f;
+    int local_slot = -1;
 #pragma unroll
     for (int j = 0; j < kSelectPerLane; ++j) {
-      if (j < per_lane && ((taken >> j) & 1u) == 0u) {
-        Pick cand;
-        cand.value = choice[j];
-        cand.index = lane + 32 * j;
-        local = better_pick(local, cand);
+      const uint32_t ex = static_cast<uint32_t>(cand_expert[j]);
+      if (cand_key[j] > local_key || (cand_key[j] == local_key && cand_key[j] != 0u &&
+                                      ex < local_index)) {
+        local_key = cand_key[j];
+        local_index = ex;
+        local_score = score[j];
+        local_slot = j;
       }
     }
-    const Pick b = warp_pick(local);
-    const int owner = b.index & 31;
-    const int slot = b.index >> 5;
-    float s = 0.0f;
+    uint32_t best_key, best_index;
+    warp_arg_max(local_key, local_index, best_key, best_index);
+    const bool owner = local_key == best_key && local_index == best_index && local_slot >= 0;
+    const int owner_lane = __ffs(__ballot_sync(0xffffffffu, owner)) - 1;
+    const float s = __shfl_sync(0xffffffffu, local_score, owner_lane < 0 ? 0 : owner_lane);
+    if (owner) {
 #pragma unroll
-    for (int j = 0; j < kSelectPerLane; ++j)
-      if (j == slot) s = score[j];
-    s = __shfl_sync(0xffffffffu, s, owner);
-    if (lane == owner) taken |= 1u << slot;
+      for (int j = 0; j < kSelectPerLane; ++j) {
+        if (j == local_slot) cand_key[j] = 0u;  // taken
+      }
+    }
     if (lane == r) {
-      my_index = b.index;
+      my_index = static_cast<int>(best_index);
       my_score = s;
     }
   }
@@ -397,35 +521,53 @@ router_select_exact_kernel(float* __restrict__ logits, const float* __restrict__
 
 }  // namespace
 
-cudaError_t launch_router_fast_logits(const CUtensorMap& tmap_split, const CUtensorMap& tmap_gate,
-                                      int rows, int split_plane_rows, int experts, int hidden,
-                                      float* logits, int32_t* error, cudaStream_t stream) {
+cudaError_t launch_router_fast_logits(const void* x, bool x_bf16, const float* inv_rms,
+                                      const float* norm_weight, const CUtensorMap& tmap_gate,
+                                      int rows, int experts, int hidden, float* logits,
+                                      int32_t* error, cudaStream_t stream) {
   if (rows <= 0 || experts % 16 != 0 || experts > 256 || hidden % kFastBlockK != 0) {
     return cudaErrorInvalidValue;
   }
   const int smem = kFastStages * (kFastABytes + experts * 128) + (2 * kFastStages + 1) * 8 + 16 + 1024;
-  cudaError_t err = cudaFuncSetAttribute(router_fast_logits_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (err != cudaSuccess) return err;
-  router_fast_logits_kernel<<<(rows + 127) / 128, kFastThreads, smem, stream>>>(
-      tmap_split, tmap_gate, rows, split_plane_rows, experts, hidden, logits, error);
+  const int grid = (rows + 127) / 128;
+  cudaError_t err;
+  if (x_bf16) {
+    err = cudaFuncSetAttribute(router_fast_logits_kernel<true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return err;
+    router_fast_logits_kernel<true><<<grid, kFastThreads, smem, stream>>>(
+        x, inv_rms, norm_weight, tmap_gate, rows, experts, hidden, logits, error);
+  } else {
+    err = cudaFuncSetAttribute(router_fast_logits_kernel<false>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return err;
+    router_fast_logits_kernel<false><<<grid, kFastThreads, smem, stream>>>(
+        x, inv_rms, norm_weight, tmap_gate, rows, experts, hidden, logits, error);
+  }
   return cudaGetLastError();
 }
 
-cudaError_t launch_router_select_exact(float* logits, const float* normalized,
+cudaError_t launch_router_select_exact(float* logits, const void* x, bool x_bf16,
+                                       const float* inv_rms, const float* norm_weight,
                                        const __nv_bfloat16* gate, const float* logit_offset,
                                        const float* bias, int rows, int experts, int hidden,
                                        int top_k, bool norm_topk_prob, float routed_scaling,
                                        float tie_margin, int32_t* top_index, float* top_weight,
                                        int32_t* expert_counts, cudaStream_t stream) {
   if (rows <= 0 || experts % 32 != 0 || experts > 32 * kSelectPerLane || top_k <= 0 ||
-      top_k > 32 || top_k > experts) {
+      top_k > 32 || top_k > experts || hidden % 8 != 0) {
     return cudaErrorInvalidValue;
   }
-  router_select_exact_kernel<<<(rows + kSelectWarps - 1) / kSelectWarps, kSelectWarps * 32, 0,
-                               stream>>>(logits, normalized, gate, logit_offset, bias, rows,
-                                         experts, hidden, top_k, norm_topk_prob, routed_scaling,
-                                         tie_margin, top_index, top_weight, expert_counts);
+  const int grid = (rows + kSelectWarps - 1) / kSelectWarps;
+  if (x_bf16) {
+    router_select_exact_kernel<true><<<grid, kSelectWarps * 32, 0, stream>>>(
+        logits, x, inv_rms, norm_weight, gate, logit_offset, bias, rows, experts, hidden, top_k,
+        norm_topk_prob, routed_scaling, tie_margin, top_index, top_weight, expert_counts);
+  } else {
+    router_select_exact_kernel<false><<<grid, kSelectWarps * 32, 0, stream>>>(
+        logits, x, inv_rms, norm_weight, gate, logit_offset, bias, rows, experts, hidden, top_k,
+        norm_topk_prob, routed_scaling, tie_margin, top_index, top_weight, expert_counts);
+  }
   return cudaGetLastError();
 }
 

@@ -45,6 +45,7 @@ class DeviceStages:
         if self.layer is None:
             raise RuntimeError("expert-parallel layer creation failed: " +
                                ExpertLayerSlice.create_error)
+        self.layer.keep_trace(False)  # expert-parallel stages expose no trace
         # the collectives run beside the persistent GEMMs: leave them some SMs
         self.reserved_sms = int(os.environ.get("NMOE_EP_RESERVED_SMS", "16")) if world > 1 else 0
         self.layer.reserve_sms(self.reserved_sms)
@@ -243,6 +244,12 @@ def _as_tensor(address: int, shape, dtype, device) -> torch.Tensor:
     return flat.view(dtype).view(shape)
 
 
+class ExpertParallelError(RuntimeError):
+    """A step cannot go on: some rank reported counts that do not add up, or more pairs
+    than a receiver can hold.  Raised on EVERY rank of the group in the same step, before
+    any record travels, so no rank is left waiting in a collective."""
+
+
 class ExpertParallelEngine:
     """The exchange protocol of one rank.  `stages` provides dispatch / experts / shared /
     combine plus recv_buffer / back_buffer; tensors may live on any device the process
@@ -375,8 +382,20 @@ class ExpertParallelEngine:
             both = torch.stack([send_counts, recv_counts]).cpu()
             send_splits = [int(v) for v in both[0]]
             recv_splits = [int(v) for v in both[1]]
+            # Every rank checks what it sent and what it was told to expect; the ranks then
+            # agree (one small all-reduce) before the variable-size exchange, so that a bad
+            # count ends the step with the same error everywhere instead of leaving the
+            # healthy ranks inside a collective that can never complete.
+            problem = ""
             if min(send_splits + recv_splits) < 0 or sum(send_splits) != send_records.shape[0]:
-                raise RuntimeError(f"rank {self.rank}: inconsistent dispatch counts {send_splits}")
+                problem = f"inconsistent dispatch counts {send_splits}"
+            elif sum(recv_splits) > getattr(st, "capacity", sum(recv_splits)):
+                problem = f"{sum(recv_splits)} pairs exceed the receive capacity"
+            verdict = send_counts.new_tensor([0 if problem else 1])
+            dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=self.group)
+            if int(verdict.item()) == 0:
+                raise ExpertParallelError(
+                    f"rank {self.rank}: " + (problem or "another rank reported bad counts"))
             recv = st.recv_buffer(sum(recv_splits))
             dist.all_to_all_single(recv, send_records, recv_splits, send_splits, group=self.group)
         st.comm_to_main()
@@ -566,6 +585,12 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
                 nccl_arm["device_error"] = True
         except Exception as error:  # noqa: BLE001 - an extra key must not lose the line
             nccl_arm = {"unavailable": str(error)[:200]}
+    stack_report = None
+    if not args.no_side:
+        try:
+            stack_report = stack_workload(args, package, synthetic, flush_buf, dist_module)
+        except Exception as error:  # noqa: BLE001 - a side workload must not lose the line
+            stack_report = {"workload": "configs[4]", "unavailable": str(error)[:300]}
     sent = capacity * (world - 1)
     if transport == "window":
         exchange = {
@@ -622,10 +647,138 @@ def bench_main(args, package, synthetic, peaks, flush_buf, dist_module, bench_mo
         "ep_overhead_efficiency_same_per_gpu_tokens": None if single_ms is None else
         value / (world * tokens / (single_ms * 1e-3)),
         "nccl_transport": nccl_arm,
+        "also": [stack_report] if stack_report is not None else [],
         "exchange_bytes_rank0": {"dispatch": sent * stages.record_bytes, "return": sent * H * 2},
         "ep_phase_end_ms_rank0_eager": {k: round(v, 4) for k, v in phases.items()},
         "roofline": None,
     }
+
+
+def segment_capacity(tokens_per_rank: int, top_k: int, world: int) -> int:
+    """Record slots per (source, destination) pair for independently routed tokens: the
+    mean share plus eight standard deviations of a binomial share and a small constant,
+    rounded up to 16.  (A step that needs more raises NMOE_ERR_CAPACITY.)"""
+    mean = tokens_per_rank * top_k / world
+    return (int(mean + 8.0 * mean ** 0.5 + 16) + 15) // 16 * 16
+
+
+def stack_workload(args, package, synthetic, flush_buf, dist_module, layers: int = 23,
+                   parity_layers: int = 2) -> dict:
+    """The 23-layer MoE stack of the benchmark definition on all ranks: independently seeded
+    layers of the baseline shape (RMSNorm weight ~U(0.9, 1.1)), residual inside every layer,
+    FP32 hidden state handed from layer to layer as the reference's caller loop does
+    (runtime/src/api/single_token_forward_model.cpp:588-656); a decode batch of 256 tokens
+    and one prefill chunk of 4096 tokens, split evenly over the ranks.  The first
+    `parity_layers` layers are also checked: expert-parallel result against the single-GPU
+    layer on the same input, and that against the CPU oracle, layer by layer with the
+    device's output of one layer as the next one's input."""
+    import numpy as np
+    from .stack import MoeLayerStack
+    rank, world = dist_module.get_rank(), dist_module.get_world_size()
+    H = synthetic.HIDDEN
+    decode_total, prefill_total = 256, 4096
+    max_tokens = prefill_total // world
+    cfg = synthetic.baseline_config(max_tokens=max_tokens)
+    capacity = segment_capacity(max_tokens, cfg.top_k, world)
+    cfg.max_recv_pairs = capacity * world
+    engines, keep = [], []
+    for index in range(layers):
+        data = synthetic.make_layer(cfg, seed=6000 + index, device="cuda",
+                                    norm_weight_uniform=True)
+        stages = DeviceStages(cfg, shard_bindings(data.bindings, rank, world), rank, world)
+        if not stages.attach_windows(capacity):
+            raise RuntimeError(f"layer {index}: peer windows unavailable: {stages.attach_error}")
+        engines.append(ExpertParallelEngine(stages, capacity_per_rank=capacity))
+        if index < parity_layers:
+            keep.append(data)
+        del data
+    torch.cuda.empty_cache()
+    stack = MoeLayerStack(engines, H, max_tokens)
+
+    def timed(total_tokens):
+        tokens = total_tokens // world
+        x_all = synthetic.make_tokens(total_tokens, H, seed=6100 + total_tokens)
+        x = x_all[rank * tokens:(rank + 1) * tokens].cuda()
+        out = torch.empty((tokens, H), dtype=torch.bfloat16, device="cuda")
+        graphed = stack.capture(x, out)
+        flag = torch.tensor([1 if graphed else 0], device="cuda")
+        dist_module.all_reduce(flag, op=dist_module.ReduceOp.MIN)
+        graphed = bool(flag.item())
+        step = stack.replay if graphed else (lambda: stack.run(x, out))
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        dist_module.barrier()
+        total = 0.0
+        steps = max(3, args.steps // 2)
+        for _ in range(steps):
+            flush_buf.add_(1)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            step()
+            end.record()
+            end.synchronize()
+            total += start.elapsed_time(end)
+        torch.cuda.synchronize()
+        dist_module.barrier()
+        t = torch.tensor([total / steps], device="cuda")
+        dist_module.all_reduce(t, op=dist_module.ReduceOp.MAX)
+        status = torch.tensor([float(stack.sync_status())], device="cuda")
+        dist_module.all_reduce(status, op=dist_module.ReduceOp.MAX)
+        stack.release_graph()
+        ms = float(t.item())
+        return {"tokens": total_tokens, "ms_per_stack_pass": ms,
+                "tokens_per_s": total_tokens / (ms * 1e-3),
+                "launch": "one CUDA graph of all layers" if graphed else "eager",
+                "device_status": int(status.item())}
+
+    decode = timed(decode_total)
+    prefill = timed(prefill_total)
+
+    # parity, layer by layer, on the decode batch
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(
+        os.path.abspath(__file__))), "tests"))
+    tokens = decode_total // world
+    x_all = synthetic.make_tokens(decode_total, H, seed=6100 + decode_total)
+    current = x_all[rank * tokens:(rank + 1) * tokens].cuda()
+    worst_vs_single, oracle_ok, summaries = 0.0, True, []
+    for index in range(parity_layers):
+        ep_out = torch.empty((tokens, H), dtype=torch.float32, device="cuda")
+        engines[index].step(current, ep_out)
+        single = package.ExpertLayerSlice.create(
+            synthetic.baseline_config(max_tokens=max(tokens, 64)), keep[index].bindings)
+        ref = torch.empty((tokens, H), dtype=torch.float32, device="cuda")
+        single.run_async(current, ref)
+        torch.cuda.synchronize()
+        worst_vs_single = max(worst_vs_single, float((ep_out - ref).abs().max().item()))
+        if rank == 0:
+            try:
+                import helpers  # the test suite's parity report (CPU oracle): checker only
+                report = helpers.compare_layer_with_oracle(single, keep[index], current, ref)
+                oracle_ok = oracle_ok and report.ok()
+                summaries.append(report.summary())
+            except Exception as error:  # noqa: BLE001
+                oracle_ok = False
+                summaries.append(str(error)[:200])
+        single.close()
+        current = ep_out  # the device's own output feeds the next layer
+    worst = torch.tensor([worst_vs_single], device="cuda")
+    dist_module.all_reduce(worst, op=dist_module.ReduceOp.MAX)
+    okay = torch.tensor([1.0 if oracle_ok else 0.0], device="cuda")
+    dist_module.all_reduce(okay, op=dist_module.ReduceOp.MIN)
+    for engine in engines:
+        engine.stages.detach_windows()
+        engine.stages.layer.close()
+    torch.cuda.empty_cache()
+    return {"workload": f"configs[4]: {layers} MoE layers, residual + RMSNorm per layer, "
+                        f"expert-parallel over {world} GPUs",
+            "decode_batch": decode, "prefill_chunk": prefill,
+            "segment_capacity": capacity,
+            "parity": {"layers_checked": parity_layers, "tokens_per_rank": tokens,
+                       "max_abs_vs_single_gpu_all_ranks": float(worst.item()),
+                       "within_2e-2_of_single_gpu": bool(worst.item() <= 2e-2),
+                       "single_gpu_vs_oracle_ok": bool(okay.item() == 1.0),
+                       "oracle_reports_rank0": summaries}}
 
 
 def ep_parity_check(package, single, data, x, out, rank, dist_module) -> dict:

@@ -15,6 +15,7 @@
 #include <cuda_runtime_api.h>
 
 #include <cstdint>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <memory>
@@ -57,16 +58,26 @@ bool FillTrace(nmoe_layer* layer, cudaStream_t stream, const ExpertLayerConfig& 
   std::vector<float> parts((has_latent ? k : k + 1) * latent);
   trace->routed_expert_activated_hidden.resize(k * inter);
   trace->routed_expert_outputs.resize(k * latent);
-  std::vector<float> shared_activated(shared_inter);
+  // nmoe_layer_export_unfused gathers on the device: stage its rows in device memory
+  float* staged = nullptr;
+  const std::size_t staged_floats = k * inter + k * latent + shared_inter;
+  if (cudaMalloc(reinterpret_cast<void**>(&staged), staged_floats * sizeof(float)) != cudaSuccess) {
+    return false;
+  }
   bool ok = Copy(layer, stream, 0, trace->normalized_input.data(), hidden * sizeof(float)) &&
             Copy(layer, stream, 1, trace->router_logits.data(),
                  trace->router_logits.size() * sizeof(float)) &&
             Copy(layer, stream, 2, index.data(), k * sizeof(std::int32_t)) &&
             Copy(layer, stream, 3, weight.data(), k * sizeof(float)) &&
             Copy(layer, stream, 7, parts.data(), parts.size() * sizeof(float)) &&
-            nmoe_layer_export_unfused(layer, stream, trace->routed_expert_activated_hidden.data(),
-                                      trace->routed_expert_outputs.data(),
-                                      shared_activated.data()) == NMOE_OK;
+            nmoe_layer_export_unfused(layer, stream, staged, staged + k * inter,
+                                      staged + k * inter + k * latent) == NMOE_OK &&
+            cudaMemcpyAsync(trace->routed_expert_activated_hidden.data(), staged,
+                            k * inter * sizeof(float), cudaMemcpyDeviceToHost,
+                            stream) == cudaSuccess &&
+            cudaMemcpyAsync(trace->routed_expert_outputs.data(), staged + k * inter,
+                            k * latent * sizeof(float), cudaMemcpyDeviceToHost,
+                            stream) == cudaSuccess;
   trace->latent_output.resize(latent);
   trace->routed_latent_output.assign(latent, 0.0f);
   trace->projected_routed_output.resize(hidden);
@@ -77,7 +88,9 @@ bool FillTrace(nmoe_layer* layer, cudaStream_t stream, const ExpertLayerConfig& 
          Copy(layer, stream, 10, trace->projected_routed_output.data(), hidden * sizeof(float)) &&
          Copy(layer, stream, 11, trace->shared_output.data(), hidden * sizeof(float));
   }
-  if (!ok || cudaStreamSynchronize(stream) != cudaSuccess) return false;
+  ok = ok && cudaStreamSynchronize(stream) == cudaSuccess;
+  cudaFree(staged);
+  if (!ok) return false;
   trace->selected_experts.resize(k);
   trace->routed_expert_order.resize(k);
   for (std::size_t i = 0; i < k; ++i) {
@@ -246,6 +259,7 @@ std::unique_ptr<ExpertLayerSlice> ExpertLayerSlice::Create(const ExpertLayerConf
   impl->config = c;
   impl->capacity = cfg.max_tokens;
   if (nmoe_layer_create(&cfg, &w, &impl->layer) != NMOE_OK) return nullptr;   // Create -> nullptr
+  nmoe_layer_keep_trace(impl->layer, 0);  // a trace is for one token (:775): nothing to keep
   return std::unique_ptr<ExpertLayerSlice>(new ExpertLayerSlice(std::move(impl)));
 }
 
@@ -258,21 +272,33 @@ bool ExpertLayerSlice::Run(CublasLtHandle&, GemmHeuristicCache*, const DeviceTen
   }
   nmoe_layer* layer = impl_->layer;
   const std::int64_t tokens = static_cast<std::int64_t>(input.shape()[0]);
+  // diagnostics go to stderr under NEMOTRON_FORWARD_DEBUG only, as in the reference (:758)
+  const bool debug = std::getenv("NEMOTRON_FORWARD_DEBUG") != nullptr;
+  auto fail = [&](const char* what, nmoe_status status) {
+    if (debug) {
+      std::fprintf(stderr, "expert_layer: %s: %s (%s)\n", what, nmoe_status_string(status),
+                   nmoe_layer_last_error(layer));
+    }
+    return false;
+  };
   cudaStream_t stream = nullptr;                               // the reference runs on the default stream
   // the reference sizes its scratch per call (:782-787): any token count is accepted
   if (tokens > impl_->capacity) {
-    if (nmoe_layer_reserve_tokens(layer, static_cast<std::int32_t>(tokens)) != NMOE_OK) return false;
+    const nmoe_status grown = nmoe_layer_reserve_tokens(layer, static_cast<std::int32_t>(tokens));
+    if (grown != NMOE_OK) return fail("growing the scratch", grown);
     impl_->capacity = tokens;
   }
   // a trace needs the FP32 activated rows, which only the unfused path keeps
   bool unfused = trace != nullptr;
-  if (unfused && nmoe_layer_set_unfused_activation(layer, 1) != NMOE_OK) return false;
+  if (unfused) {
+    const nmoe_status set = nmoe_layer_set_unfused_activation(layer, 1);
+    if (set != NMOE_OK) return fail("switching to the unfused path", set);
+  }
   nmoe_status status = NMOE_ERR_CUDA;
   for (int attempt = 0; attempt < 2; ++attempt) {
-    if (nmoe_layer_run(layer, stream, input.data(), NMOE_F32, tokens, output->data(), NMOE_F32) !=
-        NMOE_OK) {
-      break;
-    }
+    status = nmoe_layer_run(layer, stream, input.data(), NMOE_F32, tokens, output->data(),
+                            NMOE_F32);
+    if (status != NMOE_OK) break;
     status = nmoe_layer_sync_status(layer, stream);            // Run is synchronous
     if (status != NMOE_ERR_ACTIVATION_RANGE || unfused) break;
     // an activated row beyond 6*448 takes a tensor scale != 1 (nvfp4_packing.cpp:119-126):
@@ -281,7 +307,11 @@ bool ExpertLayerSlice::Run(CublasLtHandle&, GemmHeuristicCache*, const DeviceTen
     unfused = true;
   }
   bool ok = status == NMOE_OK;
-  if (ok && trace != nullptr) ok = FillTrace(layer, stream, impl_->config, trace);
+  if (!ok) fail("run", status);
+  if (ok && trace != nullptr) {
+    ok = FillTrace(layer, stream, impl_->config, trace);
+    if (!ok) fail("reading the trace", NMOE_ERR_CUDA);
+  }
   if (unfused) nmoe_layer_set_unfused_activation(layer, 0);
   return ok;
 }

@@ -40,6 +40,35 @@ class MoeLayerStack:
             self._run_one(layer, current, target)
             current = target
 
+    def capture(self, x: torch.Tensor, out: torch.Tensor) -> bool:
+        """Records the whole stack on (x, out) as ONE CUDA graph (possible when no layer
+        synchronises with the host: single-device layers, expert-parallel engines on peer
+        windows or fixed-capacity segments).  False, and eager execution, otherwise."""
+        try:
+            for _ in range(2):
+                self.run(x, out)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self.run(x, out)
+            self._graph = graph
+            return True
+        except Exception as error:  # noqa: BLE001 - any capture failure means "stay eager"
+            self.capture_error = str(error)
+            self._graph = None
+            torch.cuda.synchronize()
+            return False
+
+    def replay(self) -> None:
+        self._graph.replay()
+
+    def release_graph(self) -> None:
+        if getattr(self, "_graph", None) is not None:
+            torch.cuda.synchronize()
+            self._graph = None
+            import gc
+            gc.collect()
+
     def sync_status(self) -> int:
         status = 0
         for layer in self.layers:

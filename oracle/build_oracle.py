@@ -17,7 +17,10 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE_ROOT = os.environ.get("NMOE_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: NMOE_REFERENCE_ROOT, else a directory `reference` beside this
+# repository; when neither exists the reference-built parts are skipped
+REFERENCE_ROOT = os.environ.get("NMOE_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(HERE)), "reference")
 CUDA_INCLUDE = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
 PORT_LIB = os.path.join(HERE, "libnmoe_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")

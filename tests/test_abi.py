@@ -64,8 +64,9 @@ def test_cpp_shim_compiles_against_the_reference_headers():
     reference's expert_layer.h declares; it must compile against that very header."""
     import shutil
     import subprocess
-    reference_include = os.path.join(os.environ.get("NMOE_REFERENCE_ROOT", "/root/reference"),
-                                     "runtime", "include")
+    reference_root = os.environ.get("NMOE_REFERENCE_ROOT") or os.path.join(
+        os.path.dirname(ROOT), "reference")  # the checkout beside this repository
+    reference_include = os.path.join(reference_root, "runtime", "include")
     if not os.path.isdir(reference_include) or shutil.which("g++") is None:
         pytest.skip("needs the reference checkout and g++")
     cuda_include = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")

@@ -70,3 +70,66 @@ def test_shard_bindings_splits_experts(package, synthetic):
     assert [s.first_local_expert for s in shards] == [0, 8, 16, 24]
     assert all(len(s.routed_experts) == 8 for s in shards)
     assert shards[2].routed_experts[0] is data.bindings.routed_experts[16]
+
+
+# --- failure detection on the host side (no GPU involved) -----------------------------
+
+def _faulty_worker(rank, world, port, result_dir, fault):
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=8))
+    entry.load_package()
+    synthetic = importlib.import_module("nemotron_inference_b200.synthetic")
+    ep = importlib.import_module("nemotron_inference_b200.expert_parallel")
+    import helpers
+    from ep_cpu_stages import NumpyStages
+    cfg = synthetic.baseline_config(64, experts=32, hidden=128, routed=64, shared=128, top_k=4)
+    data = synthetic.make_layer(cfg, seed=17, device="cpu", norm_weight_uniform=True)
+    ocfg, ow = helpers.oracle_config(cfg), helpers.oracle_weights(data)
+    x = synthetic.make_tokens(6, cfg.hidden_size, seed=5 + rank)
+    stages = NumpyStages(ocfg, ow, rank, world)
+    if fault == "wrong_count" and rank == 1:
+        honest = stages.dispatch
+
+        def lying_dispatch(x, capacity=0):
+            records, counts = honest(x, capacity)
+            counts[0] += 1  # claims one more record for rank 0 than it packed
+            return records, counts
+        stages.dispatch = lying_dispatch
+    engine = ep.ExpertParallelEngine(stages)
+    out = torch.zeros((6, cfg.hidden_size), dtype=torch.float32)
+    outcome = "no error"
+    try:
+        if fault == "rank_leaves":
+            engine.step(x, out)       # a healthy step first
+            if rank == 1:
+                os._exit(0)           # leaves between steps, without a word
+        engine.step(x, out)
+    except ep.ExpertParallelError as error:
+        outcome = "ExpertParallelError: " + str(error)
+    except Exception as error:  # noqa: BLE001 - a timed-out collective raises a backend error
+        outcome = type(error).__name__
+    with open(os.path.join(result_dir, f"outcome{rank}.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)  # the group is broken by design: no orderly teardown
+
+
+def test_a_wrong_count_ends_the_step_with_the_same_error_on_every_rank(tmp_path):
+    mp.spawn(_faulty_worker, args=(2, _free_port(), str(tmp_path), "wrong_count"), nprocs=2,
+             join=True)
+    outcomes = [(tmp_path / f"outcome{r}.txt").read_text() for r in range(2)]
+    assert outcomes[1].startswith("ExpertParallelError") and "inconsistent" in outcomes[1]
+    assert outcomes[0].startswith("ExpertParallelError") and "another rank" in outcomes[0]
+
+
+@pytest.mark.timeout(60)
+def test_a_rank_that_leaves_between_steps_turns_into_an_error_not_a_hang(tmp_path):
+    import time
+    start = time.time()
+    mp.spawn(_faulty_worker, args=(2, _free_port(), str(tmp_path), "rank_leaves"), nprocs=2,
+             join=True)
+    assert time.time() - start < 45
+    outcome = (tmp_path / "outcome0.txt").read_text()
+    assert outcome != "no error", outcome  # the survivor's next collective raised

@@ -53,7 +53,8 @@ def _check(r):
     assert r["rows_over_tol_without_tie"] == 0
 
 
-@pytest.mark.parametrize("rows,variant", [(64, 0), (64, 1), (64, 3), (20, 2), (130, 3), (300, 1), (300, 0)])
+@pytest.mark.parametrize("rows,variant", [(64, 0), (64, 1), (64, 3), (20, 2), (130, 3), (300, 1),
+                                          (300, 0), (64, 4), (130, 4), (300, 4), (700, 4)])
 def test_single_expert_ffn_baseline_shape(package, oracle, synthetic, rows, variant):
     r = _run_case(package, oracle, synthetic, rows, 2688, 1856, variant)
     print(rows, variant, r)
@@ -62,7 +63,7 @@ def test_single_expert_ffn_baseline_shape(package, oracle, synthetic, rows, vari
 
 @pytest.mark.parametrize("hidden,inter", [(64, 64), (256, 128), (512, 1024)])
 def test_single_expert_ffn_small_shapes(package, oracle, synthetic, hidden, inter):
-    for rows, variant in [(3, 1), (3, 2), (40, 1), (40, 3)]:
+    for rows, variant in [(3, 1), (3, 2), (40, 1), (40, 3), (40, 4), (300, 4)]:
         r = _run_case(package, oracle, synthetic, rows, hidden, inter, variant, seed=hidden)
         print(hidden, inter, rows, variant, r)
         _check(r)

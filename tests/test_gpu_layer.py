@@ -67,6 +67,29 @@ def test_results_do_not_depend_on_batching(baseline_layer, synthetic):
         assert torch.equal(single[0], batched[t])
 
 
+def test_small_batches_replay_a_recorded_graph(baseline_layer, synthetic):
+    # on a capturable stream a small batch is recorded once and replayed afterwards: same
+    # result as the eager run, and a replay reads the CURRENT contents of its buffers
+    layer, _ = baseline_layer
+    x = synthetic.make_tokens(8, 2688, seed=91, device="cuda")
+    eager = _run(layer, x)                       # legacy default stream: eager
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    out = torch.empty_like(eager)
+    with torch.cuda.stream(stream):
+        for _ in range(3):                       # record, replay, replay
+            layer.run_async(x, out)
+        stream.synchronize()
+        assert layer.sync_status() == 0
+        assert torch.equal(out, eager)
+        other = synthetic.make_tokens(8, 2688, seed=92, device="cuda")
+        x.copy_(other)
+        layer.run_async(x, out)
+        stream.synchronize()
+    torch.cuda.synchronize()
+    assert torch.equal(out, _run(layer, other))
+
+
 def test_run_rejects_bad_shapes(baseline_layer):
     layer, _ = baseline_layer
     x = torch.zeros((2, 100), device="cuda")

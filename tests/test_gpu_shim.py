@@ -52,7 +52,7 @@ def test_reference_typed_cpp_caller_gets_the_same_rows(package, synthetic, oracl
     src, dst = tmp_path / "layer.bin", tmp_path / "rows.bin"
     src.write_bytes(blob)
     done = subprocess.run([DRIVER, str(src), str(dst)], capture_output=True, text=True,
-                          timeout=300, env=dict(os.environ))
+                          timeout=300, env=dict(os.environ, NEMOTRON_FORWARD_DEBUG="1"))
     assert done.returncode == 0, done.stderr
 
     raw = dst.read_bytes()
