@@ -362,6 +362,29 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   return true;
 }
 
+// 2-D tiled TMA load into this CTA's shared memory whose completion bytes are counted
+// on the mbarrier `leader_bar`, a shared::cluster address that may lie in the partner
+// CTA of the pair (cluster_address_of): both CTAs' loads of a stage complete on the
+// leader's barrier.  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x,
+                                                 int y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(leader_bar)
+      : "memory");
+}
+
+// The shared::cluster address of `local` (an address in this CTA's shared memory) in
+// CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_address_of(const void* local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote)
+               : "r"(smem_u32(local)), "r"(rank));
+  return remote;
+}
+
 // TMEM allocation for a pair: one warp of EACH CTA executes it, the same columns
 // are allocated in both.
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t columns) {

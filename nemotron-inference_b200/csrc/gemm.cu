@@ -158,8 +158,9 @@ __device__ __forceinline__ TileRows tile_rows_of(const GemmArgs& args, int rt, i
 
 template <class C, int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b_tail, const GemmArgs args) {
+grouped_gemm_kernel(const __grid_constant__ GemmMaps maps, const GemmArgs args) {
+  const CUtensorMap& tmap_a = maps.a;
+  const CUtensorMap& tmap_b_tail = maps.b_tail;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) &
                                              ~static_cast<uintptr_t>(1023u));
@@ -169,7 +170,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t* sSFB = sSFA + C::STAGES * C::SFA_BYTES;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(sSFB + C::STAGES * C::SFB_BYTES);
   uint64_t* empty_bar = full_bar + C::STAGES;
-  uint64_t* peer_full_bar = empty_bar + C::STAGES;  // pairs: the other CTA's operands landed
+  uint64_t* peer_full_bar = empty_bar + C::STAGES;  // (reserved)
   uint64_t* tmem_full_bar = peer_full_bar + C::STAGES;
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;
   uint64_t* sf_ready_bar = tmem_empty_bar + 2;
@@ -182,8 +183,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int lane = threadIdx.x & 31;
   constexpr bool P = C::PAIR;
   // In a pair, cluster rank 0 leads: its warp 1 issues every MMA and its scale warps
-  // every scale copy, for both CTAs.  Rank 1 loads its own operands, tells the leader
-  // when they have landed and runs the epilogue of its own 128 rows.
+  // every scale copy, for both CTAs.  Rank 1 loads its own operands (their completion is
+  // counted on the leader's barrier) and runs the epilogue of its own 128 rows.
   const uint32_t cta_rank = P ? cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0u;
   const int unit = P ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
@@ -206,6 +207,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b_tail);
+    if constexpr (P) {
+      prefetch_tensormap(&maps.b_full);
+      prefetch_tensormap(&maps.sfa);
+      prefetch_tensormap(&maps.sfb);
+    }
   }
   if (warp == 1) {
     if constexpr (P) {
@@ -253,23 +259,46 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_TX);
-          tma_load_2d(sA + stage * C::A_BYTES, &tmap_a, kb * 128, rows.load_row0,
-                      &full_bar[stage]);
-          if (kb < args.kb_full) {
-            // one contiguous, pre-swizzled panel slice: a single bulk copy
-            bulk_load(sB + stage * C::B_BYTES,
-                      args.b_full + (static_cast<size_t>(expert * args.kb_full + kb) * args.N +
-                                     b_row) * 128,
-                      C::B_BYTES, &full_bar[stage]);
+          if constexpr (P) {
+            // Every copy of both CTAs completes on the LEADER's full barrier, which
+            // expects the bytes of both; the partner arms nothing.
+            const uint32_t bar = leader ? smem_u32(&full_bar[stage])
+                                        : cluster_address_of(&full_bar[stage], 0);
+            if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * C::STAGE_TX);
+            tma_load_2d_pair(sA + stage * C::A_BYTES, &tmap_a, kb * 128, rows.load_row0, bar);
+            if (kb < args.kb_full) {
+              tma_load_2d_pair(sB + stage * C::B_BYTES, &maps.b_full, 0,
+                               (expert * args.kb_full + kb) * args.N + b_row, bar);
+            } else {
+              tma_load_2d_pair(sB + stage * C::B_BYTES, &tmap_b_tail, 0, expert * args.N + b_row,
+                               bar);
+            }
+            tma_load_2d_pair(sSFA + stage * C::SFA_BYTES, &maps.sfa, 0,
+                             ((rows.load_row0 >> 7) * args.k_blocks + kb) * (C::SFA_BYTES / 128),
+                             bar);
+            tma_load_2d_pair(sSFB + stage * C::SFB_BYTES, &maps.sfb, 0,
+                             ((expert * args.n_tiles + nt) * args.k_blocks + kb) *
+                                 (C::SFB_BYTES / 128),
+                             bar);
           } else {
-            tma_load_2d(sB + stage * C::B_BYTES, &tmap_b_tail, 0, expert * args.N + b_row,
+            mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_TX);
+            tma_load_2d(sA + stage * C::A_BYTES, &tmap_a, kb * 128, rows.load_row0,
                         &full_bar[stage]);
+            if (kb < args.kb_full) {
+              // one contiguous, pre-swizzled panel slice: a single bulk copy
+              bulk_load(sB + stage * C::B_BYTES,
+                        args.b_full + (static_cast<size_t>(expert * args.kb_full + kb) * args.N +
+                                       b_row) * 128,
+                        C::B_BYTES, &full_bar[stage]);
+            } else {
+              tma_load_2d(sB + stage * C::B_BYTES, &tmap_b_tail, 0, expert * args.N + b_row,
+                          &full_bar[stage]);
+            }
+            bulk_load(sSFA + stage * C::SFA_BYTES, sfa_src + kb * C::SFA_BYTES, C::SFA_BYTES,
+                      &full_bar[stage]);
+            bulk_load(sSFB + stage * C::SFB_BYTES, sfb_src + kb * C::SFB_BYTES, C::SFB_BYTES,
+                      &full_bar[stage]);
           }
-          bulk_load(sSFA + stage * C::SFA_BYTES, sfa_src + kb * C::SFA_BYTES, C::SFA_BYTES,
-                    &full_bar[stage]);
-          bulk_load(sSFB + stage * C::SFB_BYTES, sfb_src + kb * C::SFB_BYTES, C::SFB_BYTES,
-                    &full_bar[stage]);
           if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -301,8 +330,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int kb = 0; kb < args.k_blocks; ++kb) {
           // the operands have landed (in both CTAs) and the scale copies of this K
           // block are done
-          bool landed = mbar_wait(&full_bar[stage], phase);
-          if constexpr (P) landed = landed && mbar_wait_cluster(&peer_full_bar[stage], phase);
+          // (a pair's full barrier counts the bytes of both CTAs)
+          const bool landed = P ? mbar_wait_cluster(&full_bar[stage], phase)
+                                : mbar_wait(&full_bar[stage], phase);
           if (!landed || !mbar_wait(&sf_ready_bar[sf_buf], sf_phase)) {
             report_timeout(args.error, abort_flag);
             ok = false;
@@ -372,28 +402,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp >= kScaleWarp) {
     if (lane == 0 && !leader) {
-      // ------------------------------------------- partner: operands-landed relay
-      // The leader's MMAs read this CTA's shared memory; one thread here watches the
-      // local full barrier and raises the leader's peer-full barrier of that stage.
-      if (warp == kScaleWarp) {
-        int stage = 0;
-        uint32_t phase = 0;
-        bool ok = true;
-        for (int t = unit; t < total_tiles && ok; t += units) {
-          for (int kb = 0; kb < args.k_blocks; ++kb) {
-            if (!mbar_wait(&full_bar[stage], phase)) {
-              report_timeout(args.error, abort_flag);
-              ok = false;
-              break;
-            }
-            mbar_arrive_remote(&peer_full_bar[stage], 0);
-            if (++stage == C::STAGES) {
-              stage = 0;
-              phase ^= 1u;
-            }
-          }
-        }
-      }
+      // the partner's scale copies are issued by the leader (tcgen05.cp.cta_group::2)
     } else if (lane == 0) {
     // ------------------------------------------------------- block-scale copier
     // The copies of one K block's scales into TMEM take longer to issue than
@@ -418,8 +427,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               old_phase ^= 1u;
             }
           }
-          ready = ready && mbar_wait(&full_bar[stage], phase);
-          if constexpr (P) ready = ready && mbar_wait_cluster(&peer_full_bar[stage], phase);
+          ready = ready && (P ? mbar_wait_cluster(&full_bar[stage], phase)
+                              : mbar_wait(&full_bar[stage], phase));
           if (!ready) {
             report_timeout(args.error, abort_flag);
             ok = false;
@@ -645,8 +654,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 template <class C, int MODE>
-cudaError_t launch_kernel(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b_tail,
-                          const GemmArgs& args, int grid, cudaStream_t stream) {
+cudaError_t launch_kernel(const GemmMaps& maps, const GemmArgs& args, int grid,
+                          cudaStream_t stream) {
   auto kernel = grouped_gemm_kernel<C, MODE>;
   cudaError_t err =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -665,16 +674,15 @@ cudaError_t launch_kernel(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b_t
     attribute.val.clusterDim.z = 1;
     config.attrs = &attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, kernel, tmap_a, tmap_b_tail, args);
+    return cudaLaunchKernelEx(&config, kernel, maps, args);
   } else {
-    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(tmap_a, tmap_b_tail, args);
+    kernel<<<grid, kGemmThreads, C::SMEM_BYTES, stream>>>(maps, args);
     return cudaGetLastError();
   }
 }
 
 template <class C>
-cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a,
-                       const CUtensorMap& tmap_b_tail, const GemmArgs& args, int num_sms,
+cudaError_t launch_cfg(GemmMode mode, const GemmMaps& maps, const GemmArgs& args, int num_sms,
                        cudaStream_t stream) {
   // one persistent CTA (or CTA pair) per SM (pair of SMs), fewer when there is less work
   int units = C::PAIR ? num_sms / 2 : num_sms;
@@ -686,9 +694,9 @@ cudaError_t launch_cfg(GemmMode mode, const CUtensorMap& tmap_a,
   if (units < 1) units = 1;
   const int grid = C::PAIR ? 2 * units : units;
   if (mode == kGemmUp) {
-    return launch_kernel<C, kGemmUp>(tmap_a, tmap_b_tail, args, grid, stream);
+    return launch_kernel<C, kGemmUp>(maps, args, grid, stream);
   } else if constexpr (C::ROW_STAGING) {
-    return launch_kernel<C, kGemmDown>(tmap_a, tmap_b_tail, args, grid, stream);
+    return launch_kernel<C, kGemmDown>(maps, args, grid, stream);
   } else {
     return cudaErrorInvalidValue;  // this tile shape has no staging for the down epilogue
   }
@@ -786,16 +794,15 @@ GemmVariantInfo gemm_variant_info(GemmVariant v) {
   }
 }
 
-cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const CUtensorMap& tmap_a,
-                                const CUtensorMap& tmap_b_tail,
+cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const GemmMaps& maps,
                                 const GemmArgs& args, int num_sms, cudaStream_t stream) {
   switch (v) {
-    case kVariantPrefillUp: return launch_cfg<CfgPrefillUp>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
-    case kVariantPrefillDown: return launch_cfg<CfgPrefillDown>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
-    case kVariantDecode: return launch_cfg<CfgDecode>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
-    case kVariantDecodeWide: return launch_cfg<CfgDecodeWide>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
-    case kVariantPairUp: return launch_cfg<CfgPairUp>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
-    case kVariantPairDown: return launch_cfg<CfgPairDown>(mode, tmap_a, tmap_b_tail, args, num_sms, stream);
+    case kVariantPrefillUp: return launch_cfg<CfgPrefillUp>(mode, maps, args, num_sms, stream);
+    case kVariantPrefillDown: return launch_cfg<CfgPrefillDown>(mode, maps, args, num_sms, stream);
+    case kVariantDecode: return launch_cfg<CfgDecode>(mode, maps, args, num_sms, stream);
+    case kVariantDecodeWide: return launch_cfg<CfgDecodeWide>(mode, maps, args, num_sms, stream);
+    case kVariantPairUp: return launch_cfg<CfgPairUp>(mode, maps, args, num_sms, stream);
+    case kVariantPairDown: return launch_cfg<CfgPairDown>(mode, maps, args, num_sms, stream);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -93,9 +93,21 @@ struct GemmVariantInfo {
   int b_rows;        // weight rows one CTA stages per K block (half a tile in a pair)
 };
 
+// Tensor maps of one GEMM launch.  `a` (activation rows, 128-byte swizzle) and `b_tail`
+// (the partial last K block of the weights) are used by every variant; the CTA-pair
+// variants load everything through tensor maps, so that both CTAs' copies complete on
+// the leader's barrier: `b_full` (the K-block-major weight panels as [rows][128 B]),
+// `sfa` and `sfb` (the tiled block scales as [rows][128 B]).
+struct GemmMaps {
+  CUtensorMap a;
+  CUtensorMap b_tail;
+  CUtensorMap b_full;
+  CUtensorMap sfa;
+  CUtensorMap sfb;
+};
+
 GemmVariantInfo gemm_variant_info(GemmVariant v);
-cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const CUtensorMap& tmap_a,
-                                const CUtensorMap& tmap_b_tail,
+cudaError_t launch_grouped_gemm(GemmVariant v, GemmMode mode, const GemmMaps& maps,
                                 const GemmArgs& args, int num_sms, cudaStream_t stream);
 
 // Packed weights [experts][N][K/2] -> K-block-major (device to device): every
@@ -160,6 +172,15 @@ cudaError_t launch_router_fast_logits(const void* x, bool x_bf16, const float* i
                                       const float* norm_weight, const CUtensorMap& tmap_gate,
                                       int rows, int experts, int hidden, float* logits,
                                       int32_t* error, cudaStream_t stream);
+// Pass 1 for bf16 layer inputs: the RMSNorm weight folded into the gate (three bf16 terms of
+// fl32(w[i] * gate[e][i]), `planes` = [3][experts][hidden], built once by launch_fold_gate),
+// the input rows read by TMA through `tmap_x` ([rows][hidden] bf16, box 64 x 128, 128-byte
+// swizzle; `tmap_planes` = [3 * experts][hidden], box 64 x experts), inv_rms applied to the sums.
+cudaError_t launch_fold_gate(const __nv_bfloat16* gate, const float* norm_weight, int experts,
+                             int hidden, __nv_bfloat16* planes, cudaStream_t stream);
+cudaError_t launch_router_folded_logits(const CUtensorMap& tmap_x, const CUtensorMap& tmap_planes,
+                                        const float* inv_rms, int rows, int experts, int hidden,
+                                        float* logits, int32_t* error, cudaStream_t stream);
 cudaError_t launch_router_select_exact(float* logits, const void* x, bool x_bf16,
                                        const float* inv_rms, const float* norm_weight,
                                        const __nv_bfloat16* gate, const float* logit_offset,

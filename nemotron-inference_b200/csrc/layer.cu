@@ -131,6 +131,26 @@ CUtensorMap make_bf16_map(const void* base, size_t rows, size_t cols, int box_ro
   return map;
 }
 
+// Bytes that are already in their shared-memory order, viewed as [rows][128 B]: box =
+// 128 bytes x box_rows, no swizzle.  The CTA-pair GEMM loads its weight panels and block
+// scales through such maps.
+CUtensorMap make_raw_map(const void* base, size_t rows, int box_rows) {
+  NMOE_REQUIRE(reinterpret_cast<uintptr_t>(base) % 16 == 0, "tensor map base must be 16-byte aligned");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {128u, rows};
+  const cuuint64_t strides[1] = {128u};
+  const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem_strides[2] = {1u, 1u};
+  const CUresult rc = encode_tiled_fn()(
+      &map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) {
+    throw Failure{NMOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(rc)};
+  }
+  return map;
+}
+
 int k_blocks_of(int k) { return (k + 255) / 256; }
 size_t tiled_sf_bytes(size_t row_slots, int k) { return row_slots * k_blocks_of(k) * 2048; }
 
@@ -194,6 +214,8 @@ struct WeightStack {
   CUtensorMap tail_prefill;
   CUtensorMap tail_decode;
   CUtensorMap tail_pair;
+  CUtensorMap full_pair;  // the K-block-major panels, for the CTA-pair variants
+  CUtensorMap sf_pair;    // sf_prefill as [rows][128 B]
 
   void upload(const nmoe_nvfp4_matrix* matrices, int count, int rows, int cols, bool is_up,
               const char* name, cudaStream_t stream) {
@@ -204,30 +226,15 @@ struct WeightStack {
     pair_variant = is_up ? kVariantPairUp : kVariantPairDown;  // same BN and scale layout
     const size_t packed_each = static_cast<size_t>(rows) * cols / 2;
     const size_t sf_each = static_cast<size_t>(rows) * (cols / 16);
-    DeviceBuffer row_major;
-    row_major.allocate(packed_each * count);
     tensor_scale.allocate(sizeof(float) * count);
-    DeviceBuffer sf_row_major;
-    sf_row_major.allocate(sf_each * count);
-    for (int e = 0; e < count; ++e) {
-      validate_matrix(matrices[e], rows, cols, name);
-      NMOE_CUDA(cudaMemcpyAsync(row_major.as<uint8_t>() + packed_each * e, matrices[e].packed_data,
-                                packed_each, cudaMemcpyDefault, stream));
-      NMOE_CUDA(cudaMemcpyAsync(sf_row_major.as<uint8_t>() + sf_each * e,
-                                matrices[e].block_scales_data, sf_each, cudaMemcpyDefault,
-                                stream));
-      NMOE_CUDA(cudaMemcpyAsync(tensor_scale.as<float>() + e, matrices[e].tensor_scale_data,
-                                sizeof(float), cudaMemcpyDefault, stream));
-    }
+    for (int e = 0; e < count; ++e) validate_matrix(matrices[e], rows, cols, name);
     const GemmVariantInfo pi = gemm_variant_info(prefill_variant);
     const GemmVariantInfo di = gemm_variant_info(decode_variant);
     const int pair_rows = gemm_variant_info(pair_variant).b_rows;
-    sf_prefill.allocate(weight_scale_layout_bytes(count, rows, cols, pi.bn, pi.sfb_groups));
-    sf_decode.allocate(weight_scale_layout_bytes(count, rows, cols, di.bn, di.sfb_groups));
-    NMOE_CUDA(relayout_weight_scales(sf_row_major.as<uint8_t>(), count, rows, cols, pi.bn,
-                                     pi.sfb_groups, sf_prefill.as<uint8_t>(), stream));
-    NMOE_CUDA(relayout_weight_scales(sf_row_major.as<uint8_t>(), count, rows, cols, di.bn,
-                                     di.sfb_groups, sf_decode.as<uint8_t>(), stream));
+    const size_t sf_prefill_each = weight_scale_layout_bytes(1, rows, cols, pi.bn, pi.sfb_groups);
+    const size_t sf_decode_each = weight_scale_layout_bytes(1, rows, cols, di.bn, di.sfb_groups);
+    sf_prefill.allocate(sf_prefill_each * count);
+    sf_decode.allocate(sf_decode_each * count);
     kb_full = cols / 256;
     const int tail_bytes = (cols % 256) / 2;
     const size_t panel_rows = static_cast<size_t>(count) * rows;
@@ -259,9 +266,41 @@ struct WeightStack {
       tail_pitch = 16;
       packed_tail.allocate(16);
     }
-    NMOE_CUDA(relayout_weight_packed(row_major.as<uint8_t>(), count, rows, cols, tail_pitch,
-                                     packed.as<uint8_t>(), packed_tail.as<uint8_t>(), stream));
-    NMOE_CUDA(cudaStreamSynchronize(stream));  // the row-major staging copies die here
+    // One expert at a time through a staging buffer of one matrix: descriptor bytes
+    // (host or device) -> staging -> K-block-major panels and per-tile scale layouts.
+    // Copies and kernels share the stream, so the staging buffer is reused in order;
+    // no second copy of the whole stack exists and the host waits once, at the end.
+    DeviceBuffer staging_packed, staging_sf;
+    staging_packed.allocate(packed_each);
+    staging_sf.allocate(sf_each);
+    const size_t panel_each = static_cast<size_t>(rows) * kb_full * 128;
+    const size_t tail_each = static_cast<size_t>(rows) * tail_pitch;
+    for (int e = 0; e < count; ++e) {
+      NMOE_CUDA(cudaMemcpyAsync(staging_packed.as<void>(), matrices[e].packed_data, packed_each,
+                                cudaMemcpyDefault, stream));
+      NMOE_CUDA(cudaMemcpyAsync(staging_sf.as<void>(), matrices[e].block_scales_data, sf_each,
+                                cudaMemcpyDefault, stream));
+      NMOE_CUDA(cudaMemcpyAsync(tensor_scale.as<float>() + e, matrices[e].tensor_scale_data,
+                                sizeof(float), cudaMemcpyDefault, stream));
+      NMOE_CUDA(relayout_weight_packed(staging_packed.as<uint8_t>(), 1, rows, cols, tail_pitch,
+                                       packed.as<uint8_t>() + panel_each * e,
+                                       packed_tail.as<uint8_t>() + (tail_bytes > 0 ? tail_each * e : 0),
+                                       stream));
+      NMOE_CUDA(relayout_weight_scales(staging_sf.as<uint8_t>(), 1, rows, cols, pi.bn,
+                                       pi.sfb_groups, sf_prefill.as<uint8_t>() + sf_prefill_each * e,
+                                       stream));
+      NMOE_CUDA(relayout_weight_scales(staging_sf.as<uint8_t>(), 1, rows, cols, di.bn,
+                                       di.sfb_groups, sf_decode.as<uint8_t>() + sf_decode_each * e,
+                                       stream));
+    }
+    NMOE_CUDA(cudaStreamSynchronize(stream));  // the staging buffers die here
+    if (kb_full > 0) {
+      full_pair = make_raw_map(packed.as<uint8_t>(), panel_rows * kb_full + 256, pair_rows);
+    } else {
+      full_pair = make_raw_map(packed.as<uint8_t>(), 256, pair_rows);  // never read
+    }
+    sf_pair = make_raw_map(sf_prefill.as<uint8_t>(), sf_prefill_each * count / 128,
+                           gemm_variant_info(pair_variant).sfb_groups * 4);
     if (tail_bytes == 0) {
       // never read (k_blocks == kb_full), but the kernel takes a valid map
       tail_prefill = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, pi.bn);
@@ -289,15 +328,27 @@ struct ActivationOperand {
   const uint8_t* sf_tiled = nullptr;
   CUtensorMap map_box128;
   CUtensorMap map_box32;
+  CUtensorMap sf_map;  // the tiled scales as [rows][128 B], one K block of one row tile per box
   void bind(const uint8_t* packed_rows, const uint8_t* sf, size_t rows, int k) {
     packed = packed_rows;
     sf_tiled = sf;
+    sf_map = make_raw_map(sf, tiled_sf_bytes((rows + 127) / 128, k) / 128, 16);
     map_box128 = make_packed_map(packed_rows, rows, static_cast<size_t>(k) / 2, 128);
     map_box32 = make_packed_map(packed_rows, rows, static_cast<size_t>(k) / 2, 32);
   }
   const CUtensorMap& map(TileClass c) const { return c == kClassDecode ? map_box32 : map_box128; }
 };
 
+
+GemmMaps gemm_maps(const WeightStack& weights, TileClass tile_class, const ActivationOperand& a) {
+  GemmMaps maps;
+  maps.a = a.map(tile_class);
+  maps.b_tail = weights.tail_map(tile_class);
+  maps.b_full = weights.full_pair;
+  maps.sfa = a.sf_map;
+  maps.sfb = weights.sf_pair;
+  return maps;
+}
 
 struct Schedule {
   const RowTile* row_tiles = nullptr;  // grouped when non-null
@@ -347,8 +398,8 @@ void run_down_gemm(const WeightStack& weights, TileClass tile_class, const Activ
   d.segment_rows = segments.rows;
   d.segment_slot0 = segments.slot0;
   d.error = error;
-  NMOE_CUDA(launch_grouped_gemm(variant, kGemmDown, a.map(tile_class),
-                                weights.tail_map(tile_class), d, num_sms, stream));
+  NMOE_CUDA(launch_grouped_gemm(variant, kGemmDown, gemm_maps(weights, tile_class, a), d, num_sms,
+                                stream));
 }
 
 // up GEMM (relu^2 + quantise) followed by down GEMM (scale, weight, scatter).
@@ -378,8 +429,8 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   g.out_sf = hidden_sf;
   g.out_k_blocks = k_blocks_of(up.n);
   g.error = error;
-  NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, a.map(tile_class),
-                                up.tail_map(tile_class), g, num_sms, stream));
+  NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, gemm_maps(up, tile_class, a), g, num_sms,
+                                stream));
 
   if (between != nullptr) cudaEventRecord(between, stream);
 
@@ -658,6 +709,14 @@ struct nmoe_layer {
   float router_tie_margin = 2.0e-4f;
   DeviceBuffer gate_bf16, inv_rms;
   CUtensorMap gate_map;
+  // bf16 inputs: the norm weight folded into the gate as three bf16 planes, and the map of
+  // the last input the layer saw (its address and row count are part of the map)
+  DeviceBuffer gate_planes;
+  CUtensorMap planes_map;
+  bool folded_router = false;
+  CUtensorMap input_map;
+  const void* input_map_base = nullptr;
+  int input_map_rows = 0;
   // The FP32 normalised rows are needed by the FP64 logits kernel of small batches,
   // by the dense / scaled-FP8 linears and by the trace; the two-pass router of large
   // batches rebuilds them on the fly, so they are only written there while a trace may
@@ -989,6 +1048,13 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
     NMOE_CUDA(cudaMemcpyAsync(L->gate_bf16.as<void>(), w.gate_weight.data,
                               static_cast<size_t>(E) * H * 2, cudaMemcpyDefault, stream));
     L->gate_map = make_bf16_map(L->gate_bf16.as<void>(), E, H, E);
+    L->folded_router = std::getenv("NMOE_ROUTER_SPLIT_INPUT") == nullptr;
+    if (L->folded_router) {
+      L->gate_planes.allocate(static_cast<size_t>(3) * E * H * 2);
+      NMOE_CUDA(launch_fold_gate(L->gate_bf16.as<__nv_bfloat16>(), L->norm_weight.as<float>(), E, H,
+                                 L->gate_planes.as<__nv_bfloat16>(), stream));
+      L->planes_map = make_bf16_map(L->gate_planes.as<void>(), static_cast<size_t>(3) * E, H, E);
+    }
     if (const char* env = std::getenv("NMOE_ROUTER_TIE_MARGIN")) L->router_tie_margin = std::strtof(env, nullptr);
     if (const char* env = std::getenv("NMOE_ROUTER_FAST_MIN_TOKENS")) L->fast_router_min_tokens = std::atoi(env);
   }
@@ -1037,9 +1103,19 @@ void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dt
   NMOE_CUDA(cudaMemsetAsync(L->counts.as<int32_t>(), 0, E * sizeof(int32_t), stream));
   const float* offset = L->has_logit_offset ? L->logit_offset.as<float>() : nullptr;
   if (two_pass_router) {
-    NMOE_CUDA(launch_router_fast_logits(input, in_bf16, L->inv_rms.as<float>(),
-                                        L->norm_weight.as<float>(), L->gate_map, tokens, E, H,
-                                        L->logits.as<float>(), error, stream));
+    if (L->folded_router && in_bf16 && reinterpret_cast<uintptr_t>(input) % 16 == 0) {
+      if (L->input_map_base != input || L->input_map_rows != tokens) {
+        L->input_map = make_bf16_map(input, tokens, H, 128);
+        L->input_map_base = input;
+        L->input_map_rows = tokens;
+      }
+      NMOE_CUDA(launch_router_folded_logits(L->input_map, L->planes_map, L->inv_rms.as<float>(),
+                                            tokens, E, H, L->logits.as<float>(), error, stream));
+    } else {
+      NMOE_CUDA(launch_router_fast_logits(input, in_bf16, L->inv_rms.as<float>(),
+                                          L->norm_weight.as<float>(), L->gate_map, tokens, E, H,
+                                          L->logits.as<float>(), error, stream));
+    }
     L->mark(2, stream);
     NMOE_CUDA(launch_router_select_exact(
         L->logits.as<float>(), input, in_bf16, L->inv_rms.as<float>(),

@@ -163,11 +163,24 @@ norm_quant_kernel(const void* __restrict__ in, int rows, int cols,
     if (block_max > 0.0f) bs = clamp_scale(__fdiv_rn(block_max, __fmul_rn(kFp4Max, ts)));
     const float divisor = __fmul_rn(ts, bs);
     uint32_t word = 0;
+    // x / divisor, IEEE-rounded: one reciprocal per block and a residual correction per
+    // value give the correctly rounded quotient unless the divisor's significand is all
+    // ones (div_by_reciprocal), where the division itself is used
+    if ((__float_as_uint(divisor) & 0x007fffffu) != 0x007fffffu) {
+      const float r = __frcp_rn(divisor);
 #pragma unroll
-    for (int i = 0; i < 8; i += 2) {
-      const uint32_t byte =
-          encode_e2m1x2(__fdiv_rn(v[i], divisor), __fdiv_rn(v[i + 1], divisor));
-      word |= (byte & 0xffu) << (4 * i);
+      for (int i = 0; i < 8; i += 2) {
+        const uint32_t byte = encode_e2m1x2(div_by_reciprocal(v[i], divisor, r),
+                                            div_by_reciprocal(v[i + 1], divisor, r));
+        word |= (byte & 0xffu) << (4 * i);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; i += 2) {
+        const uint32_t byte =
+            encode_e2m1x2(__fdiv_rn(v[i], divisor), __fdiv_rn(v[i + 1], divisor));
+        word |= (byte & 0xffu) << (4 * i);
+      }
     }
     if (active && packed != nullptr) {
       *reinterpret_cast<uint32_t*>(packed + row_base / 2 + static_cast<size_t>(ch) * 4) = word;

@@ -21,6 +21,8 @@
 // If every pass-1 score is within tie_margin/2 of its exact value, the exact
 // top-k set is contained in the candidates, so indices AND weights equal the
 // all-FP64 path.  tie_margin is ~20x the largest pass-1 error measured.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -180,15 +182,19 @@ router_fast_logits_kernel(const void* __restrict__ x, const float* __restrict__ 
       const int row = row0 + row_of[j];
       rinv[j] = row < rows ? inv_rms[row] : 0.0f;
     }
-    float xv[4][8];
-    auto fetch = [&](int kb) {
+    // two K blocks of input stay in flight in registers: a row's 128-byte pieces are
+    // 5 KB apart in memory, so each fetch pays a full memory latency
+    float xv[2][4][8];
+    auto fetch = [&](int kb, float (&dst)[4][8]) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int row = min(row0 + row_of[j], rows - 1);
-        load_x8<IN_BF16>(x, static_cast<size_t>(row) * hidden + kb * kFastBlockK + chunk * 8, xv[j]);
+        load_x8<IN_BF16>(x, static_cast<size_t>(row) * hidden + kb * kFastBlockK + chunk * 8,
+                         dst[j]);
       }
     };
-    fetch(0);
+    fetch(0, xv[0]);
+    if (k_blocks > 1) fetch(1, xv[1]);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -198,25 +204,34 @@ router_fast_logits_kernel(const void* __restrict__ x, const float* __restrict__ 
           *reinterpret_cast<const float4*>(norm_weight + kb * kFastBlockK + chunk * 8 + 4);
       const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
       uint32_t words[4][3][4];
+      auto split = [&](float (&src)[4][8]) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < 4; ++j) {
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
-          // y exactly as the RMSNorm kernel rounds it: (x * inv_rms) * w
-          float rem[2] = {__fmul_rn(__fmul_rn(xv[j][i], rinv[j]), w[i]),
-                          __fmul_rn(__fmul_rn(xv[j][i + 1], rinv[j]), w[i + 1])};
+          for (int i = 0; i < 8; i += 2) {
+            // y exactly as the RMSNorm kernel rounds it: (x * inv_rms) * w
+            float rem[2] = {__fmul_rn(__fmul_rn(src[j][i], rinv[j]), w[i]),
+                            __fmul_rn(__fmul_rn(src[j][i + 1], rinv[j]), w[i + 1])};
 #pragma unroll
-          for (int term = 0; term < 3; ++term) {
-            const __nv_bfloat16 a = __float2bfloat16_rn(rem[0]);
-            const __nv_bfloat16 b = __float2bfloat16_rn(rem[1]);
-            rem[0] = __fsub_rn(rem[0], __bfloat162float(a));
-            rem[1] = __fsub_rn(rem[1], __bfloat162float(b));
-            words[j][term][i / 2] = static_cast<uint32_t>(__bfloat16_as_ushort(a)) |
-                                    (static_cast<uint32_t>(__bfloat16_as_ushort(b)) << 16);
+            for (int term = 0; term < 3; ++term) {
+              const __nv_bfloat16 a = __float2bfloat16_rn(rem[0]);
+              const __nv_bfloat16 b = __float2bfloat16_rn(rem[1]);
+              rem[0] = __fsub_rn(rem[0], __bfloat162float(a));
+              rem[1] = __fsub_rn(rem[1], __bfloat162float(b));
+              words[j][term][i / 2] = static_cast<uint32_t>(__bfloat16_as_ushort(a)) |
+                                      (static_cast<uint32_t>(__bfloat16_as_ushort(b)) << 16);
+            }
           }
         }
+      };
+      // (the buffer index is resolved at compile time: registers cannot be indexed)
+      if (kb & 1) {
+        split(xv[1]);
+        if (kb + 2 < k_blocks) fetch(kb + 2, xv[1]);
+      } else {
+        split(xv[0]);
+        if (kb + 2 < k_blocks) fetch(kb + 2, xv[0]);
       }
-      if (kb + 1 < k_blocks) fetch(kb + 1);  // in flight while this block is stored
       if (ok && !mbar_wait(&empty_bar[stage], phase ^ 1u)) {
         if (error != nullptr) atomicCAS(error, kDevOk, kDevWaitTimeout);
         ok = false;
@@ -264,6 +279,163 @@ router_fast_logits_kernel(const void* __restrict__ x, const float* __restrict__ 
       } else if (error != nullptr) {
         atomicCAS(error, kDevOk, kDevWaitTimeout);
       }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// pass 1 for bf16 layer inputs: the RMSNorm weight is folded into the gate once,
+//   logit[t][e] ~= inv_rms[t] * sum_i x[t][i] * (w[i] * gate[e][i]),
+// so the bf16 input itself is the (exact, single-term) A operand, loaded by TMA, and
+// the three bf16 terms of fl32(w[i] * gate[e][i]) are the B operands, split once when
+// the layer is created.  Same three MMAs per K step as the kernel above, but no warp
+// touches the operands: one producer lane, one MMA lane, four epilogue warps.  Against
+// the reference's y = fl(fl(x * inv_rms) * w) this drops two roundings of 2^-24 per term,
+// the size of the FP32 accumulation error already covered by the tie margin.
+// ---------------------------------------------------------------------------
+constexpr int kFoldThreads = 6 * 32;
+constexpr int kFoldABytes = 128 * 128;  // 128 rows x 64 bf16
+
+__global__ void fold_gate_kernel(const __nv_bfloat16* __restrict__ gate,
+                                 const float* __restrict__ norm_weight, int experts, int hidden,
+                                 __nv_bfloat16* __restrict__ planes) {
+  const size_t total = static_cast<size_t>(experts) * hidden;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float rem = __fmul_rn(norm_weight[i % hidden], __bfloat162float(gate[i]));
+#pragma unroll
+    for (int term = 0; term < 3; ++term) {
+      const __nv_bfloat16 part = __float2bfloat16_rn(rem);
+      rem = __fsub_rn(rem, __bfloat162float(part));
+      planes[term * total + i] = part;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kFoldThreads, 1)
+router_folded_logits_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                            const __grid_constant__ CUtensorMap tmap_planes,
+                            const float* __restrict__ inv_rms, int rows, int experts, int hidden,
+                            int stages, float* __restrict__ logits, int32_t* error) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) &
+                                             ~static_cast<uintptr_t>(1023u));
+  const int plane_bytes = experts * 128;
+  const int b_bytes = 3 * plane_bytes;
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + stages * kFoldABytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sB + stages * b_bytes);
+  uint64_t* empty_bar = full_bar + stages;
+  uint64_t* done_bar = empty_bar + stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * 128;
+  const int k_blocks = hidden / kFastBlockK;
+  const uint32_t tmem_cols = experts <= 32 ? 32 : experts <= 64 ? 64 : experts <= 128 ? 128 : 256;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(done_bar, 1);
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_x);
+    prefetch_tensormap(&tmap_planes);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, tmem_cols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
+          if (error != nullptr) atomicCAS(error, kDevOk, kDevWaitTimeout);
+          break;
+        }
+        mbar_arrive_expect_tx(&full_bar[stage], kFoldABytes + b_bytes);
+        // rows past the end of the input read as zeros (the map's extent is `rows`)
+        tma_load_2d(sA + stage * kFoldABytes, &tmap_x, kb * kFastBlockK, row0, &full_bar[stage]);
+        for (int plane = 0; plane < 3; ++plane) {
+          tma_load_2d(sB + stage * b_bytes + plane * plane_bytes, &tmap_planes, kb * kFastBlockK,
+                      plane * experts, &full_bar[stage]);
+        }
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(static_cast<uint32_t>(experts));
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; ++kb) {
+        if (!mbar_wait(&full_bar[stage], phase)) {
+          if (error != nullptr) atomicCAS(error, kDevOk, kDevWaitTimeout);
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t a_addr = smem_u32(sA + stage * kFoldABytes);
+        const uint32_t b_addr = smem_u32(sB + stage * b_bytes);
+        // smallest terms first, so that they are not absorbed by a large partial sum
+        for (int plane = 2; plane >= 0; --plane) {
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {  // K = 16 bf16 = 32 bytes per MMA
+            tcgen05_mma_bf16(tmem_base, make_smem_desc(a_addr + ks * 32, 0, 1024, 2),
+                             make_smem_desc(b_addr + plane * plane_bytes + ks * 32, 0, 1024, 2),
+                             idesc, (kb != 0 || plane != 2 || ks != 0) ? 1u : 0u);
+          }
+        }
+        tcgen05_commit(&empty_bar[stage]);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (ok) tcgen05_commit(done_bar);
+    }
+  } else {
+    // epilogue: warp w owns TMEM lane quarter w % 4
+    const int quarter = warp & 3;
+    const int row = row0 + quarter * 32 + lane;
+    const float rinv = row < rows ? inv_rms[row] : 0.0f;
+    if (mbar_wait(done_bar, 0)) {
+      tcgen05_fence_after();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      for (int c = 0; c < experts; c += 16) {
+        float v[16];
+        tmem_ld_x16(t_addr + c, v);
+        if (row < rows) {
+          float* dst = logits + static_cast<size_t>(row) * experts + c;
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) {
+            *reinterpret_cast<float4*>(dst + i) =
+                make_float4(v[i] * rinv, v[i + 1] * rinv, v[i + 2] * rinv, v[i + 3] * rinv);
+          }
+        }
+      }
+    } else if (error != nullptr) {
+      atomicCAS(error, kDevOk, kDevWaitTimeout);
     }
   }
   tcgen05_fence_before();
@@ -544,6 +716,31 @@ cudaError_t launch_router_fast_logits(const void* x, bool x_bf16, const float* i
     router_fast_logits_kernel<false><<<grid, kFastThreads, smem, stream>>>(
         x, inv_rms, norm_weight, tmap_gate, rows, experts, hidden, logits, error);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_fold_gate(const __nv_bfloat16* gate, const float* norm_weight, int experts,
+                             int hidden, __nv_bfloat16* planes, cudaStream_t stream) {
+  if (experts <= 0 || hidden <= 0) return cudaErrorInvalidValue;
+  fold_gate_kernel<<<148 * 4, 256, 0, stream>>>(gate, norm_weight, experts, hidden, planes);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_router_folded_logits(const CUtensorMap& tmap_x, const CUtensorMap& tmap_planes,
+                                        const float* inv_rms, int rows, int experts, int hidden,
+                                        float* logits, int32_t* error, cudaStream_t stream) {
+  if (rows <= 0 || experts % 16 != 0 || experts > 256 || hidden % kFastBlockK != 0) {
+    return cudaErrorInvalidValue;
+  }
+  const int stage_bytes = kFoldABytes + 3 * experts * 128;
+  const int stages = std::min(4, (220 * 1024) / stage_bytes);
+  if (stages < 2) return cudaErrorInvalidValue;
+  const int smem = stages * stage_bytes + (2 * stages + 1) * 8 + 16 + 1024;
+  cudaError_t err = cudaFuncSetAttribute(router_folded_logits_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (err != cudaSuccess) return err;
+  router_folded_logits_kernel<<<(rows + 127) / 128, kFoldThreads, smem, stream>>>(
+      tmap_x, tmap_planes, inv_rms, rows, experts, hidden, stages, logits, error);
   return cudaGetLastError();
 }
 

@@ -3,10 +3,12 @@ loop, runtime/src/api/single_token_forward_model.cpp:588-656: the caller hands e
 layer's FP32 output to the next and swaps `current` / `next`).  Every layer carries its
 own input RMSNorm and residual add, so the stack is layer(layer(...layer(x))).
 
-Works over single-device layers (`ExpertLayerSlice`) and over expert-parallel engines
-(`ExpertParallelEngine`): both expose "run x -> out" on device buffers.  The hidden state
+Works over single-device layers (`ExpertLayerSlice`), over expert-parallel engines
+(`ExpertParallelEngine`) and over plain callables `f(x, out)`: the model's layer loop
+interleaves MoE layers with Mamba and attention layers (:603-636), which stay the caller's
+own code and enter the stack as callbacks on the same device buffers.  The hidden state
 stays on the device in FP32 between layers; nothing synchronises with the host except the
-split-size exchange inside an expert-parallel step.
+split-size exchange inside a compact expert-parallel step.
 """
 from __future__ import annotations
 
@@ -24,10 +26,12 @@ class MoeLayerStack:
 
     @staticmethod
     def _run_one(layer, x: torch.Tensor, out: torch.Tensor) -> None:
-        if hasattr(layer, "step"):      # ExpertParallelEngine
+        if hasattr(layer, "step"):         # ExpertParallelEngine
             layer.step(x, out)
-        else:                           # ExpertLayerSlice
+        elif hasattr(layer, "run_async"):  # ExpertLayerSlice
             layer.run_async(x, out)
+        else:                              # another layer kind, the caller's own code
+            layer(x, out)
 
     def run(self, x: torch.Tensor, out: torch.Tensor) -> None:
         """x: [tokens, hidden] bf16 or FP32; out: same shape, bf16 or FP32 (may not alias x)."""
@@ -73,5 +77,6 @@ class MoeLayerStack:
         status = 0
         for layer in self.layers:
             owner = layer.stages if hasattr(layer, "stages") else layer
-            status = status or owner.sync_status()
+            if hasattr(owner, "sync_status"):
+                status = status or owner.sync_status()
         return status

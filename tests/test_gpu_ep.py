@@ -117,3 +117,66 @@ def test_expert_parallel_equals_single_device(tokens_per_rank):
         pytest.skip("needs at least two GPUs")
     mp.spawn(_worker, args=(world, _free_port(), (32, 512, 256, 512), tokens_per_rank),
              nprocs=world, join=True)
+
+
+def _timeout_worker(rank, world, port, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    import datetime
+    import time
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=60))
+    outcome = "unfinished"
+    try:
+        entry.load_package()
+        synthetic = importlib.import_module("nemotron_inference_b200.synthetic")
+        ep = importlib.import_module("nemotron_inference_b200.expert_parallel")
+        tokens = 24
+        cfg = synthetic.baseline_config(tokens, experts=32, hidden=512, routed=256, shared=512)
+        cfg.max_recv_pairs = tokens * world * cfg.top_k
+        data = synthetic.make_layer(cfg, seed=31, device="cuda")
+        stages = ep.DeviceStages(cfg, ep.shard_bindings(data.bindings, rank, world), rank, world)
+        capacity = 2 * tokens * cfg.top_k // world
+        engine = ep.ExpertParallelEngine(stages, capacity_per_rank=capacity)
+        assert stages.attach_windows(capacity), stages.attach_error
+        x = synthetic.make_tokens(tokens, cfg.hidden_size, seed=9 + rank, device="cuda")
+        out = torch.empty((tokens, cfg.hidden_size), dtype=torch.float32, device="cuda")
+        engine.step(x, out)                       # a healthy step
+        torch.cuda.synchronize()
+        assert stages.sync_status() == 0
+        dist.barrier()
+        # step 2: rank 1 does not take part (between steps, nothing of its own in flight);
+        # rank 0's kernels wait for flags that nobody raises, give up after the limit and
+        # leave an error status.  Rank 1 stays alive, with its window mapped, until rank 0
+        # is done.
+        stages.layer.set_wait_limit_ms(50.0)
+        if rank == 0:
+            start = time.perf_counter()
+            engine.step(x, out)
+            status = stages.sync_status()
+            elapsed = time.perf_counter() - start
+            outcome = f"status={status} elapsed={elapsed:.3f}"
+        else:
+            outcome = "skipped the step"
+        dist.barrier()
+        stages.detach_windows()
+        stages.layer.close()
+    except BaseException as error:  # noqa: BLE001
+        outcome = "exception: " + repr(error)
+    with open(os.path.join(result_dir, f"outcome{rank}.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)
+
+
+@pytest.mark.timeout(150)
+def test_a_peer_that_skips_a_step_costs_a_timeout_status_not_a_hang(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    mp.spawn(_timeout_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    survivor = (tmp_path / "outcome0.txt").read_text()
+    assert survivor.startswith("status=4 "), survivor     # NMOE_ERR_DEVICE_TIMEOUT
+    assert float(survivor.split("elapsed=")[1]) < 5.0, survivor
+    assert (tmp_path / "outcome1.txt").read_text() == "skipped the step"

@@ -90,6 +90,25 @@ def test_small_batches_replay_a_recorded_graph(baseline_layer, synthetic):
     assert torch.equal(out, _run(layer, other))
 
 
+def test_layer_from_checkpoint_tensor_names(package, synthetic):
+    # weights named as the reference's checkpoint names them, on the HOST, straight into
+    # the layer: same rows as the layer built from the synthetic bindings
+    import importlib
+    checkpoint = importlib.import_module("nemotron_inference_b200.checkpoint")
+    cfg = synthetic.baseline_config(max_tokens=64, experts=32, hidden=512, routed=256, shared=512)
+    data = synthetic.make_layer(cfg, seed=61, device="cuda", norm_weight_uniform=True)
+    tensors = {name: t.cpu() for name, t in
+               checkpoint.tensors_from_bindings(data.bindings, layer_index=3).items()}
+    bindings = checkpoint.bindings_from_tensors(tensors, 3, cfg.n_routed_experts)
+    direct = package.ExpertLayerSlice.create(cfg, data.bindings)
+    named = package.ExpertLayerSlice.create(cfg, bindings)
+    assert direct is not None and named is not None, package.ExpertLayerSlice.create_error
+    x = synthetic.make_tokens(40, cfg.hidden_size, seed=62, device="cuda")
+    assert torch.equal(_run(direct, x), _run(named, x))
+    direct.close()
+    named.close()
+
+
 def test_run_rejects_bad_shapes(baseline_layer):
     layer, _ = baseline_layer
     x = torch.zeros((2, 100), device="cuda")
@@ -144,5 +163,14 @@ def test_layer_stack_matches_oracle_applied_layer_by_layer(package, synthetic, o
         torch.cuda.synchronize()
         assert stack.sync_status() == 0
         assert torch.equal(stacked, current)
+    # another layer kind between two MoE layers, as in the model's loop: a callback
+    mixed = stack_mod.MoeLayerStack(
+        [layers[0], lambda a, b: b.copy_(a.to(torch.float32) * 0.5), layers[1]],
+        cfg.hidden_size, 512)
+    x = synthetic.make_tokens(7, cfg.hidden_size, seed=8, device="cuda")
+    got = torch.empty((7, cfg.hidden_size), dtype=torch.float32, device="cuda")
+    mixed.run(x, got)
+    want = _run(layers[1], (_run(layers[0], x) * 0.5).contiguous())
+    assert mixed.sync_status() == 0 and torch.equal(got, want)
     for layer in layers:
         layer.close()
