@@ -69,6 +69,10 @@ struct GemmArgs {
   int32_t segment_rows = 0;
   int32_t segment_slot0 = 0;
   int32_t* error = nullptr;           // device error slot (DeviceError)
+  // Timing experiments on the CTA-pair kernel only (results are WRONG when set):
+  // bit 0 the epilogue drains nothing, bit 1 no scale writes, bit 2 no operand loads,
+  // bit 3 no MMAs.  Every barrier handshake stays in place.
+  int32_t ablate = 0;
 };
 
 // Tile shapes compiled into the library.  The block scales of every MMA must
@@ -79,8 +83,8 @@ enum GemmVariant : int {
   kVariantPrefillDown = 1,  // BN 192, 128-row A box
   kVariantDecode = 2,       // BN 128, 32-row A box, deep pipeline
   kVariantDecodeWide = 3,   // BN 128, 128-row A box
-  kVariantPairUp = 4,       // BN 208 over a CTA pair (M = 256, cta_group::2)
-  kVariantPairDown = 5,     // BN 192 over a CTA pair
+  kVariantPairUp = 4,       // 256 x 176 over a CTA pair (cta_group::2), quantising epilogue
+  kVariantPairDown = 5,     // the same tile, row-storing epilogue
   kVariantCount = 6,
 };
 
@@ -95,15 +99,13 @@ struct GemmVariantInfo {
 
 // Tensor maps of one GEMM launch.  `a` (activation rows, 128-byte swizzle) and `b_tail`
 // (the partial last K block of the weights) are used by every variant; the CTA-pair
-// variants load everything through tensor maps, so that both CTAs' copies complete on
-// the leader's barrier: `b_full` (the K-block-major weight panels as [rows][128 B]),
-// `sfa` and `sfb` (the tiled block scales as [rows][128 B]).
+// variants also load the full weight K blocks through a map (`b_full`: the K-block-major
+// panels as [rows][128 B], no swizzle), so that both CTAs' copies can complete on the
+// leader's barrier.
 struct GemmMaps {
   CUtensorMap a;
   CUtensorMap b_tail;
   CUtensorMap b_full;
-  CUtensorMap sfa;
-  CUtensorMap sfb;
 };
 
 GemmVariantInfo gemm_variant_info(GemmVariant v);

@@ -205,6 +205,7 @@ struct WeightStack {
   DeviceBuffer tensor_scale;  // [experts]
   DeviceBuffer sf_prefill;    // scale layout for the prefill tile of this projection
   DeviceBuffer sf_decode;     // scale layout for the BN=128 tiles
+  DeviceBuffer sf_pair;       // scale layout for the CTA-pair tile
   GemmVariant prefill_variant = kVariantPrefillUp;
   GemmVariant decode_variant = kVariantDecode;
   GemmVariant decode_wide_variant = kVariantDecodeWide;
@@ -214,8 +215,7 @@ struct WeightStack {
   CUtensorMap tail_prefill;
   CUtensorMap tail_decode;
   CUtensorMap tail_pair;
-  CUtensorMap full_pair;  // the K-block-major panels, for the CTA-pair variants
-  CUtensorMap sf_pair;    // sf_prefill as [rows][128 B]
+  CUtensorMap full_pair;  // the K-block-major panels as [rows][128 B], for the CTA-pair variants
 
   void upload(const nmoe_nvfp4_matrix* matrices, int count, int rows, int cols, bool is_up,
               const char* name, cudaStream_t stream) {
@@ -223,7 +223,7 @@ struct WeightStack {
     n = rows;
     k = cols;
     prefill_variant = is_up ? kVariantPrefillUp : kVariantPrefillDown;
-    pair_variant = is_up ? kVariantPairUp : kVariantPairDown;  // same BN and scale layout
+    pair_variant = is_up ? kVariantPairUp : kVariantPairDown;
     const size_t packed_each = static_cast<size_t>(rows) * cols / 2;
     const size_t sf_each = static_cast<size_t>(rows) * (cols / 16);
     tensor_scale.allocate(sizeof(float) * count);
@@ -233,8 +233,11 @@ struct WeightStack {
     const int pair_rows = gemm_variant_info(pair_variant).b_rows;
     const size_t sf_prefill_each = weight_scale_layout_bytes(1, rows, cols, pi.bn, pi.sfb_groups);
     const size_t sf_decode_each = weight_scale_layout_bytes(1, rows, cols, di.bn, di.sfb_groups);
+    const GemmVariantInfo qi = gemm_variant_info(pair_variant);
+    const size_t sf_pair_each = weight_scale_layout_bytes(1, rows, cols, qi.bn, qi.sfb_groups);
     sf_prefill.allocate(sf_prefill_each * count);
     sf_decode.allocate(sf_decode_each * count);
+    sf_pair.allocate(sf_pair_each * count);
     kb_full = cols / 256;
     const int tail_bytes = (cols % 256) / 2;
     const size_t panel_rows = static_cast<size_t>(count) * rows;
@@ -292,6 +295,9 @@ struct WeightStack {
       NMOE_CUDA(relayout_weight_scales(staging_sf.as<uint8_t>(), 1, rows, cols, di.bn,
                                        di.sfb_groups, sf_decode.as<uint8_t>() + sf_decode_each * e,
                                        stream));
+      NMOE_CUDA(relayout_weight_scales(staging_sf.as<uint8_t>(), 1, rows, cols, qi.bn,
+                                       qi.sfb_groups, sf_pair.as<uint8_t>() + sf_pair_each * e,
+                                       stream));
     }
     NMOE_CUDA(cudaStreamSynchronize(stream));  // the staging buffers die here
     if (kb_full > 0) {
@@ -299,8 +305,6 @@ struct WeightStack {
     } else {
       full_pair = make_raw_map(packed.as<uint8_t>(), 256, pair_rows);  // never read
     }
-    sf_pair = make_raw_map(sf_prefill.as<uint8_t>(), sf_prefill_each * count / 128,
-                           gemm_variant_info(pair_variant).sfb_groups * 4);
     if (tail_bytes == 0) {
       // never read (k_blocks == kb_full), but the kernel takes a valid map
       tail_prefill = make_packed_map(packed.as<uint8_t>(), panel_rows * kb_full, 128, pi.bn);
@@ -318,7 +322,7 @@ struct WeightStack {
     return c == kClassPrefill ? tail_prefill : c == kClassPair ? tail_pair : tail_decode;
   }
   const uint8_t* sf(TileClass c) const {
-    return (c == kClassPrefill || c == kClassPair ? sf_prefill : sf_decode).as<uint8_t>();
+    return (c == kClassPrefill ? sf_prefill : c == kClassPair ? sf_pair : sf_decode).as<uint8_t>();
   }
 };
 
@@ -328,11 +332,9 @@ struct ActivationOperand {
   const uint8_t* sf_tiled = nullptr;
   CUtensorMap map_box128;
   CUtensorMap map_box32;
-  CUtensorMap sf_map;  // the tiled scales as [rows][128 B], one K block of one row tile per box
   void bind(const uint8_t* packed_rows, const uint8_t* sf, size_t rows, int k) {
     packed = packed_rows;
     sf_tiled = sf;
-    sf_map = make_raw_map(sf, tiled_sf_bytes((rows + 127) / 128, k) / 128, 16);
     map_box128 = make_packed_map(packed_rows, rows, static_cast<size_t>(k) / 2, 128);
     map_box32 = make_packed_map(packed_rows, rows, static_cast<size_t>(k) / 2, 32);
   }
@@ -345,9 +347,16 @@ GemmMaps gemm_maps(const WeightStack& weights, TileClass tile_class, const Activ
   maps.a = a.map(tile_class);
   maps.b_tail = weights.tail_map(tile_class);
   maps.b_full = weights.full_pair;
-  maps.sfa = a.sf_map;
-  maps.sfb = weights.sf_pair;
   return maps;
+}
+
+// NMOE_GEMM_ABLATE: timing experiments only (GemmArgs::ablate); results are wrong when set.
+int gemm_ablation() {
+  static const int value = [] {
+    const char* env = std::getenv("NMOE_GEMM_ABLATE");
+    return env != nullptr ? std::atoi(env) : 0;
+  }();
+  return value;
 }
 
 struct Schedule {
@@ -398,6 +407,7 @@ void run_down_gemm(const WeightStack& weights, TileClass tile_class, const Activ
   d.segment_rows = segments.rows;
   d.segment_slot0 = segments.slot0;
   d.error = error;
+  d.ablate = gemm_ablation();
   NMOE_CUDA(launch_grouped_gemm(variant, kGemmDown, gemm_maps(weights, tile_class, a), d, num_sms,
                                 stream));
 }
@@ -429,6 +439,7 @@ void run_expert_gemms(const WeightStack& up, const WeightStack& down, TileClass 
   g.out_sf = hidden_sf;
   g.out_k_blocks = k_blocks_of(up.n);
   g.error = error;
+  g.ablate = gemm_ablation();
   NMOE_CUDA(launch_grouped_gemm(up_variant, kGemmUp, gemm_maps(up, tile_class, a), g, num_sms,
                                 stream));
 
