@@ -746,16 +746,24 @@ def stack_workload(args, package, synthetic, flush_buf, dist_module, layers: int
     tokens = decode_total // world
     x_all = synthetic.make_tokens(decode_total, H, seed=6100 + decode_total)
     current = x_all[rank * tokens:(rank + 1) * tokens].cuda()
-    worst_vs_single, oracle_ok, summaries = 0.0, True, []
+    worst_vs_single, oracle_ok, summaries, per_layer, statuses = 0.0, True, [], [], []
     for index in range(parity_layers):
         ep_out = torch.empty((tokens, H), dtype=torch.float32, device="cuda")
+        # rank 0 spends seconds in the CPU oracle below; the others must not start the next
+        # layer's step meanwhile, or their bounded device waits run out before rank 0's
+        # records arrive
+        torch.cuda.synchronize()
+        dist_module.barrier()
         engines[index].step(current, ep_out)
         single = package.ExpertLayerSlice.create(
             synthetic.baseline_config(max_tokens=max(tokens, 64)), keep[index].bindings)
         ref = torch.empty((tokens, H), dtype=torch.float32, device="cuda")
         single.run_async(current, ref)
         torch.cuda.synchronize()
-        worst_vs_single = max(worst_vs_single, float((ep_out - ref).abs().max().item()))
+        layer_diff = float((ep_out - ref).abs().max().item())
+        per_layer.append(round(layer_diff, 6))
+        statuses.append(int(engines[index].stages.sync_status()))
+        worst_vs_single = max(worst_vs_single, layer_diff)
         if rank == 0:
             try:
                 import helpers  # the test suite's parity report (CPU oracle): checker only
@@ -771,6 +779,8 @@ def stack_workload(args, package, synthetic, flush_buf, dist_module, layers: int
     dist_module.all_reduce(worst, op=dist_module.ReduceOp.MAX)
     okay = torch.tensor([1.0 if oracle_ok else 0.0], device="cuda")
     dist_module.all_reduce(okay, op=dist_module.ReduceOp.MIN)
+    worst_status = torch.tensor([float(max(statuses) if statuses else 0)], device="cuda")
+    dist_module.all_reduce(worst_status, op=dist_module.ReduceOp.MAX)
     for engine in engines:
         engine.stages.detach_windows()
         engine.stages.layer.close()
@@ -781,6 +791,8 @@ def stack_workload(args, package, synthetic, flush_buf, dist_module, layers: int
             "segment_capacity": capacity,
             "parity": {"layers_checked": parity_layers, "tokens_per_rank": tokens,
                        "max_abs_vs_single_gpu_all_ranks": float(worst.item()),
+                       "max_abs_vs_single_gpu_rank0_by_layer": per_layer,
+                       "device_status_max_over_ranks": int(worst_status.item()),
                        "within_2e-2_of_single_gpu": bool(worst.item() <= 2e-2),
                        "single_gpu_vs_oracle_ok": bool(okay.item() == 1.0),
                        "oracle_reports_rank0": summaries}}
