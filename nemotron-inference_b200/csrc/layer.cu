@@ -1000,6 +1000,7 @@ void layer_create_impl(nmoe_layer* L, const nmoe_config& c, const nmoe_weights& 
     const double ms = std::strtod(env, nullptr);
     if (ms > 0.0) L->wait_limit_ticks = ticks_from_ms(ms);
   }
+  if (const char* env = std::getenv("NMOE_FORK_MAX_TOKENS")) L->fork_max_tokens = std::atoi(env);
   if (std::getenv("NMOE_NO_SHARED_FORK") == nullptr) {
     NMOE_CUDA(cudaStreamCreateWithFlags(&L->side_stream, cudaStreamNonBlocking));
     NMOE_CUDA(cudaEventCreateWithFlags(&L->quant_done, cudaEventDisableTiming));
