@@ -66,6 +66,26 @@ pack_records_kernel(const int32_t* __restrict__ top_index, const float* __restri
   const int token = pair / top_k;
   const int expert = top_index[pair];
   const int rank = expert / experts_per_rank;
+  // the token's bytes are fetched before the cursor's atomic, so that their loads and the
+  // atomic are in flight together
+  const int packed_quads = cols / 32;  // 16-byte pieces; cols % 64 == 0
+  const uint4* src = reinterpret_cast<const uint4*>(packed) + static_cast<size_t>(token) * packed_quads;
+  constexpr int kAhead = 3;
+  uint4 ahead[kAhead];
+#pragma unroll
+  for (int j = 0; j < kAhead; ++j) {
+    const int w = lane + 32 * j;
+    if (w < packed_quads) ahead[j] = src[w];
+  }
+  const int sf_bytes = cols / 16;
+  const uint32_t* sf_src =
+      reinterpret_cast<const uint32_t*>(sf_row_major + static_cast<size_t>(token) * sf_bytes);
+  uint32_t scale_words[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int b = lane + 32 * j;
+    if (b < sf_bytes / 4) scale_words[j] = sf_src[b];
+  }
   int position = 0;
   int slot = 0;
   if (lane == 0) {
@@ -92,15 +112,20 @@ pack_records_kernel(const int32_t* __restrict__ top_index, const float* __restri
   } else {
     record = records + static_cast<size_t>(position) * record_bytes;
   }
-  const int packed_quads = cols / 32;  // 16-byte pieces; cols % 64 == 0
-  const uint4* src = reinterpret_cast<const uint4*>(packed) + static_cast<size_t>(token) * packed_quads;
   uint4* dst = reinterpret_cast<uint4*>(record);
-  for (int w = lane; w < packed_quads; w += 32) dst[w] = src[w];
-  const int sf_bytes = cols / 16;
-  const uint32_t* sf_src =
-      reinterpret_cast<const uint32_t*>(sf_row_major + static_cast<size_t>(token) * sf_bytes);
+#pragma unroll
+  for (int j = 0; j < kAhead; ++j) {
+    const int w = lane + 32 * j;
+    if (w < packed_quads) dst[w] = ahead[j];
+  }
+  for (int w = lane + 32 * kAhead; w < packed_quads; w += 32) dst[w] = src[w];
   uint32_t* sf_dst = reinterpret_cast<uint32_t*>(record + cols / 2);
-  for (int b = lane; b < sf_bytes / 4; b += 32) sf_dst[b] = sf_src[b];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int b = lane + 32 * j;
+    if (b < sf_bytes / 4) sf_dst[b] = scale_words[j];
+  }
+  for (int b = lane + 64; b < sf_bytes / 4; b += 32) sf_dst[b] = sf_src[b];
   if (lane == 0) {
     // the tail starts at a multiple of 4: cols % 64 == 0 is required
     uint8_t* tail = record + cols / 2 + sf_bytes;

@@ -85,25 +85,44 @@ permute_kernel(PlanBuffers plan, PermuteSource src, int pairs, int experts, int 
   // a record that arrived corrupt or half written (a peer that timed out) names no
   // expert of this stack: the histogram kernel has reported it, nothing is indexed by it
   if (expert < 0 || expert >= experts) return;
+  // Everything that does not depend on the destination is fetched BEFORE the cursor's
+  // atomic, so that the row's loads, the plan's loads and the atomic are in flight
+  // together instead of one global round trip after the other.
+  const int words = cols / 8;
+  const uint8_t* from_bytes = src.packed + static_cast<size_t>(source_row) * src.packed_stride;
+  const bool wide = (reinterpret_cast<uintptr_t>(from_bytes) & 15u) == 0 && (cols & 31) == 0;
+  constexpr int kAhead = 3;  // 16-byte pieces per lane held in registers: 1536 B of a row
+  uint4 ahead[kAhead];
+  if (wide) {
+    const uint4* from = reinterpret_cast<const uint4*>(from_bytes);
+#pragma unroll
+    for (int j = 0; j < kAhead; ++j) {
+      const int q = lane + 32 * j;
+      if (q < words / 4) ahead[j] = from[q];
+    }
+  }
+  const int own_tiles = (plan.expert_counts[expert] + tile_rows - 1) / tile_rows;
+  const int first_tile = plan.expert_slot0[expert];
   int position = 0;
   if (lane == 0) position = atomicAdd(&plan.expert_cursor[expert], 1);
   position = __shfl_sync(0xffffffffu, position, 0);
   // an expert's rows stay inside the tiles the plan gave it, whatever the histogram said
-  const int own_tiles = (plan.expert_counts[expert] + tile_rows - 1) / tile_rows;
   if (position / tile_rows >= own_tiles) return;
-  const int tile = plan.expert_slot0[expert] + position / tile_rows;
+  const int tile = first_tile + position / tile_rows;
   if (tile >= max_row_tiles) return;  // plan overflow was already reported
   const int row = tile * 128 + position % tile_rows;
 
-  const int words = cols / 8;
-  const uint8_t* from_bytes = src.packed + static_cast<size_t>(source_row) * src.packed_stride;
   uint8_t* dst_bytes = sorted_packed + static_cast<size_t>(row) * (cols / 2);
-  if (((reinterpret_cast<uintptr_t>(from_bytes) | reinterpret_cast<uintptr_t>(dst_bytes)) & 15u) == 0 &&
-      (cols & 31) == 0) {
+  if (wide && (reinterpret_cast<uintptr_t>(dst_bytes) & 15u) == 0) {
     // 16 bytes per lane: a warp moves 512 contiguous bytes per instruction
     const uint4* from = reinterpret_cast<const uint4*>(from_bytes);
     uint4* dst = reinterpret_cast<uint4*>(dst_bytes);
-    for (int q = lane; q < words / 4; q += 32) dst[q] = from[q];
+#pragma unroll
+    for (int j = 0; j < kAhead; ++j) {
+      const int q = lane + 32 * j;
+      if (q < words / 4) dst[q] = ahead[j];
+    }
+    for (int q = lane + 32 * kAhead; q < words / 4; q += 32) dst[q] = from[q];
   } else {
     const uint32_t* from = reinterpret_cast<const uint32_t*>(from_bytes);
     uint32_t* dst = reinterpret_cast<uint32_t*>(dst_bytes);
