@@ -818,7 +818,7 @@ struct nmoe_layer {
   // before the combine.  Its GEMMs use a few dozen SMs at these sizes.
   cudaStream_t side_stream = nullptr;
   cudaEvent_t quant_done = nullptr, shared_done = nullptr;
-  int fork_max_tokens = 256;
+  int fork_max_tokens = 1 << 30;  // (NMOE_FORK_MAX_TOKENS)
   bool window_fork_shared = false;    // nmoe_ep_window_fork_shared
   bool window_shared_pending = false;
   RowKind window_shared_kind = kRowF32;  // type of shared_out for the pending combine
@@ -1092,7 +1092,8 @@ void run_linear(nmoe_layer* L, const DenseLinear& linear, const float* in_rows, 
 // RMSNorm + activation quantiser + router: fills normalized, y_*, logits,
 // top_index / top_weight and the per-expert histogram `counts` (global ids).
 void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dtype in_dtype,
-                  int tokens, cudaEvent_t after_quantise = nullptr) {
+                  int tokens, cudaEvent_t after_quantise = nullptr,
+                  bool fork_after_logits = false) {
   const nmoe_config& c = L->cfg;
   const int H = c.hidden_size, E = c.n_routed_experts, K = c.top_k;
   int32_t* error = L->error.device.as<int32_t>();
@@ -1109,7 +1110,9 @@ void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dt
                               L->y_sf_tiled.as<uint8_t>(), k_blocks_of(H), L->y_ts.as<float>(),
                               stream, L->inv_rms.as<float>()));
   L->last_normalized = want_normalized;
-  if (after_quantise != nullptr) NMOE_CUDA(cudaEventRecord(after_quantise, stream));
+  if (after_quantise != nullptr && !fork_after_logits) {
+    NMOE_CUDA(cudaEventRecord(after_quantise, stream));
+  }
   L->mark(1, stream);
   // gate projection (:797-799) and top-k (:881)
   NMOE_CUDA(cudaMemsetAsync(L->counts.as<int32_t>(), 0, E * sizeof(int32_t), stream));
@@ -1127,6 +1130,12 @@ void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dt
       NMOE_CUDA(launch_router_fast_logits(input, in_bf16, L->inv_rms.as<float>(),
                                           L->norm_weight.as<float>(), L->gate_map, tokens, E, H,
                                           L->logits.as<float>(), error, stream));
+    }
+    // A stream forked here runs the shared expert beside the selection, plan and permute
+    // kernels; forked before pass 1 its persistent GEMM CTAs would hold the shared memory
+    // the pass-1 CTAs need.
+    if (after_quantise != nullptr && fork_after_logits) {
+      NMOE_CUDA(cudaEventRecord(after_quantise, stream));
     }
     L->mark(2, stream);
     NMOE_CUDA(launch_router_select_exact(
@@ -1313,7 +1322,9 @@ void layer_run_impl(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_
                                  ? kRowF16 : kRowF32;
   const bool fork = L->side_stream != nullptr && !L->stage_timing &&
                     tokens <= L->fork_max_tokens && !L->latent_mode && !dense_shared;
-  route_tokens(L, stream, input, in_dtype, tokens, fork ? L->quant_done : nullptr);
+  const bool two_pass = L->fast_router && tokens >= L->fast_router_min_tokens;
+  route_tokens(L, stream, input, in_dtype, tokens, fork ? L->quant_done : nullptr,
+               fork && two_pass);
   L->last_tokens = tokens;
   L->last_parts_kind = parts_kind;
   L->last_unfused = L->unfused;

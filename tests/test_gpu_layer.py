@@ -43,6 +43,32 @@ def test_small_layer_every_stage(package, synthetic):
     layer.close()
 
 
+def test_layer_input_rows_whose_tensor_scale_is_not_one(package, synthetic, oracle):
+    """A norm weight of ~200 and rows dominated by one element put the largest normalised
+    value (about sqrt(H) * 200) beyond 6 * 448: the quantiser's tensor scale leaves 1 for
+    those rows (nvfp4_packing.cpp:119-126) and stays 1 for the ordinary rows beside them.
+    Only the layer-input quantiser is checked (such activations overflow the experts)."""
+    cfg = synthetic.baseline_config(max_tokens=64, experts=32, hidden=512, routed=256, shared=512)
+    data = synthetic.make_layer(cfg, seed=77, device="cuda", norm_weight_uniform=True)
+    data.bindings.input_norm_weight = (data.bindings.input_norm_weight.to(torch.float32) * 200.0)
+    layer = package.ExpertLayerSlice.create(cfg, data.bindings)
+    assert layer is not None, package.ExpertLayerSlice.create_error
+    x = synthetic.make_tokens(16, cfg.hidden_size, seed=78, device="cuda").to(torch.float32)
+    x[::2] *= 1e-3
+    x[::2, 5] = 40.0  # every other row: one element carries the whole norm
+    out = torch.empty_like(x)
+    layer.run(x, out)  # the status may report the experts' activation range: not the subject
+    trace = layer.trace(16)
+    y = oracle.rmsnorm(x.cpu().numpy(), data.bindings.input_norm_weight.cpu().numpy(),
+                       cfg.rms_epsilon)
+    packed, scales, ts = oracle.pack_nvfp4_per_row(y)
+    assert np.all(ts[::2] > 1.0) and np.all(ts[1::2] == 1.0)
+    assert np.array_equal(trace.act_tensor_scale.cpu().numpy(), ts)
+    assert np.array_equal(trace.act_packed.cpu().numpy(), packed)
+    assert np.array_equal(trace.act_scales.cpu().numpy(), scales)
+    layer.close()
+
+
 @pytest.mark.parametrize("tokens", [1, 8, 32, 64])
 def test_decode_sizes_config1(baseline_layer, synthetic, tokens):
     layer, data = baseline_layer
