@@ -180,10 +180,15 @@ cudaError_t launch_router_fast_logits(const void* x, bool x_bf16, const float* i
 // swizzle; `tmap_planes` = [3 * experts][hidden], box 64 x experts), inv_rms applied to the sums.
 cudaError_t launch_fold_gate(const __nv_bfloat16* gate, const float* norm_weight, int experts,
                              int hidden, __nv_bfloat16* planes, cudaStream_t stream);
+// `splits` CTAs share the contraction of one 128-row tile; split s writes its partial sums to
+// logits + s * rows * experts, and launch_router_select_exact adds them up.
+// router_folded_splits picks the split count (1, 2 or 4) for a batch.
+int router_folded_splits(int rows, int hidden, int num_sms);
 cudaError_t launch_router_folded_logits(const CUtensorMap& tmap_x, const CUtensorMap& tmap_planes,
                                         const float* inv_rms, int rows, int experts, int hidden,
-                                        float* logits, int32_t* error, cudaStream_t stream);
-cudaError_t launch_router_select_exact(float* logits, const void* x, bool x_bf16,
+                                        int splits, float* logits, int32_t* error,
+                                        cudaStream_t stream);
+cudaError_t launch_router_select_exact(float* logits, int splits, const void* x, bool x_bf16,
                                        const float* inv_rms, const float* norm_weight,
                                        const __nv_bfloat16* gate, const float* logit_offset,
                                        const float* bias, int rows, int experts, int hidden,

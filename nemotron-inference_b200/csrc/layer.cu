@@ -874,7 +874,8 @@ void allocate_scratch(nmoe_layer* L, size_t T) {
   const size_t token_slots = (T + 127) / 128;
   L->inv_rms.allocate(T * sizeof(float));
   L->normalized.allocate(T * H * sizeof(float));
-  L->logits.allocate(T * E * sizeof(float));
+  // (a split router pass 1 keeps up to four partial sums per logit for small batches)
+  L->logits.allocate(std::min<size_t>(T, 4736) * 3 * E * sizeof(float) + T * E * sizeof(float));
   L->top_index.allocate(T * K * sizeof(int32_t));
   L->top_weight.allocate(T * K * sizeof(float));
   L->y_packed.allocate(token_slots * 128 * H / 2, true);
@@ -1118,14 +1119,17 @@ void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dt
   NMOE_CUDA(cudaMemsetAsync(L->counts.as<int32_t>(), 0, E * sizeof(int32_t), stream));
   const float* offset = L->has_logit_offset ? L->logit_offset.as<float>() : nullptr;
   if (two_pass_router) {
+    int logit_splits = 1;
     if (L->folded_router && in_bf16 && reinterpret_cast<uintptr_t>(input) % 16 == 0) {
       if (L->input_map_base != input || L->input_map_rows != tokens) {
         L->input_map = make_bf16_map(input, tokens, H, 128);
         L->input_map_base = input;
         L->input_map_rows = tokens;
       }
+      logit_splits = router_folded_splits(tokens, H, L->num_sms);
       NMOE_CUDA(launch_router_folded_logits(L->input_map, L->planes_map, L->inv_rms.as<float>(),
-                                            tokens, E, H, L->logits.as<float>(), error, stream));
+                                            tokens, E, H, logit_splits, L->logits.as<float>(),
+                                            error, stream));
     } else {
       NMOE_CUDA(launch_router_fast_logits(input, in_bf16, L->inv_rms.as<float>(),
                                           L->norm_weight.as<float>(), L->gate_map, tokens, E, H,
@@ -1139,7 +1143,7 @@ void route_tokens(nmoe_layer* L, cudaStream_t stream, const void* input, nmoe_dt
     }
     L->mark(2, stream);
     NMOE_CUDA(launch_router_select_exact(
-        L->logits.as<float>(), input, in_bf16, L->inv_rms.as<float>(),
+        L->logits.as<float>(), logit_splits, input, in_bf16, L->inv_rms.as<float>(),
         L->norm_weight.as<float>(), L->gate_bf16.as<__nv_bfloat16>(), offset,
         L->bias.as<float>(), tokens, E, H, K, c.norm_topk_prob != 0, c.routed_scaling_factor,
         L->router_tie_margin, L->top_index.as<int32_t>(), L->top_weight.as<float>(),

@@ -300,6 +300,7 @@ router_fast_logits_kernel(const void* __restrict__ x, const float* __restrict__ 
 // the size of the FP32 accumulation error already covered by the tie margin.
 // ---------------------------------------------------------------------------
 constexpr int kFoldThreads = 6 * 32;
+constexpr int kFoldMaxSplits = 4;
 constexpr int kFoldABytes = 128 * 128;  // 128 rows x 64 bf16
 
 __global__ void fold_gate_kernel(const __nv_bfloat16* __restrict__ gate,
@@ -322,7 +323,7 @@ __global__ void __launch_bounds__(kFoldThreads, 1)
 router_folded_logits_kernel(const __grid_constant__ CUtensorMap tmap_x,
                             const __grid_constant__ CUtensorMap tmap_planes,
                             const float* __restrict__ inv_rms, int rows, int experts, int hidden,
-                            int stages, float* __restrict__ logits, int32_t* error) {
+                            int stages, int splits, float* __restrict__ logits, int32_t* error) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) &
                                              ~static_cast<uintptr_t>(1023u));
@@ -337,8 +338,15 @@ router_folded_logits_kernel(const __grid_constant__ CUtensorMap tmap_x,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int row0 = blockIdx.x * 128;
-  const int k_blocks = hidden / kFastBlockK;
+  // With few row tiles the contraction is split over `splits` CTAs per tile (split s
+  // writes its partial sums to logits + s * rows * experts; pass 2 adds them up), so that
+  // a batch of a few thousand tokens still spreads over the SMs.
+  const int tile = static_cast<int>(blockIdx.x) / splits;
+  const int split = static_cast<int>(blockIdx.x) - tile * splits;
+  const int row0 = tile * 128;
+  const int all_k_blocks = hidden / kFastBlockK;
+  const int kb_begin = all_k_blocks * split / splits;
+  const int k_blocks = all_k_blocks * (split + 1) / splits - kb_begin;
   const uint32_t tmem_cols = experts <= 32 ? 32 : experts <= 64 ? 64 : experts <= 128 ? 128 : 256;
 
   if (threadIdx.x == 0) {
@@ -371,10 +379,11 @@ router_folded_logits_kernel(const __grid_constant__ CUtensorMap tmap_x,
         }
         mbar_arrive_expect_tx(&full_bar[stage], kFoldABytes + b_bytes);
         // rows past the end of the input read as zeros (the map's extent is `rows`)
-        tma_load_2d(sA + stage * kFoldABytes, &tmap_x, kb * kFastBlockK, row0, &full_bar[stage]);
+        tma_load_2d(sA + stage * kFoldABytes, &tmap_x, (kb_begin + kb) * kFastBlockK, row0,
+                    &full_bar[stage]);
         for (int plane = 0; plane < 3; ++plane) {
-          tma_load_2d(sB + stage * b_bytes + plane * plane_bytes, &tmap_planes, kb * kFastBlockK,
-                      plane * experts, &full_bar[stage]);
+          tma_load_2d(sB + stage * b_bytes + plane * plane_bytes, &tmap_planes,
+                      (kb_begin + kb) * kFastBlockK, plane * experts, &full_bar[stage]);
         }
         if (++stage == stages) {
           stage = 0;
@@ -426,7 +435,7 @@ router_folded_logits_kernel(const __grid_constant__ CUtensorMap tmap_x,
         float v[16];
         tmem_ld_x16(t_addr + c, v);
         if (row < rows) {
-          float* dst = logits + static_cast<size_t>(row) * experts + c;
+          float* dst = logits + (static_cast<size_t>(split) * rows + row) * experts + c;
 #pragma unroll
           for (int i = 0; i < 16; i += 4) {
             *reinterpret_cast<float4*>(dst + i) =
@@ -482,7 +491,7 @@ __device__ __forceinline__ void warp_arg_max(uint32_t key, uint32_t index, uint3
 constexpr int kSelectBatch = 4;
 template <bool IN_BF16>
 __global__ void __launch_bounds__(kSelectWarps * 32, 8)
-router_select_exact_kernel(float* __restrict__ logits, const void* __restrict__ x,
+router_select_exact_kernel(float* __restrict__ logits, int splits, const void* __restrict__ x,
                            const float* __restrict__ inv_rms,
                            const float* __restrict__ norm_weight,
                            const __nv_bfloat16* __restrict__ gate,
@@ -510,8 +519,12 @@ router_select_exact_kernel(float* __restrict__ logits, const void* __restrict__ 
     if (j < per_lane) {
       const int e = lane + 32 * j;
       float l = row_logits[e];
-      if (logit_offset != nullptr) {
-        l = __fadd_rn(l, logit_offset[e]);
+      // partial sums of a split pass 1, in split order
+      for (int sp = 1; sp < splits; ++sp) {
+        l = __fadd_rn(l, row_logits[static_cast<size_t>(sp) * rows * experts + e]);
+      }
+      if (logit_offset != nullptr) l = __fadd_rn(l, logit_offset[e]);
+      if (logit_offset != nullptr || splits > 1) {
         row_logits[e] = l;  // what the trace shows for experts that are not re-evaluated
       }
       choice[j] = __fdividef(1.0f, 1.0f + __expf(-l)) + bias[e];
@@ -726,10 +739,22 @@ cudaError_t launch_fold_gate(const __nv_bfloat16* gate, const float* norm_weight
   return cudaGetLastError();
 }
 
+int router_folded_splits(int rows, int hidden, int num_sms) {
+  const int tiles = (rows + 127) / 128;
+  int splits = 1;
+  while (splits < kFoldMaxSplits && tiles * splits * 2 <= num_sms &&
+         hidden / kFastBlockK >= 8 * splits) {
+    splits *= 2;
+  }
+  return splits;
+}
+
 cudaError_t launch_router_folded_logits(const CUtensorMap& tmap_x, const CUtensorMap& tmap_planes,
                                         const float* inv_rms, int rows, int experts, int hidden,
-                                        float* logits, int32_t* error, cudaStream_t stream) {
-  if (rows <= 0 || experts % 16 != 0 || experts > 256 || hidden % kFastBlockK != 0) {
+                                        int splits, float* logits, int32_t* error,
+                                        cudaStream_t stream) {
+  if (rows <= 0 || experts % 16 != 0 || experts > 256 || hidden % kFastBlockK != 0 ||
+      splits < 1 || splits > kFoldMaxSplits || hidden / kFastBlockK < splits) {
     return cudaErrorInvalidValue;
   }
   const int stage_bytes = kFoldABytes + 3 * experts * 128;
@@ -739,12 +764,12 @@ cudaError_t launch_router_folded_logits(const CUtensorMap& tmap_x, const CUtenso
   cudaError_t err = cudaFuncSetAttribute(router_folded_logits_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (err != cudaSuccess) return err;
-  router_folded_logits_kernel<<<(rows + 127) / 128, kFoldThreads, smem, stream>>>(
-      tmap_x, tmap_planes, inv_rms, rows, experts, hidden, stages, logits, error);
+  router_folded_logits_kernel<<<((rows + 127) / 128) * splits, kFoldThreads, smem, stream>>>(
+      tmap_x, tmap_planes, inv_rms, rows, experts, hidden, stages, splits, logits, error);
   return cudaGetLastError();
 }
 
-cudaError_t launch_router_select_exact(float* logits, const void* x, bool x_bf16,
+cudaError_t launch_router_select_exact(float* logits, int splits, const void* x, bool x_bf16,
                                        const float* inv_rms, const float* norm_weight,
                                        const __nv_bfloat16* gate, const float* logit_offset,
                                        const float* bias, int rows, int experts, int hidden,
@@ -752,17 +777,17 @@ cudaError_t launch_router_select_exact(float* logits, const void* x, bool x_bf16
                                        float tie_margin, int32_t* top_index, float* top_weight,
                                        int32_t* expert_counts, cudaStream_t stream) {
   if (rows <= 0 || experts % 32 != 0 || experts > 32 * kSelectPerLane || top_k <= 0 ||
-      top_k > 32 || top_k > experts || hidden % 8 != 0) {
+      top_k > 32 || top_k > experts || hidden % 8 != 0 || splits < 1) {
     return cudaErrorInvalidValue;
   }
   const int grid = (rows + kSelectWarps - 1) / kSelectWarps;
   if (x_bf16) {
     router_select_exact_kernel<true><<<grid, kSelectWarps * 32, 0, stream>>>(
-        logits, x, inv_rms, norm_weight, gate, logit_offset, bias, rows, experts, hidden, top_k,
+        logits, splits, x, inv_rms, norm_weight, gate, logit_offset, bias, rows, experts, hidden, top_k,
         norm_topk_prob, routed_scaling, tie_margin, top_index, top_weight, expert_counts);
   } else {
     router_select_exact_kernel<false><<<grid, kSelectWarps * 32, 0, stream>>>(
-        logits, x, inv_rms, norm_weight, gate, logit_offset, bias, rows, experts, hidden, top_k,
+        logits, splits, x, inv_rms, norm_weight, gate, logit_offset, bias, rows, experts, hidden, top_k,
         norm_topk_prob, routed_scaling, tie_margin, top_index, top_weight, expert_counts);
   }
   return cudaGetLastError();
