@@ -132,8 +132,8 @@ CUtensorMap make_bf16_map(const void* base, size_t rows, size_t cols, int box_ro
 }
 
 // Bytes that are already in their shared-memory order, viewed as [rows][128 B]: box =
-// 128 bytes x box_rows, no swizzle.  The CTA-pair GEMM loads its weight panels and block
-// scales through such maps.
+// 128 bytes x box_rows, no swizzle.  The CTA-pair GEMM loads its weight panels through
+// such a map.
 CUtensorMap make_raw_map(const void* base, size_t rows, int box_rows) {
   NMOE_REQUIRE(reinterpret_cast<uintptr_t>(base) % 16 == 0, "tensor map base must be 16-byte aligned");
   CUtensorMap map;
@@ -188,8 +188,8 @@ void validate_matrix(const nmoe_nvfp4_matrix& m, size_t rows, size_t cols, const
 // A stack of same-shaped NVFP4 matrices resident in HBM with the scale layouts
 // and tensor maps of every GEMM tile shape that may consume it.
 // ---------------------------------------------------------------------------
-// kClassPair: the prefill tile shapes over CTA pairs (cta_group::2): each CTA stages
-// half of the weight tile, which is what the load pipeline of a single CTA runs out of.
+// kClassPair: 256 x 176 tiles over CTA pairs (cta_group::2), each CTA staging half of the
+// weight tile; measured slower than the single-CTA shapes, selected only by NMOE_GEMM_PAIR.
 enum TileClass : int { kClassPrefill = 0, kClassDecode = 1, kClassDecodeWide = 2, kClassPair = 3 };
 
 struct WeightStack {
